@@ -1,0 +1,246 @@
+"""ctypes binding of ``libdsb200.so`` (C ABI declared in ``include/dsb200.h``) plus thin per-stage
+wrappers that take torch CUDA tensors.  torch is used for device memory and the current stream only.
+
+The library is mandatory: importing a stage on a machine where ``libdsb200.so`` has not been built
+raises ``RuntimeError`` -- there is no CPU or PyTorch fallback for any stage.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libdsb200.so")
+
+DSB_FLAG_DROP_LAST_SPLAT = 1
+RECORD_FLOATS = 12
+GRAD_FLOATS = 12
+MAX_PAIRS = 1 << 30
+
+EXPORTS = (
+    "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
+    "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
+    "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_export_reference_lists",
+)
+
+
+class DsbCamera(C.Structure):
+    _fields_ = [("image_height", C.c_int32), ("image_width", C.c_int32), ("tanfovx", C.c_float), ("tanfovy", C.c_float),
+                ("scale_modifier", C.c_float), ("sh_degree", C.c_int32), ("max_sh_degree", C.c_int32),
+                ("matrices_transposed", C.c_int32), ("flags", C.c_int32), ("reserved", C.c_int32),
+                ("viewmatrix", C.c_void_p), ("projmatrix", C.c_void_p), ("campos", C.c_void_p), ("bg", C.c_void_p)]
+
+
+class DsbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"dsb200 error {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    """Load the shared library once; fail loudly when it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m ds_splat_b200.build` (needs nvcc); "
+                "this package has no fallback path")
+        l = C.CDLL(LIB_PATH)
+        l.dsb_last_error.restype = C.c_char_p
+        l.dsb_version.restype = C.c_int32
+        l.dsb_launch_count.restype = C.c_int64
+        l.dsb_plan_workspace_bytes.restype = C.c_int64
+        l.dsb_plan_workspace_bytes.argtypes = [C.c_int32]
+        l.dsb_sort_workspace_bytes.restype = C.c_int64
+        l.dsb_sort_workspace_bytes.argtypes = [C.c_int64]
+        P, I32, I64, CAM = C.c_void_p, C.c_int32, C.c_int64, C.POINTER(DsbCamera)
+        sig = {
+            "dsb_preprocess": [CAM, I32] + [P] * 7 + [P] * 5 + [P],
+            "dsb_plan_pairs": [CAM, I32, P, P, P, P, P, I64, C.POINTER(C.c_int64), P],
+            "dsb_emit_pairs": [CAM, I32, I64, P, P, P, P, P, P],
+            "dsb_sort_pairs": [P, P, I64, I32, I32, P, I64, C.POINTER(C.c_int32), P],
+            "dsb_sort_by_keys": [P, P, P, P, I64, I32, I32, P, I64, C.POINTER(C.c_int32), P],
+            "dsb_identify_tile_ranges": [P, I64, I32, I32, P, P],
+            "dsb_blend_forward": [CAM, P, P, P, P, P, P, P],
+            "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P],
+            "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
+            "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 8 + [I64, C.POINTER(C.c_int64), P],
+            "dsb_forward_render": [CAM, I32, I64] + [P] * 7 + [I64] + [P] * 5,
+            "dsb_backward": [CAM, I32] + [P] * 12 + [P] * 8 + [I32, P],
+            "dsb_export_reference_lists": [P, I64, P, P, P, P],
+        }
+        for name, argtypes in sig.items():
+            fn = getattr(l, name)
+            fn.restype = C.c_int
+            fn.argtypes = argtypes
+        _lib = l
+    return _lib
+
+
+def check(rc: int):
+    if rc != 0:
+        raise DsbError(rc, lib().dsb_last_error().decode(errors="replace"))
+
+
+def launch_count() -> int:
+    return int(lib().dsb_launch_count())
+
+
+def ptr(t):
+    """Device address of a tensor (None and empty tensors map to NULL)."""
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+def stream_ptr():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def as_f32(t, device, name):
+    """float32, contiguous, on ``device`` -- the requirements the reference checks with TORCH_CHECK
+    (cpp/rasterizer_torch.cu:13-17,176-190); non-contiguous inputs are made contiguous instead of refused."""
+    if t is None:
+        return None
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.numel() == 0:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if t.device != device:
+        raise RuntimeError(f"{name} is on {t.device}, expected {device}")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32")
+    return t.contiguous()
+
+
+def make_camera(image_height, image_width, tanfovx, tanfovy, viewmatrix, projmatrix, campos, bg=None, sh_degree=3,
+                max_sh_degree=3, scale_modifier=1.0, transposed=True, drop_last=True):
+    """Build a DsbCamera; returns (struct, keepalive list)."""
+    cam = DsbCamera()
+    cam.image_height, cam.image_width = int(image_height), int(image_width)
+    cam.tanfovx, cam.tanfovy, cam.scale_modifier = float(tanfovx), float(tanfovy), float(scale_modifier)
+    cam.sh_degree, cam.max_sh_degree = int(sh_degree), int(max_sh_degree)
+    cam.matrices_transposed = 1 if transposed else 0
+    cam.flags = DSB_FLAG_DROP_LAST_SPLAT if drop_last else 0
+    cam.viewmatrix, cam.projmatrix, cam.campos = viewmatrix.data_ptr(), projmatrix.data_ptr(), campos.data_ptr()
+    cam.bg = bg.data_ptr() if bg is not None else None
+    return cam, [viewmatrix, projmatrix, campos, bg]
+
+
+def num_tiles(h, w):
+    return ((w + 15) // 16) * ((h + 15) // 16)
+
+
+# ---- per-stage wrappers (used by the tests and the benchmark's per-stage timers) -------------------------
+
+def preprocess(cam, means3d, shs, opacities, scales, rotations, colors_precomp=None, cov3d_precomp=None):
+    n, dev = means3d.shape[0], means3d.device
+    records = torch.empty((n, RECORD_FLOATS), dtype=torch.float32, device=dev)
+    radii = torch.empty(n, dtype=torch.int32, device=dev)
+    tiles = torch.empty(n, dtype=torch.int32, device=dev)
+    cov3d = cov3d_precomp if cov3d_precomp is not None else torch.empty((n, 6), dtype=torch.float32, device=dev)
+    depth_keys = torch.empty(n, dtype=torch.int64, device=dev)
+    check(lib().dsb_preprocess(C.byref(cam), n, ptr(means3d), ptr(shs), ptr(colors_precomp), ptr(opacities), ptr(scales),
+                               ptr(rotations), ptr(cov3d_precomp), ptr(records), ptr(radii), ptr(tiles), ptr(cov3d),
+                               ptr(depth_keys), stream_ptr()))
+    return records, radii, tiles, cov3d, depth_keys
+
+
+def plan_pairs(cam, tiles, depth_keys):
+    """Sorts depth_keys in place; returns (offsets, K)."""
+    n, dev = tiles.shape[0], tiles.device
+    alt = torch.empty_like(depth_keys)
+    offsets = torch.empty(n, dtype=torch.int32, device=dev)
+    ws_bytes = int(lib().dsb_plan_workspace_bytes(n))
+    ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=dev)
+    k = C.c_int64(0)
+    check(lib().dsb_plan_pairs(C.byref(cam), n, ptr(tiles), ptr(depth_keys), ptr(alt), ptr(offsets), ws.data_ptr(),
+                               ws_bytes, C.byref(k), stream_ptr()))
+    return offsets, int(k.value)
+
+
+def emit_pairs(cam, k, records, tiles, depth_keys_sorted, offsets):
+    n = tiles.shape[0]
+    pairs = torch.empty(k, dtype=torch.int64, device=tiles.device)
+    check(lib().dsb_emit_pairs(C.byref(cam), n, k, ptr(records), ptr(tiles), ptr(depth_keys_sorted), ptr(offsets),
+                               ptr(pairs), stream_ptr()))
+    return pairs
+
+
+def sort_pairs(items, begin_bit, end_bit):
+    """Stable radix sort of int64 words on bits [begin_bit, end_bit) (unsigned digit order); returns the sorted tensor."""
+    k = items.shape[0]
+    alt = torch.empty_like(items)
+    ws_bytes = int(lib().dsb_sort_workspace_bytes(k))
+    ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=items.device)
+    in_alt = C.c_int32(0)
+    check(lib().dsb_sort_pairs(ptr(items), ptr(alt), k, begin_bit, end_bit, ws.data_ptr(), ws_bytes, C.byref(in_alt),
+                               stream_ptr()))
+    return alt if in_alt.value else items
+
+
+def sort_by_keys(keys, values, begin_bit=0, end_bit=64):
+    """(int64 key, int32 value) pair sort, the reference's sort_by_keys interface; returns (keys, values)."""
+    k = keys.shape[0]
+    kalt, valt = torch.empty_like(keys), torch.empty_like(values)
+    ws_bytes = int(lib().dsb_sort_workspace_bytes(k))
+    ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=keys.device)
+    in_alt = C.c_int32(0)
+    check(lib().dsb_sort_by_keys(ptr(keys), ptr(kalt), ptr(values), ptr(valt), k, begin_bit, end_bit, ws.data_ptr(),
+                                 ws_bytes, C.byref(in_alt), stream_ptr()))
+    return (kalt, valt) if in_alt.value else (keys, values)
+
+
+def identify_tile_ranges(sorted_items, h, w):
+    ranges = torch.empty(num_tiles(h, w) + 1, dtype=torch.int32, device=sorted_items.device)
+    check(lib().dsb_identify_tile_ranges(ptr(sorted_items), sorted_items.shape[0], h, w, ptr(ranges), stream_ptr()))
+    return ranges
+
+
+def blend_forward(cam, records, sorted_pairs, ranges):
+    h, w, dev = cam.image_height, cam.image_width, records.device
+    image = torch.empty((h, w, 3), dtype=torch.float32, device=dev)
+    final_t = torch.empty((h, w), dtype=torch.float32, device=dev)
+    final_idx = torch.empty((h, w), dtype=torch.int32, device=dev)
+    check(lib().dsb_blend_forward(C.byref(cam), ptr(records), ptr(sorted_pairs), ptr(ranges), ptr(image), ptr(final_t),
+                                  ptr(final_idx), stream_ptr()))
+    return image, final_t, final_idx
+
+
+def blend_backward(cam, records, sorted_pairs, ranges, final_t, final_idx, v_image):
+    n = records.shape[0]
+    grad_acc = torch.zeros((n, GRAD_FLOATS), dtype=torch.float32, device=records.device)
+    check(lib().dsb_blend_backward(C.byref(cam), ptr(records), ptr(sorted_pairs), ptr(ranges), ptr(final_t),
+                                   ptr(final_idx), ptr(v_image), ptr(grad_acc), stream_ptr()))
+    return grad_acc
+
+
+def geometry_backward(cam, means3d, scales, rotations, records, cov3d, radii, grad_acc, num_coeff=16, accumulate=False,
+                      out=None):
+    n, dev = means3d.shape[0], means3d.device
+    if out is None:
+        mk = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)
+        out = dict(v_means3d=mk(n, 3), v_means2d=mk(n, 3), v_shs=mk(n, num_coeff, 3), v_colors=mk(n, 3),
+                   v_opacities=mk(n, 1), v_scales=mk(n, 3), v_rotations=mk(n, 4), v_cov3d=mk(n, 6))
+    check(lib().dsb_geometry_backward(C.byref(cam), n, ptr(means3d), ptr(scales), ptr(rotations), ptr(records), ptr(cov3d),
+                                      ptr(radii), ptr(grad_acc), ptr(out["v_means3d"]), ptr(out["v_means2d"]),
+                                      ptr(out["v_shs"]), ptr(out["v_colors"]), ptr(out["v_opacities"]),
+                                      ptr(out["v_scales"]), ptr(out["v_rotations"]), ptr(out["v_cov3d"]),
+                                      1 if accumulate else 0, stream_ptr()))
+    return out
+
+
+def export_reference_lists(sorted_pairs, records):
+    k = sorted_pairs.shape[0]
+    keys = torch.empty(k, dtype=torch.int64, device=records.device)
+    ids = torch.empty(k, dtype=torch.int32, device=records.device)
+    check(lib().dsb_export_reference_lists(ptr(sorted_pairs), k, ptr(records), ptr(keys), ptr(ids), stream_ptr()))
+    return keys, ids

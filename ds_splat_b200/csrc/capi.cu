@@ -1,0 +1,214 @@
+// extern "C" surface of the library (declared in include/dsb200.h): argument checks, the camera block,
+// the last-error string and the fused forward/backward calls the Python operator uses.
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace dsb {
+
+static thread_local char g_error[1024] = "";
+static std::atomic<long long> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int make_cam_params(const DsbCamera* cam, CamParams* out) {
+    DSB_REQUIRE(cam, "camera is null");
+    DSB_REQUIRE(cam->image_height > 0 && cam->image_width > 0, "image size must be positive (got %d x %d)",
+                cam->image_width, cam->image_height);
+    DSB_REQUIRE(cam->image_height <= 16 * 65535 && cam->image_width <= 16 * 65535, "image too large for 16-bit tile bounds");
+    DSB_REQUIRE(cam->viewmatrix && cam->projmatrix && cam->campos, "camera matrices / position are null");
+    DSB_REQUIRE(cam->sh_degree >= 0 && cam->sh_degree <= 4, "sh_degree must be in 0..4 (got %d)", cam->sh_degree);
+    DSB_REQUIRE(cam->max_sh_degree >= 0 && cam->max_sh_degree <= 3, "max_sh_degree must be in 0..3 (got %d)", cam->max_sh_degree);
+    DSB_REQUIRE(cam->tanfovx > 0.f && cam->tanfovy > 0.f, "tanfov must be positive");
+    CamParams p;
+    p.view = cam->viewmatrix; p.proj = cam->projmatrix; p.campos = cam->campos; p.bg = cam->bg;
+    p.H = cam->image_height; p.W = cam->image_width;
+    p.tiles_x = (p.W + kTile - 1) / kTile; p.tiles_y = (p.H + kTile - 1) / kTile;
+    p.tanfovx = cam->tanfovx; p.tanfovy = cam->tanfovy;
+    // Forward focal: size / (2 tanfov) in single precision (cpp/rasterizer_torch.cu:144-147 in the reference).
+    p.fx = p.W / (2 * cam->tanfovx); p.fy = p.H / (2 * cam->tanfovy);
+    p.cx = p.W / 2.0f; p.cy = p.H / 2.0f;
+    // Backward focal goes through atan and tan again (cpp/rasterizer_torch.cu:78-81,297-298).
+    p.fx_bwd = (float)p.W / (2.0f * tanf((2 * atanf(cam->tanfovx)) / 2.0f));
+    p.fy_bwd = (float)p.H / (2.0f * tanf((2 * atanf(cam->tanfovy)) / 2.0f));
+    p.scale_modifier = cam->scale_modifier;
+    p.sh_degree = cam->sh_degree;
+    p.max_coeff = (cam->max_sh_degree + 1) * (cam->max_sh_degree + 1);
+    p.transposed = cam->matrices_transposed != 0;
+    p.drop_last = (cam->flags & DSB_FLAG_DROP_LAST_SPLAT) != 0;
+    *out = p;
+    return DSB_OK;
+}
+
+}  // namespace dsb
+
+using namespace dsb;
+
+#define CAM_OR_RETURN(cam, cp)                   \
+    CamParams cp;                                \
+    {                                            \
+        const int rc__ = make_cam_params(cam, &cp); \
+        if (rc__ != DSB_OK) return rc__;         \
+    }
+
+extern "C" {
+
+const char* dsb_last_error(void) { return g_error; }
+int32_t dsb_version(void) { return 100; }
+int64_t dsb_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int64_t dsb_plan_workspace_bytes(int32_t n) { return plan_workspace_bytes(n < 0 ? 0 : n); }
+int64_t dsb_sort_workspace_bytes(int64_t k) { return sort_workspace_bytes(k < 0 ? 0 : k); }
+
+int dsb_preprocess(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
+                   const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
+                   float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
+                   void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    return launch_preprocess(cp, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records,
+                             radii, tiles_touched, cov3d, reinterpret_cast<u64*>(depth_keys), (cudaStream_t)stream);
+}
+
+int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched, uint64_t* depth_keys,
+                   uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
+                   int64_t* k_host, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    return launch_plan(cp, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
+                       offsets, workspace, workspace_bytes, k_host, (cudaStream_t)stream);
+}
+
+int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
+                   const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0 && k >= 0, "n and k must be non-negative");
+    return launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
+                       reinterpret_cast<u64*>(pairs), (cudaStream_t)stream);
+}
+
+int dsb_sort_pairs(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit, void* workspace,
+                   int64_t workspace_bytes, int32_t* sorted_in_alt_host, void* stream) {
+    DSB_REQUIRE(k >= 0, "k must be non-negative");
+    int in_alt = 0;
+    const int rc = launch_sort(reinterpret_cast<u64*>(items), reinterpret_cast<u64*>(items_alt), nullptr, nullptr, k,
+                               begin_bit, end_bit, workspace, workspace_bytes, &in_alt, (cudaStream_t)stream);
+    if (sorted_in_alt_host) *sorted_in_alt_host = in_alt;
+    return rc;
+}
+
+int dsb_sort_by_keys(int64_t* keys, int64_t* keys_alt, int32_t* values, int32_t* values_alt, int64_t k,
+                     int32_t begin_bit, int32_t end_bit, void* workspace, int64_t workspace_bytes,
+                     int32_t* sorted_in_alt_host, void* stream) {
+    DSB_REQUIRE(k >= 0, "k must be non-negative");
+    DSB_REQUIRE(values && values_alt, "sort_by_keys: values are required");
+    int in_alt = 0;
+    const int rc = launch_sort(reinterpret_cast<u64*>(keys), reinterpret_cast<u64*>(keys_alt),
+                               reinterpret_cast<u32*>(values), reinterpret_cast<u32*>(values_alt), k, begin_bit, end_bit,
+                               workspace, workspace_bytes, &in_alt, (cudaStream_t)stream);
+    if (sorted_in_alt_host) *sorted_in_alt_host = in_alt;
+    return rc;
+}
+
+int dsb_identify_tile_ranges(const uint64_t* sorted, int64_t k, int32_t image_height, int32_t image_width,
+                             int32_t* ranges, void* stream) {
+    DSB_REQUIRE(k >= 0, "k must be non-negative");
+    return launch_ranges(reinterpret_cast<const u64*>(sorted), k, image_height, image_width, ranges, (cudaStream_t)stream);
+}
+
+int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
+                      float* image, float* final_T, int32_t* final_idx, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, image, final_T,
+                                final_idx, (cudaStream_t)stream);
+}
+
+int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
+                       const float* final_T, const int32_t* final_idx, const float* v_image, float* grad_acc,
+                       void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    return launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
+                                 v_image, grad_acc, (cudaStream_t)stream);
+}
+
+int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
+                          const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
+                          const float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors,
+                          float* v_opacities, float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate,
+                          void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    return launch_geometry_backward(cp, n, means3d, scales, rotations, records, cov3d, radii, grad_acc, v_means3d,
+                                    v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d, accumulate,
+                                    (cudaStream_t)stream);
+}
+
+int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
+                     const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
+                     float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
+                     uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
+                     int64_t* k_host, void* stream) {
+    int rc = dsb_preprocess(cam, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records,
+                            radii, tiles_touched, cov3d, depth_keys, stream);
+    if (rc != DSB_OK) return rc;
+    return dsb_plan_pairs(cam, n, tiles_touched, depth_keys, depth_keys_alt, offsets, workspace, workspace_bytes, k_host,
+                          stream);
+}
+
+int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
+                       const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, uint64_t* pairs_alt,
+                       void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T,
+                       int32_t* final_idx, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
+                         reinterpret_cast<u64*>(pairs), s);
+    if (rc != DSB_OK) return rc;
+    // Only the tile id needs sorting now: ceil(log2(tiles)) live bits above bit 32.
+    int tile_bits = 1;
+    while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
+    int in_alt = 0;
+    rc = launch_sort(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, 32,
+                     32 + tile_bits, workspace, workspace_bytes, &in_alt, s);
+    if (rc != DSB_OK) return rc;
+    if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
+    rc = launch_ranges(reinterpret_cast<const u64*>(pairs), k, cp.H, cp.W, ranges, s);
+    if (rc != DSB_OK) return rc;
+    return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, s);
+}
+
+int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales, const float* rotations,
+                 const float* records, const float* cov3d, const int32_t* radii, const uint64_t* sorted_pairs,
+                 const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
+                 float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
+                 float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    if (n == 0) return DSB_OK;
+    DSB_REQUIRE(grad_acc, "backward: grad_acc is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
+    int rc = launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
+                                   v_image, grad_acc, s);
+    if (rc != DSB_OK) return rc;
+    return launch_geometry_backward(cp, n, means3d, scales, rotations, records, cov3d, radii, grad_acc, v_means3d,
+                                    v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d, accumulate, s);
+}
+
+int dsb_export_reference_lists(const uint64_t* sorted_pairs, int64_t k, const float* records, int64_t* keys, int32_t* ids,
+                               void* stream) {
+    DSB_REQUIRE(k >= 0, "k must be non-negative");
+    return launch_export(reinterpret_cast<const u64*>(sorted_pairs), k, records, keys, ids, (cudaStream_t)stream);
+}
+
+}  // extern "C"

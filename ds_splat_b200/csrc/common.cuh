@@ -1,0 +1,110 @@
+// Shared declarations of the sm_100a splat pipeline: error plumbing, the device-side camera block,
+// the packed per-splat record and the kernel launchers each stage file exports to capi.cu.
+#pragma once
+#include <cstdint>
+#include <cstdio>
+#include <cuda_runtime.h>
+
+#include "../../include/dsb200.h"
+
+namespace dsb {
+
+constexpr int kTile = 16;            // tile edge in pixels (cpp/rasterizer_kernels.cuh:6 in the reference)
+constexpr int kTilePixels = 256;
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+
+// ---- host-side error plumbing -------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+void count_launch(int n = 1);
+
+#define DSB_CUDA_CHECK(expr)                                                                  \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess) {                                                             \
+            ::dsb::set_error("%s failed at %s:%d: %s", #expr, __FILE__, __LINE__, cudaGetErrorString(e__)); \
+            return DSB_ERR_CUDA;                                                              \
+        }                                                                                     \
+    } while (0)
+
+#define DSB_LAUNCH_CHECK()                                                                    \
+    do {                                                                                      \
+        ::dsb::count_launch();                                                                \
+        cudaError_t e__ = cudaPeekAtLastError();                                              \
+        if (e__ != cudaSuccess) {                                                             \
+            ::dsb::set_error("kernel launch failed at %s:%d: %s", __FILE__, __LINE__, cudaGetErrorString(e__)); \
+            return DSB_ERR_CUDA;                                                              \
+        }                                                                                     \
+    } while (0)
+
+#define DSB_REQUIRE(cond, ...)                                                                \
+    do {                                                                                      \
+        if (!(cond)) {                                                                        \
+            ::dsb::set_error(__VA_ARGS__);                                                    \
+            return DSB_ERR_INVALID_ARGUMENT;                                                  \
+        }                                                                                     \
+    } while (0)
+
+// ---- camera block handed to kernels by value ------------------------------------------------------
+struct CamParams {
+    const float* view;    // device
+    const float* proj;    // device
+    const float* campos;  // device
+    const float* bg;      // device or null
+    int H, W, tiles_x, tiles_y;
+    float tanfovx, tanfovy;
+    float fx, fy, cx, cy;        // forward focal / principal point
+    float fx_bwd, fy_bwd;        // backward recomputes focal through atan/tan
+    float scale_modifier;
+    int sh_degree, max_coeff;
+    int transposed;              // matrices still in the caller's transposed layout
+    int drop_last;
+};
+
+int make_cam_params(const DsbCamera* cam, CamParams* out);
+
+// Element (r, c) of a 4x4 stored row-major, or transposed when the caller skipped the transposes.
+__device__ __forceinline__ float mat_at(const float* m, int r, int c, int transposed) {
+    return transposed ? m[c * 4 + r] : m[r * 4 + c];
+}
+
+// ---- packed per-splat record: three float4 lanes ------------------------------------------------
+//   q0 = (x_pix, y_pix, conic_a, conic_b)   q1 = (conic_c, opacity, r, g)   q2 = (b, depth, rect_x, rect_y)
+// rect_* hold (lo | hi << 16) tile bounds as integer bits.
+__device__ __forceinline__ u32 pack_rect(int lo, int hi) { return (u32)lo | ((u32)hi << 16); }
+
+// ---- bounded waits -----------------------------------------------------------------------------
+// Every spin in this library gives up after this many polls, records why in a status word and
+// returns, so a logic error can never hang the GPU.
+constexpr u32 kSpinLimit = 1u << 22;
+
+// ---- launchers (one per stage file) -----------------------------------------------------------------
+int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
+                      const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
+                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, cudaStream_t s);
+
+int64_t sort_workspace_bytes(int64_t k);
+int64_t sort_status_offset();  // byte offset of the int status word inside a sort workspace
+int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s);
+
+int64_t plan_workspace_bytes(int n);
+int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
+                void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
+int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
+                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s);
+int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
+int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);
+
+int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
+                         float* image, float* final_T, int32_t* final_idx, cudaStream_t s);
+int launch_blend_backward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
+                          const float* final_T, const int32_t* final_idx, const float* v_image, float* grad_acc,
+                          cudaStream_t s);
+int launch_geometry_backward(const CamParams& cp, int n, const float* means, const float* scales, const float* rots,
+                             const float* records, const float* cov3d, const int32_t* radii, const float* grad_acc,
+                             float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opac,
+                             float* v_scales, float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
+
+}  // namespace dsb

@@ -1,0 +1,280 @@
+// Stage (a): per-splat projection, 3-D -> 2-D covariance, conic, SH colour, radius and tile rectangle.
+//
+// Takes the place of the reference's rasterizer_preprocessing_kernel (cpp/rasterizer_kernels.cu:57-161)
+// and its device helpers (:7-55, :163-250, :325-337, :433-659).  One thread per splat; every input
+// tensor of a 256-splat block is brought into shared memory with fully coalesced 16-byte loads (the
+// caller's tensors are row-per-splat, so a direct per-thread read would stride by 12..192 bytes), and
+// every output row goes back out through shared memory as contiguous float4 streams.
+//
+// Arithmetic note: radii, tile rectangles and depth bits feed integer stages that must agree bit for
+// bit with the reference's --use_fast_math build, so the expressions below keep the reference's
+// association and this file is compiled with the same flag (same approximate rcp/sqrt/rsqrt and the
+// same FMA contraction rules).
+#include "common.cuh"
+
+namespace dsb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kShRow4 = 13;  // padded SH row in float4 units (12 used): conflict-free 16-byte shared loads
+
+__device__ __forceinline__ float sh_channel(const float* f, int ch, int degree, float x, float y, float z) {
+    // f = 48 coefficients of one splat, coefficient-major / channel-minor.
+    float res = 0.0f;
+    res += 0.28209479177387814f * f[ch];
+    if (degree >= 1) {
+        res += 0.4886025119029199f * (-y * f[3 + ch] + z * f[6 + ch] - x * f[9 + ch]);
+        if (degree >= 2) {
+            const float xx = x * x, yy = y * y, zz = z * z, xy = x * y, xz = x * z, yz = y * z;
+            res += 1.0925484305920792f * xy * f[12 + ch] + -1.0925484305920792f * yz * f[15 + ch] +
+                   0.31539156525252005f * (2.0f * zz - xx - yy) * f[18 + ch] + -1.0925484305920792f * xz * f[21 + ch] +
+                   0.5462742152960396f * (xx - yy) * f[24 + ch];
+            if (degree >= 3) {
+                res += -0.5900435899266435f * y * (3 * xx - yy) * f[27 + ch] + 2.890611442640554f * xy * z * f[30 + ch] +
+                       -0.4570457994644658f * y * (4 * zz - xx - yy) * f[33 + ch] +
+                       0.3731763325901154f * z * (2 * zz - 3 * xx - 3 * yy) * f[36 + ch] +
+                       -0.4570457994644658f * x * (4 * zz - xx - yy) * f[39 + ch] + 1.445305721320277f * z * (xx - yy) * f[42 + ch] +
+                       -0.5900435899266435f * x * (xx - 3 * yy) * f[45 + ch];
+            }
+        }
+    }
+    return fmaxf(res + 0.5f, 0.0f);
+}
+
+// Cooperative copy of `count` floats from global to shared (coalesced 4-byte lanes).
+__device__ __forceinline__ void stage_floats(float* dst, const float* src, int count, int tid) {
+    for (int k = tid; k < count; k += kThreads) dst[k] = src[k];
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ means, const float* __restrict__ shs,
+                  const float* __restrict__ colors_precomp, const float* __restrict__ opac,
+                  const float* __restrict__ scales, const float* __restrict__ rots,
+                  const float* __restrict__ cov3d_precomp, float4* __restrict__ records, int32_t* __restrict__ radii,
+                  int32_t* __restrict__ tiles, float* __restrict__ cov3d, u64* __restrict__ depth_keys,
+                  const int sh_vec4) {
+    extern __shared__ float4 dyn4[];
+    __shared__ float s_cam[31];      // view rows 0..2 (12), projection (16), camera centre (3)
+    __shared__ float s_means[kThreads * 3];
+    __shared__ float s_scales[kThreads * 3];
+
+    const int tid = threadIdx.x;
+    const int base = blockIdx.x * kThreads;
+    const int cnt = min(kThreads, n - base);
+    const int i = base + tid;
+
+    if (tid < 12) s_cam[tid] = mat_at(cp.view, tid >> 2, tid & 3, cp.transposed);
+    else if (tid < 28) s_cam[tid] = mat_at(cp.proj, (tid - 12) >> 2, (tid - 12) & 3, cp.transposed);
+    else if (tid < 31) s_cam[tid] = cp.campos[tid - 28];
+
+    stage_floats(s_means, means + (size_t)base * 3, cnt * 3, tid);
+    if (scales) stage_floats(s_scales, scales + (size_t)base * 3, cnt * 3, tid);
+
+    const int row_floats = 3 * cp.max_coeff;
+    float* s_sh = reinterpret_cast<float*>(dyn4);
+    if (shs && !colors_precomp) {
+        if (sh_vec4) {  // 16 coefficients, 16-byte aligned rows: float4 in, padded float4 rows in shared memory
+            const float4* g = reinterpret_cast<const float4*>(shs + (size_t)base * 48);
+            const int total4 = cnt * 12;
+#pragma unroll
+            for (int r = 0; r < 12; ++r) {
+                const int k = r * kThreads + tid;
+                if (k < total4) {
+                    const int row = k / 12;
+                    dyn4[row * kShRow4 + (k - row * 12)] = __ldg(g + k);
+                }
+            }
+        } else {  // any other layout: scalar lanes, odd row stride
+            const int stride = row_floats | 1;
+            const float* g = shs + (size_t)base * row_floats;
+            for (int k = tid; k < cnt * row_floats; k += kThreads) {
+                const int row = k / row_floats;
+                s_sh[row * stride + (k - row * row_floats)] = g[k];
+            }
+        }
+    }
+    __syncthreads();
+
+    float4 q0 = make_float4(0, 0, 0, 0), q1 = q0, q2 = q0;
+    float S[6] = {0, 0, 0, 0, 0, 0};
+    int radius = 0, count = 0;
+    float tz = 0.0f;
+
+    if (tid < cnt) {
+        const float* V = s_cam;
+        const float* P = s_cam + 12;
+        const float mx = s_means[3 * tid], my = s_means[3 * tid + 1], mz = s_means[3 * tid + 2];
+
+        // 3-D covariance from scale and rotation (or taken as given).
+        if (cov3d_precomp) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) S[k] = cov3d_precomp[(size_t)i * 6 + k];
+        } else {
+            const float4 q = *reinterpret_cast<const float4*>(rots + (size_t)i * 4);
+            float r = q.x, x = q.y, y = q.z, z = q.w;
+            const float inv_norm = rsqrtf(r * r + x * x + y * y + z * z);
+            r = r * inv_norm; x = x * inv_norm; y = y * inv_norm; z = z * inv_norm;
+            const float sx = s_scales[3 * tid] * cp.scale_modifier, sy = s_scales[3 * tid + 1] * cp.scale_modifier,
+                        sz = s_scales[3 * tid + 2] * cp.scale_modifier;
+            const float r00 = 1.0f - 2.0f * (y * y + z * z), r01 = 2.0f * (x * y - r * z), r02 = 2.0f * (x * z + r * y);
+            const float r10 = 2.0f * (x * y + r * z), r11 = 1.0f - 2.0f * (x * x + z * z), r12 = 2.0f * (y * z - r * x);
+            const float r20 = 2.0f * (x * z - r * y), r21 = 2.0f * (y * z + r * x), r22 = 1.0f - 2.0f * (x * x + y * y);
+            const float m00 = sx * r00, m01 = sy * r01, m02 = sz * r02;
+            const float m10 = sx * r10, m11 = sy * r11, m12 = sz * r12;
+            const float m20 = sx * r20, m21 = sy * r21, m22 = sz * r22;
+            S[0] = m00 * m00 + m01 * m01 + m02 * m02;
+            S[1] = m00 * m10 + m01 * m11 + m02 * m12;
+            S[2] = m00 * m20 + m01 * m21 + m02 * m22;
+            S[3] = m10 * m10 + m11 * m11 + m12 * m12;
+            S[4] = m10 * m20 + m11 * m21 + m12 * m22;
+            S[5] = m20 * m20 + m21 * m21 + m22 * m22;
+        }
+
+        // Colour.
+        float cr, cg, cb;
+        if (colors_precomp) {
+            cr = colors_precomp[(size_t)i * 3]; cg = colors_precomp[(size_t)i * 3 + 1]; cb = colors_precomp[(size_t)i * 3 + 2];
+        } else if (cp.sh_degree > 3) {
+            cr = cg = cb = 0.0f;
+        } else {
+            float dx = mx - s_cam[28], dy = my - s_cam[29], dz = mz - s_cam[30];
+            const float inv_norm = rsqrtf(dx * dx + dy * dy + dz * dz);
+            dx = dx * inv_norm; dy = dy * inv_norm; dz = dz * inv_norm;
+            float f[48];
+            if (sh_vec4) {
+                const float4* row = dyn4 + tid * kShRow4;
+#pragma unroll
+                for (int j = 0; j < 12; ++j) {
+                    const float4 v = row[j];
+                    f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
+                }
+            } else {
+                const float* row = s_sh + tid * (row_floats | 1);
+                const int have = min(row_floats, 3 * (cp.sh_degree + 1) * (cp.sh_degree + 1));
+#pragma unroll
+                for (int j = 0; j < 48; ++j) f[j] = j < have ? row[j] : 0.0f;
+            }
+            cr = sh_channel(f, 0, cp.sh_degree, dx, dy, dz);
+            cg = sh_channel(f, 1, cp.sh_degree, dx, dy, dz);
+            cb = sh_channel(f, 2, cp.sh_degree, dx, dy, dz);
+        }
+
+        // Frustum test on the projected centre (strict bounds, z_ndc > 0.1).
+        const float inv_w = 1.f / (P[12] * mx + P[13] * my + P[14] * mz + P[15]);
+        const float ndc_x = inv_w * (P[0] * mx + P[1] * my + P[2] * mz + P[3]);
+        const float ndc_y = inv_w * (P[4] * mx + P[5] * my + P[6] * mz + P[7]);
+        const float ndc_z = inv_w * (P[8] * mx + P[9] * my + P[10] * mz + P[11]);
+        const int in_frustum = ndc_x > -1.f && ndc_x < 1.f && ndc_y > -1.f && ndc_y < 1.f && ndc_z > 0.1f;
+
+        // View-space centre.
+        const float tx = V[0] * mx + V[1] * my + V[2] * mz + V[3];
+        const float ty = V[4] * mx + V[5] * my + V[6] * mz + V[7];
+        tz = V[8] * mx + V[9] * my + V[10] * mz + V[11];
+
+        // EWA projection of the covariance: cov2d = (W J^T)^T Sigma (W J^T), W = view rotation columns.
+        const float limx = 1.3f * cp.tanfovx, limy = 1.3f * cp.tanfovy;
+        const float txtz = tx / tz, tytz = ty / tz;
+        const float t0 = min(limx, max(-limx, txtz)) * tz, t1 = min(limy, max(-limy, tytz)) * tz, t2 = tz;
+        const float J[3][3] = {{cp.fx / t2, 0, -(cp.fx * t0) / (t2 * t2)}, {0, cp.fy / t2, -(cp.fy * t1) / (t2 * t2)}, {0, 0, 0}};
+        const float Wc[3][3] = {{V[0], V[4], V[8]}, {V[1], V[5], V[9]}, {V[2], V[6], V[10]}};
+        float Tm[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+#pragma unroll
+            for (int b = 0; b < 3; ++b)
+#pragma unroll
+                for (int k = 0; k < 3; ++k) Tm[a][b] += Wc[a][k] * J[b][k];
+        const float Sm[3][3] = {{S[0], S[1], S[2]}, {S[1], S[3], S[4]}, {S[2], S[4], S[5]}};
+        float half[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+#pragma unroll
+            for (int b = 0; b < 3; ++b)
+#pragma unroll
+                for (int k = 0; k < 3; ++k) half[a][b] += Tm[k][a] * Sm[k][b];
+        float c2[2][2] = {{0, 0}, {0, 0}};
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int k = 0; k < 3; ++k) c2[a][b] += half[a][k] * Tm[k][b];
+        const float ca = c2[0][0] + 0.3f, cb2 = c2[0][1], cc = c2[1][1] + 0.3f;
+
+        // Pixel centre.
+        const float z_inv = 1.f / (tz + 1e-6f);
+        const float px = cp.fx * tx * z_inv + cp.cx, py = cp.fy * ty * z_inv + cp.cy;
+
+        // Radius from the larger eigenvalue, 3 sigma, rounded up.
+        const float det = ca * cc - cb2 * cb2;
+        const float mid = 0.5f * (ca + cc);
+        const float diff = mid * mid - det;
+        const float lambda1 = mid + sqrtf(max(0.1f, diff));
+        const float lambda2 = mid - sqrtf(max(0.1f, diff));
+        radius = ceilf(3 * sqrtf(max(lambda1, lambda2))) * (det > 1e-6f && in_frustum > 0);
+
+        // Tile rectangle (float -> int conversion truncates toward zero) and its size.
+        const float cxt = px / kTile, cyt = py / kTile, dt = radius / (float)kTile;
+        const int x0 = min(max(0, (int)(cxt - dt)), cp.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cp.tiles_x);
+        const int y0 = min(max(0, (int)(cyt - dt)), cp.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cp.tiles_y);
+        count = (x1 - x0) * (y1 - y0) * (radius > 0);
+
+        // Conic = inverse of the dilated 2-D covariance.
+        const float det_inv = 1.0f / (det + 1e-6f);
+        q0 = make_float4(px, py, cc * det_inv, -cb2 * det_inv);
+        q1 = make_float4(ca * det_inv, opac[i], cr, cg);
+        q2 = make_float4(cb, tz, __uint_as_float(pack_rect(x0, x1)), __uint_as_float(pack_rect(y0, y1)));
+
+        radii[i] = radius;
+        tiles[i] = count;
+        depth_keys[i] = ((u64)__float_as_uint(tz) << 32) | (u32)i;
+    }
+
+    // Outputs leave through shared memory so that global stores are contiguous 16-byte lanes.
+    __syncthreads();
+    float4* s_rec = dyn4;                                   // [256][3]
+    float* s_cov = reinterpret_cast<float*>(dyn4 + kThreads * 3);  // [256][6]
+    s_rec[tid * 3] = q0; s_rec[tid * 3 + 1] = q1; s_rec[tid * 3 + 2] = q2;
+#pragma unroll
+    for (int k = 0; k < 6; ++k) s_cov[tid * 6 + k] = S[k];
+    __syncthreads();
+    float4* grec = records + (size_t)base * 3;
+    for (int k = tid; k < cnt * 3; k += kThreads) grec[k] = s_rec[k];
+    if (cov3d && !cov3d_precomp) {
+        float* gcov = cov3d + (size_t)base * 6;
+        for (int k = tid; k < cnt * 6; k += kThreads) gcov[k] = s_cov[k];
+    }
+}
+
+}  // namespace
+
+int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
+                      const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
+                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, cudaStream_t s) {
+    if (n == 0) return DSB_OK;
+    DSB_REQUIRE(means && opac && records && radii && tiles && depth_keys, "preprocess: null required pointer");
+    DSB_REQUIRE(colors_precomp || shs, "preprocess: need shs or colors_precomp");
+    DSB_REQUIRE(cov3d_precomp || (scales && rots), "preprocess: need scales and rotations, or cov3d_precomp");
+    DSB_REQUIRE(((uintptr_t)records & 15) == 0, "preprocess: records must be 16-byte aligned");
+    DSB_REQUIRE(!rots || ((uintptr_t)rots & 15) == 0, "preprocess: rotations must be 16-byte aligned");
+    const int sh_vec4 = shs && cp.max_coeff == 16 && ((uintptr_t)shs & 15) == 0;
+    // dynamic shared memory: padded SH rows on the way in, record + covariance rows on the way out
+    const size_t sh_bytes = sh_vec4 ? (size_t)kThreads * kShRow4 * 16 : (size_t)kThreads * ((3 * cp.max_coeff) | 1) * 4;
+    const size_t out_bytes = (size_t)kThreads * (3 * 16 + 6 * 4);
+    const size_t dyn = sh_bytes > out_bytes ? sh_bytes : out_bytes;
+    static bool attr_set = false;
+    if (!attr_set) {
+        DSB_CUDA_CHECK(cudaFuncSetAttribute(preprocess_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        attr_set = true;
+    }
+    DSB_REQUIRE(dyn <= 64 * 1024, "preprocess: SH layout too large for shared memory");
+    const int blocks = (n + kThreads - 1) / kThreads;
+    preprocess_kernel<<<blocks, kThreads, dyn, s>>>(cp, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp,
+                                                   reinterpret_cast<float4*>(records), radii, tiles, cov3d, depth_keys,
+                                                   sh_vec4);
+    DSB_LAUNCH_CHECK();
+    return DSB_OK;
+}
+
+}  // namespace dsb

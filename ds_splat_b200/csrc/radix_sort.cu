@@ -1,0 +1,269 @@
+// Stage (c): stable least-significant-digit radix sort, "onesweep" style.
+//
+// Takes the place of thrust::sort_by_key in the reference (cpp/rasterizer_torch.cu:70-76).  One
+// histogram kernel reads the keys once and counts every 8-bit digit of the requested bit range; then
+// each digit takes ONE kernel that reads and writes every item exactly once: a block ranks its 4096
+// items, publishes its per-digit counts, and learns the counts of all earlier blocks by decoupled
+// look-back (each block polls its predecessors' status words instead of waiting for a separate scan
+// kernel).  Only the live bits are sorted: callers pass [begin_bit, end_bit).
+//
+// Stability (equal digits keep their input order) is what makes the result identical to the
+// reference's sort: within a warp items are ranked in memory order with match_any, warps are
+// ordered by a scan, blocks by the look-back.
+//
+// Every poll loop is bounded (kSpinLimit): on expiry the block records DSB_ERR_DEVICE_WAIT_EXPIRED in
+// the workspace status word and carries on with whatever it has, so the kernel always terminates.
+#include <cstddef>
+
+#include "common.cuh"
+
+namespace dsb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kItems = 16;                      // items per thread
+constexpr int kTileItems = kThreads * kItems;   // 4096 items per block
+constexpr int kRadix = 256;
+constexpr int kMaxPasses = 8;
+constexpr u32 kFlagAggregate = 1u << 30;        // status word holds this block's own count
+constexpr u32 kFlagInclusive = 1u << 31;        // status word holds the count of this and all earlier blocks
+constexpr u32 kValueMask = (1u << 30) - 1;
+
+struct SortHeader {                  // start of the workspace, zeroed before every sort
+    u32 hist[kMaxPasses][kRadix];
+    u32 tile_counter[kMaxPasses];
+    int status;
+    int pad[7];
+};
+
+__device__ __forceinline__ u32 digit_of(u64 key, int shift, u32 mask, u32 flip) {
+    return ((u32)(key >> shift) & mask) ^ flip;
+}
+
+// Counts all digits of all passes in one read of the keys.  Per-warp aggregation with match_any keeps
+// the shared-memory atomics to one per distinct digit per warp, which matters when a digit is nearly
+// constant (the exponent byte of depth keys, the high tile bits).
+__global__ void __launch_bounds__(kThreads)
+radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const int begin_bit, const int npass,
+                       const u32 last_mask, const u32 last_flip, u32* __restrict__ hist) {
+    __shared__ u32 s_hist[kMaxPasses][kRadix];
+    for (int k = threadIdx.x; k < npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
+    __syncthreads();
+    const u32 lane = threadIdx.x & 31;
+    const u32 n_round = (n + 31u) & ~31u;  // whole warps stay converged for match_any
+    for (u32 i = blockIdx.x * kThreads + threadIdx.x; i < n_round; i += gridDim.x * kThreads) {
+        const bool valid = i < n;
+        const u64 key = valid ? keys[i] : 0ull;
+        for (int p = 0; p < npass; ++p) {
+            const bool last = p == npass - 1;
+            const u32 d = digit_of(key, begin_bit + 8 * p, last ? last_mask : 0xffu, last ? last_flip : 0u);
+            const u32 m = __match_any_sync(0xffffffffu, valid ? d : 0xffffffffu);
+            if (valid && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[p][d], (u32)__popc(m));
+        }
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < npass * kRadix; k += kThreads) {
+        const u32 c = (&s_hist[0][0])[k];
+        if (c) atomicAdd(hist + k, c);
+    }
+}
+
+__device__ __forceinline__ u32 block_exclusive_scan_256(u32 v, u32* s_warp_sums, int tid) {
+    // exclusive prefix of v over the 256 threads of the block; s_warp_sums has kWarps entries
+    const int lane = tid & 31, warp = tid >> 5;
+    u32 incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+    }
+    __syncthreads();  // protects s_warp_sums across consecutive calls
+    if (lane == 31) s_warp_sums[warp] = incl;
+    __syncthreads();
+    u32 prefix = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) prefix += (w < warp) ? s_warp_sums[w] : 0u;
+    return prefix + incl - v;
+}
+
+template <bool HAS_VALS>
+__global__ void __launch_bounds__(kThreads)
+onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
+                const u32 n, const int shift, const u32 mask, const u32 flip, const u32* __restrict__ hist,
+                u32* __restrict__ tile_counter, u32* __restrict__ lookback, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    u64* s_keys = reinterpret_cast<u64*>(dyn);                         // [4096]
+    u32* s_vals = reinterpret_cast<u32*>(dyn + kTileItems * sizeof(u64));  // [4096] when HAS_VALS
+    __shared__ u32 s_wcnt[kWarps][kRadix];   // per-warp digit counts, later per-warp digit offsets
+    __shared__ u32 s_dstart[kRadix];         // first slot of each digit inside the block's sorted tile
+    __shared__ u32 s_glob[kRadix];           // global position of slot p with digit d is s_glob[d] + p
+    __shared__ u32 s_wsum[kWarps];
+    __shared__ u32 s_tile;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_tile = atomicAdd(tile_counter, 1u);  // blocks take tiles in the order they start running
+    for (int k = tid; k < kWarps * kRadix; k += kThreads) (&s_wcnt[0][0])[k] = 0;
+    __syncthreads();
+    const u32 tile = s_tile;
+    const u32 tile_base = tile * (u32)kTileItems;
+    const u32 tile_n = min((u32)kTileItems, n - tile_base);
+    const u32 wbase = tile_base + (u32)warp * (32 * kItems);
+
+    // Load: item i of lane l sits at wbase + 32 i + l, so (i, l) order is memory order.
+    u64 key[kItems];
+    u32 val[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const u32 pos = wbase + 32 * i + lane;
+        key[i] = pos < n ? kin[pos] : ~0ull;
+        if (HAS_VALS) val[i] = pos < n ? vin[pos] : 0u;
+    }
+
+    // Rank inside the warp: lanes holding the same digit find each other with match_any; the lowest
+    // of them bumps the warp's counter for that digit by the group size.
+    u32 rank[kItems];
+    const u32 lanemask_lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const bool valid = wbase + 32 * i + lane < n;
+        const u32 d = digit_of(key[i], shift, mask, flip);
+        const u32 m = __match_any_sync(0xffffffffu, valid ? d : 0xffffffffu);
+        const u32 lower = m & lanemask_lt;
+        u32 before = 0;
+        if (lower == 0 && valid) {
+            before = s_wcnt[warp][d];
+            s_wcnt[warp][d] = before + (u32)__popc(m);
+        }
+        before = __shfl_sync(0xffffffffu, before, __ffs(m) - 1);
+        rank[i] = before + (u32)__popc(lower);
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // Thread d owns digit d: order the warps, publish the block's count, find the digit's first slot.
+    u32 total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const u32 c = s_wcnt[w][tid];
+        s_wcnt[w][tid] = total;
+        total += c;
+    }
+    volatile u32* my_status = lookback + (size_t)tile * kRadix + tid;
+    *my_status = total | (tile == 0 ? kFlagInclusive : kFlagAggregate);
+
+    const u32 dstart = block_exclusive_scan_256(total, s_wsum, tid);
+    const u32 gstart = block_exclusive_scan_256(hist[tid], s_wsum, tid);
+    s_dstart[tid] = dstart;
+
+    // Decoupled look-back over earlier tiles for this digit.
+    u32 earlier = 0;
+    if (tile > 0) {
+        int p = (int)tile - 1;
+        u32 polls = 0;
+        while (p >= 0) {
+            const u32 v = *(volatile const u32*)(lookback + (size_t)p * kRadix + tid);
+            if ((v >> 30) == 0) {
+                if (++polls > kSpinLimit) { atomicExch(status, DSB_ERR_DEVICE_WAIT_EXPIRED); break; }
+                __nanosleep(40);
+                continue;
+            }
+            earlier += v & kValueMask;
+            if (v & kFlagInclusive) break;
+            --p;
+        }
+        *my_status = ((earlier + total) & kValueMask) | kFlagInclusive;
+    }
+    s_glob[tid] = gstart + earlier - dstart;
+    __syncthreads();
+
+    // Scatter into block-sorted order in shared memory, then stream out: consecutive slots of one
+    // digit are consecutive in global memory, so the stores coalesce.
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        if (wbase + 32 * i + lane < n) {
+            const u32 d = digit_of(key[i], shift, mask, flip);
+            const u32 slot = s_dstart[d] + s_wcnt[warp][d] + rank[i];
+            s_keys[slot] = key[i];
+            if (HAS_VALS) s_vals[slot] = val[i];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+        const u32 slot = j * kThreads + tid;
+        if (slot < tile_n) {
+            const u64 k = s_keys[slot];
+            const u32 dst = s_glob[digit_of(k, shift, mask, flip)] + slot;
+            kout[dst] = k;
+            if (HAS_VALS) vout[dst] = s_vals[slot];
+        }
+    }
+}
+
+}  // namespace
+
+int64_t sort_workspace_bytes(int64_t k) {
+    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    return (int64_t)sizeof(SortHeader) + (int64_t)kMaxPasses * tiles * kRadix * (int64_t)sizeof(u32);
+}
+
+int64_t sort_status_offset() { return (int64_t)offsetof(SortHeader, status); }
+
+// Sorts k items on bits [begin_bit, end_bit).  vals may be null.  *in_alt tells where the result is.
+int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s) {
+    if (in_alt) *in_alt = 0;
+    DSB_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit < end_bit, "sort: bad bit range [%d, %d)", begin_bit, end_bit);
+    if (k <= 1) return DSB_OK;
+    if (k >= DSB_MAX_PAIRS) {
+        set_error("sort: %lld items exceed the supported maximum of 2^30 - 1", (long long)k);
+        return DSB_ERR_TOO_MANY_PAIRS;
+    }
+    DSB_REQUIRE(items && items_alt && ws, "sort: null pointer");
+    DSB_REQUIRE(!vals == !vals_alt, "sort: values and alternate values must both be given or both be null");
+    const int bits = end_bit - begin_bit;
+    const int npass = (bits + 7) / 8;
+    const int last_bits = bits - 8 * (npass - 1);
+    const u32 last_mask = (1u << last_bits) - 1u;
+    const u32 last_flip = (end_bit == 64 && vals) ? (1u << (last_bits - 1)) : 0u;  // signed keys in the pair interface
+    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int64_t need = (int64_t)sizeof(SortHeader) + (int64_t)npass * tiles * kRadix * (int64_t)sizeof(u32);
+    if (ws_bytes < need) {
+        set_error("sort: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
+        return DSB_ERR_WORKSPACE_TOO_SMALL;
+    }
+    DSB_REQUIRE(((uintptr_t)ws & 15) == 0, "sort: workspace must be 16-byte aligned");
+    SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
+    u32* lookback = reinterpret_cast<u32*>(hdr + 1);
+    DSB_CUDA_CHECK(cudaMemsetAsync(ws, 0, (size_t)need, s));
+
+    const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
+    radix_histogram_kernel<<<hist_blocks, kThreads, 0, s>>>(items, (u32)k, begin_bit, npass, last_mask, last_flip, &hdr->hist[0][0]);
+    DSB_LAUNCH_CHECK();
+
+    const size_t dyn = kTileItems * (sizeof(u64) + (vals ? sizeof(u32) : 0));
+    if (vals) DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    else DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    u64 *src = items, *dst = items_alt;
+    u32 *vsrc = vals, *vdst = vals_alt;
+    for (int p = 0; p < npass; ++p) {
+        const bool last = p == npass - 1;
+        const u32 mask = last ? last_mask : 0xffu, flip = last ? last_flip : 0u;
+        u32* lb = lookback + (size_t)p * tiles * kRadix;
+        if (vals)
+            onesweep_kernel<true><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, (u32)k, begin_bit + 8 * p, mask, flip,
+                                                                      hdr->hist[p], &hdr->tile_counter[p], lb, &hdr->status);
+        else
+            onesweep_kernel<false><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, nullptr, nullptr, (u32)k, begin_bit + 8 * p, mask,
+                                                                       flip, hdr->hist[p], &hdr->tile_counter[p], lb, &hdr->status);
+        DSB_LAUNCH_CHECK();
+        u64* t = src; src = dst; dst = t;
+        u32* tv = vsrc; vsrc = vdst; vdst = tv;
+    }
+    if (in_alt) *in_alt = npass & 1;
+    return DSB_OK;
+}
+
+}  // namespace dsb

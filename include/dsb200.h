@@ -1,0 +1,184 @@
+/*
+ * dsb200 -- C ABI of the sm_100a Gaussian-splat rasterizer.
+ *
+ * Plain pointers and sizes only: every buffer is caller-owned DEVICE memory unless a parameter says
+ * "host"; every call enqueues its work on `stream` (a cudaStream_t passed as void*) and returns an int
+ * status (0 = ok, negative = error, text from dsb_last_error()).  The library keeps no state between
+ * calls except the last error string and a launch counter.
+ *
+ * Each entry point replaces one function of the reference's torch extension `ds_splat_cuda`
+ * (bound in cpp/rasterizer_python.cpp:3-23); the comment above it cites that function.
+ */
+#ifndef DSB200_H_
+#define DSB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSB_OK 0
+#define DSB_ERR_INVALID_ARGUMENT (-1)
+#define DSB_ERR_CUDA (-2)
+#define DSB_ERR_WORKSPACE_TOO_SMALL (-3)
+#define DSB_ERR_TOO_MANY_PAIRS (-4)
+#define DSB_ERR_DEVICE_WAIT_EXPIRED (-5)
+#define DSB_ERR_UNSUPPORTED (-6)
+
+/* The reference never emits (tile, splat) pairs for the splat with the highest index: it takes the
+ * exclusive prefix of the last splat as the pair total (cpp/rasterizer_torch.cu:97-104).  With this
+ * flag set the library reproduces that, which bit-exact parity of the sorted lists needs. */
+#define DSB_FLAG_DROP_LAST_SPLAT 1
+
+#define DSB_RECORD_FLOATS 12  /* packed per-splat record: 3 x float4, see DsbCamera notes below   */
+#define DSB_GRAD_FLOATS 12    /* per-splat accumulator row written by dsb_blend_backward          */
+#define DSB_MAX_PAIRS ((int64_t)1 << 30)
+
+/*
+ * Camera and render settings: the fields of the reference's TorchRasterizationSettings
+ * (cpp/ds_cuda_rasterizer/rasterizer_torch.hpp:7-22).  The struct lives in HOST memory; the four
+ * pointers inside it point to DEVICE memory (as the reference's settings tensors do).
+ *   matrices_transposed = 0: viewmatrix/projmatrix are row-major [R|t] and P*V, the form the reference
+ *                            kernels read after ds_splat/rasterizer.py:147-148 transposed them;
+ *   matrices_transposed = 1: they are still in the caller's (graphdeco) transposed form, and the
+ *                            kernels index them accordingly -- saves the two transposes per call.
+ * prefiltered / debug of the reference are accepted by the Python layer and, like there, unused.
+ */
+typedef struct DsbCamera {
+    int32_t image_height;
+    int32_t image_width;
+    float tanfovx;
+    float tanfovy;
+    float scale_modifier;
+    int32_t sh_degree;            /* active degree, 0..3                                          */
+    int32_t max_sh_degree;        /* degree the shs tensor is laid out for: (max+1)^2 rows of 3   */
+    int32_t matrices_transposed;
+    int32_t flags;                /* DSB_FLAG_*                                                   */
+    int32_t reserved;
+    const float* viewmatrix;      /* device, 16 floats */
+    const float* projmatrix;      /* device, 16 floats */
+    const float* campos;          /* device, 3 floats  */
+    const float* bg;              /* device, 3 floats, or NULL for black                          */
+} DsbCamera;
+
+const char* dsb_last_error(void);
+int32_t dsb_version(void);
+/* Number of kernels this library has launched in this process (monotonic). */
+int64_t dsb_launch_count(void);
+
+/* ---- workspace sizes (host arithmetic only) ------------------------------------------------- */
+/* Scratch for dsb_plan_pairs (depth ordering of n splats + scan). */
+int64_t dsb_plan_workspace_bytes(int32_t n);
+/* Scratch for dsb_sort_pairs / dsb_sort_by_keys over k items (excludes the alternate buffers). */
+int64_t dsb_sort_workspace_bytes(int64_t k);
+
+/* ---- stage (a) ------------------------------------------------------------------------------
+ * Replaces rasterizer_forward_preprocessing + rasterizer_preprocessing_kernel
+ * (cpp/rasterizer_torch.cu:115-168, cpp/rasterizer_kernels.cu:57-161).
+ * shs may be NULL when colors_precomp is given; scales/rotations may be NULL when cov3d_precomp is.
+ * Outputs: records [n][12] = (x_pix, y_pix, conic_a, conic_b | conic_c, opacity, r, g | b, depth,
+ * rect_x, rect_y) with rect_* = (lo | hi << 16) tile bounds as integer bits; radii [n] int32;
+ * tiles_touched [n] int32; cov3d [n][6]; depth_keys [n] = (depth bits << 32) | splat id. */
+int dsb_preprocess(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs,
+                   const float* colors_precomp, const float* opacities, const float* scales,
+                   const float* rotations, const float* cov3d_precomp, float* records, int32_t* radii,
+                   int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys, void* stream);
+
+/* ---- stage (b), first half ------------------------------------------------------------------
+ * Replaces the thrust::exclusive_scan + the two host read-backs of duplicate_keys
+ * (cpp/rasterizer_torch.cu:83-104).  Orders the splats by (depth, id) with the radix sort of stage
+ * (c), scans tiles_touched in that order and returns the pair total through *k_host (HOST pointer;
+ * the call synchronises `stream` once to read it).  depth_keys is sorted in place (depth_keys_alt is
+ * an equally sized scratch buffer); offsets [n] receives each ordered splat's first pair position. */
+int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched, uint64_t* depth_keys,
+                   uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
+                   int64_t* k_host, void* stream);
+
+/* ---- stage (b), second half -----------------------------------------------------------------
+ * Replaces calculate_keys_and_indices_kernel (cpp/rasterizer_kernels.cu:252-306).  Writes k packed
+ * pairs (tile id << 32 | splat id), splats in (depth, id) order, each rectangle row-major. */
+int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records,
+                   const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
+                   uint64_t* pairs, void* stream);
+
+/* ---- stage (c) ------------------------------------------------------------------------------
+ * Replaces sort_by_keys / thrust::sort_by_key (cpp/rasterizer_torch.cu:70-76).
+ * dsb_sort_pairs: stable LSD radix sort of k 64-bit words on bits [begin_bit, end_bit); the sorted
+ * data ends in `items` when *sorted_in_alt_host (HOST int) is 0, else in `items_alt`.
+ * dsb_sort_by_keys: the reference's interface -- (int64 key, int32 value) pairs, keys compared as
+ * signed when end_bit == 64 -- sorted on the given bit range; same ping-pong convention. */
+int dsb_sort_pairs(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit,
+                   void* workspace, int64_t workspace_bytes, int32_t* sorted_in_alt_host, void* stream);
+int dsb_sort_by_keys(int64_t* keys, int64_t* keys_alt, int32_t* values, int32_t* values_alt, int64_t k,
+                     int32_t begin_bit, int32_t end_bit, void* workspace, int64_t workspace_bytes,
+                     int32_t* sorted_in_alt_host, void* stream);
+
+/* ---- stage (d) ------------------------------------------------------------------------------
+ * Replaces identify_tile_ranges (cpp/rasterizer_torch.cu:23-42, kernel cpp/rasterizer_kernels.cu:
+ * 308-323).  `sorted` holds k 64-bit words whose high 32 bits are the tile id (the reference's keys
+ * and this library's packed pairs both qualify).  ranges [tiles+1] int32: tile t owns [r[t], r[t+1]). */
+int dsb_identify_tile_ranges(const uint64_t* sorted, int64_t k, int32_t image_height, int32_t image_width,
+                             int32_t* ranges, void* stream);
+
+/* ---- stage (e) ------------------------------------------------------------------------------
+ * Replaces rasterizer_cuda_forward + render_image_kernel (cpp/rasterizer_torch.cu:44-68,
+ * cpp/rasterizer_kernels.cu:341-431).  image [H][W][3], final_T [H][W], final_idx [H][W] int32. */
+int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs,
+                      const int32_t* ranges, float* image, float* final_T, int32_t* final_idx, void* stream);
+
+/* ---- stage (f1) -----------------------------------------------------------------------------
+ * Replaces rasterize_backward_tensor + rasterize_backward_kernel (cpp/gsplat/bindings.cu:140-194,
+ * cpp/gsplat/backward.cu:25-202).  grad_acc [n][12] must be zero on entry; on exit row i holds
+ * (v_x, v_y, v_conic_a, v_conic_b | v_conic_c, v_opacity, v_r, v_g | v_b, 0, 0, 0). */
+int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs,
+                       const int32_t* ranges, const float* final_T, const int32_t* final_idx,
+                       const float* v_image, float* grad_acc, void* stream);
+
+/* ---- stage (f2) -----------------------------------------------------------------------------
+ * Replaces compute_sh_backward_tensor, project_gaussians_backward_tensor and the host glue of
+ * rasterizer_backward_deepsense (cpp/gsplat/bindings.cu:22-131, cpp/rasterizer_torch.cu:263-316).
+ * Writes the reference's eight gradients: v_means3d [n][3], v_means2d [n][3] (third column zero),
+ * v_shs [n][(max+1)^2][3], v_colors [n][3], v_opacities [n][1], v_scales [n][3], v_rotations [n][4],
+ * v_cov3d [n][6].  Any output pointer may be NULL.  accumulate != 0 adds into the outputs instead of
+ * overwriting them (multi-view gradient accumulation). */
+int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
+                          const float* rotations, const float* records, const float* cov3d,
+                          const int32_t* radii, const float* grad_acc, float* v_means3d, float* v_means2d,
+                          float* v_shs, float* v_colors, float* v_opacities, float* v_scales,
+                          float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
+
+/* ---- fused calls the Python operator uses ----------------------------------------------------
+ * dsb_forward_plan   = dsb_preprocess + dsb_plan_pairs            (first half of
+ *                      rasterizer_forward_deepsense, cpp/rasterizer_torch.cu:170-196)
+ * dsb_forward_render = dsb_emit_pairs + dsb_sort_pairs + dsb_identify_tile_ranges + dsb_blend_forward
+ *                      (second half, :196-207); sorted pairs end in `pairs` (copied back if needed)
+ * dsb_backward       = dsb_blend_backward + dsb_geometry_backward (rasterizer_backward_deepsense,
+ *                      cpp/rasterizer_torch.cu:263-316); grad_acc is zeroed inside. */
+int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs,
+                     const float* colors_precomp, const float* opacities, const float* scales,
+                     const float* rotations, const float* cov3d_precomp, float* records, int32_t* radii,
+                     int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys, uint64_t* depth_keys_alt,
+                     uint32_t* offsets, void* workspace, int64_t workspace_bytes, int64_t* k_host, void* stream);
+int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records,
+                       const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
+                       uint64_t* pairs, uint64_t* pairs_alt, void* workspace, int64_t workspace_bytes,
+                       int32_t* ranges, float* image, float* final_T, int32_t* final_idx, void* stream);
+int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
+                 const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
+                 const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,
+                 const int32_t* final_idx, const float* v_image, float* grad_acc, float* v_means3d,
+                 float* v_means2d, float* v_shs, float* v_colors, float* v_opacities, float* v_scales,
+                 float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
+
+/* Test/export helper: rebuild the reference-format sorted lists from this library's packed pairs:
+ * keys[i] = (tile << 32) | sign-extended depth bits of the splat, ids[i] = splat id
+ * (the layout cpp/rasterizer_kernels.cu:283,299-301 produces and thrust sorts). */
+int dsb_export_reference_lists(const uint64_t* sorted_pairs, int64_t k, const float* records, int64_t* keys,
+                               int32_t* ids, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSB200_H_ */
