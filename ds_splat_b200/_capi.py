@@ -24,6 +24,7 @@ EXPORTS = (
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
     "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_export_reference_lists",
+    "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
 )
 
 
@@ -59,6 +60,10 @@ def lib():
         l.dsb_plan_workspace_bytes.argtypes = [C.c_int32]
         l.dsb_sort_workspace_bytes.restype = C.c_int64
         l.dsb_sort_workspace_bytes.argtypes = [C.c_int64]
+        l.dsb_stage_name.restype = C.c_char_p
+        l.dsb_stage_name.argtypes = [C.c_int32]
+        l.dsb_stage_count.restype = C.c_int32
+        l.dsb_stage_timing_enable.argtypes = [C.c_int32]
         P, I32, I64, CAM = C.c_void_p, C.c_int32, C.c_int64, C.POINTER(DsbCamera)
         sig = {
             "dsb_preprocess": [CAM, I32] + [P] * 7 + [P] * 5 + [P],
@@ -90,6 +95,19 @@ def check(rc: int):
 
 def launch_count() -> int:
     return int(lib().dsb_launch_count())
+
+
+def stage_timing(enable: bool):
+    check(lib().dsb_stage_timing_enable(1 if enable else 0))
+
+
+def read_stage_timings():
+    """Returns {stage name: (total ms, calls)} for the stages recorded since timing was enabled."""
+    n = int(lib().dsb_stage_count())
+    ms = (C.c_double * n)()
+    calls = (C.c_int64 * n)()
+    check(lib().dsb_stage_timing_read(n, ms, calls))
+    return {lib().dsb_stage_name(i).decode(): (float(ms[i]), int(calls[i])) for i in range(n)}
 
 
 def ptr(t):

@@ -211,12 +211,17 @@ int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_key
 
     // (depth, id) order: sort the packed (depth bits << 32 | id) words on their depth bits; ids are already ascending.
     int in_alt = 0;
-    int rc = launch_sort(depth_keys, depth_keys_alt, nullptr, nullptr, n, 32, 64, ws, sort_bytes, &in_alt, s);
-    if (rc != DSB_OK) return rc;
-    if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(depth_keys, depth_keys_alt, (size_t)n * 8, cudaMemcpyDeviceToDevice, s));
-
-    scan_counts_kernel<<<(unsigned)scan_tiles, kScanThreads, 0, s>>>(depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail);
-    DSB_LAUNCH_CHECK();
+    {
+        StageScope scope(kStageDepthSort, s);
+        int rc = launch_sort(depth_keys, depth_keys_alt, nullptr, nullptr, n, 32, 64, ws, sort_bytes, &in_alt, s);
+        if (rc != DSB_OK) return rc;
+        if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(depth_keys, depth_keys_alt, (size_t)n * 8, cudaMemcpyDeviceToDevice, s));
+    }
+    {
+        StageScope scope(kStageScan, s);
+        scan_counts_kernel<<<(unsigned)scan_tiles, kScanThreads, 0, s>>>(depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail);
+        DSB_LAUNCH_CHECK();
+    }
 
     struct { u64 total; u32 counter; int status; } host_tail;
     int sort_status = 0;

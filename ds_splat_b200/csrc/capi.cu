@@ -4,6 +4,8 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -20,6 +22,31 @@ void set_error(const char* fmt, ...) {
 }
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// ---- stage timing ------------------------------------------------------------------------------
+struct EventPair { cudaEvent_t a, b; int stage; };
+static bool g_timing = false;
+static std::vector<EventPair*> g_pending;
+static std::mutex g_timing_mutex;
+static const char* kStageNames[kStageCount] = {"preprocess", "depth_sort", "scan", "emit_pairs", "tile_sort", "tile_ranges",
+                                               "blend_forward", "blend_backward", "geometry_backward"};
+
+StageScope::StageScope(int stage, cudaStream_t s) : stage_(stage), stream_(s), slot_(nullptr) {
+    if (!g_timing) return;
+    EventPair* p = new EventPair;
+    p->stage = stage;
+    if (cudaEventCreate(&p->a) != cudaSuccess || cudaEventCreate(&p->b) != cudaSuccess) { delete p; return; }
+    cudaEventRecord(p->a, s);
+    slot_ = p;
+}
+
+StageScope::~StageScope() {
+    if (!slot_) return;
+    EventPair* p = static_cast<EventPair*>(slot_);
+    cudaEventRecord(p->b, stream_);
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    g_pending.push_back(p);
+}
 
 int make_cam_params(const DsbCamera* cam, CamParams* out) {
     DSB_REQUIRE(cam, "camera is null");
@@ -67,6 +94,34 @@ const char* dsb_last_error(void) { return g_error; }
 int32_t dsb_version(void) { return 100; }
 int64_t dsb_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
+int dsb_stage_timing_enable(int32_t on) {
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    for (EventPair* p : g_pending) { cudaEventDestroy(p->a); cudaEventDestroy(p->b); delete p; }
+    g_pending.clear();
+    g_timing = on != 0;
+    return DSB_OK;
+}
+
+int32_t dsb_stage_count(void) { return kStageCount; }
+const char* dsb_stage_name(int32_t stage) { return (stage >= 0 && stage < kStageCount) ? kStageNames[stage] : ""; }
+
+int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls) {
+    DSB_REQUIRE(ms_total && calls && stage_count >= kStageCount, "stage_timing_read: need room for %d stages", (int)kStageCount);
+    for (int i = 0; i < stage_count; ++i) { ms_total[i] = 0.0; calls[i] = 0; }
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    for (EventPair* p : g_pending) {
+        DSB_CUDA_CHECK(cudaEventSynchronize(p->b));
+        float ms = 0.f;
+        DSB_CUDA_CHECK(cudaEventElapsedTime(&ms, p->a, p->b));
+        ms_total[p->stage] += ms;
+        calls[p->stage] += 1;
+        cudaEventDestroy(p->a); cudaEventDestroy(p->b);
+        delete p;
+    }
+    g_pending.clear();
+    return DSB_OK;
+}
+
 int64_t dsb_plan_workspace_bytes(int32_t n) { return plan_workspace_bytes(n < 0 ? 0 : n); }
 int64_t dsb_sort_workspace_bytes(int64_t k) { return sort_workspace_bytes(k < 0 ? 0 : k); }
 
@@ -76,6 +131,7 @@ int dsb_preprocess(const DsbCamera* cam, int32_t n, const float* means3d, const 
                    void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
+    StageScope scope(kStagePreprocess, (cudaStream_t)stream);
     return launch_preprocess(cp, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records,
                              radii, tiles_touched, cov3d, reinterpret_cast<u64*>(depth_keys), (cudaStream_t)stream);
 }
@@ -171,19 +227,30 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                        int32_t* final_idx, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
-    int rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
+    int rc;
+    {
+        StageScope scope(kStageEmit, s);
+        rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
                          reinterpret_cast<u64*>(pairs), s);
+    }
     if (rc != DSB_OK) return rc;
     // Only the tile id needs sorting now: ceil(log2(tiles)) live bits above bit 32.
     int tile_bits = 1;
     while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
     int in_alt = 0;
-    rc = launch_sort(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, 32,
-                     32 + tile_bits, workspace, workspace_bytes, &in_alt, s);
+    {
+        StageScope scope(kStageTileSort, s);
+        rc = launch_sort(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, 32,
+                         32 + tile_bits, workspace, workspace_bytes, &in_alt, s);
+        if (rc != DSB_OK) return rc;
+        if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
+    }
+    {
+        StageScope scope(kStageRanges, s);
+        rc = launch_ranges(reinterpret_cast<const u64*>(pairs), k, cp.H, cp.W, ranges, s);
+    }
     if (rc != DSB_OK) return rc;
-    if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
-    rc = launch_ranges(reinterpret_cast<const u64*>(pairs), k, cp.H, cp.W, ranges, s);
-    if (rc != DSB_OK) return rc;
+    StageScope scope(kStageBlendForward, s);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, s);
 }
 
@@ -197,10 +264,15 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(grad_acc, "backward: grad_acc is null");
     cudaStream_t s = (cudaStream_t)stream;
-    DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
-    int rc = launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
+    int rc;
+    {
+        StageScope scope(kStageBlendBackward, s);
+        DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
+        rc = launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
                                    v_image, grad_acc, s);
+    }
     if (rc != DSB_OK) return rc;
+    StageScope scope(kStageGeometryBackward, s);
     return launch_geometry_backward(cp, n, means3d, scales, rotations, records, cov3d, radii, grad_acc, v_means3d,
                                     v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d, accumulate, s);
 }

@@ -46,6 +46,20 @@ void count_launch(int n = 1);
         }                                                                                     \
     } while (0)
 
+// ---- optional per-stage device timing -------------------------------------------------------------
+// When enabled through dsb_stage_timing_enable(), a StageScope records a cudaEvent pair on the caller's
+// stream around the kernels of one stage; dsb_stage_timing_read() sums the elapsed times.  Disabled
+// scopes cost one branch.
+enum Stage { kStagePreprocess = 0, kStageDepthSort, kStageScan, kStageEmit, kStageTileSort, kStageRanges,
+             kStageBlendForward, kStageBlendBackward, kStageGeometryBackward, kStageCount };
+struct StageScope {
+    StageScope(int stage, cudaStream_t s);
+    ~StageScope();
+    int stage_;
+    cudaStream_t stream_;
+    void* slot_;
+};
+
 // ---- camera block handed to kernels by value ------------------------------------------------------
 struct CamParams {
     const float* view;    // device

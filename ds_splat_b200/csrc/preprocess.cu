@@ -218,7 +218,10 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
         const float cxt = px / kTile, cyt = py / kTile, dt = radius / (float)kTile;
         const int x0 = min(max(0, (int)(cxt - dt)), cp.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cp.tiles_x);
         const int y0 = min(max(0, (int)(cyt - dt)), cp.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cp.tiles_y);
-        count = (x1 - x0) * (y1 - y0) * (radius > 0);
+        // A centre behind the camera can pass the frustum test (w < 0 flips both signs).  The reference
+        // still reports its radius but, because the negative depth bits spill over the tile id of its
+        // keys, never draws it; here it simply gets no pairs.
+        count = (x1 - x0) * (y1 - y0) * (radius > 0 && tz > 0.f);
 
         // Conic = inverse of the dilated 2-D covariance.
         const float det_inv = 1.0f / (det + 1e-6f);

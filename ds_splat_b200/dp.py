@@ -1,0 +1,186 @@
+"""Multi-view data-parallel rendering step: cameras sharded over ranks, splats replicated, one
+gradient all-reduce per step.
+
+The reference has no multi-GPU code; this module is the camera-sharded training step the benchmark's
+multi-GPU configuration describes: every rank (one process per GPU) renders its share of the batch's
+cameras against the full replicated splat cloud, accumulates the parameter gradients of its views, and
+the ranks sum them with one NCCL all-reduce over NVLink.
+
+Layout choices:
+  * ``GradientBuffer`` is ONE flat fp32 allocation holding the five gradient tensors back to back
+    (means 3 | sh 48 | opacity 1 | scale 3 | rotation 4 = 59 floats per splat).  The fused backward
+    kernel adds each view's gradients straight into these views (``accumulate`` flag of
+    ``dsb_backward``), so the buffer that is all-reduced is the buffer the kernels write -- no copy,
+    no per-tensor collectives.
+  * ``ViewRenderer`` bypasses autograd and calls the fused C-ABI entry points with buffers that are
+    allocated once and reused across views and steps (only the pair list grows with the largest K seen).
+
+Everything that is not a kernel launch (sharding, buffer layout, the collective) works on CPU tensors
+too, which is how the world_size-2 gloo tests exercise it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+SEGMENTS = (("means3d", 3), ("shs", 48), ("opacities", 1), ("scales", 3), ("rotations", 4))
+FLOATS_PER_SPLAT = sum(w for _, w in SEGMENTS)  # 59
+
+
+def shard_views(num_views: int, rank: int, world_size: int) -> List[int]:
+    """Round-robin assignment of view indices to ranks; every view lands on exactly one rank."""
+    if not (0 <= rank < world_size):
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    return list(range(rank, num_views, world_size))
+
+
+class GradientBuffer:
+    """Flat fp32 gradient block with per-tensor views (see module docstring)."""
+
+    def __init__(self, n: int, device, sh_coeffs: int = 16):
+        self.n = n
+        widths = dict(SEGMENTS)
+        widths["shs"] = 3 * sh_coeffs
+        self.flat = torch.zeros(n * sum(widths.values()), dtype=torch.float32, device=device)
+        self.views: Dict[str, torch.Tensor] = {}
+        off = 0
+        for name, _ in SEGMENTS:
+            w = widths[name]
+            v = self.flat[off:off + n * w]
+            self.views[name] = v.view(n, sh_coeffs, 3) if name == "shs" else v.view(n, w)
+            off += n * w
+
+    def zero_(self):
+        self.flat.zero_()
+
+    def nbytes(self) -> int:
+        return self.flat.numel() * 4
+
+
+def allreduce_gradients(buf: GradientBuffer, group=None) -> None:
+    """Sum the flat gradient block over all ranks (no-op in a single-process run)."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(buf.flat, op=dist.ReduceOp.SUM, group=group)
+
+
+@dataclass
+class CameraTensors:
+    """Device-resident camera in the layout GaussianRasterizationSettings carries (transposed matrices)."""
+    H: int
+    W: int
+    tanfovx: float
+    tanfovy: float
+    viewmatrix: torch.Tensor
+    projmatrix: torch.Tensor
+    campos: torch.Tensor
+    bg: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def from_view(view, device) -> "CameraTensors":
+        t = lambda a: torch.from_numpy(a).to(device)
+        import numpy as np
+        return CameraTensors(view.H, view.W, view.tanfovx, view.tanfovy, t(view.viewmatrix_t), t(view.projmatrix_t),
+                             t(np.ascontiguousarray(view.campos)), torch.zeros(3, device=device))
+
+
+class ViewRenderer:
+    """Forward + backward of one view at a time through the fused C-ABI calls, with reusable buffers."""
+
+    def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True):
+        from . import _capi
+        self._capi = _capi
+        self.lib = _capi.lib()
+        self.p = dict(means3d=means3d.contiguous(), shs=shs.contiguous(), opacities=opacities.contiguous(),
+                      scales=scales.contiguous(), rotations=rotations.contiguous())
+        self.n = means3d.shape[0]
+        self.dev = means3d.device
+        self.sh_degree = sh_degree
+        self.coeffs = shs.shape[1]
+        self.strict = strict_reference
+        n, dev = self.n, self.dev
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.records = torch.empty((n, _capi.RECORD_FLOATS), **f32)
+        self.radii = torch.empty(n, dtype=torch.int32, device=dev)
+        self.tiles = torch.empty(n, dtype=torch.int32, device=dev)
+        self.cov3d = torch.empty((n, 6), **f32)
+        self.depth_keys = torch.empty((2, n), dtype=torch.int64, device=dev)
+        self.offsets = torch.empty(n, dtype=torch.int32, device=dev)
+        self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes(n))
+        self.plan_ws = torch.empty(self.plan_bytes, dtype=torch.uint8, device=dev)
+        self.grad_acc = torch.empty((n, _capi.GRAD_FLOATS), **f32)
+        self.pairs = None
+        self.sort_ws = None
+        self.sort_bytes = 0
+        self.img = {}
+        self.last_k = 0
+
+    def _image_buffers(self, h, w):
+        key = (h, w)
+        if key not in self.img:
+            f32 = dict(dtype=torch.float32, device=self.dev)
+            self.img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
+                             torch.empty((h, w), dtype=torch.int32, device=self.dev),
+                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev))
+        return self.img[key]
+
+    def _camera(self, cam: CameraTensors):
+        max_deg = {1: 0, 4: 1, 9: 2, 16: 3}[self.coeffs]
+        return self._capi.make_camera(cam.H, cam.W, cam.tanfovx, cam.tanfovy, cam.viewmatrix, cam.projmatrix, cam.campos,
+                                      cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict)
+
+    def forward(self, cam: CameraTensors):
+        """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size)."""
+        capi, lib, p = self._capi, self.lib, self.p
+        c, keep = self._camera(cam)
+        stream = capi.stream_ptr()
+        k = C.c_int64(0)
+        capi.check(lib.dsb_forward_plan(
+            C.byref(c), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
+            p["scales"].data_ptr(), p["rotations"].data_ptr(), None, self.records.data_ptr(), self.radii.data_ptr(),
+            self.tiles.data_ptr(), self.cov3d.data_ptr(), self.depth_keys[0].data_ptr(), self.depth_keys[1].data_ptr(),
+            self.offsets.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes, C.byref(k), stream))
+        k = int(k.value)
+        if self.pairs is None or self.pairs.shape[1] < k:
+            cap = max(int(k * 1.25), 1024)
+            self.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
+            self.sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
+            self.sort_ws = torch.empty(self.sort_bytes, dtype=torch.uint8, device=self.dev)
+        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        capi.check(lib.dsb_forward_render(
+            C.byref(c), self.n, k, self.records.data_ptr(), self.tiles.data_ptr(), self.depth_keys[0].data_ptr(),
+            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(), self.sort_ws.data_ptr(),
+            self.sort_bytes, ranges.data_ptr(), image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), stream))
+        self.last_k = k
+        self._last_cam = (c, keep, cam)
+        return image
+
+    def backward(self, v_image: torch.Tensor, grads: GradientBuffer, accumulate: bool = True):
+        """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
+        capi, lib, p = self._capi, self.lib, self.p
+        c, keep, cam = self._last_cam
+        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        g = grads.views
+        capi.check(lib.dsb_backward(
+            C.byref(c), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
+            self.records.data_ptr(), self.cov3d.data_ptr(), self.radii.data_ptr(), self.pairs[0].data_ptr(),
+            ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), self.grad_acc.data_ptr(),
+            g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
+            g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
+
+
+def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads: Sequence[torch.Tensor],
+                       grads: GradientBuffer, group=None) -> None:
+    """One step of the multi-view batch on this rank: for each local camera forward + backward (gradients
+    accumulated in ``grads``), then the all-reduce.  ``cameras`` / ``image_grads`` are this rank's shard."""
+    first = True
+    for cam, v_image in zip(cameras, image_grads):
+        renderer.forward(cam)
+        renderer.backward(v_image, grads, accumulate=not first)
+        first = False
+    if first:
+        grads.zero_()  # a rank without views still takes part in the collective
+    allreduce_gradients(grads, group)

@@ -68,6 +68,16 @@ int32_t dsb_version(void);
 /* Number of kernels this library has launched in this process (monotonic). */
 int64_t dsb_launch_count(void);
 
+/* ---- per-stage device timing (no reference counterpart: the reference times with std::chrono in
+ * its tests, tests/rasterizer_test.cpp:112-143) --------------------------------------------------
+ * While enabled, every stage inside the calls below is bracketed by a cudaEvent pair on the caller's
+ * stream.  dsb_stage_timing_read() waits for the recorded events, writes the summed milliseconds and
+ * call counts per stage (arrays of at least dsb_stage_count() entries, HOST memory) and clears them. */
+int dsb_stage_timing_enable(int32_t on);
+int32_t dsb_stage_count(void);
+const char* dsb_stage_name(int32_t stage);
+int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls);
+
 /* ---- workspace sizes (host arithmetic only) ------------------------------------------------- */
 /* Scratch for dsb_plan_pairs (depth ordering of n splats + scan). */
 int64_t dsb_plan_workspace_bytes(int32_t n);

@@ -24,6 +24,7 @@
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
+#include <parallel/algorithm>
 #endif
 
 namespace {
@@ -252,7 +253,11 @@ void orc_duplicate_keys(const Cam* cam, int N, const float* xy, const float* dep
 void orc_sort_pairs(int64_t K, int64_t* keys, int32_t* ids) {
     std::vector<int64_t> order(K);
     std::iota(order.begin(), order.end(), (int64_t)0);
+#ifdef _OPENMP
+    __gnu_parallel::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return keys[a] < keys[b]; });
+#else
     std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return keys[a] < keys[b]; });
+#endif
     std::vector<int64_t> k2(K);
     std::vector<int32_t> v2(K);
     for (int64_t i = 0; i < K; ++i) { k2[i] = keys[order[i]]; v2[i] = ids[order[i]]; }

@@ -1,0 +1,98 @@
+"""Multi-rank host logic of the data-parallel step, on CPU with the gloo backend (world_size 2):
+view sharding, the flat gradient buffer and the all-reduce.  The per-view gradients come from the CPU
+checker on a tiny scene, so the assertion is the real property: the all-reduced buffer of the sharded
+run equals the serial sum over all views."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.distributed as dist  # noqa: E402
+import torch.multiprocessing as mp  # noqa: E402
+
+from ds_splat_b200 import dp, scenes  # noqa: E402
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class OracleRenderer:
+    """Stands in for ViewRenderer on CPU: same forward/backward protocol, gradients from the CPU checker."""
+
+    def __init__(self, scene):
+        from oracle import oracle as O
+        self.O, self.sc = O, scene
+
+    def forward(self, view):
+        O, sc = self.O, self.sc
+        self.cam = O.Camera(view=view.view, proj=view.proj, campos=view.campos, tanfovx=view.tanfovx, tanfovy=view.tanfovy,
+                            H=view.H, W=view.W, sh_degree=3)
+        self.fwd = O.forward(self.cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)
+        return self.fwd["image"]
+
+    def backward(self, v_image, grads, accumulate=True):
+        sc = self.sc
+        b = self.O.backward(self.cam, self.fwd, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image.numpy())
+        pairs = (("means3d", "v_means3d"), ("shs", "v_shs"), ("opacities", "v_opacities"), ("scales", "v_scales"),
+                 ("rotations", "v_rotations"))
+        for dst, src in pairs:
+            g = torch.from_numpy(b[src])
+            if accumulate:
+                grads.views[dst] += g
+            else:
+                grads.views[dst].copy_(g)
+
+
+def _scene():
+    return scenes.headline(n=1500, seed=9, W=96, H=64, focal=60.0, views=5)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sc = _scene()
+    mine = dp.shard_views(len(sc.views), rank, world)
+    grads = dp.GradientBuffer(sc.n, "cpu")
+    grads.flat.fill_(123.0)  # stale contents must not leak into the result
+    dp.data_parallel_step(OracleRenderer(sc), [sc.views[i] for i in mine],
+                          [torch.from_numpy(sc.image_grad(i)) for i in mine], grads)
+    if rank == 0:
+        np.save(out, grads.flat.numpy())
+    dist.destroy_process_group()
+
+
+def test_shard_views_partition():
+    for world in (1, 2, 3, 8):
+        seen = sorted(i for r in range(world) for i in dp.shard_views(11, r, world))
+        assert seen == list(range(11))
+    assert dp.shard_views(3, 5, 8) == []
+    with pytest.raises(ValueError):
+        dp.shard_views(4, 2, 2)
+
+
+def test_gradient_buffer_layout():
+    g = dp.GradientBuffer(7, "cpu")
+    assert g.flat.numel() == 7 * dp.FLOATS_PER_SPLAT == 7 * 59 and g.nbytes() == 7 * 236
+    assert g.views["shs"].shape == (7, 16, 3) and g.views["rotations"].shape == (7, 4)
+    g.views["opacities"].fill_(2.0)
+    assert float(g.flat.sum()) == 14.0
+    assert g.views["means3d"].data_ptr() == g.flat.data_ptr()
+
+
+def test_two_rank_step_equals_serial_sum(tmp_path):
+    out = str(tmp_path / "rank0.npy")
+    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = np.load(out)
+    sc = _scene()
+    serial = dp.GradientBuffer(sc.n, "cpu")
+    r = OracleRenderer(sc)
+    for i, v in enumerate(sc.views):
+        r.forward(v)
+        r.backward(torch.from_numpy(sc.image_grad(i)), serial, accumulate=i > 0)
+    np.testing.assert_allclose(got, serial.flat.numpy(), rtol=1e-5, atol=1e-9)
+    assert np.abs(got).max() > 0

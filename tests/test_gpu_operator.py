@@ -1,0 +1,164 @@
+"""The Python operator end to end on the GPU: agreement with the CPU checker from raw inputs, the edge
+cases the reference leaves unhandled (no visible splat, a single splat, ragged image sizes), the optional
+input forms (colors_precomp, lower SH degrees, cov_3d_precomp), stream use and error reporting."""
+import numpy as np
+import pytest
+
+from conftest import oracle_camera, scene_tensors, settings_for
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from ds_splat_b200 import GaussianRasterizer, _capi, scenes  # noqa: E402
+from ds_splat_b200.dp import CameraTensors, GradientBuffer, ViewRenderer, data_parallel_step  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+
+def _run_operator(sc, view, sh_degree=3, colors=None, **settings_kw):
+    t = scene_tensors(sc)
+    p = {k: v.clone().requires_grad_(True) for k, v in t.items()}
+    m2 = torch.zeros_like(p["means"], requires_grad=True)
+    rast = GaussianRasterizer(settings_for(view, sh_degree=sh_degree, **settings_kw))
+    if colors is None:
+        image, radii = rast(p["means"], m2, p["shs"], None, p["opacities"], p["scales"], p["rotations"], None)
+    else:
+        p["colors"] = colors.clone().requires_grad_(True)
+        image, radii = rast(p["means"], m2, None, p["colors"], p["opacities"], p["scales"], p["rotations"], None)
+    return p, m2, image, radii
+
+
+def _rel(a, b):
+    return float(np.abs(a - b).max()) / max(float(np.abs(b).max()), 1e-20)
+
+
+@pytest.mark.parametrize("sh_degree", [0, 1, 2, 3])
+def test_operator_matches_checker_from_raw_inputs(sh_degree):
+    sc = scenes.tiny(n=8000, seed=31 + sh_degree, W=256, H=160, focal=220.0)
+    view = sc.views[0]
+    p, m2, image, radii = _run_operator(sc, view, sh_degree=sh_degree)
+    v_image = sc.image_grad()
+    image.backward(torch.from_numpy(v_image).cuda())
+    cam = oracle_camera(view, sh_degree=sh_degree)
+    fwd = O.forward(cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)
+    bwd = O.backward(cam, fwd, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image)
+    assert image.shape == (view.H, view.W, 3) and radii.dtype == torch.int32
+    err = np.abs(image.detach().cpu().numpy() - fwd["image"]).max(axis=2)
+    assert (err > 1e-5).mean() < 2e-3 and err.max() < 5e-2
+    assert (radii.cpu().numpy() != fwd["pre"]["radii"]).mean() < 3e-3
+    # from raw inputs a flipped radius changes a splat's pair list, so gradients are compared at 1e-2
+    assert _rel(p["opacities"].grad.cpu().numpy(), bwd["v_opacities"]) < 1e-2
+    assert _rel(p["shs"].grad.cpu().numpy(), bwd["v_shs"]) < 1e-2
+    assert _rel(p["means"].grad.cpu().numpy(), bwd["v_means3d"]) < 1e-2
+    assert _rel(p["scales"].grad.cpu().numpy(), bwd["v_scales"]) < 1e-2
+    assert _rel(p["rotations"].grad.cpu().numpy(), bwd["v_rotations"]) < 1e-2
+    assert _rel(m2.grad.cpu().numpy(), bwd["v_means2d"]) < 1e-2
+    nb = (sh_degree + 1) ** 2
+    assert (p["shs"].grad[:, nb:, :] == 0).all()  # inactive bands get exact zeros
+
+
+def test_colors_precomp_path_and_channels_first():
+    sc = scenes.tiny(n=3000, seed=41, W=128, H=96, focal=110.0)
+    view = sc.views[0]
+    cam = oracle_camera(view)
+    pre = O.preprocess(cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)
+    colors = torch.from_numpy(pre["rgb"]).cuda()
+    p, m2, image, _ = _run_operator(sc, view, colors=colors, channels_first=True)
+    assert image.shape == (3, view.H, view.W)
+    fwd = O.forward(cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)
+    err = np.abs(image.detach().permute(1, 2, 0).cpu().numpy() - fwd["image"]).max(axis=2)
+    assert (err > 1e-5).mean() < 2e-3
+    v = torch.from_numpy(sc.image_grad()).cuda().permute(2, 0, 1)
+    image.backward(v)
+    bwd = O.backward(cam, fwd, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, sc.image_grad())
+    assert _rel(p["colors"].grad.cpu().numpy(), bwd["v_colors"]) < 1e-2
+    assert p["shs"].grad is None
+
+
+def test_no_visible_splats_and_single_splat():
+    sc = scenes.tiny(n=64, seed=51, W=64, H=48, focal=50.0)
+    sc.means[:, 0] += 1000.0  # everything far outside the frustum: K == 0, which the reference cannot handle
+    p, m2, image, radii = _run_operator(sc, sc.views[0])
+    image.sum().backward()
+    torch.cuda.synchronize()
+    assert float(image.detach().abs().max()) == 0.0 and int(radii.max()) == 0
+    for name in ("means", "shs", "opacities", "scales", "rotations"):
+        assert float(p[name].grad.abs().max()) == 0.0
+    # centres behind the camera pass the frustum test (w < 0): radii are reported as the reference does,
+    # but nothing is drawn and all gradients are finite zeros
+    behind = scenes.tiny(n=64, seed=53, W=64, H=48, focal=50.0)
+    behind.means[:, 2] = -50.0
+    p, m2, image, radii = _run_operator(behind, behind.views[0])
+    image.sum().backward()
+    torch.cuda.synchronize()
+    assert float(image.detach().abs().max()) == 0.0 and int(radii.max()) > 0
+    for name in ("means", "shs", "opacities", "scales", "rotations"):
+        assert torch.isfinite(p[name].grad).all() and float(p[name].grad.abs().max()) == 0.0
+    one = scenes.tiny(n=1, seed=52, W=64, H=48, focal=50.0)
+    one.means[:] = 0.0
+    p, m2, image, radii = _run_operator(one, one.views[0], strict_reference=False)
+    assert int(radii[0]) > 0 and float(image.max()) > 0.0
+    p2, _, image2, radii2 = _run_operator(one, one.views[0], strict_reference=True)
+    # with the reference's rule the splat with the highest index is never drawn, but its radius is reported
+    assert int(radii2[0]) == int(radii[0]) and float(image2.max()) == 0.0
+
+
+def test_cov3d_precomp_forward_equals_scale_rotation_forward():
+    sc = scenes.tiny(n=2000, seed=61, W=96, H=80, focal=90.0)
+    view = sc.views[0]
+    t = scene_tensors(sc)
+    rast = GaussianRasterizer(settings_for(view))
+    img_a, rad_a = rast(t["means"], None, t["shs"], None, t["opacities"], t["scales"], t["rotations"], None)
+    cam = oracle_camera(view)
+    cov = torch.from_numpy(O.preprocess(cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)["cov3d"]).cuda()
+    img_b, rad_b = rast(means3D=t["means"], means2D=None, shs=t["shs"], opacities=t["opacities"], cov3D_precomp=cov)
+    assert (rad_a != rad_b).float().mean() < 5e-3
+    assert float((img_a - img_b).abs().max()) < 1e-2
+
+
+def test_runs_on_the_current_stream_and_other_device_buffers_untouched():
+    sc = scenes.tiny(n=5000, seed=71, W=160, H=128, focal=140.0)
+    view = sc.views[0]
+    t = scene_tensors(sc)
+    rast = GaussianRasterizer(settings_for(view))
+    ref_img, _ = rast(t["means"], None, t["shs"], None, t["opacities"], t["scales"], t["rotations"], None)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        img, _ = rast(t["means"], None, t["shs"], None, t["opacities"], t["scales"], t["rotations"], None)
+    s.synchronize()
+    assert torch.equal(img, ref_img)  # forward is deterministic
+
+
+def test_errors_are_python_exceptions():
+    sc = scenes.tiny(n=100, seed=81, W=64, H=48, focal=50.0)
+    view = sc.views[0]
+    t = scene_tensors(sc)
+    rast = GaussianRasterizer(settings_for(view))
+    with pytest.raises(RuntimeError, match="float32"):
+        rast(t["means"].double(), None, t["shs"], None, t["opacities"], t["scales"], t["rotations"], None)
+    with pytest.raises(RuntimeError, match="shs must be"):
+        rast(t["means"], None, t["shs"][:, :9].contiguous(), None, t["opacities"], t["scales"], t["rotations"], None)
+    with pytest.raises(RuntimeError, match="cov3D"):
+        rast(t["means"], None, t["shs"], None, t["opacities"], None, None, None)
+    with pytest.raises(_capi.DsbError):
+        cam, keep = _capi.make_camera(0, 0, 1.0, 1.0, t["means"], t["means"], t["means"])
+        _capi.blend_forward(cam, t["means"], t["means"].long(), t["means"].int())
+
+
+def test_view_renderer_accumulates_like_autograd():
+    """The fused multi-view path (gradient accumulation into the flat buffer) equals summed autograd gradients."""
+    sc = scenes.headline(n=20_000, seed=91, W=320, H=192, focal=200.0, views=3)
+    t = scene_tensors(sc)
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    grads = GradientBuffer(sc.n, "cuda")
+    grads.flat.fill_(5.0)
+    cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
+    vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
+    data_parallel_step(r, cams, vimgs, grads)
+    p = {k: v.clone().requires_grad_(True) for k, v in t.items()}
+    for v, vi in zip(sc.views, vimgs):
+        img, _ = GaussianRasterizer(settings_for(v))(p["means"], None, p["shs"], None, p["opacities"], p["scales"], p["rotations"], None)
+        img.backward(vi)
+    torch.cuda.synchronize()
+    for name, key in (("means", "means3d"), ("shs", "shs"), ("opacities", "opacities"), ("scales", "scales"), ("rotations", "rotations")):
+        assert _rel(grads.views[key].cpu().numpy(), p[name].grad.cpu().numpy()) < 1e-3, name
