@@ -25,7 +25,9 @@ EXPORTS = (
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
     "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
+    "dsb_sort_pairs_static",
 )
+STATIC_SORT_MAX_ITEMS = 1 << 21
 
 
 class DsbCamera(C.Structure):
@@ -71,6 +73,7 @@ def lib():
             "dsb_emit_pairs": [CAM, I32, I64, P, P, P, P, P, P],
             "dsb_sort_pairs": [P, P, I64, I32, I32, P, I64, C.POINTER(C.c_int32), P],
             "dsb_sort_by_keys": [P, P, P, P, I64, I32, I32, P, I64, C.POINTER(C.c_int32), P],
+            "dsb_sort_pairs_static": [P, P, I64, I32, I32, C.POINTER(C.c_int32), P],
             "dsb_identify_tile_ranges": [P, I64, I32, I32, P, P],
             "dsb_blend_forward": [CAM, P, P, P, P, P, P, P],
             "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P],
@@ -203,6 +206,18 @@ def sort_pairs(items, begin_bit, end_bit):
     check(lib().dsb_sort_pairs(ptr(items), ptr(alt), k, begin_bit, end_bit, ws.data_ptr(), ws_bytes, C.byref(in_alt),
                                stream_ptr()))
     return alt if in_alt.value else items
+
+
+def sort_pairs_static(items, items_alt, begin_bit, end_bit):
+    """Same sort as sort_pairs() for callers that cannot allocate device memory when they need it (a plug-in inside
+    another engine's frame loop, a loop where cudaMalloc's device-wide stall is unacceptable): the scratch is a fixed
+    array inside the library, so the entry point itself allocates nothing -- which is why ``items_alt``, an int64
+    tensor as long as ``items``, must be supplied by the caller here.  At most STATIC_SORT_MAX_ITEMS items; calls on
+    one device must not overlap on the GPU.  Returns whichever of the two tensors holds the sorted list."""
+    in_alt = C.c_int32(0)
+    check(lib().dsb_sort_pairs_static(ptr(items), ptr(items_alt), items.shape[0], begin_bit, end_bit, C.byref(in_alt),
+                                      stream_ptr()))
+    return items_alt if in_alt.value else items
 
 
 def sort_by_keys(keys, values, begin_bit=0, end_bit=64):

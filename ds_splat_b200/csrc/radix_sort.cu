@@ -14,6 +14,7 @@
 // Every poll loop is bounded (kSpinLimit): on expiry the block records DSB_ERR_DEVICE_WAIT_EXPIRED in
 // the workspace status word and carries on with whatever it has, so the kernel always terminates.
 #include <cstddef>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -266,4 +267,60 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     return DSB_OK;
 }
 
+// ---- sort without any allocation ------------------------------------------------------------------
+// Some users of this library cannot obtain device memory at the moment they need a sort: a renderer that
+// runs as a plug-in inside another engine's frame loop has usually handed every byte of the GPU to that
+// engine's pool and has no right to ask the driver for more, and a latency-critical loop cannot afford
+// cudaMalloc at all because it serialises the whole device.  For them the sort's scratch (digit
+// histograms, tile counters, look-back status words) lives in the fixed device array below, which is part
+// of the library image: every GPU that loads the library carries these ~4 MB until the process exits.
+constexpr int64_t kStaticSortMaxItems = DSB_STATIC_SORT_MAX_ITEMS;
+constexpr size_t kStaticSortScratchBytes =
+    sizeof(SortHeader) + (size_t)kMaxPasses * (size_t)(kStaticSortMaxItems / kTileItems) * kRadix * sizeof(u32);
+static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+static void* g_static_scratch_address[kMaxStaticDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// On the host the array's name is only a handle, not an address a kernel could use; the real device
+// address differs per GPU and is looked up once per device, with that device current.
+static int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    DSB_CUDA_CHECK(cudaGetDevice(&dev));
+    DSB_REQUIRE(dev >= 0 && dev < kMaxStaticDevices, "static sort: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_address[dev]) {
+        void* p = nullptr;
+        DSB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+        DSB_REQUIRE(p != nullptr, "static sort: the scratch array has no device address");
+        g_static_scratch_address[dev] = p;
+    }
+    *out = g_static_scratch_address[dev];
+    return DSB_OK;
+}
+
 }  // namespace dsb
+
+extern "C" int dsb_sort_pairs_static(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit,
+                                     int32_t* sorted_in_alt_host, void* stream) {
+    using namespace dsb;
+    if (sorted_in_alt_host) *sorted_in_alt_host = 0;
+    DSB_REQUIRE(k >= 0, "k must be non-negative");
+    if (k > kStaticSortMaxItems) {
+        set_error("dsb_sort_pairs_static: %lld items exceed the built-in scratch, which holds at most %lld; "
+                  "use dsb_sort_pairs with a caller-provided workspace for larger lists",
+                  (long long)k, (long long)kStaticSortMaxItems);
+        return DSB_ERR_WORKSPACE_TOO_SMALL;
+    }
+    void* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != DSB_OK) return rc;
+    int in_alt = 0;
+    // launch_sort clears the part of the scratch it is about to use, so whatever the previous call left
+    // behind does not matter; it issues memset + kernels only, nothing that allocates.
+    const int rc2 = launch_sort(reinterpret_cast<u64*>(items), reinterpret_cast<u64*>(items_alt), nullptr, nullptr, k,
+                                begin_bit, end_bit, scratch, (int64_t)kStaticSortScratchBytes, &in_alt, (cudaStream_t)stream);
+    if (sorted_in_alt_host) *sorted_in_alt_host = in_alt;
+    return rc2;
+}

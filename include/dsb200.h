@@ -125,6 +125,26 @@ int dsb_sort_by_keys(int64_t* keys, int64_t* keys_alt, int32_t* values, int32_t*
                      int32_t begin_bit, int32_t end_bit, void* workspace, int64_t workspace_bytes,
                      int32_t* sorted_in_alt_host, void* stream);
 
+/* dsb_sort_pairs_static: dsb_sort_pairs for callers that cannot allocate.  It has no counterpart in
+ * the reference (whose sort, thrust::sort_by_key, allocates its temporary storage with cudaMalloc on
+ * every call).  Meant for hosts where the library is a guest: a renderer plugged into another engine's
+ * frame loop that owns all device memory, or a latency-critical loop in which cudaMalloc -- which stalls
+ * the whole device -- is off limits.  The caller passes only the list and an equally sized alternate
+ * buffer; the histograms, tile counters and look-back words the sort needs come out of a fixed array
+ * compiled into the library (about 4 MB of every GPU that loads it, held until the process exits).
+ *   - k may be at most DSB_STATIC_SORT_MAX_ITEMS; larger lists are refused with
+ *     DSB_ERR_WORKSPACE_TOO_SMALL and a message naming the limit.
+ *   - The call issues memset and kernel launches only: no cudaMalloc, cudaFree or other allocating routine.
+ *   - The first call on each device looks up that device's address of the built-in array (the device must
+ *     be current); make that first call during start-up, before any stream capture is begun.
+ *   - All calls on a device share the one array.  Each call clears what it needs first, so leftovers of
+ *     the previous call are harmless, but two calls whose kernels overlap on the GPU (different streams)
+ *     would corrupt each other: keep calls on one device ordered.
+ * Results are identical to dsb_sort_pairs. */
+#define DSB_STATIC_SORT_MAX_ITEMS ((int64_t)1 << 21)
+int dsb_sort_pairs_static(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit,
+                          int32_t* sorted_in_alt_host, void* stream);
+
 /* ---- stage (d) ------------------------------------------------------------------------------
  * Replaces identify_tile_ranges (cpp/rasterizer_torch.cu:23-42, kernel cpp/rasterizer_kernels.cu:
  * 308-323).  `sorted` holds k 64-bit words whose high 32 bits are the tile id (the reference's keys
