@@ -12,7 +12,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdsb200.so")
+# DSB200_LIBRARY points at a libdsb200.so built elsewhere (default: the in-tree build next to this file).
+LIB_PATH = os.environ.get("DSB200_LIBRARY") or os.path.join(_HERE, "libdsb200.so")
 
 DSB_FLAG_DROP_LAST_SPLAT = 1
 RECORD_FLOATS = 12

@@ -1,23 +1,29 @@
 // Stage (f1): reverse-order blend, per-splat gradient accumulation.
 //
-// Takes the place of the reference's rasterize_backward_kernel (cpp/gsplat/backward.cu:25-202).  One
-// 256-thread block per 16x16 tile walks the tile's list back to front in rounds of 64 splats; each pixel
-// recovers its transmittance by dividing by (1 - alpha) and produces nine partial derivatives per splat
-// (pixel mean 2, conic 3, opacity 1, colour 3).
+// Takes the place of the reference's rasterize_backward_kernel (cpp/gsplat/backward.cu:25-202).  The
+// reference runs one 256-thread block per 16x16 tile that marches through the tile's list in lock step
+// (two block barriers per 256 entries), evaluates every entry for every pixel, reduces 9 values with 9
+// full warp reductions (45 shuffles) and issues 9 scalar atomics per warp per entry.
 //
-// The reduction over pixels is where the reference spends its time (9 full warp reductions and 9
-// scalar atomics per warp per splat).  Here:
-//   * a warp reduces the 9 values with a transposing butterfly -- at each step half of the values move
-//     to the partner lane, so 8 values cost 4+2+1+1+1 shuffles instead of 40 -- and the ninth with a
-//     plain butterfly: 14 shuffles in all;
-//   * each warp parks its sums in its own shared-memory slot (plain stores, no shared atomics);
-//   * after the round the block adds the 8 warps' slots and issues ONE vector reduction per splat and
-//     row quarter to global memory (red.global.add.v4.f32), i.e. 3 global atomics per (tile, splat)
-//     instead of 72.
+// Here each WARP is on its own.  Warp w of a block owns the 16x2-pixel strip (rows 2w, 2w+1) of the
+// block's tile and walks the tile's list back to front in chunks of 32 entries, with no block barrier
+// anywhere, so a strip whose pixels ended early is finished early and nobody waits for the slowest strip:
+//   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether
+//     the splat can reach the strip at all (blend_common.cuh); a ballot gives the survivors;
+//   * blend: survivors are parked in the warp's private shared-memory slice and processed one by one.
+//     exp is only evaluated for pixels with q <= ln(255 opacity) + margin, after which the reference's own
+//     test (clamped alpha < 1/255) decides.  Per pixel the nine sums are moments that need few multiplies,
+//         S0 = sum v_s, Sx = sum v_s dx, Sy = sum v_s dy, Sxx, Sxy, Syy, and the three colour sums;
+//     the warp reduces them with a transposing butterfly (8 values in 4+2+1+1+1 shuffles, the ninth in 5)
+//     into the entry's row of the warp's accumulator slice;
+//   * flush: lane l, which still holds entry l's record in registers, turns its row of moments into
+//         v_xy = (a Sx + b Sy, b Sx + c Sy), v_conic = (Sxx/2, Sxy, Syy/2), v_opacity = -S0 / opacity
+//     and issues two red.global.add.v4.f32 and one scalar red: 3 vector atomics per (strip, splat) that
+//     received anything, instead of 9 scalar ones.
 //
 // The per-pixel arithmetic follows the reference: alpha clamp 0.99, 1/255 skip, opacity and visibility
 // gradients without clamp masking, and the background term in v_alpha.
-#include "common.cuh"
+#include "blend_common.cuh"
 
 namespace dsb {
 
@@ -25,7 +31,6 @@ namespace {
 
 constexpr int kThreads = kTilePixels;
 constexpr int kWarps = kThreads / 32;
-constexpr int kRound = 64;  // splats per round
 
 __device__ __forceinline__ void red_add_v4(float4* addr, const float4 v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
@@ -68,11 +73,8 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
                       const u64* __restrict__ sorted, const int32_t* __restrict__ ranges,
                       const float* __restrict__ final_T, const int32_t* __restrict__ final_idx,
                       const float* __restrict__ v_image, float4* __restrict__ grad_acc) {
-    __shared__ float4 s_rec[kRound][3];
-    __shared__ u32 s_id[kRound];
-    __shared__ float s_acc[kWarps][kRound][12];
-    __shared__ u64 s_touched[kWarps];
-    __shared__ int s_wmax[kWarps];
+    __shared__ float4 s_rec[kWarps][32][3];   // x,y,a,b | c,opacity,r,g | blue, threshold, -, -
+    __shared__ float s_acc[kWarps][32][12];   // moments of the chunk's entries
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -80,6 +82,7 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
     const int y = blockIdx.y * kTile + (tid >> 4);
     const bool inside = x < W && y < H;
     const float px = (float)x + 0.5f, py = (float)y + 0.5f;
+    const float X0 = (float)(blockIdx.x * kTile), Y0 = (float)(blockIdx.y * kTile);
     const int start = ranges[tile], end = ranges[tile + 1];
 
     float Tf = 1.0f, vo0 = 0.0f, vo1 = 0.0f, vo2 = 0.0f;
@@ -91,105 +94,91 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
         vo0 = v_image[3 * pix]; vo1 = v_image[3 * pix + 1]; vo2 = v_image[3 * pix + 2];
     }
     const float bgdot = bg ? (bg[0] * vo0 + bg[1] * vo1 + bg[2] * vo2) : 0.0f;
-    const int warp_max = __reduce_max_sync(0xffffffffu, fin);
-    if (lane == 0) s_wmax[warp] = warp_max;
-    __syncthreads();
-    int block_max = s_wmax[0];
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) block_max = max(block_max, s_wmax[w]);
-    const int top = min(end - 1, block_max);
-    if (top < start) return;  // uniform: nothing in this tile reached any pixel
-    const int rounds = (top - start + kRound) / kRound;
-
+    // Entries after the last one any pixel of the strip blended cannot contribute.
+    const int top = min(end - 1, __reduce_max_sync(0xffffffffu, fin));
     float T = Tf, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f;
 
-    // Staging: 4 threads per splat, three of them carry one float4 of its record.
-    const int g = tid >> 2, part = tid & 3;
-    float4 nv = make_float4(0, 0, 0, 0);
-    u32 nid = 0;
-    {
-        const int pos = top - g;
-        if (pos >= start && part < 3) {
-            nid = (u32)sorted[pos];
-            nv = __ldg(records + (size_t)nid * 3 + part);
+    float4 (*rec)[3] = s_rec[warp];
+    float (*acc)[12] = s_acc[warp];
+
+    for (int base = top; base >= start; base -= 32) {
+        // ---- fetch + cull: lane l takes the entry at list position base - l
+        const int my_pos = base - lane;
+        u32 id = 0;
+        float4 q0 = make_float4(0, 0, 0, 0), q1 = q0;
+        float blue = 0.f, thr = 0.f;
+        bool hit = false;
+        if (my_pos >= start) {
+            id = (u32)sorted[my_pos];
+            const float4* r = records + (size_t)id * 3;
+            q0 = __ldg(r); q1 = __ldg(r + 1); blue = __ldg(r + 2).x;
+            thr = __logf(255.0f * q1.y) + kStripMargin;
+            hit = strip_mask8(q0.x, q0.y, q0.z, q0.w, q1.x, thr, X0, Y0, warp, 1) != 0;
         }
-    }
-    for (int r = 0; r < rounds; ++r) {
-        __syncthreads();  // the previous round's flush has finished with the shared arrays
-        if (part < 3) s_rec[g][part] = nv;
-        if (part == 0) s_id[g] = nid;
-        __syncthreads();
-        const int round_top = top - r * kRound;
-        {
-            const int pos = round_top - kRound - g;
-            if (pos >= start && part < 3) {
-                nid = (u32)sorted[pos];
-                nv = __ldg(records + (size_t)nid * 3 + part);
-            }
-        }
-        const int cnt = min(kRound, round_top - start + 1);
-        u64 touched = 0;
-        for (int t = max(0, round_top - warp_max); t < cnt; ++t) {
-            const int pos = round_top - t;
-            bool valid = inside && pos <= fin;
-            const float4 qa = s_rec[t][0];  // x, y, conic a, conic b
-            const float4 qb = s_rec[t][1];  // conic c, opacity, r, g
+        u32 todo = __ballot_sync(0xffffffffu, hit);
+        if (todo == 0) continue;
+        rec[lane][0] = q0; rec[lane][1] = q1; rec[lane][2] = make_float4(blue, thr, 0.f, 0.f);
+        __syncwarp();
+
+        // ---- blend the survivors, nearest list position last (ascending lane = descending position)
+        u32 touched = 0;
+        while (todo) {
+            const int t = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int pos = base - t;
+            const float4 qa = rec[t][0];
+            const float4 qb = rec[t][1];
+            const float4 qc = rec[t][2];
             const float dx = qa.x - px, dy = qa.y - py;
             const float sigma = 0.5f * (qa.z * dx * dx + qb.x * dy * dy) + qa.w * dx * dy;
-            const float vis = __expf(-sigma);
-            const float alpha = min(0.99f, qb.y * vis);
-            valid = valid && !(sigma < 0.f || alpha < 1.f / 255.f);
+            const bool valid = inside && pos <= fin && sigma >= 0.f && sigma <= qc.y;
             if (!__any_sync(0xffffffffu, valid)) continue;
             float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             float v8 = 0.f;
             if (valid) {
-                const float blue = s_rec[t][2].x;
-                const float ra = 1.f / (1.f - alpha);
-                T *= ra;
-                const float fac = alpha * T;
-                float v_alpha = 0.f;
-                v_alpha += (qb.z * T - b0 * ra) * vo0;
-                v_alpha += (qb.w * T - b1 * ra) * vo1;
-                v_alpha += (blue * T - b2 * ra) * vo2;
-                v_alpha += -Tf * ra * bgdot;
-                b0 += qb.z * fac; b1 += qb.w * fac; b2 += blue * fac;
-                const float v_sigma = -qb.y * vis * v_alpha;
-                v[0] = v_sigma * (qa.z * dx + qa.w * dy);
-                v[1] = v_sigma * (qa.w * dx + qb.x * dy);
-                v[2] = 0.5f * v_sigma * dx * dx;
-                v[3] = v_sigma * dx * dy;
-                v[4] = 0.5f * v_sigma * dy * dy;
-                v[5] = vis * v_alpha;
-                v[6] = fac * vo0;
-                v[7] = fac * vo1;
-                v8 = fac * vo2;
+                const float vis = __expf(-sigma);
+                const float alpha = min(0.99f, qb.y * vis);
+                if (!(alpha < 1.f / 255.f)) {
+                    const float ra = 1.f / (1.f - alpha);
+                    T *= ra;
+                    const float fac = alpha * T;
+                    float v_alpha = 0.f;
+                    v_alpha += (qb.z * T - b0 * ra) * vo0;
+                    v_alpha += (qb.w * T - b1 * ra) * vo1;
+                    v_alpha += (qc.x * T - b2 * ra) * vo2;
+                    v_alpha += -Tf * ra * bgdot;
+                    b0 += qb.z * fac; b1 += qb.w * fac; b2 += qc.x * fac;
+                    const float v_sigma = -qb.y * vis * v_alpha;
+                    v[0] = v_sigma * dx;   // Sx
+                    v[1] = v_sigma * dy;   // Sy
+                    v[2] = v[0] * dx;      // Sxx
+                    v[3] = v[0] * dy;      // Sxy
+                    v[4] = v[1] * dy;      // Syy
+                    v[5] = v_sigma;        // S0
+                    v[6] = fac * vo0;
+                    v[7] = fac * vo1;
+                    v8 = fac * vo2;
+                }
             }
             const float sum = butterfly8(v, lane);
             const float sum8 = butterfly1(v8);
-            if ((lane & 3) == 0) s_acc[warp][t][lane >> 2] = sum;
-            if (lane == 0) s_acc[warp][t][8] = sum8;
-            touched |= 1ull << t;
+            if ((lane & 3) == 0) acc[t][lane >> 2] = sum;
+            if (lane == 0) acc[t][8] = sum8;
+            touched |= 1u << t;
         }
-        if (lane == 0) s_touched[warp] = touched;
-        __syncthreads();
-        // Flush: thread (g, part) adds the warps' slots of float4 `part` of splat g and issues one reduction.
-        if (g < cnt && part < 3) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            bool any = false;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                if ((s_touched[w] >> g) & 1ull) {
-                    const float4 p = *reinterpret_cast<const float4*>(&s_acc[w][g][4 * part]);
-                    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-                    any = true;
-                }
-            }
-            if (any) {
-                float4* dst = grad_acc + (size_t)s_id[g] * 3 + part;
-                if (part < 2) red_add_v4(dst, acc);
-                else red_add(reinterpret_cast<float*>(dst), acc.x);
-            }
+        __syncwarp();
+
+        // ---- flush: lane l owns entry l of the chunk and still has its record in registers
+        if ((touched >> lane) & 1u) {
+            const float4 m0 = *reinterpret_cast<const float4*>(&acc[lane][0]);  // Sx, Sy, Sxx, Sxy
+            const float4 m1 = *reinterpret_cast<const float4*>(&acc[lane][4]);  // Syy, S0, r, g
+            const float m2 = acc[lane][8];                                      // b
+            float4* dst = grad_acc + (size_t)id * 3;
+            red_add_v4(dst, make_float4(q0.z * m0.x + q0.w * m0.y, q0.w * m0.x + q1.x * m0.y, 0.5f * m0.z, m0.w));
+            red_add_v4(dst + 1, make_float4(0.5f * m1.x, -m1.y / q1.y, m1.z, m1.w));
+            red_add(reinterpret_cast<float*>(dst + 2), m2);
         }
+        __syncwarp();  // the slices are reused by the next chunk
     }
 }
 
