@@ -99,10 +99,18 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
 // One warp per 32 depth-ordered splats: their pair ranges are consecutive, so the warp walks the
 // concatenated range 32 positions at a time; each lane finds the owning splat by a 5-step search over
 // the lanes' running counts and writes one packed pair.  All stores are consecutive 8-byte lanes.
+// With HIST the kernel also counts the digits the following tile sort will look at (it knows every tile id
+// it writes), which spares that sort a pass over the list.
+template <bool HIST>
 __global__ void __launch_bounds__(256)
 emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_last, const float4* __restrict__ records,
                   const int32_t* __restrict__ tiles, const u64* __restrict__ depth_keys_sorted,
-                  const u32* __restrict__ offsets, u64* __restrict__ pairs) {
+                  const u32* __restrict__ offsets, u64* __restrict__ pairs, const SortPlan plan, u32* __restrict__ hist) {
+    __shared__ u32 s_hist[HIST ? 4 : 1][256];
+    if (HIST) {
+        for (int i = threadIdx.x; i < plan.npass * 256; i += 256) (&s_hist[0][0])[i] = 0;
+        __syncthreads();
+    }
     const int lane = threadIdx.x & 31;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;  // position in depth order; warps are aligned to 32
     u32 id = 0, c = 0, off = 0;
@@ -144,12 +152,33 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
         const int o_x0 = __shfl_sync(0xffffffffu, x0, owner);
         const int o_y0 = __shfl_sync(0xffffffffu, y0, owner);
         const int o_w = __shfl_sync(0xffffffffu, w, owner);
+        u64 pair = 0;
+        bool wrote = false;
         if (p < total) {
             const u32 r = p - o_excl;
             const u32 ry = r / (u32)o_w;
             const u32 tile = (u32)(o_y0 + (int)ry) * (u32)tiles_x + (u32)o_x0 + (r - ry * (u32)o_w);
             const u32 dst = warp_base + p;
-            if (dst < k) pairs[dst] = ((u64)tile << 32) | o_id;
+            pair = ((u64)tile << 32) | o_id;
+            wrote = dst < k;
+            if (wrote) pairs[dst] = pair;
+        }
+        if (HIST) {
+            // Lowest digit: consecutive lanes hold consecutive tile ids, so the counters rarely collide.
+            if (wrote) atomicAdd(&s_hist[0][sort_digit(pair, plan.shift[0], plan.mask[0], plan.flip[0])], 1u);
+            // Higher digits are nearly constant inside a warp: one atomic per group of equal digits.
+            for (int q = 1; q < plan.npass; ++q) {
+                const u32 d = sort_digit(pair, plan.shift[q], plan.mask[q], plan.flip[q]);
+                const u32 m = warp_peers(d, wrote, plan.bits[q]);
+                if (wrote && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[q][d], (u32)__popc(m));
+            }
+        }
+    }
+    if (HIST) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < plan.npass * 256; i += 256) {
+            const u32 c = (&s_hist[0][0])[i];
+            if (c) atomicAdd(hist + i, c);
         }
     }
 }
@@ -242,13 +271,20 @@ int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_key
 }
 
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
-                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s) {
+                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, const SortPlan* plan, u32* hist,
+                cudaStream_t s) {
     if (n == 0 || k == 0) return DSB_OK;
     DSB_REQUIRE(records && tiles && depth_keys_sorted && offsets && pairs, "emit: null pointer");
     DSB_REQUIRE(k < DSB_MAX_PAIRS, "emit: too many pairs");
-    emit_pairs_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last,
-                                                     reinterpret_cast<const float4*>(records), tiles, depth_keys_sorted,
-                                                     offsets, pairs);
+    const float4* rec4 = reinterpret_cast<const float4*>(records);
+    if (hist && plan && plan->npass <= 4)
+        emit_pairs_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last, rec4, tiles,
+                                                               depth_keys_sorted, offsets, pairs, *plan, hist);
+    else {
+        DSB_REQUIRE(!hist, "emit: fused digit counting supports at most 4 passes");
+        emit_pairs_kernel<false><<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last, rec4, tiles,
+                                                                depth_keys_sorted, offsets, pairs, SortPlan{}, nullptr);
+    }
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -1,16 +1,16 @@
 // Stage (e): per-tile front-to-back alpha blending.
 //
-// Takes the place of the reference's render_image_kernel (cpp/rasterizer_kernels.cu:341-431).  One
-// 256-thread block per 16x16 tile, one pixel per thread, warp w = rows 2w, 2w+1 of the tile.  The tile's
-// depth-ordered list is consumed in rounds of 256 entries:
-//   * staging: thread i fetches entry i's 48-byte record (the next round's records are already in flight
-//     in registers while the current round is blended), works out which of the 8 warp strips the splat can
-//     reach at all (blend_common.cuh) and the round's survivors are compacted into shared memory in list
-//     order -- splats that cannot reach any pixel of the tile cost nothing further;
-//   * blending: every warp walks the compacted round; one shared-memory word tells it whether the splat
-//     can reach its strip, and only then are the record and the per-pixel arithmetic touched.
-// A pixel stops at the first splat that would push its transmittance under 1e-4; a warp whose 32 pixels
-// have all stopped leaves the inner loop; the tile stops fetching rounds once all 256 pixels have stopped.
+// Takes the place of the reference's render_image_kernel (cpp/rasterizer_kernels.cu:341-431), which runs
+// one 256-thread block per 16x16 tile in lock step: rounds of 256 list entries, two block barriers per
+// round, every entry evaluated for every pixel until all 256 pixels have stopped.
+//
+// Here each WARP is on its own (as in the backward blend): warp w of a block owns the 16x2-pixel strip
+// (rows 2w, 2w+1) of the block's tile and walks the tile's depth-ordered list in chunks of 32 entries, with
+// no block barrier anywhere, so a strip stops as soon as ITS 32 pixels have stopped.
+//   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether the splat can reach the strip at
+//     all (blend_common.cuh); a ballot gives the survivors;
+//   * blend: survivors are parked in the warp's private shared-memory slice and each pixel consumes them
+//     in list order until its transmittance would fall under 1e-4.
 //
 // Per-pixel arithmetic (order of operations, 0.999 alpha clamp, 1/255 skip, no background term) is the
 // reference's and the strip test is conservative, so images agree to rounding and final_idx exactly.
@@ -22,16 +22,36 @@ namespace {
 
 constexpr int kThreads = kTilePixels;
 constexpr int kWarps = kThreads / 32;
+#ifndef DSB_FWD_PREFETCH
+#define DSB_FWD_PREFETCH 0  // 1: fetch the next chunk's records while the current chunk is blended (costs occupancy)
+#endif
+
+struct Fetched {
+    float4 q0, q1;
+    float blue;
+    bool have;
+};
+
+__device__ __forceinline__ Fetched fetch_entry(const float4* __restrict__ records, const u64* __restrict__ sorted,
+                                               const int pos, const int end) {
+    Fetched f;
+    f.q0 = make_float4(0, 0, 0, 0); f.q1 = f.q0; f.blue = 0.f;
+    f.have = pos < end;
+    if (f.have) {
+        const u32 id = (u32)sorted[pos];
+        const float4* r = records + (size_t)id * 3;
+        f.q0 = __ldg(r); f.q1 = __ldg(r + 1); f.blue = __ldg(r + 2).x;
+    }
+    return f;
+}
 
 __global__ void __launch_bounds__(kThreads)
 blend_forward_kernel(const int W, const int H, const float4* __restrict__ records, const u64* __restrict__ sorted,
                      const int32_t* __restrict__ ranges, float* __restrict__ image, float* __restrict__ final_T,
                      int32_t* __restrict__ final_idx) {
-    __shared__ float4 s_q0[kThreads];  // x, y, conic a, conic b
-    __shared__ float4 s_q1[kThreads];  // conic c, opacity, r, g
-    __shared__ float s_b[kThreads];    // b
-    __shared__ u32 s_mp[kThreads];     // (position inside the round << 8) | strip mask
-    __shared__ int s_wcount[kWarps];
+    __shared__ float4 s_q0[kWarps][32];  // x, y, conic a, conic b
+    __shared__ float4 s_q1[kWarps][32];  // conic c, opacity, r, g
+    __shared__ float s_b[kWarps][32];    // b
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -46,48 +66,34 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
     int last = 0;
     bool done = !inside;
 
-    float4 n0 = make_float4(0, 0, 0, 0), n1 = n0;
-    float nb = 0.0f;
-    bool have = start + tid < end;
-    if (have) {
-        const u32 id = (u32)sorted[start + tid];
-        const float4* r = records + (size_t)id * 3;
-        n0 = __ldg(r); n1 = __ldg(r + 1); nb = __ldg(r + 2).x;
-    }
-    const int rounds = (end - start + kThreads - 1) / kThreads;
-    for (int s = 0; s < rounds; ++s) {
-        // Also the barrier that lets the previous round's shared memory be overwritten.
-        if (__syncthreads_count(done) == kThreads) break;
-        u32 mask = 0;
-        if (have) mask = strip_mask8(n0.x, n0.y, n0.z, n0.w, n1.x, __logf(255.0f * n1.y) + kStripMargin, X0, Y0);
-        const u32 keep = __ballot_sync(0xffffffffu, mask != 0);
-        if (lane == 0) s_wcount[warp] = __popc(keep);
-        __syncthreads();
-        int slot = __popc(keep & ((1u << lane) - 1u)), total = 0;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const int cw = s_wcount[w];
-            slot += (w < warp) ? cw : 0;
-            total += cw;
+    float4* q0s = s_q0[warp];
+    float4* q1s = s_q1[warp];
+    float* bs = s_b[warp];
+
+#if DSB_FWD_PREFETCH
+    Fetched nxt = fetch_entry(records, sorted, start + lane, end);
+#endif
+    for (int base = start; base < end; base += 32) {
+        if (__all_sync(0xffffffffu, done)) break;
+#if DSB_FWD_PREFETCH
+        const Fetched cur = nxt;
+        nxt = fetch_entry(records, sorted, base + 32 + lane, end);
+#else
+        const Fetched cur = fetch_entry(records, sorted, base + lane, end);
+#endif
+        bool hit = false;
+        if (cur.have) {
+            const float thr = __logf(255.0f * cur.q1.y) + kStripMargin;
+            hit = strip_mask8(cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w, cur.q1.x, thr, X0, Y0, warp, 1) != 0;
         }
-        if (mask) {
-            s_q0[slot] = n0; s_q1[slot] = n1; s_b[slot] = nb;
-            s_mp[slot] = ((u32)tid << 8) | mask;
-        }
-        __syncthreads();
-        const int round_base = start + s * kThreads;
-        const int next = round_base + kThreads + tid;
-        have = next < end;
-        if (have) {
-            const u32 id = (u32)sorted[next];
-            const float4* r = records + (size_t)id * 3;
-            n0 = __ldg(r); n1 = __ldg(r + 1); nb = __ldg(r + 2).x;
-        }
-        for (int i = 0; i < total && !done; ++i) {
-            const u32 mp = s_mp[i];
-            if (!((mp >> warp) & 1u)) continue;  // this splat cannot reach the warp's strip
-            const float4 a = s_q0[i];
-            const float4 b = s_q1[i];
+        const u32 todo = __ballot_sync(0xffffffffu, hit);
+        if (todo == 0) continue;
+        q0s[lane] = cur.q0; q1s[lane] = cur.q1; bs[lane] = cur.blue;
+        __syncwarp();
+        for (u32 m = todo; m != 0 && !done; m &= m - 1) {
+            const int t = __ffs(m) - 1;
+            const float4 a = q0s[t];
+            const float4 b = q1s[t];
             const float dx = pxf - a.x, dy = pyf - a.y;
             const float power = -0.5f * (a.z * dx * dx + b.x * dy * dy) - a.w * dx * dy;
             const float alpha = min(0.999f, b.y * __expf(power));
@@ -95,10 +101,11 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
             const float Tn = (1.0f - alpha) * T;
             if (!(Tn >= 0.0001f)) { done = true; break; }
             const float wgt = alpha * T;
-            c0 += wgt * b.z; c1 += wgt * b.w; c2 += wgt * s_b[i];
+            c0 += wgt * b.z; c1 += wgt * b.w; c2 += wgt * bs[t];
             T = Tn;
-            last = round_base + (int)(mp >> 8);
+            last = base + t;
         }
+        __syncwarp();  // the slice is reused by the next chunk
     }
     if (inside) {
         const size_t pix = (size_t)y * W + x;

@@ -150,7 +150,7 @@ int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* reco
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0 && k >= 0, "n and k must be non-negative");
     return launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
-                       reinterpret_cast<u64*>(pairs), (cudaStream_t)stream);
+                       reinterpret_cast<u64*>(pairs), nullptr, nullptr, (cudaStream_t)stream);
 }
 
 int dsb_sort_pairs(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit, void* workspace,
@@ -227,21 +227,28 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                        int32_t* final_idx, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
+    // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The emit kernel counts
+    // the sort's digits while it writes the pairs, so the sort itself is just its passes.
+    int tile_bits = 1;
+    while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
+    DSB_REQUIRE(k < DSB_MAX_PAIRS, "too many pairs");
+    DSB_REQUIRE(k <= 1 || (pairs && pairs_alt && workspace), "forward_render: null pair buffers or workspace");
+    const SortPlan plan = make_sort_plan(32, 32 + tile_bits, false);
+    u32* hist = nullptr;
     int rc;
     {
         StageScope scope(kStageEmit, s);
+        rc = sort_begin(k, plan, workspace, workspace_bytes, &hist, s);
+        if (rc != DSB_OK) return rc;
         rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
-                         reinterpret_cast<u64*>(pairs), s);
+                         reinterpret_cast<u64*>(pairs), &plan, hist, s);
     }
     if (rc != DSB_OK) return rc;
-    // Only the tile id needs sorting now: ceil(log2(tiles)) live bits above bit 32.
-    int tile_bits = 1;
-    while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
     int in_alt = 0;
     {
         StageScope scope(kStageTileSort, s);
-        rc = launch_sort(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, 32,
-                         32 + tile_bits, workspace, workspace_bytes, &in_alt, s);
+        rc = sort_passes(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, plan,
+                         workspace, &in_alt, s);
         if (rc != DSB_OK) return rc;
         if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
     }

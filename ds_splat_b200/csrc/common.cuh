@@ -98,16 +98,52 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
                       const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
                       float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, cudaStream_t s);
 
+// Radix-sort pass layout: which bits each pass looks at.  flip is XORed into the digit (sign bit of signed keys).
+constexpr int kMaxSortPasses = 8;
+struct SortPlan {
+    int npass;
+    int shift[kMaxSortPasses];
+    int bits[kMaxSortPasses];   // digit width of the pass, 1..8
+    u32 mask[kMaxSortPasses];
+    u32 flip[kMaxSortPasses];
+};
+__device__ __forceinline__ u32 sort_digit(u64 key, int shift, u32 mask, u32 flip) {
+    return ((u32)(key >> shift) & mask) ^ flip;
+}
+// Lanes of the warp that are valid and hold the same nbits-wide digit as the calling lane: one ballot per
+// digit bit.  (match.any gives the same answer but its latency grows with the number of distinct values in
+// the warp, which is the common case for the low digits of tile ids and depth keys.)
+__device__ __forceinline__ u32 warp_peers(const u32 d, const bool valid, const int nbits) {
+    u32 peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        if (b < nbits) {
+            const bool bit = (d >> b) & 1u;
+            const u32 vote = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? vote : ~vote;
+        }
+    }
+    return peers;
+}
+SortPlan make_sort_plan(int begin_bit, int end_bit, bool signed_top);
+
 int64_t sort_workspace_bytes(int64_t k);
 int64_t sort_status_offset();  // byte offset of the int status word inside a sort workspace
 int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
                 void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s);
+// Two-step form for producers that count the digits themselves while writing the items:
+// sort_begin clears the workspace and returns the histogram to fill, sort_passes runs the passes.
+int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s);
+int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, const SortPlan& plan, void* ws,
+                int* in_alt, cudaStream_t s);
 
 int64_t plan_workspace_bytes(int n);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
+// plan/hist: when hist is not null the kernel also counts the sort digits of every pair it writes.
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
-                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s);
+                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, const SortPlan* plan, u32* hist,
+                cudaStream_t s);
 int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
 int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);
 

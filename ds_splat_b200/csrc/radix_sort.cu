@@ -1,14 +1,16 @@
 // Stage (c): stable least-significant-digit radix sort, "onesweep" style.
 //
-// Takes the place of thrust::sort_by_key in the reference (cpp/rasterizer_torch.cu:70-76).  One
-// histogram kernel reads the keys once and counts every 8-bit digit of the requested bit range; then
-// each digit takes ONE kernel that reads and writes every item exactly once: a block ranks its 4096
-// items, publishes its per-digit counts, and learns the counts of all earlier blocks by decoupled
-// look-back (each block polls its predecessors' status words instead of waiting for a separate scan
-// kernel).  Only the live bits are sorted: callers pass [begin_bit, end_bit).
+// Takes the place of thrust::sort_by_key in the reference (cpp/rasterizer_torch.cu:70-76).  The digits of
+// the requested bit range are counted once (by a histogram kernel, or by the kernel that produced the
+// items: emit_pairs_kernel already knows every tile id it writes); then each digit takes ONE kernel that
+// reads and writes every item exactly once: a block ranks its 4096 items, publishes its per-digit counts,
+// and learns the counts of all earlier blocks by decoupled look-back (each block polls its predecessors'
+// status words instead of waiting for a separate scan kernel).  Only the live bits are sorted: callers
+// pass [begin_bit, end_bit), and the bits are split evenly over the passes (13 tile bits -> 7 + 6), which
+// keeps the scatter runs of the first pass long.
 //
 // Stability (equal digits keep their input order) is what makes the result identical to the
-// reference's sort: within a warp items are ranked in memory order with match_any, warps are
+// reference's sort: within a warp items are ranked in memory order, warps are
 // ordered by a scan, blocks by the look-back.
 //
 // Every poll loop is bounded (kSpinLimit): on expiry the block records DSB_ERR_DEVICE_WAIT_EXPIRED in
@@ -24,48 +26,44 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kItems = 16;                      // items per thread
+#ifndef DSB_SORT_ITEMS
+#define DSB_SORT_ITEMS 16
+#endif
+constexpr int kItems = DSB_SORT_ITEMS;          // items per thread (multiple of 4)
 constexpr int kTileItems = kThreads * kItems;   // 4096 items per block
 constexpr int kRadix = 256;
-constexpr int kMaxPasses = 8;
 constexpr u32 kFlagAggregate = 1u << 30;        // status word holds this block's own count
 constexpr u32 kFlagInclusive = 1u << 31;        // status word holds the count of this and all earlier blocks
 constexpr u32 kValueMask = (1u << 30) - 1;
 
 struct SortHeader {                  // start of the workspace, zeroed before every sort
-    u32 hist[kMaxPasses][kRadix];
-    u32 tile_counter[kMaxPasses];
+    u32 hist[kMaxSortPasses][kRadix];
+    u32 tile_counter[kMaxSortPasses];
     int status;
     int pad[7];
 };
 
-__device__ __forceinline__ u32 digit_of(u64 key, int shift, u32 mask, u32 flip) {
-    return ((u32)(key >> shift) & mask) ^ flip;
-}
-
-// Counts all digits of all passes in one read of the keys.  Per-warp aggregation with match_any keeps
+// Counts all digits of all passes in one read of the keys.  Per-warp aggregation (warp_peers) keeps
 // the shared-memory atomics to one per distinct digit per warp, which matters when a digit is nearly
 // constant (the exponent byte of depth keys, the high tile bits).
 __global__ void __launch_bounds__(kThreads)
-radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const int begin_bit, const int npass,
-                       const u32 last_mask, const u32 last_flip, u32* __restrict__ hist) {
-    __shared__ u32 s_hist[kMaxPasses][kRadix];
-    for (int k = threadIdx.x; k < npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
+radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan plan, u32* __restrict__ hist) {
+    __shared__ u32 s_hist[kMaxSortPasses][kRadix];
+    for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
     __syncthreads();
     const u32 lane = threadIdx.x & 31;
-    const u32 n_round = (n + 31u) & ~31u;  // whole warps stay converged for match_any
+    const u32 n_round = (n + 31u) & ~31u;  // whole warps stay converged for the ballots
     for (u32 i = blockIdx.x * kThreads + threadIdx.x; i < n_round; i += gridDim.x * kThreads) {
         const bool valid = i < n;
         const u64 key = valid ? keys[i] : 0ull;
-        for (int p = 0; p < npass; ++p) {
-            const bool last = p == npass - 1;
-            const u32 d = digit_of(key, begin_bit + 8 * p, last ? last_mask : 0xffu, last ? last_flip : 0u);
-            const u32 m = __match_any_sync(0xffffffffu, valid ? d : 0xffffffffu);
+        for (int p = 0; p < plan.npass; ++p) {
+            const u32 d = sort_digit(key, plan.shift[p], plan.mask[p], plan.flip[p]);
+            const u32 m = warp_peers(d, valid, plan.bits[p]);
             if (valid && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[p][d], (u32)__popc(m));
         }
     }
     __syncthreads();
-    for (int k = threadIdx.x; k < npass * kRadix; k += kThreads) {
+    for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) {
         const u32 c = (&s_hist[0][0])[k];
         if (c) atomicAdd(hist + k, c);
     }
@@ -89,10 +87,13 @@ __device__ __forceinline__ u32 block_exclusive_scan_256(u32 v, u32* s_warp_sums,
     return prefix + incl - v;
 }
 
+#ifndef DSB_SORT_MIN_BLOCKS
+#define DSB_SORT_MIN_BLOCKS 3  // caps registers at 80: three resident blocks per SM beat two with more registers
+#endif
 template <bool HAS_VALS>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
 onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
-                const u32 n, const int shift, const u32 mask, const u32 flip, const u32* __restrict__ hist,
+                const u32 n, const int shift, const int nbits, const u32 mask, const u32 flip, const u32* __restrict__ hist,
                 u32* __restrict__ tile_counter, u32* __restrict__ lookback, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char dyn[];
     u64* s_keys = reinterpret_cast<u64*>(dyn);                         // [4096]
@@ -122,24 +123,34 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
         if (HAS_VALS) val[i] = pos < n ? vin[pos] : 0u;
     }
 
-    // Rank inside the warp: lanes holding the same digit find each other with match_any; the lowest
-    // of them bumps the warp's counter for that digit by the group size.
+    // Rank inside the warp: lanes holding the same digit find each other (warp_peers); the lowest of them
+    // bumps the warp's counter for that digit by the group size.  The peer masks of four items are worked
+    // out together so that their latencies overlap; the counter updates stay in item order.
     u32 rank[kItems];
     const u32 lanemask_lt = (1u << lane) - 1u;
 #pragma unroll
-    for (int i = 0; i < kItems; ++i) {
-        const bool valid = wbase + 32 * i + lane < n;
-        const u32 d = digit_of(key[i], shift, mask, flip);
-        const u32 m = __match_any_sync(0xffffffffu, valid ? d : 0xffffffffu);
-        const u32 lower = m & lanemask_lt;
-        u32 before = 0;
-        if (lower == 0 && valid) {
-            before = s_wcnt[warp][d];
-            s_wcnt[warp][d] = before + (u32)__popc(m);
+    for (int i0 = 0; i0 < kItems; i0 += 4) {
+        u32 m[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool valid = wbase + 32 * (i0 + j) + lane < n;
+            const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
+            m[j] = warp_peers(d, valid, nbits);
         }
-        before = __shfl_sync(0xffffffffu, before, __ffs(m) - 1);
-        rank[i] = before + (u32)__popc(lower);
-        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool valid = wbase + 32 * (i0 + j) + lane < n;
+            const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
+            const u32 lower = m[j] & lanemask_lt;
+            u32 before = 0;
+            if (lower == 0 && valid) {
+                before = s_wcnt[warp][d];
+                s_wcnt[warp][d] = before + (u32)__popc(m[j]);
+            }
+            before = __shfl_sync(0xffffffffu, before, valid ? __ffs(m[j]) - 1 : lane);
+            rank[i0 + j] = before + (u32)__popc(lower);
+            __syncwarp();
+        }
     }
     __syncthreads();
 
@@ -184,7 +195,7 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         if (wbase + 32 * i + lane < n) {
-            const u32 d = digit_of(key[i], shift, mask, flip);
+            const u32 d = sort_digit(key[i], shift, mask, flip);
             const u32 slot = s_dstart[d] + s_wcnt[warp][d] + rank[i];
             s_keys[slot] = key[i];
             if (HAS_VALS) s_vals[slot] = val[i];
@@ -196,7 +207,7 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
         const u32 slot = j * kThreads + tid;
         if (slot < tile_n) {
             const u64 k = s_keys[slot];
-            const u32 dst = s_glob[digit_of(k, shift, mask, flip)] + slot;
+            const u32 dst = s_glob[sort_digit(k, shift, mask, flip)] + slot;
             kout[dst] = k;
             if (HAS_VALS) vout[dst] = s_vals[slot];
         }
@@ -207,64 +218,107 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
 
 int64_t sort_workspace_bytes(int64_t k) {
     const int64_t tiles = (k + kTileItems - 1) / kTileItems;
-    return (int64_t)sizeof(SortHeader) + (int64_t)kMaxPasses * tiles * kRadix * (int64_t)sizeof(u32);
+    return (int64_t)sizeof(SortHeader) + (int64_t)kMaxSortPasses * tiles * kRadix * (int64_t)sizeof(u32);
 }
 
 int64_t sort_status_offset() { return (int64_t)offsetof(SortHeader, status); }
 
-// Sorts k items on bits [begin_bit, end_bit).  vals may be null.  *in_alt tells where the result is.
-int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
-                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s) {
-    if (in_alt) *in_alt = 0;
+// Splits bits [begin_bit, end_bit) evenly over ceil(bits / 8) passes, low digits first.
+SortPlan make_sort_plan(int begin_bit, int end_bit, bool signed_top) {
+    SortPlan plan = {};
+    const int bits = end_bit - begin_bit;
+    plan.npass = (bits + 7) / 8;
+    const int base = bits / plan.npass, extra = bits % plan.npass;
+    int shift = begin_bit;
+    for (int p = 0; p < plan.npass; ++p) {
+        const int w = base + (p < extra ? 1 : 0);
+        plan.shift[p] = shift;
+        plan.bits[p] = w;
+        plan.mask[p] = (1u << w) - 1u;
+        plan.flip[p] = 0;
+        shift += w;
+        if (p == plan.npass - 1 && signed_top) plan.flip[p] = 1u << (w - 1);
+    }
+    return plan;
+}
+
+static int check_sort_args(const void* items, const void* items_alt, const void* ws, int64_t k, int begin_bit, int end_bit) {
     DSB_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit < end_bit, "sort: bad bit range [%d, %d)", begin_bit, end_bit);
-    if (k <= 1) return DSB_OK;
     if (k >= DSB_MAX_PAIRS) {
         set_error("sort: %lld items exceed the supported maximum of 2^30 - 1", (long long)k);
         return DSB_ERR_TOO_MANY_PAIRS;
     }
-    DSB_REQUIRE(items && items_alt && ws, "sort: null pointer");
-    DSB_REQUIRE(!vals == !vals_alt, "sort: values and alternate values must both be given or both be null");
-    const int bits = end_bit - begin_bit;
-    const int npass = (bits + 7) / 8;
-    const int last_bits = bits - 8 * (npass - 1);
-    const u32 last_mask = (1u << last_bits) - 1u;
-    const u32 last_flip = (end_bit == 64 && vals) ? (1u << (last_bits - 1)) : 0u;  // signed keys in the pair interface
+    if (k > 1) {
+        DSB_REQUIRE(items && items_alt && ws, "sort: null pointer");
+        DSB_REQUIRE(((uintptr_t)ws & 15) == 0, "sort: workspace must be 16-byte aligned");
+    }
+    return DSB_OK;
+}
+
+// Step 1 of a sort whose digit counts come from the producer of the items: clears the workspace and hands
+// back the histogram the producer has to fill (plan.npass rows of 256 counters).
+int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s) {
+    *hist_out = nullptr;
+    if (k <= 1) return DSB_OK;
     const int64_t tiles = (k + kTileItems - 1) / kTileItems;
-    const int64_t need = (int64_t)sizeof(SortHeader) + (int64_t)npass * tiles * kRadix * (int64_t)sizeof(u32);
+    const int64_t need = (int64_t)sizeof(SortHeader) + (int64_t)plan.npass * tiles * kRadix * (int64_t)sizeof(u32);
     if (ws_bytes < need) {
         set_error("sort: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
         return DSB_ERR_WORKSPACE_TOO_SMALL;
     }
-    DSB_REQUIRE(((uintptr_t)ws & 15) == 0, "sort: workspace must be 16-byte aligned");
+    DSB_CUDA_CHECK(cudaMemsetAsync(ws, 0, (size_t)need, s));
+    *hist_out = &reinterpret_cast<SortHeader*>(ws)->hist[0][0];
+    return DSB_OK;
+}
+
+// Step 2: the onesweep passes, given a filled histogram.
+int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, const SortPlan& plan, void* ws,
+                int* in_alt, cudaStream_t s) {
+    if (in_alt) *in_alt = 0;
+    if (k <= 1) return DSB_OK;
+    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
     SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
     u32* lookback = reinterpret_cast<u32*>(hdr + 1);
-    DSB_CUDA_CHECK(cudaMemsetAsync(ws, 0, (size_t)need, s));
-
-    const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
-    radix_histogram_kernel<<<hist_blocks, kThreads, 0, s>>>(items, (u32)k, begin_bit, npass, last_mask, last_flip, &hdr->hist[0][0]);
-    DSB_LAUNCH_CHECK();
-
     const size_t dyn = kTileItems * (sizeof(u64) + (vals ? sizeof(u32) : 0));
     if (vals) DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     else DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     u64 *src = items, *dst = items_alt;
     u32 *vsrc = vals, *vdst = vals_alt;
-    for (int p = 0; p < npass; ++p) {
-        const bool last = p == npass - 1;
-        const u32 mask = last ? last_mask : 0xffu, flip = last ? last_flip : 0u;
+    for (int p = 0; p < plan.npass; ++p) {
         u32* lb = lookback + (size_t)p * tiles * kRadix;
         if (vals)
-            onesweep_kernel<true><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, (u32)k, begin_bit + 8 * p, mask, flip,
-                                                                      hdr->hist[p], &hdr->tile_counter[p], lb, &hdr->status);
+            onesweep_kernel<true><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, (u32)k, plan.shift[p], plan.bits[p],
+                                                                      plan.mask[p], plan.flip[p], hdr->hist[p],
+                                                                      &hdr->tile_counter[p], lb, &hdr->status);
         else
-            onesweep_kernel<false><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, nullptr, nullptr, (u32)k, begin_bit + 8 * p, mask,
-                                                                       flip, hdr->hist[p], &hdr->tile_counter[p], lb, &hdr->status);
+            onesweep_kernel<false><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, nullptr, nullptr, (u32)k, plan.shift[p],
+                                                                       plan.bits[p], plan.mask[p], plan.flip[p], hdr->hist[p],
+                                                                       &hdr->tile_counter[p], lb, &hdr->status);
         DSB_LAUNCH_CHECK();
         u64* t = src; src = dst; dst = t;
         u32* tv = vsrc; vsrc = vdst; vdst = tv;
     }
-    if (in_alt) *in_alt = npass & 1;
+    if (in_alt) *in_alt = plan.npass & 1;
     return DSB_OK;
+}
+
+// Sorts k items on bits [begin_bit, end_bit).  vals may be null.  *in_alt tells where the result is.
+int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s) {
+    if (in_alt) *in_alt = 0;
+    int rc = check_sort_args(items, items_alt, ws, k, begin_bit, end_bit);
+    if (rc != DSB_OK) return rc;
+    if (k <= 1) return DSB_OK;
+    DSB_REQUIRE(!vals == !vals_alt, "sort: values and alternate values must both be given or both be null");
+    const SortPlan plan = make_sort_plan(begin_bit, end_bit, end_bit == 64 && vals != nullptr);  // signed keys in the pair interface
+    u32* hist = nullptr;
+    rc = sort_begin(k, plan, ws, ws_bytes, &hist, s);
+    if (rc != DSB_OK) return rc;
+    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
+    radix_histogram_kernel<<<hist_blocks, kThreads, 0, s>>>(items, (u32)k, plan, hist);
+    DSB_LAUNCH_CHECK();
+    return sort_passes(items, items_alt, vals, vals_alt, k, plan, ws, in_alt, s);
 }
 
 // ---- sort without any allocation ------------------------------------------------------------------
@@ -276,7 +330,7 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
 // of the library image: every GPU that loads the library carries these ~4 MB until the process exits.
 constexpr int64_t kStaticSortMaxItems = DSB_STATIC_SORT_MAX_ITEMS;
 constexpr size_t kStaticSortScratchBytes =
-    sizeof(SortHeader) + (size_t)kMaxPasses * (size_t)(kStaticSortMaxItems / kTileItems) * kRadix * sizeof(u32);
+    sizeof(SortHeader) + (size_t)kMaxSortPasses * (size_t)(kStaticSortMaxItems / kTileItems) * kRadix * sizeof(u32);
 static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortScratchBytes];
 
 constexpr int kMaxStaticDevices = 64;
