@@ -11,6 +11,7 @@
 // association and this file is compiled with the same flag (same approximate rcp/sqrt/rsqrt and the
 // same FMA contraction rules).
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace dsb {
 
@@ -53,11 +54,12 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
                   const float* __restrict__ scales, const float* __restrict__ rots,
                   const float* __restrict__ cov3d_precomp, float4* __restrict__ records, int32_t* __restrict__ radii,
                   int32_t* __restrict__ tiles, float* __restrict__ cov3d, u64* __restrict__ depth_keys,
-                  const int sh_vec4) {
-    extern __shared__ float4 dyn4[];
+                  const int sh_vec4, const int use_bulk) {
+    extern __shared__ __align__(16) float4 dyn4[];
     __shared__ float s_cam[31];      // view rows 0..2 (12), projection (16), camera centre (3)
-    __shared__ float s_means[kThreads * 3];
-    __shared__ float s_scales[kThreads * 3];
+    __shared__ __align__(16) float s_means[kThreads * 3];
+    __shared__ __align__(16) float s_scales[kThreads * 3];
+    __shared__ __align__(8) uint64_t s_bar;
 
     const int tid = threadIdx.x;
     const int base = blockIdx.x * kThreads;
@@ -68,12 +70,32 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
     else if (tid < 28) s_cam[tid] = mat_at(cp.proj, (tid - 12) >> 2, (tid - 12) & 3, cp.transposed);
     else if (tid < 31) s_cam[tid] = cp.campos[tid - 28];
 
-    stage_floats(s_means, means + (size_t)base * 3, cnt * 3, tid);
-    if (scales) stage_floats(s_scales, scales + (size_t)base * 3, cnt * 3, tid);
+    // Full blocks with 16-byte aligned inputs are staged by the bulk copy engine (TMA): every thread asks for
+    // its own 192-byte SH row (into the padded row layout), one thread asks for the block's 3 KB of means
+    // and of scales, and one mbarrier counts the bytes in.  No registers or load instructions are spent on
+    // the 54 KB a block brings in.  The wait is bounded; if it ever expires the ordinary loads below run.
+    bool staged = false;
+    if (use_bulk && cnt == kThreads) {
+        if (tid == 0) mbar_init(&s_bar, 1);
+        __syncthreads();
+        if (tid == 0) {
+            mbar_arrive_expect_tx(&s_bar, kThreads * 192u + 2u * kThreads * 12u);
+            bulk_load(s_means, means + (size_t)base * 3, kThreads * 12u, &s_bar);
+            bulk_load(s_scales, scales + (size_t)base * 3, kThreads * 12u, &s_bar);
+        }
+        bulk_load(dyn4 + tid * kShRow4, shs + (size_t)i * 48, 192u, &s_bar);
+        bool ok = mbar_wait_bounded(&s_bar, 0);
+        if (!ok) ok = mbar_wait_bounded(&s_bar, 0);  // copies still in flight get a second, equally bounded chance
+        staged = __syncthreads_and(ok);
+    }
+    if (!staged) {
+        stage_floats(s_means, means + (size_t)base * 3, cnt * 3, tid);
+        if (scales) stage_floats(s_scales, scales + (size_t)base * 3, cnt * 3, tid);
+    }
 
     const int row_floats = 3 * cp.max_coeff;
     float* s_sh = reinterpret_cast<float*>(dyn4);
-    if (shs && !colors_precomp) {
+    if (shs && !colors_precomp && !staged) {
         if (sh_vec4) {  // 16 coefficients, 16-byte aligned rows: float4 in, padded float4 rows in shared memory
             const float4* g = reinterpret_cast<const float4*>(shs + (size_t)base * 48);
             const int total4 = cnt * 12;
@@ -262,6 +284,9 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
     DSB_REQUIRE(((uintptr_t)records & 15) == 0, "preprocess: records must be 16-byte aligned");
     DSB_REQUIRE(!rots || ((uintptr_t)rots & 15) == 0, "preprocess: rotations must be 16-byte aligned");
     const int sh_vec4 = shs && cp.max_coeff == 16 && ((uintptr_t)shs & 15) == 0;
+    // bulk-copy staging needs every streamed input 16-byte aligned and the default input form
+    const int use_bulk = sh_vec4 && !colors_precomp && !cov3d_precomp && scales && ((uintptr_t)means & 15) == 0 &&
+                         ((uintptr_t)scales & 15) == 0;
     // dynamic shared memory: padded SH rows on the way in, record + covariance rows on the way out
     const size_t sh_bytes = sh_vec4 ? (size_t)kThreads * kShRow4 * 16 : (size_t)kThreads * ((3 * cp.max_coeff) | 1) * 4;
     const size_t out_bytes = (size_t)kThreads * (3 * 16 + 6 * 4);
@@ -275,7 +300,7 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
     const int blocks = (n + kThreads - 1) / kThreads;
     preprocess_kernel<<<blocks, kThreads, dyn, s>>>(cp, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp,
                                                    reinterpret_cast<float4*>(records), radii, tiles, cov3d, depth_keys,
-                                                   sh_vec4);
+                                                   sh_vec4, use_bulk);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
