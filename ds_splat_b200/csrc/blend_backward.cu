@@ -5,11 +5,11 @@
 // (two block barriers per 256 entries), evaluates every entry for every pixel, reduces 9 values with 9
 // full warp reductions (45 shuffles) and issues 9 scalar atomics per warp per entry.
 //
-// Here each WARP is on its own.  Warp w of a block owns the 16x2-pixel strip (rows 2w, 2w+1) of the
-// block's tile and walks the tile's list back to front in chunks of 32 entries, with no block barrier
-// anywhere, so a strip whose pixels ended early is finished early and nobody waits for the slowest strip:
+// Here each WARP is on its own.  Every warp of a block owns a compact 8x4-pixel block of the block's tile
+// (blend_common.cuh) and walks the tile's list back to front in chunks of 32 entries, with no block barrier
+// anywhere, so a warp whose pixels ended early is finished early and nobody waits for the slowest warp:
 //   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether
-//     the splat can reach the strip at all (blend_common.cuh); a ballot gives the survivors;
+//     the splat can reach the warp's pixels at all; a ballot gives the survivors;
 //   * blend: survivors are parked in the warp's private shared-memory slice and processed one by one.
 //     exp is only evaluated for pixels with q <= ln(255 opacity) + margin, after which the reference's own
 //     test (clamped alpha < 1/255) decides.  Per pixel the nine sums are moments that need few multiplies,
@@ -18,7 +18,7 @@
 //     into the entry's row of the warp's accumulator slice;
 //   * flush: lane l, which still holds entry l's record in registers, turns its row of moments into
 //         v_xy = (a Sx + b Sy, b Sx + c Sy), v_conic = (Sxx/2, Sxy, Syy/2), v_opacity = -S0 / opacity
-//     and issues two red.global.add.v4.f32 and one scalar red: 3 vector atomics per (strip, splat) that
+//     and issues two red.global.add.v4.f32 and one scalar red: 3 vector atomics per (warp, splat) that
 //     received anything, instead of 9 scalar ones.
 //
 // The per-pixel arithmetic follows the reference: alpha clamp 0.99, 1/255 skip, opacity and visibility
@@ -78,11 +78,10 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const int x = blockIdx.x * kTile + (tid & (kTile - 1));
-    const int y = blockIdx.y * kTile + (tid >> 4);
+    const WarpPixels wp = warp_pixels(blockIdx.x, blockIdx.y, warp, lane);
+    const int x = wp.x, y = wp.y;
     const bool inside = x < W && y < H;
     const float px = (float)x + 0.5f, py = (float)y + 0.5f;
-    const float X0 = (float)(blockIdx.x * kTile), Y0 = (float)(blockIdx.y * kTile);
     const int start = ranges[tile], end = ranges[tile + 1];
 
     float Tf = 1.0f, vo0 = 0.0f, vo1 = 0.0f, vo2 = 0.0f;
@@ -94,7 +93,7 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
         vo0 = v_image[3 * pix]; vo1 = v_image[3 * pix + 1]; vo2 = v_image[3 * pix + 2];
     }
     const float bgdot = bg ? (bg[0] * vo0 + bg[1] * vo1 + bg[2] * vo2) : 0.0f;
-    // Entries after the last one any pixel of the strip blended cannot contribute.
+    // Entries after the last one any pixel of the warp blended cannot contribute.
     const int top = min(end - 1, __reduce_max_sync(0xffffffffu, fin));
     float T = Tf, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f;
 
@@ -112,8 +111,8 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             id = (u32)sorted[my_pos];
             const float4* r = records + (size_t)id * 3;
             q0 = __ldg(r); q1 = __ldg(r + 1); blue = __ldg(r + 2).x;
-            thr = __logf(255.0f * q1.y) + kStripMargin;
-            hit = strip_mask8(q0.x, q0.y, q0.z, q0.w, q1.x, thr, X0, Y0, warp, 1) != 0;
+            thr = __logf(255.0f * q1.y) + kCullMargin;
+            hit = splat_reaches_block(q0.x, q0.y, q0.z, q0.w, q1.x, thr, wp.x0, wp.y0);
         }
         u32 todo = __ballot_sync(0xffffffffu, hit);
         if (todo == 0) continue;

@@ -1,13 +1,17 @@
-// Shared by the forward and backward blend kernels: which 16x2-pixel strips of a tile can a splat reach?
+// Shared by the forward and backward blend kernels: how a tile's 256 pixels map to warps, and the test
+// "can this splat reach this warp's pixels at all?".
 //
-// A 256-thread block owns a 16x16 tile; warp w owns the strip of rows 2w and 2w+1.  A pixel receives a
-// splat only if opacity * exp(-q) >= 1/255, i.e. q <= tau = ln(255 * opacity), where
+// A 256-thread block owns a 16x16 tile.  Each warp owns a compact 8x4 block of it (not a 16x2 strip: for a
+// splat of a given size the compact shape is met about 15% less often and has more live pixels when it is
+// met).  Warp w sits at column (w & 1), row (w >> 1) of the 2x4 arrangement; lane l is pixel (l & 7, l >> 3).
+//
+// A pixel receives a splat only if opacity * exp(-q) >= 1/255, i.e. q <= tau = ln(255 * opacity), where
 // q(d) = 0.5 (a dx^2 + c dy^2) + b dx dy is the conic form at the pixel's offset d from the splat centre.
-// For each strip the exact minimum of q over the strip's pixel-centre rectangle is computed in closed
-// form (q is convex, so the minimum over a rectangle that does not contain the centre lies on one of
-// the at most two edges facing it) and compared with tau plus a margin.  The margin makes the test
-// conservative against rounding: a strip is dropped only when no pixel in it could pass the per-pixel
-// test, so results are exactly those of testing every pixel, and the per-pixel test stays in place.
+// The exact minimum of q over the warp's rectangle of pixel centres is computed in closed form (q is
+// convex, so the minimum over a rectangle that does not contain the centre lies on one of the at most
+// two edges facing it) and compared with tau plus a margin.  The margin makes the test conservative
+// against rounding: a splat is dropped only when no pixel of the warp could pass the per-pixel test, so
+// results are exactly those of testing every pixel, and the per-pixel test stays in place.
 //
 // The reference fetches and evaluates every splat of the tile's list for all 256 pixels
 // (cpp/rasterizer_kernels.cu:386-414, cpp/gsplat/backward.cu:112-145); its lists come from the 3-sigma
@@ -17,42 +21,46 @@
 
 namespace dsb {
 
-constexpr float kStripMargin = 0.02f;
+constexpr float kCullMargin = 0.02f;
+constexpr int kWarpPixelsX = 8, kWarpPixelsY = 4;
 
-// Bit w of the result is set when strip w of the tile at pixel origin (X0, Y0) may contain a pixel whose
-// q is <= thr.  (gx, gy) splat centre in pixels, (a, b, c) conic.
-__device__ __forceinline__ u32 strip_mask8(const float gx, const float gy, const float a, const float b, const float c,
-                                           const float thr, const float X0, const float Y0, const int first = 0,
-                                           const int count = 8) {
+struct WarpPixels {
+    int x, y;        // this lane's pixel
+    float x0, y0;    // pixel-coordinate origin of the warp's 8x4 block
+};
+
+__device__ __forceinline__ WarpPixels warp_pixels(const int tile_x, const int tile_y, const int warp, const int lane) {
+    WarpPixels p;
+    const int bx = tile_x * kTile + (warp & 1) * kWarpPixelsX, by = tile_y * kTile + (warp >> 1) * kWarpPixelsY;
+    p.x = bx + (lane & 7);
+    p.y = by + (lane >> 3);
+    p.x0 = (float)bx;
+    p.y0 = (float)by;
+    return p;
+}
+
+// True when some pixel centre of the 8x4 block at origin (x0, y0) may have q <= thr.
+// (gx, gy) splat centre in pixels, (a, b, c) conic.
+__device__ __forceinline__ bool splat_reaches_block(const float gx, const float gy, const float a, const float b,
+                                                    const float c, const float thr, const float x0, const float y0) {
     // Anything that is not a proper ellipse with a finite threshold is left to the per-pixel test.
-    if (!(a > 0.f && c > 0.f && a * c > b * b) || !(thr == thr)) return 0xffu;
-    const float dxl = X0 + 0.5f - gx, dxh = dxl + 15.0f;
-    const float ex = fminf(fmaxf(0.f, dxl), dxh);
-    const bool in_x = ex == 0.f;
-    const float kc = -b / c, ka = -b / a;
-    const float q_ex = 0.5f * a * ex * ex;
-    u32 mask = 0;
-#pragma unroll
-    for (int w = first; w < first + count; ++w) {
-        const float dyl = Y0 + (float)(2 * w) + 0.5f - gy, dyh = dyl + 1.0f;
-        const float ey = fminf(fmaxf(0.f, dyl), dyh);
-        const bool in_y = ey == 0.f;
-        float minq = 0.f;
-        if (!(in_x && in_y)) {
-            float q1 = 3.0e38f, q2 = 3.0e38f;
-            if (!in_x) {  // edge dx = ex, best dy on it
-                const float dy = fminf(fmaxf(kc * ex, dyl), dyh);
-                q1 = q_ex + 0.5f * c * dy * dy + b * ex * dy;
-            }
-            if (!in_y) {  // edge dy = ey, best dx on it
-                const float dx = fminf(fmaxf(ka * ey, dxl), dxh);
-                q2 = 0.5f * (a * dx * dx + c * ey * ey) + b * dx * ey;
-            }
-            minq = fminf(q1, q2);
-        }
-        if (!(minq > thr)) mask |= 1u << w;
+    if (!(a > 0.f && c > 0.f && a * c > b * b) || !(thr == thr)) return true;
+    const float dxl = x0 + 0.5f - gx, dxh = dxl + (float)(kWarpPixelsX - 1);
+    const float dyl = y0 + 0.5f - gy, dyh = dyl + (float)(kWarpPixelsY - 1);
+    const float ex = fminf(fmaxf(0.f, dxl), dxh);  // offset of the block's nearest column / row to the centre
+    const float ey = fminf(fmaxf(0.f, dyl), dyh);
+    const bool in_x = ex == 0.f, in_y = ey == 0.f;
+    if (in_x && in_y) return !(0.f > thr);
+    float q1 = 3.0e38f, q2 = 3.0e38f;
+    if (!in_x) {  // edge dx = ex, best dy on it
+        const float dy = fminf(fmaxf(-b / c * ex, dyl), dyh);
+        q1 = 0.5f * (a * ex * ex + c * dy * dy) + b * ex * dy;
     }
-    return mask;
+    if (!in_y) {  // edge dy = ey, best dx on it
+        const float dx = fminf(fmaxf(-b / a * ey, dxl), dxh);
+        q2 = 0.5f * (a * dx * dx + c * ey * ey) + b * dx * ey;
+    }
+    return !(fminf(q1, q2) > thr);
 }
 
 }  // namespace dsb

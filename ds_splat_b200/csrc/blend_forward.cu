@@ -4,16 +4,16 @@
 // one 256-thread block per 16x16 tile in lock step: rounds of 256 list entries, two block barriers per
 // round, every entry evaluated for every pixel until all 256 pixels have stopped.
 //
-// Here each WARP is on its own (as in the backward blend): warp w of a block owns the 16x2-pixel strip
-// (rows 2w, 2w+1) of the block's tile and walks the tile's depth-ordered list in chunks of 32 entries, with
-// no block barrier anywhere, so a strip stops as soon as ITS 32 pixels have stopped.
-//   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether the splat can reach the strip at
-//     all (blend_common.cuh); a ballot gives the survivors;
+// Here each WARP is on its own (as in the backward blend): every warp of a block owns a compact 8x4-pixel
+// block of the block's tile (blend_common.cuh) and walks the tile's depth-ordered list in chunks of 32
+// entries, with no block barrier anywhere, so a warp stops as soon as ITS 32 pixels have stopped.
+//   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether
+//     the splat can reach the warp's pixels at all; a ballot gives the survivors;
 //   * blend: survivors are parked in the warp's private shared-memory slice and each pixel consumes them
 //     in list order until its transmittance would fall under 1e-4.
 //
 // Per-pixel arithmetic (order of operations, 0.999 alpha clamp, 1/255 skip, no background term) is the
-// reference's and the strip test is conservative, so images agree to rounding and final_idx exactly.
+// reference's and the cull test is conservative, so images agree to rounding and final_idx exactly.
 #include "blend_common.cuh"
 
 namespace dsb {
@@ -55,12 +55,11 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const int x = blockIdx.x * kTile + (tid & (kTile - 1));
-    const int y = blockIdx.y * kTile + (tid >> 4);
+    const WarpPixels wp = warp_pixels(blockIdx.x, blockIdx.y, warp, lane);
+    const int x = wp.x, y = wp.y;
     const bool inside = x < W && y < H;
     const int start = ranges[tile], end = ranges[tile + 1];
     const float pxf = x + 0.5f, pyf = y + 0.5f;
-    const float X0 = (float)(blockIdx.x * kTile), Y0 = (float)(blockIdx.y * kTile);
 
     float T = 1.0f, c0 = 0.0f, c1 = 0.0f, c2 = 0.0f;
     int last = 0;
@@ -83,8 +82,8 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
 #endif
         bool hit = false;
         if (cur.have) {
-            const float thr = __logf(255.0f * cur.q1.y) + kStripMargin;
-            hit = strip_mask8(cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w, cur.q1.x, thr, X0, Y0, warp, 1) != 0;
+            const float thr = __logf(255.0f * cur.q1.y) + kCullMargin;
+            hit = splat_reaches_block(cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w, cur.q1.x, thr, wp.x0, wp.y0);
         }
         const u32 todo = __ballot_sync(0xffffffffu, hit);
         if (todo == 0) continue;
