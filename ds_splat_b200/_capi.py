@@ -26,7 +26,7 @@ EXPORTS = (
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
     "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
-    "dsb_sort_pairs_static",
+    "dsb_sort_pairs_static", "dsb_tile_marks_bytes",
 )
 STATIC_SORT_MAX_ITEMS = 1 << 21
 
@@ -63,6 +63,8 @@ def lib():
         l.dsb_plan_workspace_bytes.argtypes = [C.c_int32]
         l.dsb_sort_workspace_bytes.restype = C.c_int64
         l.dsb_sort_workspace_bytes.argtypes = [C.c_int64]
+        l.dsb_tile_marks_bytes.restype = C.c_int64
+        l.dsb_tile_marks_bytes.argtypes = [C.c_int32, C.c_int32]
         l.dsb_stage_name.restype = C.c_char_p
         l.dsb_stage_name.argtypes = [C.c_int32]
         l.dsb_stage_count.restype = C.c_int32
@@ -79,8 +81,8 @@ def lib():
             "dsb_blend_forward": [CAM, P, P, P, P, P, P, P],
             "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P],
             "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
-            "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 8 + [I64, C.POINTER(C.c_int64), P],
-            "dsb_forward_render": [CAM, I32, I64] + [P] * 7 + [I64] + [P] * 5,
+            "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
+            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 5,
             "dsb_backward": [CAM, I32] + [P] * 12 + [P] * 8 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
         }

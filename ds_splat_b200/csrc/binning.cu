@@ -99,18 +99,10 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
 // One warp per 32 depth-ordered splats: their pair ranges are consecutive, so the warp walks the
 // concatenated range 32 positions at a time; each lane finds the owning splat by a 5-step search over
 // the lanes' running counts and writes one packed pair.  All stores are consecutive 8-byte lanes.
-// With HIST the kernel also counts the digits the following tile sort will look at (it knows every tile id
-// it writes), which spares that sort a pass over the list.
-template <bool HIST>
 __global__ void __launch_bounds__(256)
 emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_last, const float4* __restrict__ records,
                   const int32_t* __restrict__ tiles, const u64* __restrict__ depth_keys_sorted,
-                  const u32* __restrict__ offsets, u64* __restrict__ pairs, const SortPlan plan, u32* __restrict__ hist) {
-    __shared__ u32 s_hist[HIST ? 4 : 1][256];
-    if (HIST) {
-        for (int i = threadIdx.x; i < plan.npass * 256; i += 256) (&s_hist[0][0])[i] = 0;
-        __syncthreads();
-    }
+                  const u32* __restrict__ offsets, u64* __restrict__ pairs) {
     const int lane = threadIdx.x & 31;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;  // position in depth order; warps are aligned to 32
     u32 id = 0, c = 0, off = 0;
@@ -152,35 +144,111 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
         const int o_x0 = __shfl_sync(0xffffffffu, x0, owner);
         const int o_y0 = __shfl_sync(0xffffffffu, y0, owner);
         const int o_w = __shfl_sync(0xffffffffu, w, owner);
-        u64 pair = 0;
-        bool wrote = false;
         if (p < total) {
             const u32 r = p - o_excl;
             const u32 ry = r / (u32)o_w;
             const u32 tile = (u32)(o_y0 + (int)ry) * (u32)tiles_x + (u32)o_x0 + (r - ry * (u32)o_w);
             const u32 dst = warp_base + p;
-            pair = ((u64)tile << 32) | o_id;
-            wrote = dst < k;
-            if (wrote) pairs[dst] = pair;
+            if (dst < k) pairs[dst] = ((u64)tile << 32) | o_id;
         }
-        if (HIST) {
-            // Lowest digit: consecutive lanes hold consecutive tile ids, so the counters rarely collide.
-            if (wrote) atomicAdd(&s_hist[0][sort_digit(pair, plan.shift[0], plan.mask[0], plan.flip[0])], 1u);
-            // Higher digits are nearly constant inside a warp: one atomic per group of equal digits.
-            for (int q = 1; q < plan.npass; ++q) {
-                const u32 d = sort_digit(pair, plan.shift[q], plan.mask[q], plan.flip[q]);
-                const u32 m = warp_peers(d, wrote, plan.bits[q]);
-                if (wrote && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[q][d], (u32)__popc(m));
+    }
+}
+
+// From the corner marks to the tile layout, one block: prefix sums along x, then along y, turn the grid
+// into pairs-per-tile; an exclusive scan in tile order gives the ranges (tile t owns sorted positions
+// [ranges[t], ranges[t+1])), and every tile adds its count to the sort's digit counters.
+constexpr int kLayoutThreads = 1024;
+__global__ void __launch_bounds__(kLayoutThreads)
+tile_layout_kernel(int* __restrict__ marks, const int tiles_x, const int tiles_y, const SortPlan plan,
+                   u32* __restrict__ hist, int32_t* __restrict__ ranges, const int use_smem) {
+    extern __shared__ int s_grid[];
+    __shared__ u32 s_hist[4][256];
+    __shared__ u32 s_wsum[32];
+    __shared__ u32 s_carry;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int stride = tiles_x + 1, rows = tiles_y + 1;
+    for (int i = tid; i < 4 * 256; i += kLayoutThreads) (&s_hist[0][0])[i] = 0;
+    // The grid is worked on in shared memory when it fits (up to about 4K images), else in place.
+    int* diff = marks;
+    if (use_smem) {
+        for (int i = tid; i < rows * stride; i += kLayoutThreads) s_grid[i] = marks[i];
+        diff = s_grid;
+    }
+    __syncthreads();
+    // along x: one warp per row, 32 columns at a time with a running carry
+    for (int y = warp; y < rows; y += kLayoutThreads / 32) {
+        int carry = 0;
+        for (int x = lane; x - lane < stride; x += 32) {
+            int v = x < stride ? diff[y * stride + x] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            v += carry;
+            if (x < stride) diff[y * stride + x] = v;
+            carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    // along y: one thread per column, eight rows in flight at a time
+    for (int x = tid; x < stride; x += kLayoutThreads) {
+        int acc = 0;
+        for (int y0 = 0; y0 < rows; y0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = (y0 + q < rows) ? diff[(y0 + q) * stride + x] : 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                acc += v[q];
+                if (y0 + q < rows) diff[(y0 + q) * stride + x] = acc;
             }
         }
     }
-    if (HIST) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < plan.npass * 256; i += 256) {
-            const u32 c = (&s_hist[0][0])[i];
-            if (c) atomicAdd(hist + i, c);
+    __syncthreads();
+    // exclusive scan of the per-tile counts in tile order: every thread owns a run of consecutive tiles
+    const int num_tiles = tiles_x * tiles_y;
+    const int per_thread = (num_tiles + kLayoutThreads - 1) / kLayoutThreads;
+    const int t_begin = min(tid * per_thread, num_tiles), t_end = min(t_begin + per_thread, num_tiles);
+    u32 mine = 0;
+    for (int t = t_begin; t < t_end; ++t) {
+        const int ty = t / tiles_x, tx = t - ty * tiles_x;
+        const u32 c = (u32)max(diff[ty * stride + tx], 0);
+        mine += c;
+        if (c && hist) {
+            const u64 key = (u64)(u32)t << 32;
+            for (int q = 0; q < plan.npass && q < 4; ++q)
+                atomicAdd(&s_hist[q][sort_digit(key, plan.shift[q], plan.mask[q], plan.flip[q])], c);
         }
     }
+    u32 incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u32 v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        u32 w = s_wsum[lane], wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u32 v = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += v;
+        }
+        s_wsum[lane] = wi - w;
+        if (lane == 31) s_carry = wi;  // grand total
+    }
+    __syncthreads();
+    u32 running = s_wsum[warp] + incl - mine;
+    for (int t = t_begin; t < t_end; ++t) {
+        const int ty = t / tiles_x, tx = t - ty * tiles_x;
+        ranges[t] = (int32_t)running;
+        running += (u32)max(diff[ty * stride + tx], 0);
+    }
+    if (tid == 0) ranges[num_tiles] = (int32_t)s_carry;
+    if (hist)
+        for (int i = tid; i < plan.npass * 256 && i < 4 * 256; i += kLayoutThreads) hist[i] = (&s_hist[0][0])[i];
 }
 
 // ranges[t] = number of sorted items whose tile id (high 32 bits, signed) is < t, t = 0..T.
@@ -271,20 +339,34 @@ int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_key
 }
 
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
-                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, const SortPlan* plan, u32* hist,
-                cudaStream_t s) {
+                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s) {
     if (n == 0 || k == 0) return DSB_OK;
     DSB_REQUIRE(records && tiles && depth_keys_sorted && offsets && pairs, "emit: null pointer");
     DSB_REQUIRE(k < DSB_MAX_PAIRS, "emit: too many pairs");
-    const float4* rec4 = reinterpret_cast<const float4*>(records);
-    if (hist && plan && plan->npass <= 4)
-        emit_pairs_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last, rec4, tiles,
-                                                               depth_keys_sorted, offsets, pairs, *plan, hist);
-    else {
-        DSB_REQUIRE(!hist, "emit: fused digit counting supports at most 4 passes");
-        emit_pairs_kernel<false><<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last, rec4, tiles,
-                                                                depth_keys_sorted, offsets, pairs, SortPlan{}, nullptr);
-    }
+    emit_pairs_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, (u32)k, cp.tiles_x, cp.drop_last,
+                                                     reinterpret_cast<const float4*>(records), tiles, depth_keys_sorted,
+                                                     offsets, pairs);
+    DSB_LAUNCH_CHECK();
+    return DSB_OK;
+}
+
+int64_t tile_marks_bytes(int H, int W) {
+    const int64_t tx = (W + kTile - 1) / kTile, ty = (H + kTile - 1) / kTile;
+    return align256((tx + 1) * (ty + 1) * 4);
+}
+
+// tile_marks: the grid the preprocess kernel filled (destroyed here); hist: the tile sort's digit counters
+// (plan.npass rows of 256, may be null when there is nothing to sort); ranges: [tiles + 1].
+int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
+                       cudaStream_t s) {
+    DSB_REQUIRE(tile_marks && ranges, "tile_layout: null pointer");
+    DSB_REQUIRE(!hist || plan.npass <= 4, "tile_layout: at most 4 digit passes");
+    const size_t grid_bytes = (size_t)(cp.tiles_x + 1) * (cp.tiles_y + 1) * sizeof(int);
+    const int use_smem = grid_bytes <= 200 * 1024;
+    if (use_smem && grid_bytes > 40 * 1024)
+        DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
+    tile_layout_kernel<<<1, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(tile_marks, cp.tiles_x, cp.tiles_y, plan, hist,
+                                                                           ranges, use_smem);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -124,6 +124,9 @@ int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls)
 
 int64_t dsb_plan_workspace_bytes(int32_t n) { return plan_workspace_bytes(n < 0 ? 0 : n); }
 int64_t dsb_sort_workspace_bytes(int64_t k) { return sort_workspace_bytes(k < 0 ? 0 : k); }
+int64_t dsb_tile_marks_bytes(int32_t image_height, int32_t image_width) {
+    return (image_height > 0 && image_width > 0) ? tile_marks_bytes(image_height, image_width) : 0;
+}
 
 int dsb_preprocess(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
                    const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
@@ -133,7 +136,8 @@ int dsb_preprocess(const DsbCamera* cam, int32_t n, const float* means3d, const 
     DSB_REQUIRE(n >= 0, "n must be non-negative");
     StageScope scope(kStagePreprocess, (cudaStream_t)stream);
     return launch_preprocess(cp, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records,
-                             radii, tiles_touched, cov3d, reinterpret_cast<u64*>(depth_keys), (cudaStream_t)stream);
+                             radii, tiles_touched, cov3d, reinterpret_cast<u64*>(depth_keys), nullptr,
+                             (cudaStream_t)stream);
 }
 
 int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched, uint64_t* depth_keys,
@@ -150,7 +154,7 @@ int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* reco
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0 && k >= 0, "n and k must be non-negative");
     return launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
-                       reinterpret_cast<u64*>(pairs), nullptr, nullptr, (cudaStream_t)stream);
+                       reinterpret_cast<u64*>(pairs), (cudaStream_t)stream);
 }
 
 int dsb_sort_pairs(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit, void* workspace,
@@ -212,26 +216,37 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
 int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
                      const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
                      float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
-                     uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
-                     int64_t* k_host, void* stream) {
-    int rc = dsb_preprocess(cam, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records,
-                            radii, tiles_touched, cov3d, depth_keys, stream);
-    if (rc != DSB_OK) return rc;
-    return dsb_plan_pairs(cam, n, tiles_touched, depth_keys, depth_keys_alt, offsets, workspace, workspace_bytes, k_host,
-                          stream);
+                     uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* workspace,
+                     int64_t workspace_bytes, int64_t* k_host, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    DSB_REQUIRE(tile_marks, "forward_plan: tile_marks is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    {
+        StageScope scope(kStagePreprocess, s);
+        DSB_CUDA_CHECK(cudaMemsetAsync(tile_marks, 0, (size_t)tile_marks_bytes(cp.H, cp.W), s));
+        const int rc = launch_preprocess(cp, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp,
+                                         records, radii, tiles_touched, cov3d, reinterpret_cast<u64*>(depth_keys),
+                                         tile_marks, s);
+        if (rc != DSB_OK) return rc;
+    }
+    return launch_plan(cp, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
+                       offsets, workspace, workspace_bytes, k_host, s);
 }
 
 int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
                        const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, uint64_t* pairs_alt,
-                       void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T,
-                       int32_t* final_idx, void* stream) {
+                       int32_t* tile_marks, void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image,
+                       float* final_T, int32_t* final_idx, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
-    // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The emit kernel counts
-    // the sort's digits while it writes the pairs, so the sort itself is just its passes.
+    // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The preprocess kernel marked
+    // every splat's tile rectangle in a small grid; one block turns that grid into the tile ranges and the sort's
+    // digit counts, so nothing reads the K pairs except the sort passes themselves.
     int tile_bits = 1;
     while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
     DSB_REQUIRE(k < DSB_MAX_PAIRS, "too many pairs");
+    DSB_REQUIRE(tile_marks && ranges, "forward_render: null tile_marks or ranges");
     DSB_REQUIRE(k <= 1 || (pairs && pairs_alt && workspace), "forward_render: null pair buffers or workspace");
     const SortPlan plan = make_sort_plan(32, 32 + tile_bits, false);
     u32* hist = nullptr;
@@ -241,7 +256,12 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
         rc = sort_begin(k, plan, workspace, workspace_bytes, &hist, s);
         if (rc != DSB_OK) return rc;
         rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
-                         reinterpret_cast<u64*>(pairs), &plan, hist, s);
+                         reinterpret_cast<u64*>(pairs), s);
+    }
+    if (rc != DSB_OK) return rc;
+    {
+        StageScope scope(kStageRanges, s);
+        rc = launch_tile_layout(cp, tile_marks, plan, hist, ranges, s);
     }
     if (rc != DSB_OK) return rc;
     int in_alt = 0;
@@ -252,11 +272,6 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
         if (rc != DSB_OK) return rc;
         if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
     }
-    {
-        StageScope scope(kStageRanges, s);
-        rc = launch_ranges(reinterpret_cast<const u64*>(pairs), k, cp.H, cp.W, ranges, s);
-    }
-    if (rc != DSB_OK) return rc;
     StageScope scope(kStageBlendForward, s);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, s);
 }

@@ -96,7 +96,8 @@ constexpr u32 kSpinLimit = 1u << 22;
 // ---- launchers (one per stage file) -----------------------------------------------------------------
 int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
                       const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
-                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, cudaStream_t s);
+                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, int* tile_marks,
+                      cudaStream_t s);
 
 // Radix-sort pass layout: which bits each pass looks at.  flip is XORed into the digit (sign bit of signed keys).
 constexpr int kMaxSortPasses = 8;
@@ -140,10 +141,13 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
 int64_t plan_workspace_bytes(int n);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
-// plan/hist: when hist is not null the kernel also counts the sort digits of every pair it writes.
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
-                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, const SortPlan* plan, u32* hist,
-                cudaStream_t s);
+                const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s);
+// Grid of rectangle corner marks filled by the preprocess kernel; launch_tile_layout turns it into tile ranges
+// and the tile sort's digit counts.
+int64_t tile_marks_bytes(int H, int W);
+int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
+                       cudaStream_t s);
 int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
 int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);
 

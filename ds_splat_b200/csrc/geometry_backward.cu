@@ -25,7 +25,11 @@ constexpr int kThreads = 128;
 constexpr int kWarps = kThreads / 32;
 constexpr int kShStride = 49;  // odd stride: conflict-free row-per-lane writes
 
-__device__ __forceinline__ void put(float* p, float v, int accumulate) { *p = accumulate ? *p + v : v; }
+// In accumulate mode a zero contribution costs nothing: no load, no store (most splats are outside any given view).
+__device__ __forceinline__ void put(float* p, float v, int accumulate) {
+    if (!accumulate) *p = v;
+    else if (v != 0.f) *p += v;
+}
 
 __global__ void __launch_bounds__(kThreads)
 geometry_backward_kernel(const CamParams cp, const int n, const float* __restrict__ means, const float* __restrict__ scales,
@@ -209,8 +213,13 @@ geometry_backward_kernel(const CamParams cp, const int n, const float* __restric
         if (v_rots) {
             float4* p = reinterpret_cast<float4*>(v_rots + (size_t)i * 4);
             float4 o = make_float4(vq0, vq1, vq2, vq3);
-            if (accumulate) { const float4 c = *p; o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w; }
-            *p = o;
+            if (!accumulate) {
+                *p = o;
+            } else if (vq0 != 0.f || vq1 != 0.f || vq2 != 0.f || vq3 != 0.f) {
+                const float4 c = *p;
+                o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                *p = o;
+            }
         }
         if (v_cov3d) {
             float* p = v_cov3d + (size_t)i * 6;
@@ -228,7 +237,8 @@ geometry_backward_kernel(const CamParams cp, const int n, const float* __restric
             for (int k = lane; k < total; k += 32) {
                 const int r = k / row_floats;
                 const float val = s_sh[warp][r * kShStride + (k - r * row_floats)];
-                out[k] = accumulate ? out[k] + val : val;
+                if (!accumulate) out[k] = val;
+                else if (val != 0.f) out[k] += val;
             }
         }
     }

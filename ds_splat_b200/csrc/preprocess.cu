@@ -54,7 +54,7 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
                   const float* __restrict__ scales, const float* __restrict__ rots,
                   const float* __restrict__ cov3d_precomp, float4* __restrict__ records, int32_t* __restrict__ radii,
                   int32_t* __restrict__ tiles, float* __restrict__ cov3d, u64* __restrict__ depth_keys,
-                  const int sh_vec4, const int use_bulk) {
+                  const int sh_vec4, const int use_bulk, int* __restrict__ tile_marks) {
     extern __shared__ __align__(16) float4 dyn4[];
     __shared__ float s_cam[31];      // view rows 0..2 (12), projection (16), camera centre (3)
     __shared__ __align__(16) float s_means[kThreads * 3];
@@ -244,6 +244,17 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
         // still reports its radius but, because the negative depth bits spill over the tile id of its
         // keys, never draws it; here it simply gets no pairs.
         count = (x1 - x0) * (y1 - y0) * (radius > 0 && tz > 0.f);
+        // Corner marks of the tile rectangle (+1, -1, -1, +1) in a (tiles_y + 1) x (tiles_x + 1) grid: its 2-D
+        // prefix sum is the number of (tile, splat) pairs per tile, from which tile ranges and the tile sort's
+        // digit counts follow without a pass over the pairs.  Fire-and-forget reductions, hidden behind the
+        // kernel's memory traffic.
+        if (tile_marks && count > 0 && !(cp.drop_last && i == n - 1)) {
+            const int stride = cp.tiles_x + 1;
+            atomicAdd(tile_marks + y0 * stride + x0, 1);
+            atomicAdd(tile_marks + y0 * stride + x1, -1);
+            atomicAdd(tile_marks + y1 * stride + x0, -1);
+            atomicAdd(tile_marks + y1 * stride + x1, 1);
+        }
 
         // Conic = inverse of the dilated 2-D covariance.
         const float det_inv = 1.0f / (det + 1e-6f);
@@ -276,7 +287,8 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
 
 int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
                       const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
-                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, cudaStream_t s) {
+                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, int* tile_marks,
+                      cudaStream_t s) {
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(means && opac && records && radii && tiles && depth_keys, "preprocess: null required pointer");
     DSB_REQUIRE(colors_precomp || shs, "preprocess: need shs or colors_precomp");
@@ -300,7 +312,7 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
     const int blocks = (n + kThreads - 1) / kThreads;
     preprocess_kernel<<<blocks, kThreads, dyn, s>>>(cp, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp,
                                                    reinterpret_cast<float4*>(records), radii, tiles, cov3d, depth_keys,
-                                                   sh_vec4, use_bulk);
+                                                   sh_vec4, use_bulk, tile_marks);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -124,7 +124,8 @@ class ViewRenderer:
             f32 = dict(dtype=torch.float32, device=self.dev)
             self.img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
                              torch.empty((h, w), dtype=torch.int32, device=self.dev),
-                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev))
+                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev),
+                             torch.empty(int(self.lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=self.dev))
         return self.img[key]
 
     def _camera(self, cam: CameraTensors):
@@ -138,22 +139,23 @@ class ViewRenderer:
         c, keep = self._camera(cam)
         stream = capi.stream_ptr()
         k = C.c_int64(0)
+        image, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
         capi.check(lib.dsb_forward_plan(
             C.byref(c), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
             p["scales"].data_ptr(), p["rotations"].data_ptr(), None, self.records.data_ptr(), self.radii.data_ptr(),
             self.tiles.data_ptr(), self.cov3d.data_ptr(), self.depth_keys[0].data_ptr(), self.depth_keys[1].data_ptr(),
-            self.offsets.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes, C.byref(k), stream))
+            self.offsets.data_ptr(), tile_marks.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes, C.byref(k), stream))
         k = int(k.value)
         if self.pairs is None or self.pairs.shape[1] < k:
             cap = max(int(k * 1.25), 1024)
             self.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
             self.sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
             self.sort_ws = torch.empty(self.sort_bytes, dtype=torch.uint8, device=self.dev)
-        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
         capi.check(lib.dsb_forward_render(
             C.byref(c), self.n, k, self.records.data_ptr(), self.tiles.data_ptr(), self.depth_keys[0].data_ptr(),
-            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(), self.sort_ws.data_ptr(),
-            self.sort_bytes, ranges.data_ptr(), image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), stream))
+            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(), tile_marks.data_ptr(),
+            self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(), image.data_ptr(), final_t.data_ptr(),
+            final_idx.data_ptr(), stream))
         self.last_k = k
         self._last_cam = (c, keep, cam)
         return image
@@ -162,7 +164,7 @@ class ViewRenderer:
         """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
         capi, lib, p = self._capi, self.lib, self.p
         c, keep, cam = self._last_cam
-        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        image, final_t, final_idx, ranges, _marks = self._image_buffers(cam.H, cam.W)
         g = grads.views
         capi.check(lib.dsb_backward(
             C.byref(c), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),

@@ -125,6 +125,7 @@ class DsRasterizerFunction(torch.autograd.Function):
             cov3d = cov_3d_precomp if cov_3d_precomp is not None else torch.empty((n, 6), **f32)
             depth_keys = torch.empty((2, n), dtype=torch.int64, device=dev)
             offsets = torch.empty(n, dtype=torch.int32, device=dev)
+            tile_marks = torch.empty(int(lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=dev)
             plan_bytes = int(lib.dsb_plan_workspace_bytes(n))
             plan_ws = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
             k = C.c_int64(0)
@@ -132,7 +133,7 @@ class DsRasterizerFunction(torch.autograd.Function):
                 C.byref(cam), n, _capi.ptr(means_3d), _capi.ptr(shs), _capi.ptr(colors_precomp), _capi.ptr(opacities),
                 _capi.ptr(scales), _capi.ptr(rotations), _capi.ptr(cov_3d_precomp), records.data_ptr(), radii.data_ptr(),
                 tiles.data_ptr(), cov3d.data_ptr(), depth_keys[0].data_ptr(), depth_keys[1].data_ptr(),
-                offsets.data_ptr(), plan_ws.data_ptr(), plan_bytes, C.byref(k), stream))
+                offsets.data_ptr(), tile_marks.data_ptr(), plan_ws.data_ptr(), plan_bytes, C.byref(k), stream))
             k = int(k.value)
 
             pairs = torch.empty((2, max(k, 1)), dtype=torch.int64, device=dev)
@@ -144,7 +145,8 @@ class DsRasterizerFunction(torch.autograd.Function):
             final_idx = torch.empty((h, w), dtype=torch.int32, device=dev)
             _capi.check(lib.dsb_forward_render(
                 C.byref(cam), n, k, records.data_ptr(), tiles.data_ptr(), depth_keys[0].data_ptr(), offsets.data_ptr(),
-                pairs[0].data_ptr(), pairs[1].data_ptr(), sort_ws.data_ptr(), sort_bytes, ranges.data_ptr(),
+                pairs[0].data_ptr(), pairs[1].data_ptr(), tile_marks.data_ptr(), sort_ws.data_ptr(), sort_bytes,
+                ranges.data_ptr(),
                 image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), stream))
             sorted_pairs = pairs[0][:k]
 

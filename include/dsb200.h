@@ -83,6 +83,9 @@ int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls)
 int64_t dsb_plan_workspace_bytes(int32_t n);
 /* Scratch for dsb_sort_pairs / dsb_sort_by_keys over k items (excludes the alternate buffers). */
 int64_t dsb_sort_workspace_bytes(int64_t k);
+/* Size of the tile_marks grid shared by dsb_forward_plan and dsb_forward_render:
+ * (tiles_y + 1) x (tiles_x + 1) int32, rounded up to 256 bytes. */
+int64_t dsb_tile_marks_bytes(int32_t image_height, int32_t image_width);
 
 /* ---- stage (a) ------------------------------------------------------------------------------
  * Replaces rasterizer_forward_preprocessing + rasterizer_preprocessing_kernel
@@ -183,18 +186,26 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
  * dsb_forward_plan   = dsb_preprocess + dsb_plan_pairs            (first half of
  *                      rasterizer_forward_deepsense, cpp/rasterizer_torch.cu:170-196)
  * dsb_forward_render = dsb_emit_pairs + dsb_sort_pairs + dsb_identify_tile_ranges + dsb_blend_forward
- *                      (second half, :196-207); sorted pairs end in `pairs` (copied back if needed)
+ *                      (second half, :196-207); sorted pairs end in `pairs` (copied back if needed).
+ *                      Same results as the four calls, but the tile ranges and the sort's digit counts come
+ *                      from tile_marks -- a small grid in which dsb_forward_plan's preprocess kernel marked the
+ *                      corners of every splat's tile rectangle and whose 2-D prefix sum is the number of pairs
+ *                      per tile -- instead of passes over the pairs.  tile_marks (dsb_tile_marks_bytes) is
+ *                      written by dsb_forward_plan and consumed (destroyed) by dsb_forward_render;
+ *                      workspace: dsb_sort_workspace_bytes(k)
  * dsb_backward       = dsb_blend_backward + dsb_geometry_backward (rasterizer_backward_deepsense,
  *                      cpp/rasterizer_torch.cu:263-316); grad_acc is zeroed inside. */
 int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs,
                      const float* colors_precomp, const float* opacities, const float* scales,
                      const float* rotations, const float* cov3d_precomp, float* records, int32_t* radii,
                      int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys, uint64_t* depth_keys_alt,
-                     uint32_t* offsets, void* workspace, int64_t workspace_bytes, int64_t* k_host, void* stream);
+                     uint32_t* offsets, int32_t* tile_marks, void* workspace, int64_t workspace_bytes,
+                     int64_t* k_host, void* stream);
 int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records,
                        const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
-                       uint64_t* pairs, uint64_t* pairs_alt, void* workspace, int64_t workspace_bytes,
-                       int32_t* ranges, float* image, float* final_T, int32_t* final_idx, void* stream);
+                       uint64_t* pairs, uint64_t* pairs_alt, int32_t* tile_marks, void* workspace,
+                       int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T, int32_t* final_idx,
+                       void* stream);
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,

@@ -162,3 +162,29 @@ def test_view_renderer_accumulates_like_autograd():
     torch.cuda.synchronize()
     for name, key in (("means", "means3d"), ("shs", "shs"), ("opacities", "opacities"), ("scales", "scales"), ("rotations", "rotations")):
         assert _rel(grads.views[key].cpu().numpy(), p[name].grad.cpu().numpy()) < 1e-3, name
+
+
+def test_fused_render_matches_stage_calls():
+    """dsb_forward_render derives tile ranges and sort digit counts from a per-tile count grid; its sorted list,
+    ranges and image must equal those of the individual stage calls bit for bit (ragged image size on purpose)."""
+    sc = scenes.headline(n=60_000, seed=93, W=500, H=297, focal=300.0)
+    view = sc.views[0]
+    t = scene_tensors(sc)
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
+    k = r.last_k
+    fused_pairs = r.pairs[0][:k].clone()
+    _, _, _, fused_ranges, _ = r._image_buffers(view.H, view.W)
+    from conftest import capi_camera
+    cam, keep = capi_camera(view)
+    records, radii, tiles, cov3d, dk = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    offsets, k2 = _capi.plan_pairs(cam, tiles, dk)
+    pairs = _capi.emit_pairs(cam, k2, records, tiles, dk, offsets)
+    bits = max(1, int(np.ceil(np.log2(view.num_tiles))))
+    sp = _capi.sort_pairs(pairs, 32, 32 + bits)
+    ranges = _capi.identify_tile_ranges(sp, view.H, view.W)
+    img2, _, _ = _capi.blend_forward(cam, records, sp, ranges)
+    assert k == k2 and k > 0
+    assert torch.equal(fused_pairs, sp)
+    assert torch.equal(fused_ranges, ranges)
+    assert torch.equal(image, img2)
