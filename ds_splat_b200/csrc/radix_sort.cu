@@ -24,7 +24,10 @@ namespace dsb {
 
 namespace {
 
-constexpr int kThreads = 256;
+#ifndef DSB_SORT_THREADS
+#define DSB_SORT_THREADS 256
+#endif
+constexpr int kThreads = DSB_SORT_THREADS;   // 256 or 512; the first 256 threads also own one digit each
 constexpr int kWarps = kThreads / 32;
 #ifndef DSB_SORT_ITEMS
 #define DSB_SORT_ITEMS 16
@@ -87,6 +90,9 @@ __device__ __forceinline__ u32 block_exclusive_scan_256(u32 v, u32* s_warp_sums,
     return prefix + incl - v;
 }
 
+#ifndef DSB_SORT_GROUP
+#define DSB_SORT_GROUP 4  // items whose ranking steps are overlapped (divides the items per thread)
+#endif
 #ifndef DSB_SORT_MIN_BLOCKS
 #define DSB_SORT_MIN_BLOCKS 3  // caps registers at 80: three resident blocks per SM beat two with more registers
 #endif
@@ -124,54 +130,60 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
     }
 
     // Rank inside the warp: lanes holding the same digit find each other (warp_peers); the lowest of them
-    // bumps the warp's counter for that digit by the group size.  The peer masks of four items are worked
-    // out together so that their latencies overlap; the counter updates stay in item order.
+    // bumps the warp's counter for that digit by the group size with a shared-memory atomic, whose old value
+    // is the number of equal digits among the warp's earlier items.  Items are handled in groups: first all
+    // peer masks, then the atomics in item order (a warp barrier between two of them keeps that order), and
+    // only then the broadcasts of the old values -- so no item waits for the previous item's round trip.
     u32 rank[kItems];
     const u32 lanemask_lt = (1u << lane) - 1u;
+    constexpr int kGroup = DSB_SORT_GROUP;
 #pragma unroll
-    for (int i0 = 0; i0 < kItems; i0 += 4) {
-        u32 m[4];
+    for (int i0 = 0; i0 < kItems; i0 += kGroup) {
+        u32 m[kGroup], before[kGroup];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kGroup; ++j) {
             const bool valid = wbase + 32 * (i0 + j) + lane < n;
             const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
             m[j] = warp_peers(d, valid, nbits);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kGroup; ++j) {
             const bool valid = wbase + 32 * (i0 + j) + lane < n;
             const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
-            const u32 lower = m[j] & lanemask_lt;
-            u32 before = 0;
-            if (lower == 0 && valid) {
-                before = s_wcnt[warp][d];
-                s_wcnt[warp][d] = before + (u32)__popc(m[j]);
-            }
-            before = __shfl_sync(0xffffffffu, before, valid ? __ffs(m[j]) - 1 : lane);
-            rank[i0 + j] = before + (u32)__popc(lower);
+            before[j] = 0;
+            if ((m[j] & lanemask_lt) == 0 && valid) before[j] = atomicAdd(&s_wcnt[warp][d], (u32)__popc(m[j]));
             __syncwarp();
+        }
+#pragma unroll
+        for (int j = 0; j < kGroup; ++j) {
+            const bool valid = wbase + 32 * (i0 + j) + lane < n;
+            const u32 b = __shfl_sync(0xffffffffu, before[j], valid ? __ffs(m[j]) - 1 : lane);
+            rank[i0 + j] = b + (u32)__popc(m[j] & lanemask_lt);
         }
     }
     __syncthreads();
 
-    // Thread d owns digit d: order the warps, publish the block's count, find the digit's first slot.
+    // Thread d (d < 256) owns digit d: order the warps, publish the block's count, find the digit's first slot.
+    const bool owner = tid < kRadix;
     u32 total = 0;
+    volatile u32* my_status = lookback + (size_t)tile * kRadix + (owner ? tid : 0);
+    if (owner) {
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const u32 c = s_wcnt[w][tid];
-        s_wcnt[w][tid] = total;
-        total += c;
+        for (int w = 0; w < kWarps; ++w) {
+            const u32 c = s_wcnt[w][tid];
+            s_wcnt[w][tid] = total;
+            total += c;
+        }
+        *my_status = total | (tile == 0 ? kFlagInclusive : kFlagAggregate);
     }
-    volatile u32* my_status = lookback + (size_t)tile * kRadix + tid;
-    *my_status = total | (tile == 0 ? kFlagInclusive : kFlagAggregate);
 
     const u32 dstart = block_exclusive_scan_256(total, s_wsum, tid);
-    const u32 gstart = block_exclusive_scan_256(hist[tid], s_wsum, tid);
-    s_dstart[tid] = dstart;
+    const u32 gstart = block_exclusive_scan_256(owner ? hist[tid] : 0u, s_wsum, tid);
+    if (owner) s_dstart[tid] = dstart;
 
     // Decoupled look-back over earlier tiles for this digit.
     u32 earlier = 0;
-    if (tile > 0) {
+    if (tile > 0 && owner) {
         int p = (int)tile - 1;
         u32 polls = 0;
         while (p >= 0) {
@@ -187,7 +199,7 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
         }
         *my_status = ((earlier + total) & kValueMask) | kFlagInclusive;
     }
-    s_glob[tid] = gstart + earlier - dstart;
+    if (owner) s_glob[tid] = gstart + earlier - dstart;
     __syncthreads();
 
     // Scatter into block-sorted order in shared memory, then stream out: consecutive slots of one
