@@ -94,92 +94,124 @@ __device__ __forceinline__ u32 block_exclusive_scan_256(u32 v, u32* s_warp_sums,
 #define DSB_SORT_GROUP 4  // items whose ranking steps are overlapped (divides the items per thread)
 #endif
 #ifndef DSB_SORT_MIN_BLOCKS
-#define DSB_SORT_MIN_BLOCKS 3  // caps registers at 80: three resident blocks per SM beat two with more registers
+#define DSB_SORT_MIN_BLOCKS 4
 #endif
-template <bool HAS_VALS>
-__global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
-onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
-                const u32 n, const int shift, const int nbits, const u32 mask, const u32 flip, const u32* __restrict__ hist,
-                u32* __restrict__ tile_counter, u32* __restrict__ lookback, int* __restrict__ status) {
-    extern __shared__ __align__(16) unsigned char dyn[];
-    u64* s_keys = reinterpret_cast<u64*>(dyn);                         // [4096]
-    u32* s_vals = reinterpret_cast<u32*>(dyn + kTileItems * sizeof(u64));  // [4096] when HAS_VALS
-    __shared__ u32 s_wcnt[kWarps][kRadix];   // per-warp digit counts, later per-warp digit offsets
-    __shared__ u32 s_dstart[kRadix];         // first slot of each digit inside the block's sorted tile
-    __shared__ u32 s_glob[kRadix];           // global position of slot p with digit d is s_glob[d] + p
-    __shared__ u32 s_wsum[kWarps];
-    __shared__ u32 s_tile;
 
+// Where a pass finds its digit inside the 64-bit item.  A digit never straddles more than the two 32-bit
+// halves, so one funnel shift (or a plain shift of the high half) replaces 64-bit shifting.
+struct DigitSpec {
+    int high;   // digit lies entirely in the high word
+    int sh;     // shift within the chosen word / funnel
+    u32 mask, flip;
+};
+__device__ __forceinline__ u32 digit_of(const u64 key, const DigitSpec& ds) {
+    const u32 lo = (u32)key, hi = (u32)(key >> 32);
+    const u32 w = ds.high ? (hi >> ds.sh) : __funnelshift_r(lo, hi, ds.sh);
+    return (w & ds.mask) ^ ds.flip;
+}
+// Lanes holding the same NB-bit digit as the caller; digits narrower than NB have zero upper bits, which
+// cost a ballot each but change nothing.  ALL: every lane of the warp holds a valid item.
+template <int NB, bool ALL>
+__device__ __forceinline__ u32 peers_of(const u32 d, const bool valid) {
+    u32 peers = ALL ? 0xffffffffu : __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        const bool bit = (d >> b) & 1u;
+        const u32 vote = __ballot_sync(0xffffffffu, bit);
+        peers &= bit ? vote : ~vote;
+    }
+    return peers;
+}
+
+struct SweepShared {
+    u64* keys;        // [kTileItems]
+    u32* vals;        // [kTileItems] when values travel with the keys
+    u32* wcnt;        // [kWarps][kRadix] per-warp digit counts, later first slot of (warp, digit)
+    u32* glob;        // [kRadix] global position of slot p with digit d is glob[d] + p
+    u32* wsum;        // [kWarps]
+};
+
+// One block-sized tile of one pass.  FULL: the tile holds kTileItems items, so no bounds checks.
+template <bool HAS_VALS, int NB, bool FULL>
+__device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin,
+                                           u32* __restrict__ vout, const u32 n, const DigitSpec ds,
+                                           const u32* __restrict__ hist, u32* __restrict__ lookback, int* __restrict__ status,
+                                           const u32 tile, const SweepShared sh) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_tile = atomicAdd(tile_counter, 1u);  // blocks take tiles in the order they start running
-    for (int k = tid; k < kWarps * kRadix; k += kThreads) (&s_wcnt[0][0])[k] = 0;
-    __syncthreads();
-    const u32 tile = s_tile;
     const u32 tile_base = tile * (u32)kTileItems;
-    const u32 tile_n = min((u32)kTileItems, n - tile_base);
+    const u32 tile_n = FULL ? (u32)kTileItems : n - tile_base;
     const u32 wbase = tile_base + (u32)warp * (32 * kItems);
+    u32* my_wcnt = sh.wcnt + warp * kRadix;
 
     // Load: item i of lane l sits at wbase + 32 i + l, so (i, l) order is memory order.
     u64 key[kItems];
     u32 val[kItems];
+    {
+        const u64* src = kin + wbase + lane;
+        const u32* vsrc = HAS_VALS ? vin + wbase + lane : nullptr;
 #pragma unroll
-    for (int i = 0; i < kItems; ++i) {
-        const u32 pos = wbase + 32 * i + lane;
-        key[i] = pos < n ? kin[pos] : ~0ull;
-        if (HAS_VALS) val[i] = pos < n ? vin[pos] : 0u;
+        for (int i = 0; i < kItems; ++i) {
+            const bool ok = FULL || wbase + 32 * i + lane < n;
+            key[i] = ok ? src[32 * i] : ~0ull;
+            if (HAS_VALS) val[i] = ok ? vsrc[32 * i] : 0u;
+        }
     }
 
-    // Rank inside the warp: lanes holding the same digit find each other (warp_peers); the lowest of them
+    // Rank inside the warp: lanes holding the same digit find each other (peers_of); the lowest of them
     // bumps the warp's counter for that digit by the group size with a shared-memory atomic, whose old value
     // is the number of equal digits among the warp's earlier items.  Items are handled in groups: first all
     // peer masks, then the atomics in item order (a warp barrier between two of them keeps that order), and
     // only then the broadcasts of the old values -- so no item waits for the previous item's round trip.
-    u32 rank[kItems];
+    // rd[i] packs the item's rank among equal digits of its warp (low 16 bits) with its digit (bits 16..23).
+    u32 rd[kItems];
     const u32 lanemask_lt = (1u << lane) - 1u;
     constexpr int kGroup = DSB_SORT_GROUP;
 #pragma unroll
     for (int i0 = 0; i0 < kItems; i0 += kGroup) {
-        u32 m[kGroup], before[kGroup];
+        u32 m[kGroup], d[kGroup], before[kGroup];
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
-            const bool valid = wbase + 32 * (i0 + j) + lane < n;
-            const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
-            m[j] = warp_peers(d, valid, nbits);
+            const bool valid = FULL || wbase + 32 * (i0 + j) + lane < n;
+            d[j] = digit_of(key[i0 + j], ds);
+            m[j] = peers_of<NB, FULL>(d[j], valid);
         }
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
-            const bool valid = wbase + 32 * (i0 + j) + lane < n;
-            const u32 d = sort_digit(key[i0 + j], shift, mask, flip);
+            const bool valid = FULL || wbase + 32 * (i0 + j) + lane < n;
             before[j] = 0;
-            if ((m[j] & lanemask_lt) == 0 && valid) before[j] = atomicAdd(&s_wcnt[warp][d], (u32)__popc(m[j]));
+            if ((m[j] & lanemask_lt) == 0 && valid) before[j] = atomicAdd(&my_wcnt[d[j]], (u32)__popc(m[j]));
             __syncwarp();
         }
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
-            const bool valid = wbase + 32 * (i0 + j) + lane < n;
+            const bool valid = FULL || wbase + 32 * (i0 + j) + lane < n;
             const u32 b = __shfl_sync(0xffffffffu, before[j], valid ? __ffs(m[j]) - 1 : lane);
-            rank[i0 + j] = b + (u32)__popc(m[j] & lanemask_lt);
+            rd[i0 + j] = (b + (u32)__popc(m[j] & lanemask_lt)) | (d[j] << 16);
         }
     }
     __syncthreads();
 
-    // Thread d (d < 256) owns digit d: order the warps, publish the block's count, find the digit's first slot.
+    // Thread d (d < 256) owns digit d: add up the warps, publish the block's count, find the digit's first slot.
     const bool owner = tid < kRadix;
     u32 total = 0;
     volatile u32* my_status = lookback + (size_t)tile * kRadix + (owner ? tid : 0);
     if (owner) {
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const u32 c = s_wcnt[w][tid];
-            s_wcnt[w][tid] = total;
-            total += c;
-        }
+        for (int w = 0; w < kWarps; ++w) total += sh.wcnt[w * kRadix + tid];
         *my_status = total | (tile == 0 ? kFlagInclusive : kFlagAggregate);
     }
 
-    const u32 dstart = block_exclusive_scan_256(total, s_wsum, tid);
-    const u32 gstart = block_exclusive_scan_256(owner ? hist[tid] : 0u, s_wsum, tid);
-    if (owner) s_dstart[tid] = dstart;
+    const u32 dstart = block_exclusive_scan_256(total, sh.wsum, tid);
+    const u32 gstart = block_exclusive_scan_256(owner ? hist[tid] : 0u, sh.wsum, tid);
+    if (owner) {
+        u32 run = dstart;   // wcnt[w][d] becomes the first slot of warp w's items with digit d
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const u32 c = sh.wcnt[w * kRadix + tid];
+            sh.wcnt[w * kRadix + tid] = run;
+            run += c;
+        }
+    }
 
     // Decoupled look-back over earlier tiles for this digit.
     u32 earlier = 0;
@@ -199,31 +231,71 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
         }
         *my_status = ((earlier + total) & kValueMask) | kFlagInclusive;
     }
-    if (owner) s_glob[tid] = gstart + earlier - dstart;
+    if (owner) sh.glob[tid] = gstart + earlier - dstart;
     __syncthreads();
 
     // Scatter into block-sorted order in shared memory, then stream out: consecutive slots of one
     // digit are consecutive in global memory, so the stores coalesce.
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
-        if (wbase + 32 * i + lane < n) {
-            const u32 d = sort_digit(key[i], shift, mask, flip);
-            const u32 slot = s_dstart[d] + s_wcnt[warp][d] + rank[i];
-            s_keys[slot] = key[i];
-            if (HAS_VALS) s_vals[slot] = val[i];
+        if (FULL || wbase + 32 * i + lane < n) {
+            const u32 slot = my_wcnt[rd[i] >> 16] + (rd[i] & 0xffffu);
+            sh.keys[slot] = key[i];
+            if (HAS_VALS) sh.vals[slot] = val[i];
         }
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < kItems; ++j) {
         const u32 slot = j * kThreads + tid;
-        if (slot < tile_n) {
-            const u64 k = s_keys[slot];
-            const u32 dst = s_glob[sort_digit(k, shift, mask, flip)] + slot;
+        if (FULL || slot < tile_n) {
+            const u64 k = sh.keys[slot];
+            const u32 dst = sh.glob[digit_of(k, ds)] + slot;
             kout[dst] = k;
-            if (HAS_VALS) vout[dst] = s_vals[slot];
+            if (HAS_VALS) vout[dst] = sh.vals[slot];
         }
     }
+}
+
+template <bool HAS_VALS, int NB>
+__global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
+onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
+                const u32 n, const DigitSpec ds, const u32* __restrict__ hist, u32* __restrict__ tile_counter,
+                u32* __restrict__ lookback, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ u32 s_wcnt[kWarps * kRadix];
+    __shared__ u32 s_glob[kRadix];
+    __shared__ u32 s_wsum[kWarps];
+    __shared__ u32 s_tile;
+    SweepShared sh;
+    sh.keys = reinterpret_cast<u64*>(dyn);
+    sh.vals = reinterpret_cast<u32*>(dyn + kTileItems * sizeof(u64));
+    sh.wcnt = s_wcnt;
+    sh.glob = s_glob;
+    sh.wsum = s_wsum;
+
+    const int tid = threadIdx.x;
+    if (tid == 0) s_tile = atomicAdd(tile_counter, 1u);  // blocks take tiles in the order they start running
+    for (int k = tid; k < kWarps * kRadix; k += kThreads) s_wcnt[k] = 0;
+    __syncthreads();
+    const u32 tile = s_tile;
+    if (n - tile * (u32)kTileItems >= (u32)kTileItems)
+        sweep_tile<HAS_VALS, NB, true>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+    else
+        sweep_tile<HAS_VALS, NB, false>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+}
+
+template <bool HAS_VALS, int NB>
+int launch_sweep(const u64* src, u64* dst, const u32* vsrc, u32* vdst, u32 n, const DigitSpec& ds, const u32* hist,
+                 u32* tile_counter, u32* lookback, int* status, int64_t tiles, size_t dyn, cudaStream_t s) {
+    // Keys alone fit the default 48 KB of shared memory per block; with values the block opts in to more.  The
+    // attribute belongs to the current device's context, so it is set at every launch rather than cached.
+    if (HAS_VALS || dyn + 10 * 1024 > 48 * 1024)
+        DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<HAS_VALS, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    onesweep_kernel<HAS_VALS, NB><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, n, ds, hist, tile_counter,
+                                                                         lookback, status);
+    DSB_LAUNCH_CHECK();
+    return DSB_OK;
 }
 
 }  // namespace
@@ -292,21 +364,23 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
     u32* lookback = reinterpret_cast<u32*>(hdr + 1);
     const size_t dyn = kTileItems * (sizeof(u64) + (vals ? sizeof(u32) : 0));
-    if (vals) DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    else DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     u64 *src = items, *dst = items_alt;
     u32 *vsrc = vals, *vdst = vals_alt;
     for (int p = 0; p < plan.npass; ++p) {
         u32* lb = lookback + (size_t)p * tiles * kRadix;
-        if (vals)
-            onesweep_kernel<true><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, (u32)k, plan.shift[p], plan.bits[p],
-                                                                      plan.mask[p], plan.flip[p], hdr->hist[p],
-                                                                      &hdr->tile_counter[p], lb, &hdr->status);
-        else
-            onesweep_kernel<false><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, nullptr, nullptr, (u32)k, plan.shift[p],
-                                                                       plan.bits[p], plan.mask[p], plan.flip[p], hdr->hist[p],
-                                                                       &hdr->tile_counter[p], lb, &hdr->status);
-        DSB_LAUNCH_CHECK();
+        DigitSpec ds;
+        ds.high = plan.shift[p] >= 32;
+        ds.sh = plan.shift[p] & 31;
+        ds.mask = plan.mask[p];
+        ds.flip = plan.flip[p];
+        const int nb = plan.bits[p] <= 5 ? 5 : plan.bits[p];
+        int rc;
+#define DSB_SWEEP(V, NB) launch_sweep<V, NB>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb, \
+                                             &hdr->status, tiles, dyn, s)
+        if (vals) rc = nb == 5 ? DSB_SWEEP(true, 5) : nb == 6 ? DSB_SWEEP(true, 6) : nb == 7 ? DSB_SWEEP(true, 7) : DSB_SWEEP(true, 8);
+        else rc = nb == 5 ? DSB_SWEEP(false, 5) : nb == 6 ? DSB_SWEEP(false, 6) : nb == 7 ? DSB_SWEEP(false, 7) : DSB_SWEEP(false, 8);
+#undef DSB_SWEEP
+        if (rc != DSB_OK) return rc;
         u64* t = src; src = dst; dst = t;
         u32* tv = vsrc; vsrc = vdst; vdst = tv;
     }
