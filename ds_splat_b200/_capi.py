@@ -78,12 +78,12 @@ def lib():
             "dsb_sort_by_keys": [P, P, P, P, I64, I32, I32, P, I64, C.POINTER(C.c_int32), P],
             "dsb_sort_pairs_static": [P, P, I64, I32, I32, C.POINTER(C.c_int32), P],
             "dsb_identify_tile_ranges": [P, I64, I32, I32, P, P],
-            "dsb_blend_forward": [CAM, P, P, P, P, P, P, P],
-            "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P],
+            "dsb_blend_forward": [CAM, P, P, P, P, P, P, P, P],
+            "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P, P],
             "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
             "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
-            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 5,
-            "dsb_backward": [CAM, I32] + [P] * 12 + [P] * 8 + [I32, P],
+            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
+            "dsb_backward": [CAM, I32] + [P] * 13 + [P] * 8 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
         }
         for name, argtypes in sig.items():
@@ -241,21 +241,23 @@ def identify_tile_ranges(sorted_items, h, w):
     return ranges
 
 
-def blend_forward(cam, records, sorted_pairs, ranges):
+def blend_forward(cam, records, sorted_pairs, ranges, with_depth=False):
+    """Returns (image, final_T, final_idx), plus the blended depth map when ``with_depth``."""
     h, w, dev = cam.image_height, cam.image_width, records.device
+    depth = torch.empty((h, w), dtype=torch.float32, device=dev) if with_depth else None
     image = torch.empty((h, w, 3), dtype=torch.float32, device=dev)
     final_t = torch.empty((h, w), dtype=torch.float32, device=dev)
     final_idx = torch.empty((h, w), dtype=torch.int32, device=dev)
     check(lib().dsb_blend_forward(C.byref(cam), ptr(records), ptr(sorted_pairs), ptr(ranges), ptr(image), ptr(final_t),
-                                  ptr(final_idx), stream_ptr()))
-    return image, final_t, final_idx
+                                  ptr(final_idx), ptr(depth), stream_ptr()))
+    return (image, final_t, final_idx, depth) if with_depth else (image, final_t, final_idx)
 
 
-def blend_backward(cam, records, sorted_pairs, ranges, final_t, final_idx, v_image):
+def blend_backward(cam, records, sorted_pairs, ranges, final_t, final_idx, v_image, v_depth=None):
     n = records.shape[0]
     grad_acc = torch.zeros((n, GRAD_FLOATS), dtype=torch.float32, device=records.device)
     check(lib().dsb_blend_backward(C.byref(cam), ptr(records), ptr(sorted_pairs), ptr(ranges), ptr(final_t),
-                                   ptr(final_idx), ptr(v_image), ptr(grad_acc), stream_ptr()))
+                                   ptr(final_idx), ptr(v_image), ptr(v_depth), ptr(grad_acc), stream_ptr()))
     return grad_acc
 
 

@@ -23,6 +23,12 @@
 //
 // The per-pixel arithmetic follows the reference: alpha clamp 0.99, 1/255 skip, opacity and visibility
 // gradients without clamp masking, and the background term in v_alpha.
+//
+// Optional depth gradient (the reference has no depth map): in the DEPTH instantiation the splat's view-space
+// z acts as a fourth colour channel without background.  Its upstream gradient joins v_alpha, and a tenth
+// sum, v_z = sum alpha T v_depth, lands in slot 9 of the splat's accumulator row, from where the per-splat
+// backward feeds it to the mean exactly where the reference's projection backward takes its v_depth
+// (cpp/gsplat/backward.cu:253-259).
 #include "blend_common.cuh"
 
 namespace dsb {
@@ -35,6 +41,10 @@ constexpr int kWarps = kThreads / 32;
 __device__ __forceinline__ void red_add_v4(float4* addr, const float4 v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
                  : "memory");
+}
+
+__device__ __forceinline__ void red_add_v2(float* addr, const float a, const float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
 }
 
 __device__ __forceinline__ void red_add(float* addr, const float v) {
@@ -68,12 +78,13 @@ __device__ __forceinline__ float butterfly1(float v) {
     return v;
 }
 
+template <bool DEPTH>
 __global__ void __launch_bounds__(kThreads)
 blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, const float4* __restrict__ records,
                       const u64* __restrict__ sorted, const int32_t* __restrict__ ranges,
                       const float* __restrict__ final_T, const int32_t* __restrict__ final_idx,
-                      const float* __restrict__ v_image, float4* __restrict__ grad_acc) {
-    __shared__ float4 s_rec[kWarps][32][3];   // x,y,a,b | c,opacity,r,g | blue, threshold, -, -
+                      const float* __restrict__ v_image, const float* __restrict__ v_depth, float4* __restrict__ grad_acc) {
+    __shared__ float4 s_rec[kWarps][32][3];   // x,y,a,b | c,opacity,r,g | blue, threshold, z, -
     __shared__ float s_acc[kWarps][32][12];   // moments of the chunk's entries
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -84,18 +95,19 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
     const float px = (float)x + 0.5f, py = (float)y + 0.5f;
     const int start = ranges[tile], end = ranges[tile + 1];
 
-    float Tf = 1.0f, vo0 = 0.0f, vo1 = 0.0f, vo2 = 0.0f;
+    float Tf = 1.0f, vo0 = 0.0f, vo1 = 0.0f, vo2 = 0.0f, vod = 0.0f;
     int fin = -1;
     if (inside) {
         const size_t pix = (size_t)y * W + x;
         Tf = final_T[pix];
         fin = final_idx[pix];
         vo0 = v_image[3 * pix]; vo1 = v_image[3 * pix + 1]; vo2 = v_image[3 * pix + 2];
+        if (DEPTH) vod = v_depth[pix];
     }
     const float bgdot = bg ? (bg[0] * vo0 + bg[1] * vo1 + bg[2] * vo2) : 0.0f;
     // Entries after the last one any pixel of the warp blended cannot contribute.
     const int top = min(end - 1, __reduce_max_sync(0xffffffffu, fin));
-    float T = Tf, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f;
+    float T = Tf, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, bz = 0.0f;
 
     float4 (*rec)[3] = s_rec[warp];
     float (*acc)[12] = s_acc[warp];
@@ -105,18 +117,20 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
         const int my_pos = base - lane;
         u32 id = 0;
         float4 q0 = make_float4(0, 0, 0, 0), q1 = q0;
-        float blue = 0.f, thr = 0.f;
+        float blue = 0.f, thr = 0.f, zview = 0.f;
         bool hit = false;
         if (my_pos >= start) {
             id = (u32)sorted[my_pos];
             const float4* r = records + (size_t)id * 3;
-            q0 = __ldg(r); q1 = __ldg(r + 1); blue = __ldg(r + 2).x;
+            q0 = __ldg(r); q1 = __ldg(r + 1);
+            const float4 q2 = __ldg(r + 2);
+            blue = q2.x; zview = q2.y;
             thr = __logf(255.0f * q1.y) + kCullMargin;
             hit = splat_reaches_block(q0.x, q0.y, q0.z, q0.w, q1.x, thr, wp.x0, wp.y0);
         }
         u32 todo = __ballot_sync(0xffffffffu, hit);
         if (todo == 0) continue;
-        rec[lane][0] = q0; rec[lane][1] = q1; rec[lane][2] = make_float4(blue, thr, 0.f, 0.f);
+        rec[lane][0] = q0; rec[lane][1] = q1; rec[lane][2] = make_float4(blue, thr, zview, 0.f);
         __syncwarp();
 
         // ---- blend the survivors, nearest list position last (ascending lane = descending position)
@@ -133,7 +147,7 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             const bool valid = inside && pos <= fin && sigma >= 0.f && sigma <= qc.y;
             if (!__any_sync(0xffffffffu, valid)) continue;
             float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            float v8 = 0.f;
+            float v8 = 0.f, v9 = 0.f;
             if (valid) {
                 const float vis = __expf(-sigma);
                 const float alpha = min(0.99f, qb.y * vis);
@@ -146,6 +160,11 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
                     v_alpha += (qb.w * T - b1 * ra) * vo1;
                     v_alpha += (qc.x * T - b2 * ra) * vo2;
                     v_alpha += -Tf * ra * bgdot;
+                    if (DEPTH) {
+                        v_alpha += (qc.z * T - bz * ra) * vod;
+                        bz += qc.z * fac;
+                        v9 = fac * vod;
+                    }
                     b0 += qb.z * fac; b1 += qb.w * fac; b2 += qc.x * fac;
                     const float v_sigma = -qb.y * vis * v_alpha;
                     v[0] = v_sigma * dx;   // Sx
@@ -163,6 +182,10 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             const float sum8 = butterfly1(v8);
             if ((lane & 3) == 0) acc[t][lane >> 2] = sum;
             if (lane == 0) acc[t][8] = sum8;
+            if (DEPTH) {
+                const float sum9 = butterfly1(v9);
+                if (lane == 0) acc[t][9] = sum9;
+            }
             touched |= 1u << t;
         }
         __syncwarp();
@@ -175,7 +198,8 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             float4* dst = grad_acc + (size_t)id * 3;
             red_add_v4(dst, make_float4(q0.z * m0.x + q0.w * m0.y, q0.w * m0.x + q1.x * m0.y, 0.5f * m0.z, m0.w));
             red_add_v4(dst + 1, make_float4(0.5f * m1.x, -m1.y / q1.y, m1.z, m1.w));
-            red_add(reinterpret_cast<float*>(dst + 2), m2);
+            if (DEPTH) red_add_v2(reinterpret_cast<float*>(dst + 2), m2, acc[lane][9]);
+            else red_add(reinterpret_cast<float*>(dst + 2), m2);
         }
         __syncwarp();  // the slices are reused by the next chunk
     }
@@ -183,15 +207,21 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
 
 }  // namespace
 
+// v_depth may be null (no depth map was rendered, or nothing depends on it).
 int launch_blend_backward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
-                          const float* final_T, const int32_t* final_idx, const float* v_image, float* grad_acc,
-                          cudaStream_t s) {
+                          const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
+                          float* grad_acc, cudaStream_t s) {
     DSB_REQUIRE(ranges && final_T && final_idx && v_image && grad_acc, "blend_backward: null pointer");
     DSB_REQUIRE(((uintptr_t)grad_acc & 15) == 0, "blend_backward: grad_acc must be 16-byte aligned");
     const dim3 grid(cp.tiles_x, cp.tiles_y);
-    blend_backward_kernel<<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.bg, reinterpret_cast<const float4*>(records), sorted,
-                                                   ranges, final_T, final_idx, v_image,
-                                                   reinterpret_cast<float4*>(grad_acc));
+    if (v_depth)
+        blend_backward_kernel<true><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.bg, reinterpret_cast<const float4*>(records),
+                                                             sorted, ranges, final_T, final_idx, v_image, v_depth,
+                                                             reinterpret_cast<float4*>(grad_acc));
+    else
+        blend_backward_kernel<false><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.bg, reinterpret_cast<const float4*>(records),
+                                                              sorted, ranges, final_T, final_idx, v_image, nullptr,
+                                                              reinterpret_cast<float4*>(grad_acc));
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -14,6 +14,9 @@
 //
 // Per-pixel arithmetic (order of operations, 0.999 alpha clamp, 1/255 skip, no background term) is the
 // reference's and the cull test is conservative, so images agree to rounding and final_idx exactly.
+//
+// Optional depth map (the reference has none): the DEPTH instantiation blends the splat's view-space z like
+// a fourth colour channel, depth = sum z_i alpha_i T_i.
 #include "blend_common.cuh"
 
 namespace dsb {
@@ -28,30 +31,34 @@ constexpr int kWarps = kThreads / 32;
 
 struct Fetched {
     float4 q0, q1;
-    float blue;
+    float blue, z;
     bool have;
 };
 
 __device__ __forceinline__ Fetched fetch_entry(const float4* __restrict__ records, const u64* __restrict__ sorted,
                                                const int pos, const int end) {
     Fetched f;
-    f.q0 = make_float4(0, 0, 0, 0); f.q1 = f.q0; f.blue = 0.f;
+    f.q0 = make_float4(0, 0, 0, 0); f.q1 = f.q0; f.blue = 0.f; f.z = 0.f;
     f.have = pos < end;
     if (f.have) {
         const u32 id = (u32)sorted[pos];
         const float4* r = records + (size_t)id * 3;
-        f.q0 = __ldg(r); f.q1 = __ldg(r + 1); f.blue = __ldg(r + 2).x;
+        f.q0 = __ldg(r); f.q1 = __ldg(r + 1);
+        const float4 q2 = __ldg(r + 2);
+        f.blue = q2.x; f.z = q2.y;
     }
     return f;
 }
 
+template <bool DEPTH>
 __global__ void __launch_bounds__(kThreads)
 blend_forward_kernel(const int W, const int H, const float4* __restrict__ records, const u64* __restrict__ sorted,
                      const int32_t* __restrict__ ranges, float* __restrict__ image, float* __restrict__ final_T,
-                     int32_t* __restrict__ final_idx) {
+                     int32_t* __restrict__ final_idx, float* __restrict__ depth) {
     __shared__ float4 s_q0[kWarps][32];  // x, y, conic a, conic b
     __shared__ float4 s_q1[kWarps][32];  // conic c, opacity, r, g
     __shared__ float s_b[kWarps][32];    // b
+    __shared__ float s_z[DEPTH ? kWarps : 1][32];  // view-space depth
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -61,13 +68,14 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
     const int start = ranges[tile], end = ranges[tile + 1];
     const float pxf = x + 0.5f, pyf = y + 0.5f;
 
-    float T = 1.0f, c0 = 0.0f, c1 = 0.0f, c2 = 0.0f;
+    float T = 1.0f, c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, cz = 0.0f;
     int last = 0;
     bool done = !inside;
 
     float4* q0s = s_q0[warp];
     float4* q1s = s_q1[warp];
     float* bs = s_b[warp];
+    float* zs = s_z[DEPTH ? warp : 0];
 
 #if DSB_FWD_PREFETCH
     Fetched nxt = fetch_entry(records, sorted, start + lane, end);
@@ -88,6 +96,7 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
         const u32 todo = __ballot_sync(0xffffffffu, hit);
         if (todo == 0) continue;
         q0s[lane] = cur.q0; q1s[lane] = cur.q1; bs[lane] = cur.blue;
+        if (DEPTH) zs[lane] = cur.z;
         __syncwarp();
         for (u32 m = todo; m != 0 && !done; m &= m - 1) {
             const int t = __ffs(m) - 1;
@@ -101,6 +110,7 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
             if (!(Tn >= 0.0001f)) { done = true; break; }
             const float wgt = alpha * T;
             c0 += wgt * b.z; c1 += wgt * b.w; c2 += wgt * bs[t];
+            if (DEPTH) cz += wgt * zs[t];
             T = Tn;
             last = base + t;
         }
@@ -111,17 +121,23 @@ blend_forward_kernel(const int W, const int H, const float4* __restrict__ record
         image[3 * pix] = c0; image[3 * pix + 1] = c1; image[3 * pix + 2] = c2;
         final_T[pix] = T;
         final_idx[pix] = last;
+        if (DEPTH) depth[pix] = cz;
     }
 }
 
 }  // namespace
 
+// depth may be null (no depth map wanted).
 int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
-                         float* image, float* final_T, int32_t* final_idx, cudaStream_t s) {
+                         float* image, float* final_T, int32_t* final_idx, float* depth, cudaStream_t s) {
     DSB_REQUIRE(ranges && image && final_T && final_idx, "blend_forward: null pointer");
     const dim3 grid(cp.tiles_x, cp.tiles_y);
-    blend_forward_kernel<<<grid, kThreads, 0, s>>>(cp.W, cp.H, reinterpret_cast<const float4*>(records), sorted, ranges,
-                                                  image, final_T, final_idx);
+    if (depth)
+        blend_forward_kernel<true><<<grid, kThreads, 0, s>>>(cp.W, cp.H, reinterpret_cast<const float4*>(records), sorted,
+                                                            ranges, image, final_T, final_idx, depth);
+    else
+        blend_forward_kernel<false><<<grid, kThreads, 0, s>>>(cp.W, cp.H, reinterpret_cast<const float4*>(records), sorted,
+                                                             ranges, image, final_T, final_idx, nullptr);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

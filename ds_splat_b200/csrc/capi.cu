@@ -187,18 +187,18 @@ int dsb_identify_tile_ranges(const uint64_t* sorted, int64_t k, int32_t image_he
 }
 
 int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
-                      float* image, float* final_T, int32_t* final_idx, void* stream) {
+                      float* image, float* final_T, int32_t* final_idx, float* depth, void* stream) {
     CAM_OR_RETURN(cam, cp);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, image, final_T,
-                                final_idx, (cudaStream_t)stream);
+                                final_idx, depth, (cudaStream_t)stream);
 }
 
 int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
-                       const float* final_T, const int32_t* final_idx, const float* v_image, float* grad_acc,
-                       void* stream) {
+                       const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
+                       float* grad_acc, void* stream) {
     CAM_OR_RETURN(cam, cp);
     return launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
-                                 v_image, grad_acc, (cudaStream_t)stream);
+                                 v_image, v_depth, grad_acc, (cudaStream_t)stream);
 }
 
 int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
@@ -237,7 +237,7 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
 int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
                        const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, uint64_t* pairs_alt,
                        int32_t* tile_marks, void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image,
-                       float* final_T, int32_t* final_idx, void* stream) {
+                       float* final_T, int32_t* final_idx, float* depth, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
     // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The preprocess kernel marked
@@ -273,13 +273,14 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
         if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
     }
     StageScope scope(kStageBlendForward, s);
-    return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, s);
+    return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, depth,
+                                s);
 }
 
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales, const float* rotations,
                  const float* records, const float* cov3d, const int32_t* radii, const uint64_t* sorted_pairs,
                  const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
-                 float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
+                 const float* v_depth, float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
                  float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
@@ -291,7 +292,7 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
         StageScope scope(kStageBlendBackward, s);
         DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
         rc = launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
-                                   v_image, grad_acc, s);
+                                   v_image, v_depth, grad_acc, s);
     }
     if (rc != DSB_OK) return rc;
     StageScope scope(kStageGeometryBackward, s);

@@ -51,12 +51,13 @@ geometry_backward_kernel(const CamParams cp, const int n, const float* __restric
     const bool live = i < n;
 
     float4 g0 = make_float4(0, 0, 0, 0), g1 = g0;
-    float gb = 0.f;
+    float gb = 0.f, gz = 0.f;
     float mx = 0.f, my = 0.f, mz = 0.f;
     if (live) {
         g0 = grad_acc[(size_t)i * 3];      // v_x, v_y, v_conic_a, v_conic_b
         g1 = grad_acc[(size_t)i * 3 + 1];  // v_conic_c, v_opacity, v_r, v_g
-        gb = grad_acc[(size_t)i * 3 + 2].x;
+        const float4 g2 = grad_acc[(size_t)i * 3 + 2];  // v_b, v_z (zero unless a depth map's gradient came in), -, -
+        gb = g2.x; gz = g2.y;
         mx = means[(size_t)i * 3]; my = means[(size_t)i * 3 + 1]; mz = means[(size_t)i * 3 + 2];
     }
 
@@ -118,6 +119,8 @@ geometry_backward_kernel(const CamParams cp, const int n, const float* __restric
             vm1 = V[1] * a + V[5] * b + V[9] * c;
             vm2 = V[2] * a + V[6] * b + V[10] * c;
         }
+        // view-space depth gradient (cpp/gsplat/backward.cu:253-259; the reference always feeds zeros here)
+        vm0 += V[8] * gz; vm1 += V[9] * gz; vm2 += V[10] * gz;
         // conic -> 2-D covariance: v_Sigma = -X G X with X the conic, G the symmetrised conic gradient
         float s00, s01, s11;
         {

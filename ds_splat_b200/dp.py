@@ -155,7 +155,7 @@ class ViewRenderer:
             C.byref(c), self.n, k, self.records.data_ptr(), self.tiles.data_ptr(), self.depth_keys[0].data_ptr(),
             self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(), tile_marks.data_ptr(),
             self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(), image.data_ptr(), final_t.data_ptr(),
-            final_idx.data_ptr(), stream))
+            final_idx.data_ptr(), None, stream))
         self.last_k = k
         self._last_cam = (c, keep, cam)
         return image
@@ -169,7 +169,8 @@ class ViewRenderer:
         capi.check(lib.dsb_backward(
             C.byref(c), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
             self.records.data_ptr(), self.cov3d.data_ptr(), self.radii.data_ptr(), self.pairs[0].data_ptr(),
-            ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), self.grad_acc.data_ptr(),
+            ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
+            self.grad_acc.data_ptr(),
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 

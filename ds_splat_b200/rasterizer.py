@@ -5,7 +5,9 @@ Drop-in by import swap: ``from ds_splat_b200 import GaussianRasterizationSetting
 The positional call of the reference ``rasterizer(means_3d, means_2d, shs, colors_precomp, opacities,
 scales, rotations, cov_3d_precomp)`` works unchanged; graphdeco's keyword names (``means3D=...,
 cov3D_precomp=...``) are accepted too.  The result is ``(image[H,W,3], radii[N])`` as in the reference
-(``channels_first=True`` in the settings gives graphdeco's ``[3,H,W]``).
+(``channels_first=True`` in the settings gives graphdeco's ``[3,H,W]``).  ``return_depth=True`` adds a third
+result, the blended view-space depth map ``[H,W]`` (``sum z_i alpha_i T_i``; the reference has no depth
+output), which is differentiable like the image.
 
 Differences from the reference that a caller can observe, all deliberate:
   * work is enqueued on the *current* torch stream of the inputs' device (the reference uses the
@@ -30,7 +32,8 @@ from . import _capi
 class GaussianRasterizationSettings:
     """Same thirteen fields, in the same order, as the reference's dataclass
     (ds_splat/rasterizer.py:115-129).  ``max_sh_degree`` defaults to 3 so that graphdeco-style keyword
-    construction (which has no such field) works; ``channels_first`` and ``strict_reference`` are additions."""
+    construction (which has no such field) works; ``channels_first``, ``strict_reference`` and ``return_depth``
+    are additions."""
     image_height: int
     image_width: int
     tanfovx: float
@@ -46,10 +49,11 @@ class GaussianRasterizationSettings:
     debug: bool
     channels_first: bool
     strict_reference: bool
+    return_depth: bool
 
     def __init__(self, image_height, image_width, tanfovx, tanfovy, bg, scale_modifier, viewmatrix, projmatrix,
                  sh_degree, max_sh_degree=3, campos=None, prefiltered=False, debug=False, channels_first=False,
-                 strict_reference=True):
+                 strict_reference=True, return_depth=False):
         if campos is None:
             raise TypeError("GaussianRasterizationSettings: campos is required")
         self.image_height, self.image_width = int(image_height), int(image_width)
@@ -61,6 +65,8 @@ class GaussianRasterizationSettings:
         # strict_reference keeps the reference's habit of never drawing the splat with the highest index
         # (cpp/rasterizer_torch.cu:97-104), which bit-exact parity of the sorted lists requires.
         self.channels_first, self.strict_reference = bool(channels_first), bool(strict_reference)
+        # return_depth makes the rasterizer return (image, radii, depth) instead of the reference's (image, radii).
+        self.return_depth = bool(return_depth)
 
 
 def _camera_for(settings: GaussianRasterizationSettings, device):
@@ -84,7 +90,8 @@ def _camera_for(settings: GaussianRasterizationSettings, device):
 
 class DsRasterizerFunction(torch.autograd.Function):
     """Counterpart of the reference's autograd Function (ds_splat/rasterizer.py:7-112): eight tensor inputs
-    plus the settings; returns (image, radii); backward returns one gradient per tensor input."""
+    plus the settings; returns (image, radii) -- (image, radii, depth) with ``return_depth`` -- and backward returns
+    one gradient per tensor input."""
 
     @staticmethod
     def forward(ctx, means_3d, means_2d, shs, colors_precomp, opacities, scales, rotations, cov_3d_precomp,
@@ -143,11 +150,12 @@ class DsRasterizerFunction(torch.autograd.Function):
             image = torch.empty((h, w, 3), **f32)
             final_t = torch.empty((h, w), **f32)
             final_idx = torch.empty((h, w), dtype=torch.int32, device=dev)
+            depth = torch.empty((h, w), **f32) if raster_settings.return_depth else None
             _capi.check(lib.dsb_forward_render(
                 C.byref(cam), n, k, records.data_ptr(), tiles.data_ptr(), depth_keys[0].data_ptr(), offsets.data_ptr(),
                 pairs[0].data_ptr(), pairs[1].data_ptr(), tile_marks.data_ptr(), sort_ws.data_ptr(), sort_bytes,
                 ranges.data_ptr(),
-                image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), stream))
+                image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), _capi.ptr(depth), stream))
             sorted_pairs = pairs[0][:k]
 
         ctx.raster_settings = raster_settings
@@ -160,19 +168,24 @@ class DsRasterizerFunction(torch.autograd.Function):
         ctx.mark_non_differentiable(radii)
         if raster_settings.channels_first:
             image = image.permute(2, 0, 1)
+        if raster_settings.return_depth:
+            return image, radii, depth
         return image, radii
 
     @staticmethod
-    def backward(ctx, rendered_img_grad, _radii_grad):
+    def backward(ctx, rendered_img_grad, _radii_grad, depth_grad=None):
         lib = _capi.lib()
         (means_3d, scales, rotations, records, cov3d, radii, sorted_pairs, ranges, final_t, final_idx) = ctx.saved_tensors
         settings = ctx.raster_settings
         had_shs, had_colors, had_scales, had_rots, had_cov = ctx.had
         dev = means_3d.device
         n = means_3d.shape[0]
-        if settings.channels_first:
+        if rendered_img_grad is None:  # only the depth map took part in the loss
+            rendered_img_grad = final_t.new_zeros((settings.image_height, settings.image_width, 3))
+        elif settings.channels_first:
             rendered_img_grad = rendered_img_grad.permute(1, 2, 0)
         v_image = rendered_img_grad.to(dtype=torch.float32).contiguous()
+        v_depth = depth_grad.to(dtype=torch.float32).contiguous() if depth_grad is not None else None
         need = ctx.needs_input_grad
         coeffs = (settings.max_sh_degree + 1) ** 2
 
@@ -191,7 +204,8 @@ class DsRasterizerFunction(torch.autograd.Function):
             _capi.check(lib.dsb_backward(
                 C.byref(cam), n, means_3d.data_ptr(), _capi.ptr(scales), _capi.ptr(rotations), records.data_ptr(),
                 cov3d.data_ptr(), radii.data_ptr(), _capi.ptr(sorted_pairs), ranges.data_ptr(), final_t.data_ptr(),
-                final_idx.data_ptr(), v_image.data_ptr(), grad_acc.data_ptr(), _capi.ptr(v_means3d), _capi.ptr(v_means2d),
+                final_idx.data_ptr(), v_image.data_ptr(), _capi.ptr(v_depth), grad_acc.data_ptr(), _capi.ptr(v_means3d),
+                _capi.ptr(v_means2d),
                 _capi.ptr(v_shs), _capi.ptr(v_colors), _capi.ptr(v_opac), _capi.ptr(v_scales), _capi.ptr(v_rots),
                 _capi.ptr(v_cov3d), 0, _capi.stream_ptr()))
         return v_means3d, v_means2d, v_shs, v_colors, v_opac, v_scales, v_rots, v_cov3d, None

@@ -157,17 +157,25 @@ int dsb_identify_tile_ranges(const uint64_t* sorted, int64_t k, int32_t image_he
 
 /* ---- stage (e) ------------------------------------------------------------------------------
  * Replaces rasterizer_cuda_forward + render_image_kernel (cpp/rasterizer_torch.cu:44-68,
- * cpp/rasterizer_kernels.cu:341-431).  image [H][W][3], final_T [H][W], final_idx [H][W] int32. */
+ * cpp/rasterizer_kernels.cu:341-431).  image [H][W][3], final_T [H][W], final_idx [H][W] int32.
+ * depth [H][W] may be NULL; when given it receives sum_i z_i alpha_i T_i, the view-space depth of the
+ * splats blended like a fourth colour channel (no reference counterpart: the reference returns colour
+ * and radii only). */
 int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs,
-                      const int32_t* ranges, float* image, float* final_T, int32_t* final_idx, void* stream);
+                      const int32_t* ranges, float* image, float* final_T, int32_t* final_idx, float* depth,
+                      void* stream);
 
 /* ---- stage (f1) -----------------------------------------------------------------------------
  * Replaces rasterize_backward_tensor + rasterize_backward_kernel (cpp/gsplat/bindings.cu:140-194,
  * cpp/gsplat/backward.cu:25-202).  grad_acc [n][12] must be zero on entry; on exit row i holds
- * (v_x, v_y, v_conic_a, v_conic_b | v_conic_c, v_opacity, v_r, v_g | v_b, 0, 0, 0). */
+ * (v_x, v_y, v_conic_a, v_conic_b | v_conic_c, v_opacity, v_r, v_g | v_b, v_z, 0, 0).
+ * v_depth [H][W] may be NULL; when given it is the gradient of dsb_blend_forward's depth map, it takes
+ * part in the opacity / mean / conic gradients, and v_z = sum alpha T v_depth is what dsb_geometry_backward
+ * feeds to the mean through the v_depth slot of the reference's projection backward
+ * (cpp/gsplat/backward.cu:253-259).  Without it v_z stays 0, which is what the reference always passes. */
 int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
-                       const float* v_image, float* grad_acc, void* stream);
+                       const float* v_image, const float* v_depth, float* grad_acc, void* stream);
 
 /* ---- stage (f2) -----------------------------------------------------------------------------
  * Replaces compute_sh_backward_tensor, project_gaussians_backward_tensor and the host glue of
@@ -205,11 +213,12 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                        const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
                        uint64_t* pairs, uint64_t* pairs_alt, int32_t* tile_marks, void* workspace,
                        int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T, int32_t* final_idx,
-                       void* stream);
+                       float* depth /* may be NULL */, void* stream);
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,
-                 const int32_t* final_idx, const float* v_image, float* grad_acc, float* v_means3d,
+                 const int32_t* final_idx, const float* v_image, const float* v_depth /* may be NULL */,
+                 float* grad_acc, float* v_means3d,
                  float* v_means2d, float* v_shs, float* v_colors, float* v_opacities, float* v_scales,
                  float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
 

@@ -280,9 +280,12 @@ void orc_tile_ranges(int64_t K, const int64_t* keys, int H, int W, int32_t* out)
 
 // Stage (e).  cpp/rasterizer_kernels.cu:341-431.  Per pixel, front to back over its tile's run.
 // pairs_out[0] = (pixel, splat) pairs evaluated, each pixel stopping on its own.
+// Optional depth map (no reference counterpart: the reference returns colour only): when z (per-splat
+// view-space depth) and depth_out are given, depth_out = sum_i z_i alpha_i T_i, i.e. z blended exactly
+// like a fourth colour channel.
 void orc_blend_forward(const Cam* cam, const int32_t* ids, const int32_t* ranges, const float* xy,
                        const float* conic, const float* rgb, const float* opac, float* image, float* final_T,
-                       int32_t* final_idx, int64_t* pairs_out) {
+                       int32_t* final_idx, int64_t* pairs_out, const float* z, float* depth_out) {
     const Cam& c = *cam;
     const int tw = tiles_x(c), th = tiles_y(c);
     int64_t pairs = 0;
@@ -294,7 +297,7 @@ void orc_blend_forward(const Cam* cam, const int32_t* ids, const int32_t* ranges
             for (int lx = 0; lx < kTile; ++lx) {
                 const int x = tx0 + lx, y = ty0 + ly;
                 if (x >= c.W || y >= c.H) continue;
-                float T = 1.0f, C0 = 0, C1 = 0, C2 = 0;
+                float T = 1.0f, C0 = 0, C1 = 0, C2 = 0, D = 0;
                 int last = 0;
                 for (int p = s; p < e; ++p) {
                     ++pairs;
@@ -308,6 +311,7 @@ void orc_blend_forward(const Cam* cam, const int32_t* ids, const int32_t* ranges
                     if (!(Tn >= 0.0001f)) break;
                     const float w = alpha * T;
                     C0 += w * rgb[3 * (size_t)g]; C1 += w * rgb[3 * (size_t)g + 1]; C2 += w * rgb[3 * (size_t)g + 2];
+                    if (z) D += w * z[g];
                     T = Tn;
                     last = p;
                 }
@@ -315,6 +319,7 @@ void orc_blend_forward(const Cam* cam, const int32_t* ids, const int32_t* ranges
                 image[3 * pix] = C0; image[3 * pix + 1] = C1; image[3 * pix + 2] = C2;  // no background: kernel has no bg argument
                 final_T[pix] = T;
                 final_idx[pix] = last;
+                if (z && depth_out) depth_out[pix] = D;
             }
     }
     if (pairs_out) pairs_out[0] = pairs;
@@ -322,13 +327,18 @@ void orc_blend_forward(const Cam* cam, const int32_t* ids, const int32_t* ranges
 
 // Stage (f1).  cpp/gsplat/backward.cu:25-202.  Per pixel, back to front from final_idx; per-splat sums
 // are accumulated in double (the GPU's atomic order is not deterministic, so no fp32 order exists to follow).
+// Optional depth gradient (no reference counterpart): with z, v_depth_img (dL/d depth map) and v_z given,
+// z takes part as a fourth colour channel without background -- its term joins v_alpha and
+// v_z[g] = sum over pixels of alpha T v_depth, the quantity cpp/gsplat/backward.cu:253-259 expects as v_depth.
 void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t* ranges, const float* xy,
                         const float* conic, const float* rgb, const float* opac, const float* final_T,
                         const int32_t* final_idx, const float* v_image, float* v_xy, float* v_conic, float* v_rgb,
-                        float* v_opac, int64_t* pairs_out) {
+                        float* v_opac, int64_t* pairs_out, const float* z, const float* v_depth_img, float* v_z) {
     const Cam& c = *cam;
     const int tw = tiles_x(c), th = tiles_y(c);
-    std::vector<double> acc((size_t)N * 9, 0.0);
+    const bool with_depth = z && v_depth_img && v_z;
+    constexpr int kA = 10;  // 9 reference sums + v_z
+    std::vector<double> acc((size_t)N * kA, 0.0);
     int64_t pairs = 0;
 #pragma omp parallel reduction(+ : pairs)
     {
@@ -337,7 +347,7 @@ void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t
         for (int tile = 0; tile < tw * th; ++tile) {
             const int s = ranges[tile], e = ranges[tile + 1];
             if (e <= s) continue;
-            loc.assign((size_t)(e - s) * 9, 0.0);
+            loc.assign((size_t)(e - s) * kA, 0.0);
             const int tx0 = (tile % tw) * kTile, ty0 = (tile / tw) * kTile;
             for (int ly = 0; ly < kTile; ++ly)
                 for (int lx = 0; lx < kTile; ++lx) {
@@ -346,8 +356,9 @@ void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t
                     const size_t pix = (size_t)y * c.W + x;
                     const float px = (float)x + 0.5f, py = (float)y + 0.5f;
                     const float Tf = final_T[pix];
-                    float T = Tf, b0 = 0, b1 = 0, b2 = 0;
+                    float T = Tf, b0 = 0, b1 = 0, b2 = 0, bz = 0;
                     const float vo0 = v_image[3 * pix], vo1 = v_image[3 * pix + 1], vo2 = v_image[3 * pix + 2];
+                    const float vod = with_depth ? v_depth_img[pix] : 0.0f;
                     const int fin = final_idx[pix];
                     for (int p = std::min(e - 1, fin); p >= s; --p) {
                         ++pairs;
@@ -370,9 +381,13 @@ void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t
                         va += -Tf * ra * c.bg[0] * vo0;
                         va += -Tf * ra * c.bg[1] * vo1;
                         va += -Tf * ra * c.bg[2] * vo2;
+                        if (with_depth) {
+                            va += (z[g] * T - bz * ra) * vod;
+                            bz += z[g] * fac;
+                        }
                         b0 += col[0] * fac; b1 += col[1] * fac; b2 += col[2] * fac;
                         const float vs = -o * vis * va;
-                        double* a = loc.data() + (size_t)(p - s) * 9;
+                        double* a = loc.data() + (size_t)(p - s) * kA;
                         a[0] += vs * (q[0] * dx + q[1] * dy);
                         a[1] += vs * (q[1] * dx + q[2] * dy);
                         a[2] += 0.5f * vs * dx * dx;
@@ -380,12 +395,13 @@ void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t
                         a[4] += 0.5f * vs * dy * dy;
                         a[5] += fac * vo0; a[6] += fac * vo1; a[7] += fac * vo2;
                         a[8] += vis * va;
+                        if (with_depth) a[9] += fac * vod;
                     }
                 }
             for (int p = s; p < e; ++p) {
-                const double* a = loc.data() + (size_t)(p - s) * 9;
-                double* d = acc.data() + (size_t)ids[p] * 9;
-                for (int k = 0; k < 9; ++k)
+                const double* a = loc.data() + (size_t)(p - s) * kA;
+                double* d = acc.data() + (size_t)ids[p] * kA;
+                for (int k = 0; k < kA; ++k)
                     if (a[k] != 0.0) {
 #pragma omp atomic
                         d[k] += a[k];
@@ -394,7 +410,8 @@ void orc_blend_backward(const Cam* cam, int N, const int32_t* ids, const int32_t
         }
     }
     for (int i = 0; i < N; ++i) {
-        const double* a = acc.data() + (size_t)i * 9;
+        const double* a = acc.data() + (size_t)i * kA;
+        if (with_depth) v_z[i] = (float)a[9];
         v_xy[2 * (size_t)i] = (float)a[0]; v_xy[2 * (size_t)i + 1] = (float)a[1];
         v_conic[3 * (size_t)i] = (float)a[2]; v_conic[3 * (size_t)i + 1] = (float)a[3]; v_conic[3 * (size_t)i + 2] = (float)a[4];
         v_rgb[3 * (size_t)i] = (float)a[5]; v_rgb[3 * (size_t)i + 1] = (float)a[6]; v_rgb[3 * (size_t)i + 2] = (float)a[7];
@@ -430,7 +447,8 @@ void orc_sh_backward(const Cam* cam, int N, int num_bases, const float* means, c
 // Only splats with radius > 0 get gradients; every output row of the others is zero.
 void orc_project_backward(const Cam* cam, int N, const float* means, const float* scales, const float* rots,
                           const float* conic, const float* cov3d, const int32_t* radii, const float* v_xy,
-                          const float* v_conic, float* v_mean, float* v_scale, float* v_rot, float* v_cov3d) {
+                          const float* v_conic, float* v_mean, float* v_scale, float* v_rot, float* v_cov3d,
+                          const float* v_z) {
     const Cam& c = *cam;
     const float fx = c.W / (2.0f * std::tan((2 * std::atan(c.tanfovx)) / 2.0f));
     const float fy = c.H / (2.0f * std::tan((2 * std::atan(c.tanfovy)) / 2.0f));
@@ -456,6 +474,10 @@ void orc_project_backward(const Cam* cam, int N, const float* means, const float
             vm[0] = V[0] * vv[0] + V[4] * vv[1] + V[8] * vv[2];
             vm[1] = V[1] * vv[0] + V[5] * vv[1] + V[9] * vv[2];
             vm[2] = V[2] * vv[0] + V[6] * vv[1] + V[10] * vv[2];
+        }
+        // view-space depth gradient: backward.cu:253-259 (the reference always passes zeros here)
+        if (v_z) {
+            vm[0] += V[8] * v_z[i]; vm[1] += V[9] * v_z[i]; vm[2] += V[10] * v_z[i];
         }
         // conic -> cov2d: helpers.cuh:68-79  (v_Sigma = -X G X)
         float vcov2[3];

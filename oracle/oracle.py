@@ -145,8 +145,9 @@ def tile_ranges(keys, H, W):
     return out
 
 
-def blend_forward(cam: Camera, ids, ranges, xy, conic, rgb, opac):
-    """Stage (e): returns image[H,W,3], final_T[H,W], final_idx[H,W], pairs evaluated."""
+def blend_forward(cam: Camera, ids, ranges, xy, conic, rgb, opac, z=None):
+    """Stage (e): returns image[H,W,3], final_T[H,W], final_idx[H,W], pairs evaluated -- and, when the per-splat
+    view-space depths ``z`` are given, the blended depth map[H,W] as a fifth value."""
     ids, ranges = np.ascontiguousarray(ids, np.int32), np.ascontiguousarray(ranges, np.int32)
     xy, conic, rgb, opac = _f32(xy), _f32(conic), _f32(rgb), _f32(opac).reshape(-1)
     image = np.zeros((cam.H, cam.W, 3), np.float32)
@@ -154,13 +155,21 @@ def blend_forward(cam: Camera, ids, ranges, xy, conic, rgb, opac):
     fi = np.zeros((cam.H, cam.W), np.int32)
     pairs = np.zeros(2, np.int64)
     cs = cam.c()
+    depth = None
+    if z is not None:
+        z = _f32(z).reshape(-1)
+        depth = np.zeros((cam.H, cam.W), np.float32)
     lib().orc_blend_forward(C.byref(cs), _p(ids), _p(ranges), _p(xy), _p(conic), _p(rgb), _p(opac), _p(image),
-                            _p(ft), _p(fi), _p(pairs))
+                            _p(ft), _p(fi), _p(pairs), _p(z) if z is not None else None,
+                            _p(depth) if depth is not None else None)
+    if z is not None:
+        return image, ft, fi, int(pairs[0]), depth
     return image, ft, fi, int(pairs[0])
 
 
-def blend_backward(cam: Camera, n, ids, ranges, xy, conic, rgb, opac, final_T, final_idx, v_image):
-    """Stage (f1): returns v_xy[N,2], v_conic[N,3], v_rgb[N,3], v_opacity[N], pairs visited."""
+def blend_backward(cam: Camera, n, ids, ranges, xy, conic, rgb, opac, final_T, final_idx, v_image, z=None, v_depth=None):
+    """Stage (f1): returns v_xy[N,2], v_conic[N,3], v_rgb[N,3], v_opacity[N], pairs visited -- and, when ``z`` and the
+    depth map's gradient ``v_depth`` are given, v_z[N] as a sixth value."""
     ids, ranges = np.ascontiguousarray(ids, np.int32), np.ascontiguousarray(ranges, np.int32)
     xy, conic, rgb, opac = _f32(xy), _f32(conic), _f32(rgb), _f32(opac).reshape(-1)
     final_T, v_image = _f32(final_T), _f32(v_image)
@@ -168,10 +177,18 @@ def blend_backward(cam: Camera, n, ids, ranges, xy, conic, rgb, opac, final_T, f
     v_xy, v_conic = np.empty((n, 2), np.float32), np.empty((n, 3), np.float32)
     v_rgb, v_op = np.empty((n, 3), np.float32), np.empty(n, np.float32)
     pairs = np.zeros(2, np.int64)
+    with_depth = z is not None and v_depth is not None
+    if with_depth:
+        z, v_depth, v_z = _f32(z).reshape(-1), _f32(v_depth), np.zeros(n, np.float32)
+        depth_args = (_p(z), _p(v_depth), _p(v_z))
+    else:
+        depth_args = (None, None, None)
     cs = cam.c()
     lib().orc_blend_backward(C.byref(cs), C.c_int(n), _p(ids), _p(ranges), _p(xy), _p(conic), _p(rgb), _p(opac),
                              _p(final_T), _p(final_idx), _p(v_image), _p(v_xy), _p(v_conic), _p(v_rgb), _p(v_op),
-                             _p(pairs))
+                             _p(pairs), *depth_args)
+    if with_depth:
+        return v_xy, v_conic, v_rgb, v_op, int(pairs[0]), v_z
     return v_xy, v_conic, v_rgb, v_op, int(pairs[0])
 
 
@@ -184,20 +201,22 @@ def sh_backward(cam: Camera, means, v_rgb, num_bases=16):
     return out
 
 
-def project_backward(cam: Camera, means, scales, rots, conic, cov3d, radii, v_xy, v_conic):
+def project_backward(cam: Camera, means, scales, rots, conic, cov3d, radii, v_xy, v_conic, v_z=None):
     means, scales, rots = _f32(means), _f32(scales), _f32(rots)
     conic, cov3d, v_xy, v_conic = _f32(conic), _f32(cov3d), _f32(v_xy), _f32(v_conic)
     radii = np.ascontiguousarray(radii, np.int32)
     n = means.shape[0]
     v_mean, v_scale = np.empty((n, 3), np.float32), np.empty((n, 3), np.float32)
     v_rot, v_cov3d = np.empty((n, 4), np.float32), np.empty((n, 6), np.float32)
+    v_z = None if v_z is None else _f32(v_z).reshape(-1)
     cs = cam.c()
     lib().orc_project_backward(C.byref(cs), C.c_int(n), _p(means), _p(scales), _p(rots), _p(conic), _p(cov3d),
-                               _p(radii), _p(v_xy), _p(v_conic), _p(v_mean), _p(v_scale), _p(v_rot), _p(v_cov3d))
+                               _p(radii), _p(v_xy), _p(v_conic), _p(v_mean), _p(v_scale), _p(v_rot), _p(v_cov3d),
+                               _p(v_z))
     return v_mean, v_scale, v_rot, v_cov3d
 
 
-def forward(cam: Camera, means, shs, opacities, scales, rots, drop_last=True):
+def forward(cam: Camera, means, shs, opacities, scales, rots, drop_last=True, with_depth=False):
     """Whole forward the way cpp/rasterizer_torch.cu:170-208 chains the stages; returns a dict of every
     intermediate (pre, keys, ids, ranges, image, final_T, final_idx, K, pairs_fwd)."""
     pre = preprocess(cam, means, shs, opacities, scales, rots)
@@ -205,22 +224,33 @@ def forward(cam: Camera, means, shs, opacities, scales, rots, drop_last=True):
     keys, ids = sort_pairs(keys, ids)
     ranges = tile_ranges(keys, cam.H, cam.W)
     opac = _f32(opacities).reshape(-1)
-    image, ft, fi, pairs = blend_forward(cam, ids, ranges, pre["xy"], pre["conic"], pre["rgb"], opac)
+    depth = None
+    if with_depth:
+        image, ft, fi, pairs, depth = blend_forward(cam, ids, ranges, pre["xy"], pre["conic"], pre["rgb"], opac, pre["depth"])
+    else:
+        image, ft, fi, pairs = blend_forward(cam, ids, ranges, pre["xy"], pre["conic"], pre["rgb"], opac)
     return dict(pre=pre, keys=keys, ids=ids, ranges=ranges, image=image, final_T=ft, final_idx=fi,
-                K=int(keys.shape[0]), pairs_fwd=pairs)
+                K=int(keys.shape[0]), pairs_fwd=pairs, depth=depth)
 
 
-def backward(cam: Camera, fwd, means, shs, opacities, scales, rots, v_image):
-    """Whole backward (cpp/rasterizer_torch.cu:263-316); returns the reference's 8 gradients by name."""
+def backward(cam: Camera, fwd, means, shs, opacities, scales, rots, v_image, v_depth=None):
+    """Whole backward (cpp/rasterizer_torch.cu:263-316); returns the reference's 8 gradients by name.  ``v_depth``
+    (gradient of the optional depth map) is routed through the v_depth slot of the projection backward."""
     pre = fwd["pre"]
     n = _f32(means).shape[0]
     opac = _f32(opacities).reshape(-1)
-    v_xy, v_conic, v_rgb, v_op, pairs = blend_backward(cam, n, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"],
-                                                       pre["rgb"], opac, fwd["final_T"], fwd["final_idx"], v_image)
+    v_z = None
+    if v_depth is not None:
+        v_xy, v_conic, v_rgb, v_op, pairs, v_z = blend_backward(cam, n, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"],
+                                                                pre["rgb"], opac, fwd["final_T"], fwd["final_idx"], v_image,
+                                                                pre["depth"], v_depth)
+    else:
+        v_xy, v_conic, v_rgb, v_op, pairs = blend_backward(cam, n, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"],
+                                                           pre["rgb"], opac, fwd["final_T"], fwd["final_idx"], v_image)
     num_bases = _f32(shs).shape[-2]
     v_sh = sh_backward(cam, means, v_rgb, num_bases)
     v_mean, v_scale, v_rot, v_cov3d = project_backward(cam, means, scales, rots, pre["conic"], pre["cov3d"],
-                                                       pre["radii"], v_xy, v_conic)
+                                                       pre["radii"], v_xy, v_conic, v_z)
     v_means2d = np.concatenate([v_xy, np.zeros((n, 1), np.float32)], axis=1)
     return dict(v_means3d=v_mean, v_means2d=v_means2d, v_shs=v_sh, v_colors=v_rgb, v_opacities=v_op.reshape(n, 1),
                 v_scales=v_scale, v_rotations=v_rot, v_cov3d=v_cov3d, v_conic=v_conic, pairs_bwd=pairs)

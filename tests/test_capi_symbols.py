@@ -47,7 +47,7 @@ def test_host_only_calls(lib):
 def test_argument_errors_are_reported_not_crashed(lib):
     from ds_splat_b200 import _capi
     cam = _capi.DsbCamera()  # all zero: invalid image size
-    rc = lib.dsb_blend_forward(C.byref(cam), None, None, None, None, None, None, None)
+    rc = lib.dsb_blend_forward(C.byref(cam), None, None, None, None, None, None, None, None)
     assert rc == -1
     assert b"image size" in lib.dsb_last_error()
     rc = lib.dsb_sort_pairs(None, None, 10, 40, 32, None, 0, None, None)

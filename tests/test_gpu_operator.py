@@ -188,3 +188,29 @@ def test_fused_render_matches_stage_calls():
     assert torch.equal(fused_pairs, sp)
     assert torch.equal(fused_ranges, ranges)
     assert torch.equal(image, img2)
+
+
+def test_return_depth_is_differentiable_and_leaves_the_image_alone():
+    sc = scenes.tiny(n=6000, seed=77, W=208, H=144, focal=200.0)
+    view = sc.views[0]
+    p0, _, image0, radii0 = _run_operator(sc, view)
+    t = scene_tensors(sc)
+    p = {k: v.clone().requires_grad_(True) for k, v in t.items()}
+    rast = GaussianRasterizer(settings_for(view, return_depth=True))
+    image, radii, depth = rast(p["means"], None, p["shs"], None, p["opacities"], p["scales"], p["rotations"], None)
+    assert torch.equal(image, image0) and torch.equal(radii, radii0) and depth.shape == (view.H, view.W)
+    cam = oracle_camera(view)
+    fwd = O.forward(cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, with_depth=True)
+    err = np.abs(depth.detach().cpu().numpy() - fwd["depth"])
+    assert (err > 1e-4).mean() < 2e-3  # raw-input comparison: a flipped radius or threshold moves a few pixels
+    # a loss on the depth map alone reaches the geometry but not the colours
+    rng = np.random.default_rng(3)
+    v_depth = rng.normal(0, 1e-3, (view.H, view.W)).astype(np.float32)
+    depth.backward(torch.from_numpy(v_depth).cuda())
+    torch.cuda.synchronize()
+    bwd = O.backward(cam, fwd, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations,
+                     np.zeros((view.H, view.W, 3), np.float32), v_depth)
+    assert float(p["shs"].grad.abs().max()) == 0.0
+    assert _rel(p["means"].grad.cpu().numpy(), bwd["v_means3d"]) < 1e-2
+    assert _rel(p["opacities"].grad.cpu().numpy(), bwd["v_opacities"]) < 1e-2
+    assert _rel(p["scales"].grad.cpu().numpy(), bwd["v_scales"]) < 1e-2

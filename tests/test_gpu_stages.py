@@ -194,3 +194,43 @@ def test_backward_matches_oracle(run):
                                    run["cov3d"], run["radii"], acc, accumulate=True, out={k: v.clone() for k, v in out.items()})
     for name in ("v_means3d", "v_shs", "v_scales", "v_rotations", "v_opacities"):
         np.testing.assert_allclose(out2[name].cpu().numpy(), 2 * g[name], rtol=1e-6, atol=0)
+
+
+def test_depth_map_and_its_gradient_match_oracle(run):
+    """Optional depth output (no reference counterpart): checked against the CPU checker's definition, the
+    view-space z blended like a fourth colour channel, on the GPU's own records and lists."""
+    sc, view = run["sc"], run["view"]
+    rec = unpack_records(run["records"].cpu().numpy())
+    ids = (run["sorted_pairs"].cpu().numpy().view(np.uint64) & np.uint64(0xFFFFFFFF)).astype(np.int32)
+    ranges = run["ranges"].cpu().numpy()
+    image, ft, fi, depth = _capi.blend_forward(run["cam"], run["records"], run["sorted_pairs"], run["ranges"], with_depth=True)
+    torch.cuda.synchronize()
+    assert torch.equal(image, run["image"]) and torch.equal(fi, run["final_idx"])  # colour path untouched by the depth path
+    _, _, fi_o, _, depth_o = O.blend_forward(run["ocam"], ids, ranges, rec["xy"], rec["conic"], rec["rgb"], rec["opac"], rec["depth"])
+    same = fi.cpu().numpy() == fi_o
+    err = np.abs(depth.cpu().numpy() - depth_o)
+    scale = float(depth_o.max())
+    assert (err[same] <= 1e-5 * max(scale, 1.0)).mean() > 0.9998 and same.mean() > 0.9998
+
+    rng = np.random.default_rng(11)
+    v_image = sc.image_grad()
+    v_depth = rng.normal(0, 1e-3, (view.H, view.W)).astype(np.float32)
+    v_xy, v_conic, v_rgb, v_op, _, v_z = O.blend_backward(run["ocam"], sc.n, ids, ranges, rec["xy"], rec["conic"], rec["rgb"],
+                                                          rec["opac"], ft.cpu().numpy(), fi.cpu().numpy(), v_image,
+                                                          rec["depth"], v_depth)
+    acc = _capi.blend_backward(run["cam"], run["records"], run["sorted_pairs"], run["ranges"], ft, fi,
+                               torch.from_numpy(v_image).cuda(), torch.from_numpy(v_depth).cuda())
+    a = acc.cpu().numpy()
+    assert _rel_err(a[:, 0:2], v_xy) < 1e-3
+    assert _rel_err(np.stack([a[:, 2], a[:, 3], a[:, 4]], 1), v_conic) < 1e-3
+    assert _rel_err(a[:, 5], v_op) < 1e-3
+    assert _rel_err(np.stack([a[:, 6], a[:, 7], a[:, 8]], 1), v_rgb) < 1e-3
+    assert _rel_err(a[:, 9], v_z) < 1e-3
+    np.testing.assert_array_equal(a[:, 10:], 0)
+    out = _capi.geometry_backward(run["cam"], run["t"]["means"], run["t"]["scales"], run["t"]["rotations"], run["records"],
+                                  run["cov3d"], run["radii"], acc)
+    v_conic_g = np.ascontiguousarray(np.stack([a[:, 2], a[:, 3], a[:, 4]], 1))
+    vm, _, _, _ = O.project_backward(run["ocam"], sc.means, sc.scales, sc.rotations, rec["conic"], run["cov3d"].cpu().numpy(),
+                                     run["radii"].cpu().numpy(), np.ascontiguousarray(a[:, 0:2]), v_conic_g,
+                                     np.ascontiguousarray(a[:, 9]))
+    assert _rel_err(out["v_means3d"].cpu().numpy(), vm) < 1e-3

@@ -113,3 +113,43 @@ def test_scene_generators_are_deterministic():
     v = a.views[0]
     np.testing.assert_allclose(v.view[:3, :3] @ v.view[:3, :3].T, np.eye(3), atol=1e-6)
     np.testing.assert_array_equal(v.viewmatrix_t, v.view.T)
+
+
+def test_depth_map_is_a_fourth_colour_channel(small):
+    """The optional depth output has no reference counterpart; the checker defines it as the splat's view-space
+    z blended like a colour.  Pin that definition against the colour path itself: rendering with z in the red
+    channel must give the depth map, and its gradient must come back as v_z (and reach the same v_xy, v_conic,
+    v_opacity) when the depth map's gradient is fed as the red channel's."""
+    sc, cam, fwd = small
+    pre = fwd["pre"]
+    opac = sc.opacities.reshape(-1)
+    z = pre["depth"]
+    rgb_z = np.zeros_like(pre["rgb"])
+    rgb_z[:, 0] = z
+    img_z, ft, fi, _ = O.blend_forward(cam, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"], rgb_z, opac)
+    image, ft2, fi2, _, depth = O.blend_forward(cam, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"], pre["rgb"], opac, z)
+    np.testing.assert_array_equal(image, fwd["image"])
+    np.testing.assert_array_equal(depth, img_z[:, :, 0])
+    assert depth.max() > 0 and np.isfinite(depth).all()
+
+    rng = np.random.default_rng(5)
+    v_depth = rng.normal(0, 1e-3, (cam.H, cam.W)).astype(np.float32)
+    v_img_z = np.zeros((cam.H, cam.W, 3), np.float32)
+    v_img_z[:, :, 0] = v_depth
+    zero_img = np.zeros_like(v_img_z)
+    a = O.blend_backward(cam, sc.n, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"], rgb_z, opac, ft, fi, v_img_z)
+    b = O.blend_backward(cam, sc.n, fwd["ids"], fwd["ranges"], pre["xy"], pre["conic"], pre["rgb"], opac, ft, fi, zero_img,
+                         z, v_depth)
+    np.testing.assert_allclose(b[0], a[0], rtol=1e-5, atol=1e-12)        # v_xy
+    np.testing.assert_allclose(b[1], a[1], rtol=1e-5, atol=1e-12)        # v_conic
+    np.testing.assert_allclose(b[3], a[3], rtol=1e-5, atol=1e-12)        # v_opacity
+    np.testing.assert_allclose(b[5], a[2][:, 0], rtol=1e-5, atol=1e-12)  # v_z == gradient of the "red = z" channel
+    assert np.abs(b[2]).max() == 0                                       # no colour gradient from a depth-only loss
+    # v_z reaches the mean along the view matrix's third row (cpp/gsplat/backward.cu:253-259)
+    zeros2, zeros3 = np.zeros((sc.n, 2), np.float32), np.zeros((sc.n, 3), np.float32)
+    vm, _, _, _ = O.project_backward(cam, sc.means, sc.scales, sc.rotations, pre["conic"], pre["cov3d"], pre["radii"],
+                                     zeros2, zeros3, b[5])
+    vis = pre["radii"] > 0
+    V = np.asarray(sc.views[0].view, np.float32).reshape(4, 4)
+    np.testing.assert_allclose(vm[vis], b[5][vis, None] * V[2, :3][None, :], rtol=1e-6, atol=1e-12)
+    assert np.abs(vm[~vis]).max() == 0
