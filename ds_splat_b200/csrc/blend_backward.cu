@@ -5,17 +5,21 @@
 // (two block barriers per 256 entries), evaluates every entry for every pixel, reduces 9 values with 9
 // full warp reductions (45 shuffles) and issues 9 scalar atomics per warp per entry.
 //
-// Here each WARP is on its own.  Every warp of a block owns a compact 8x4-pixel block of the block's tile
-// (blend_common.cuh) and walks the tile's list back to front in chunks of 32 entries, with no block barrier
-// anywhere, so a warp whose pixels ended early is finished early and nobody waits for the slowest warp:
+// Here each WARP is on its own.  A warp owns a compact block of kPix * 32 pixels of a tile (8 x 16 by default)
+// and every lane works on kPix pixels of one column (rows y, y + 4, ...).  The warp walks the tile's list back
+// to front in chunks of 32 entries, with no block barrier anywhere, so a warp whose pixels ended early is
+// finished early and nobody waits for the slowest warp; thread blocks are small (two warps) so that a
+// finished warp's registers go back to the scheduler at once.
 //   * fetch + cull: lane l fetches entry l of the chunk (48-byte record) and tests in closed form whether
 //     the splat can reach the warp's pixels at all; a ballot gives the survivors;
 //   * blend: survivors are parked in the warp's private shared-memory slice and processed one by one.
 //     exp is only evaluated for pixels with q <= ln(255 opacity) + margin, after which the reference's own
 //     test (clamped alpha < 1/255) decides.  Per pixel the nine sums are moments that need few multiplies,
 //         S0 = sum v_s, Sx = sum v_s dx, Sy = sum v_s dy, Sxx, Sxy, Syy, and the three colour sums;
-//     the warp reduces them with a transposing butterfly (8 values in 4+2+1+1+1 shuffles, the ninth in 5)
-//     into the entry's row of the warp's accumulator slice;
+//     a lane adds the moments of its kPix pixels in registers, then the warp reduces them with a transposing
+//     butterfly (8 values in 4+2+1+1+1 shuffles, the ninth in 5) into the entry's row of the warp's
+//     accumulator slice -- so the reduction, the record reads and the loop control are paid once per
+//     kPix * 32 pixels, and the kPix independent transmittance chains of a lane hide each other's latency;
 //   * flush: lane l, which still holds entry l's record in registers, turns its row of moments into
 //         v_xy = (a Sx + b Sy, b Sx + c Sy), v_conic = (Sxx/2, Sxy, Syy/2), v_opacity = -S0 / opacity
 //     and issues two red.global.add.v4.f32 and one scalar red: 3 vector atomics per (warp, splat) that
@@ -35,8 +39,6 @@ namespace dsb {
 
 namespace {
 
-constexpr int kThreads = kTilePixels;
-constexpr int kWarps = kThreads / 32;
 
 __device__ __forceinline__ void red_add_v4(float4* addr, const float4 v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
@@ -78,36 +80,76 @@ __device__ __forceinline__ float butterfly1(float v) {
     return v;
 }
 
+// ---- mapping of pixels to warps and lanes ------------------------------------------------------------------
+// Measured on B200 (1M splats at 1080p / 3M at 4K / 2M wide splats, ms): one pixel per lane in 256-thread
+// blocks 0.71 / 3.93 / 0.97; 2 pixels, 8x8 block, 64 threads 0.57 / 2.95 / 0.80; 4 pixels, 8x16 block,
+// 64 threads 0.55 / 2.74 / 0.85 (the default); 16-wide blocks and 32- or 256-thread blocks are slower.
+#ifndef DSB_BWD_PIX
+#define DSB_BWD_PIX 4   // pixels per lane: 1, 2, 4 or 8
+#endif
+#ifndef DSB_BWD_BLOCK_W
+#define DSB_BWD_BLOCK_W 8    // width of a warp's pixel block: 16 or 8
+#endif
+constexpr int kPix = DSB_BWD_PIX;
+constexpr int kBlockW = DSB_BWD_BLOCK_W;
+constexpr int kRowsPerPass = 32 / kBlockW;               // rows the 32 lanes cover at once
+constexpr int kBlockH = kRowsPerPass * kPix;             // pixel block of one warp is kBlockW x kBlockH
+constexpr int kBlocksPerTileX = kTile / kBlockW, kBlocksPerTileY = kTile / kBlockH;
+constexpr int kBlocksPerTile = kBlocksPerTileX * kBlocksPerTileY;
+static_assert(kBlockH <= kTile && kTile % kBlockH == 0, "a warp's pixel block must tile the 16x16 tile");
+// Warps never synchronise with each other, and their lists differ in length; small thread blocks give the
+// slots of a finished warp back to the scheduler instead of holding them until the block's slowest warp ends.
+#ifndef DSB_BWD_THREADS
+#define DSB_BWD_THREADS 64
+#endif
+#ifndef DSB_BWD_MIN_BLOCKS
+#define DSB_BWD_MIN_BLOCKS 1
+#endif
+constexpr int kThreads = DSB_BWD_THREADS, kWarps = kThreads / 32;
+
 template <bool DEPTH>
-__global__ void __launch_bounds__(kThreads)
-blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, const float4* __restrict__ records,
-                      const u64* __restrict__ sorted, const int32_t* __restrict__ ranges,
-                      const float* __restrict__ final_T, const int32_t* __restrict__ final_idx,
-                      const float* __restrict__ v_image, const float* __restrict__ v_depth, float4* __restrict__ grad_acc) {
+__global__ void __launch_bounds__(kThreads, DSB_BWD_MIN_BLOCKS)
+blend_backward_kernel(const int W, const int H, const int tiles_x, const int num_tiles, const float* __restrict__ bg,
+                            const float4* __restrict__ records, const u64* __restrict__ sorted,
+                            const int32_t* __restrict__ ranges, const float* __restrict__ final_T,
+                            const int32_t* __restrict__ final_idx, const float* __restrict__ v_image,
+                            const float* __restrict__ v_depth, float4* __restrict__ grad_acc) {
     __shared__ float4 s_rec[kWarps][32][3];   // x,y,a,b | c,opacity,r,g | blue, threshold, z, -
     __shared__ float s_acc[kWarps][32][12];   // moments of the chunk's entries
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const WarpPixels wp = warp_pixels(blockIdx.x, blockIdx.y, warp, lane);
-    const int x = wp.x, y = wp.y;
-    const bool inside = x < W && y < H;
-    const float px = (float)x + 0.5f, py = (float)y + 0.5f;
+    const int wb = blockIdx.x * kWarps + warp;             // warp-level pixel block
+    const int tile = wb / kBlocksPerTile;
+    if (tile >= num_tiles) return;                         // whole warps only; no block-wide barrier below
+    const int sub = wb - tile * kBlocksPerTile;
+    const int tile_x = tile % tiles_x, tile_y = tile / tiles_x;
+    const int bx = tile_x * kTile + (sub % kBlocksPerTileX) * kBlockW, by = tile_y * kTile + (sub / kBlocksPerTileX) * kBlockH;
+    const int x = bx + (lane % kBlockW), y0 = by + (lane / kBlockW);
+    const float px = (float)x + 0.5f, py0 = (float)y0 + 0.5f;
     const int start = ranges[tile], end = ranges[tile + 1];
 
-    float Tf = 1.0f, vo0 = 0.0f, vo1 = 0.0f, vo2 = 0.0f, vod = 0.0f;
-    int fin = -1;
-    if (inside) {
-        const size_t pix = (size_t)y * W + x;
-        Tf = final_T[pix];
-        fin = final_idx[pix];
-        vo0 = v_image[3 * pix]; vo1 = v_image[3 * pix + 1]; vo2 = v_image[3 * pix + 2];
-        if (DEPTH) vod = v_depth[pix];
+    float T[kPix], b0[kPix], b1[kPix], b2[kPix], bz[kPix], vo0[kPix], vo1[kPix], vo2[kPix], vod[kPix], tfbg[kPix];
+    int fin[kPix];
+    int fin_max = -1;
+#pragma unroll
+    for (int p = 0; p < kPix; ++p) {
+        const int y = y0 + kRowsPerPass * p;
+        T[p] = 1.0f; b0[p] = b1[p] = b2[p] = bz[p] = 0.0f;
+        vo0[p] = vo1[p] = vo2[p] = vod[p] = tfbg[p] = 0.0f;
+        fin[p] = -1;                                       // outside the image: never valid
+        if (x < W && y < H) {
+            const size_t pix = (size_t)y * W + x;
+            T[p] = final_T[pix];
+            fin[p] = final_idx[pix];
+            vo0[p] = v_image[3 * pix]; vo1[p] = v_image[3 * pix + 1]; vo2[p] = v_image[3 * pix + 2];
+            if (DEPTH) vod[p] = v_depth[pix];
+            const float bgdot = bg ? (bg[0] * vo0[p] + bg[1] * vo1[p] + bg[2] * vo2[p]) : 0.0f;
+            tfbg[p] = T[p] * bgdot;
+        }
+        fin_max = max(fin_max, fin[p]);
     }
-    const float bgdot = bg ? (bg[0] * vo0 + bg[1] * vo1 + bg[2] * vo2) : 0.0f;
     // Entries after the last one any pixel of the warp blended cannot contribute.
-    const int top = min(end - 1, __reduce_max_sync(0xffffffffu, fin));
-    float T = Tf, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, bz = 0.0f;
+    const int top = min(end - 1, __reduce_max_sync(0xffffffffu, fin_max));
 
     float4 (*rec)[3] = s_rec[warp];
     float (*acc)[12] = s_acc[warp];
@@ -126,7 +168,7 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             const float4 q2 = __ldg(r + 2);
             blue = q2.x; zview = q2.y;
             thr = __logf(255.0f * q1.y) + kCullMargin;
-            hit = splat_reaches_block(q0.x, q0.y, q0.z, q0.w, q1.x, thr, wp.x0, wp.y0);
+            hit = splat_reaches_rect<kBlockW, kBlockH>(q0.x, q0.y, q0.z, q0.w, q1.x, thr, (float)bx, (float)by);
         }
         u32 todo = __ballot_sync(0xffffffffu, hit);
         if (todo == 0) continue;
@@ -142,48 +184,54 @@ blend_backward_kernel(const int W, const int H, const float* __restrict__ bg, co
             const float4 qa = rec[t][0];
             const float4 qb = rec[t][1];
             const float4 qc = rec[t][2];
-            const float dx = qa.x - px, dy = qa.y - py;
-            const float sigma = 0.5f * (qa.z * dx * dx + qb.x * dy * dy) + qa.w * dx * dy;
-            const bool valid = inside && pos <= fin && sigma >= 0.f && sigma <= qc.y;
-            if (!__any_sync(0xffffffffu, valid)) continue;
-            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            float v8 = 0.f, v9 = 0.f;
-            if (valid) {
-                const float vis = __expf(-sigma);
-                const float alpha = min(0.99f, qb.y * vis);
-                if (!(alpha < 1.f / 255.f)) {
-                    const float ra = 1.f / (1.f - alpha);
-                    T *= ra;
-                    const float fac = alpha * T;
-                    float v_alpha = 0.f;
-                    v_alpha += (qb.z * T - b0 * ra) * vo0;
-                    v_alpha += (qb.w * T - b1 * ra) * vo1;
-                    v_alpha += (qc.x * T - b2 * ra) * vo2;
-                    v_alpha += -Tf * ra * bgdot;
-                    if (DEPTH) {
-                        v_alpha += (qc.z * T - bz * ra) * vod;
-                        bz += qc.z * fac;
-                        v9 = fac * vod;
+            const float dx = qa.x - px;
+            float dy[kPix], sigma[kPix];
+            bool valid[kPix], any = false;
+#pragma unroll
+            for (int p = 0; p < kPix; ++p) {
+                dy[p] = qa.y - (py0 + (float)(kRowsPerPass * p));
+                sigma[p] = 0.5f * (qa.z * dx * dx + qb.x * dy[p] * dy[p]) + qa.w * dx * dy[p];
+                valid[p] = pos <= fin[p] && sigma[p] >= 0.f && sigma[p] <= qc.y;
+                any = any || valid[p];
+            }
+            if (!__any_sync(0xffffffffu, any)) continue;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, cr = 0.f, cg = 0.f, cb = 0.f, cz = 0.f;
+#pragma unroll
+            for (int p = 0; p < kPix; ++p) {
+                if (valid[p]) {
+                    const float vis = __expf(-sigma[p]);
+                    const float alpha = min(0.99f, qb.y * vis);
+                    if (!(alpha < 1.f / 255.f)) {
+                        const float ra = 1.f / (1.f - alpha);
+                        T[p] *= ra;
+                        const float fac = alpha * T[p];
+                        float v_alpha = 0.f;
+                        v_alpha += (qb.z * T[p] - b0[p] * ra) * vo0[p];
+                        v_alpha += (qb.w * T[p] - b1[p] * ra) * vo1[p];
+                        v_alpha += (qc.x * T[p] - b2[p] * ra) * vo2[p];
+                        v_alpha += -tfbg[p] * ra;
+                        if (DEPTH) {
+                            v_alpha += (qc.z * T[p] - bz[p] * ra) * vod[p];
+                            bz[p] += qc.z * fac;
+                            cz += fac * vod[p];
+                        }
+                        b0[p] += qb.z * fac; b1[p] += qb.w * fac; b2[p] += qc.x * fac;
+                        const float v_sigma = -qb.y * vis * v_alpha;
+                        s0 += v_sigma;
+                        s1 += v_sigma * dy[p];
+                        s2 += v_sigma * dy[p] * dy[p];
+                        cr += fac * vo0[p]; cg += fac * vo1[p]; cb += fac * vo2[p];
                     }
-                    b0 += qb.z * fac; b1 += qb.w * fac; b2 += qc.x * fac;
-                    const float v_sigma = -qb.y * vis * v_alpha;
-                    v[0] = v_sigma * dx;   // Sx
-                    v[1] = v_sigma * dy;   // Sy
-                    v[2] = v[0] * dx;      // Sxx
-                    v[3] = v[0] * dy;      // Sxy
-                    v[4] = v[1] * dy;      // Syy
-                    v[5] = v_sigma;        // S0
-                    v[6] = fac * vo0;
-                    v[7] = fac * vo1;
-                    v8 = fac * vo2;
                 }
             }
+            const float sx = s0 * dx;
+            const float v[8] = {sx, s1, sx * dx, s1 * dx, s2, s0, cr, cg};   // Sx, Sy, Sxx, Sxy, Syy, S0, r, g
             const float sum = butterfly8(v, lane);
-            const float sum8 = butterfly1(v8);
+            const float sum8 = butterfly1(cb);
             if ((lane & 3) == 0) acc[t][lane >> 2] = sum;
             if (lane == 0) acc[t][8] = sum8;
             if (DEPTH) {
-                const float sum9 = butterfly1(v9);
+                const float sum9 = butterfly1(cz);
                 if (lane == 0) acc[t][9] = sum9;
             }
             touched |= 1u << t;
@@ -213,15 +261,18 @@ int launch_blend_backward(const CamParams& cp, const float* records, const u64* 
                           float* grad_acc, cudaStream_t s) {
     DSB_REQUIRE(ranges && final_T && final_idx && v_image && grad_acc, "blend_backward: null pointer");
     DSB_REQUIRE(((uintptr_t)grad_acc & 15) == 0, "blend_backward: grad_acc must be 16-byte aligned");
-    const dim3 grid(cp.tiles_x, cp.tiles_y);
+    const int num_tiles = cp.tiles_x * cp.tiles_y;
+    const int blocks = (num_tiles * kBlocksPerTile + kWarps - 1) / kWarps;
     if (v_depth)
-        blend_backward_kernel<true><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.bg, reinterpret_cast<const float4*>(records),
-                                                             sorted, ranges, final_T, final_idx, v_image, v_depth,
-                                                             reinterpret_cast<float4*>(grad_acc));
+        blend_backward_kernel<true><<<blocks, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles, cp.bg,
+                                                                     reinterpret_cast<const float4*>(records), sorted, ranges,
+                                                                     final_T, final_idx, v_image, v_depth,
+                                                                     reinterpret_cast<float4*>(grad_acc));
     else
-        blend_backward_kernel<false><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.bg, reinterpret_cast<const float4*>(records),
-                                                              sorted, ranges, final_T, final_idx, v_image, nullptr,
-                                                              reinterpret_cast<float4*>(grad_acc));
+        blend_backward_kernel<false><<<blocks, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles, cp.bg,
+                                                                      reinterpret_cast<const float4*>(records), sorted, ranges,
+                                                                      final_T, final_idx, v_image, nullptr,
+                                                                      reinterpret_cast<float4*>(grad_acc));
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -39,14 +39,15 @@ __device__ __forceinline__ WarpPixels warp_pixels(const int tile_x, const int ti
     return p;
 }
 
-// True when some pixel centre of the 8x4 block at origin (x0, y0) may have q <= thr.
+// True when some pixel centre of the BX x BY block at origin (x0, y0) may have q <= thr.
 // (gx, gy) splat centre in pixels, (a, b, c) conic.
-__device__ __forceinline__ bool splat_reaches_block(const float gx, const float gy, const float a, const float b,
-                                                    const float c, const float thr, const float x0, const float y0) {
+template <int BX, int BY>
+__device__ __forceinline__ bool splat_reaches_rect(const float gx, const float gy, const float a, const float b,
+                                                   const float c, const float thr, const float x0, const float y0) {
     // Anything that is not a proper ellipse with a finite threshold is left to the per-pixel test.
     if (!(a > 0.f && c > 0.f && a * c > b * b) || !(thr == thr)) return true;
-    const float dxl = x0 + 0.5f - gx, dxh = dxl + (float)(kWarpPixelsX - 1);
-    const float dyl = y0 + 0.5f - gy, dyh = dyl + (float)(kWarpPixelsY - 1);
+    const float dxl = x0 + 0.5f - gx, dxh = dxl + (float)(BX - 1);
+    const float dyl = y0 + 0.5f - gy, dyh = dyl + (float)(BY - 1);
     const float ex = fminf(fmaxf(0.f, dxl), dxh);  // offset of the block's nearest column / row to the centre
     const float ey = fminf(fmaxf(0.f, dyl), dyh);
     const bool in_x = ex == 0.f, in_y = ey == 0.f;
@@ -61,6 +62,12 @@ __device__ __forceinline__ bool splat_reaches_block(const float gx, const float 
         q2 = 0.5f * (a * dx * dx + c * ey * ey) + b * dx * ey;
     }
     return !(fminf(q1, q2) > thr);
+}
+
+// The 8x4 block of warp_pixels().
+__device__ __forceinline__ bool splat_reaches_block(const float gx, const float gy, const float a, const float b,
+                                                    const float c, const float thr, const float x0, const float y0) {
+    return splat_reaches_rect<kWarpPixelsX, kWarpPixelsY>(gx, gy, a, b, c, thr, x0, y0);
 }
 
 }  // namespace dsb
