@@ -1,9 +1,11 @@
 // Shared by the forward and backward blend kernels: how a tile's 256 pixels map to warps, and the test
 // "can this splat reach this warp's pixels at all?".
 //
-// A 256-thread block owns a 16x16 tile.  Each warp owns a compact 8x4 block of it (not a 16x2 strip: for a
-// splat of a given size the compact shape is met about 15% less often and has more live pixels when it is
-// met).  Warp w sits at column (w & 1), row (w >> 1) of the 2x4 arrangement; lane l is pixel (l & 7, l >> 3).
+// Warps work independently.  In the forward blend a warp owns a compact 8x4 block of a 16x16 tile (not a 16x2
+// strip: for a splat of a given size the compact shape is met about 15% less often and has more live pixels
+// when it is met); block w of a tile sits at column (w & 1), row (w >> 1) of the 2x4 arrangement and lane l is
+// pixel (l & 7, l >> 3).  The backward blend uses larger blocks (several pixels per lane) and the same test
+// through splat_reaches_rect.
 //
 // A pixel receives a splat only if opacity * exp(-q) >= 1/255, i.e. q <= tau = ln(255 * opacity), where
 // q(d) = 0.5 (a dx^2 + c dy^2) + b dx dy is the conic form at the pixel's offset d from the splat centre.
