@@ -83,7 +83,7 @@ def lib():
             "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
             "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
             "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
-            "dsb_backward": [CAM, I32] + [P] * 13 + [P] * 8 + [I32, P],
+            "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
         }
         for name, argtypes in sig.items():

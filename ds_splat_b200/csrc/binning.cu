@@ -157,6 +157,9 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
 // From the corner marks to the tile layout, one block: prefix sums along x, then along y, turn the grid
 // into pairs-per-tile; an exclusive scan in tile order gives the ranges (tile t owns sorted positions
 // [ranges[t], ranges[t+1])), and every tile adds its count to the sort's digit counters.
+// When the grid was worked on in shared memory its global copy is free afterwards and receives the tile
+// order: the tile ids sorted by falling pair count (in 256 logarithmic classes), which the blend kernels use
+// to start their longest lists first so that no long list is left running alone at the end of the launch.
 constexpr int kLayoutThreads = 1024;
 __global__ void __launch_bounds__(kLayoutThreads)
 tile_layout_kernel(int* __restrict__ marks, const int tiles_x, const int tiles_y, const SortPlan plan,
@@ -249,6 +252,44 @@ tile_layout_kernel(int* __restrict__ marks, const int tiles_x, const int tiles_y
     if (tid == 0) ranges[num_tiles] = (int32_t)s_carry;
     if (hist)
         for (int i = tid; i < plan.npass * 256 && i < 4 * 256; i += kLayoutThreads) hist[i] = (&s_hist[0][0])[i];
+    if (!use_smem) return;  // the grid lives in `marks` itself: no room for the order, callers fall back to tile order
+
+    // ---- tile order by falling count: counting sort over 256 classes (exponent and three mantissa bits)
+    __syncthreads();
+    u32* s_class = &s_hist[0][0];  // [256] class sizes, then class offsets
+    if (tid < 256) s_class[tid] = 0;
+    __syncthreads();
+    auto count_class = [](const u32 c) -> u32 {
+        if (c == 0) return 255u;
+        const int e = 31 - __clz(c);
+        const u32 m = e >= 3 ? (c >> (e - 3)) & 7u : (c << (3 - e)) & 7u;
+        return 254u - min(((u32)e << 3) | m, 254u);
+    };
+    for (int t = t_begin; t < t_end; ++t) {
+        const int ty = t / tiles_x, tx = t - ty * tiles_x;
+        atomicAdd(&s_class[count_class((u32)max(diff[ty * stride + tx], 0))], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the 256 class sizes, eight per lane
+        u32 v[8], sum = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { v[q] = s_class[lane * 8 + q]; sum += v[q]; }
+        u32 inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u32 u = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += u;
+        }
+        u32 run = inc - sum;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { s_class[lane * 8 + q] = run; run += v[q]; }
+    }
+    __syncthreads();
+    for (int t = t_begin; t < t_end; ++t) {
+        const int ty = t / tiles_x, tx = t - ty * tiles_x;
+        const u32 slot = atomicAdd(&s_class[count_class((u32)max(diff[ty * stride + tx], 0))], 1u);
+        marks[slot] = t;
+    }
 }
 
 // ranges[t] = number of sorted items whose tile id (high 32 bits, signed) is < t, t = 0..T.
@@ -357,12 +398,19 @@ int64_t tile_marks_bytes(int H, int W) {
 
 // tile_marks: the grid the preprocess kernel filled (destroyed here); hist: the tile sort's digit counters
 // (plan.npass rows of 256, may be null when there is nothing to sort); ranges: [tiles + 1].
+bool tile_order_available(int H, int W) {
+    const int tx = (W + kTile - 1) / kTile, ty = (H + kTile - 1) / kTile;
+    return (size_t)(tx + 1) * (ty + 1) * sizeof(int) <= 200 * 1024;
+}
+
+// *has_order tells whether tile_marks[0 .. tiles) holds the tile order afterwards.
 int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
-                       cudaStream_t s) {
+                       int* has_order, cudaStream_t s) {
     DSB_REQUIRE(tile_marks && ranges, "tile_layout: null pointer");
     DSB_REQUIRE(!hist || plan.npass <= 4, "tile_layout: at most 4 digit passes");
     const size_t grid_bytes = (size_t)(cp.tiles_x + 1) * (cp.tiles_y + 1) * sizeof(int);
-    const int use_smem = grid_bytes <= 200 * 1024;
+    const int use_smem = tile_order_available(cp.H, cp.W);
+    if (has_order) *has_order = use_smem;
     if (use_smem && grid_bytes > 40 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
     tile_layout_kernel<<<1, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(tile_marks, cp.tiles_x, cp.tiles_y, plan, hist,

@@ -113,15 +113,17 @@ blend_backward_kernel(const int W, const int H, const int tiles_x, const int num
                             const float4* __restrict__ records, const u64* __restrict__ sorted,
                             const int32_t* __restrict__ ranges, const float* __restrict__ final_T,
                             const int32_t* __restrict__ final_idx, const float* __restrict__ v_image,
-                            const float* __restrict__ v_depth, float4* __restrict__ grad_acc) {
+                            const float* __restrict__ v_depth, float4* __restrict__ grad_acc,
+                            const int32_t* __restrict__ tile_order) {
     __shared__ float4 s_rec[kWarps][32][3];   // x,y,a,b | c,opacity,r,g | blue, threshold, z, -
     __shared__ float s_acc[kWarps][32][12];   // moments of the chunk's entries
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wb = blockIdx.x * kWarps + warp;             // warp-level pixel block
-    const int tile = wb / kBlocksPerTile;
-    if (tile >= num_tiles) return;                         // whole warps only; no block-wide barrier below
-    const int sub = wb - tile * kBlocksPerTile;
+    const int slot = wb / kBlocksPerTile;
+    if (slot >= num_tiles) return;                         // whole warps only; no block-wide barrier below
+    const int sub = wb - slot * kBlocksPerTile;
+    const int tile = tile_order ? tile_order[slot] : slot; // longest lists first when the order is known
     const int tile_x = tile % tiles_x, tile_y = tile / tiles_x;
     const int bx = tile_x * kTile + (sub % kBlocksPerTileX) * kBlockW, by = tile_y * kTile + (sub / kBlocksPerTileX) * kBlockH;
     const int x = bx + (lane % kBlockW), y0 = by + (lane / kBlockW);
@@ -255,10 +257,10 @@ blend_backward_kernel(const int W, const int H, const int tiles_x, const int num
 
 }  // namespace
 
-// v_depth may be null (no depth map was rendered, or nothing depends on it).
+// v_depth may be null (no depth map was rendered, or nothing depends on it); tile_order may be null.
 int launch_blend_backward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
                           const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
-                          float* grad_acc, cudaStream_t s) {
+                          float* grad_acc, const int32_t* tile_order, cudaStream_t s) {
     DSB_REQUIRE(ranges && final_T && final_idx && v_image && grad_acc, "blend_backward: null pointer");
     DSB_REQUIRE(((uintptr_t)grad_acc & 15) == 0, "blend_backward: grad_acc must be 16-byte aligned");
     const int num_tiles = cp.tiles_x * cp.tiles_y;
@@ -267,12 +269,12 @@ int launch_blend_backward(const CamParams& cp, const float* records, const u64* 
         blend_backward_kernel<true><<<blocks, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles, cp.bg,
                                                                      reinterpret_cast<const float4*>(records), sorted, ranges,
                                                                      final_T, final_idx, v_image, v_depth,
-                                                                     reinterpret_cast<float4*>(grad_acc));
+                                                                     reinterpret_cast<float4*>(grad_acc), tile_order);
     else
         blend_backward_kernel<false><<<blocks, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles, cp.bg,
                                                                       reinterpret_cast<const float4*>(records), sorted, ranges,
                                                                       final_T, final_idx, v_image, nullptr,
-                                                                      reinterpret_cast<float4*>(grad_acc));
+                                                                      reinterpret_cast<float4*>(grad_acc), tile_order);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kThreads)
 blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_tiles,
                      const float4* __restrict__ records, const u64* __restrict__ sorted,
                      const int32_t* __restrict__ ranges, float* __restrict__ image, float* __restrict__ final_T,
-                     int32_t* __restrict__ final_idx, float* __restrict__ depth) {
+                     int32_t* __restrict__ final_idx, float* __restrict__ depth, const int32_t* __restrict__ tile_order) {
     __shared__ float4 s_q0[kWarps][32];  // x, y, conic a, conic b
     __shared__ float4 s_q1[kWarps][32];  // conic c, opacity, r, g
     __shared__ float s_b[kWarps][32];    // b
@@ -72,8 +72,9 @@ blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wb = blockIdx.x * kWarps + warp;   // warp-level pixel block: 8 per tile
-    const int tile = wb / kWarpsPerTile;
-    if (tile >= num_tiles) return;               // whole warps only; no block-wide barrier below
+    const int slot = wb / kWarpsPerTile;
+    if (slot >= num_tiles) return;               // whole warps only; no block-wide barrier below
+    const int tile = tile_order ? tile_order[slot] : slot;   // longest lists first when the order is known
     const WarpPixels wp = warp_pixels(tile % tiles_x, tile / tiles_x, wb % kWarpsPerTile, lane);
     const int x = wp.x, y = wp.y;
     const bool inside = x < W && y < H;
@@ -139,20 +140,21 @@ blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_
 
 }  // namespace
 
-// depth may be null (no depth map wanted).
+// depth may be null (no depth map wanted); tile_order may be null (tiles are then taken in index order).
 int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
-                         float* image, float* final_T, int32_t* final_idx, float* depth, cudaStream_t s) {
+                         float* image, float* final_T, int32_t* final_idx, float* depth, const int32_t* tile_order,
+                         cudaStream_t s) {
     DSB_REQUIRE(ranges && image && final_T && final_idx, "blend_forward: null pointer");
     const int num_tiles = cp.tiles_x * cp.tiles_y;
     const int grid = (num_tiles * kWarpsPerTile + kWarps - 1) / kWarps;
     if (depth)
         blend_forward_kernel<true><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles,
                                                             reinterpret_cast<const float4*>(records), sorted, ranges, image,
-                                                            final_T, final_idx, depth);
+                                                            final_T, final_idx, depth, tile_order);
     else
         blend_forward_kernel<false><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles,
                                                              reinterpret_cast<const float4*>(records), sorted, ranges, image,
-                                                             final_T, final_idx, nullptr);
+                                                             final_T, final_idx, nullptr, tile_order);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

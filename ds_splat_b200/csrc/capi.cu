@@ -190,7 +190,7 @@ int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t
                       float* image, float* final_T, int32_t* final_idx, float* depth, void* stream) {
     CAM_OR_RETURN(cam, cp);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, image, final_T,
-                                final_idx, depth, (cudaStream_t)stream);
+                                final_idx, depth, nullptr, (cudaStream_t)stream);
 }
 
 int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
@@ -198,7 +198,7 @@ int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_
                        float* grad_acc, void* stream) {
     CAM_OR_RETURN(cam, cp);
     return launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
-                                 v_image, v_depth, grad_acc, (cudaStream_t)stream);
+                                 v_image, v_depth, grad_acc, nullptr, (cudaStream_t)stream);
 }
 
 int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
@@ -249,6 +249,7 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
     DSB_REQUIRE(tile_marks && ranges, "forward_render: null tile_marks or ranges");
     DSB_REQUIRE(k <= 1 || (pairs && pairs_alt && workspace), "forward_render: null pair buffers or workspace");
     const SortPlan plan = make_sort_plan(32, 32 + tile_bits, false);
+    int has_order = 0;
     u32* hist = nullptr;
     int rc;
     {
@@ -261,7 +262,10 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
     if (rc != DSB_OK) return rc;
     {
         StageScope scope(kStageRanges, s);
-        rc = launch_tile_layout(cp, tile_marks, plan, hist, ranges, s);
+        rc = launch_tile_layout(cp, tile_marks, plan, hist, ranges, &has_order, s);
+#ifdef DSB_NO_TILE_ORDER
+        has_order = 0;
+#endif
     }
     if (rc != DSB_OK) return rc;
     int in_alt = 0;
@@ -274,13 +278,13 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
     }
     StageScope scope(kStageBlendForward, s);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, depth,
-                                s);
+                                has_order ? tile_marks : nullptr, s);
 }
 
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales, const float* rotations,
                  const float* records, const float* cov3d, const int32_t* radii, const uint64_t* sorted_pairs,
                  const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
-                 const float* v_depth, float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
+                 const float* v_depth, const int32_t* tile_order, float* grad_acc, float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
                  float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
@@ -292,7 +296,12 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
         StageScope scope(kStageBlendBackward, s);
         DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
         rc = launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
-                                   v_image, v_depth, grad_acc, s);
+                                   v_image, v_depth, grad_acc,
+#ifdef DSB_NO_TILE_ORDER
+                                   nullptr, s);
+#else
+                                   tile_order && tile_order_available(cp.H, cp.W) ? tile_order : nullptr, s);
+#endif
     }
     if (rc != DSB_OK) return rc;
     StageScope scope(kStageGeometryBackward, s);

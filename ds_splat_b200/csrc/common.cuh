@@ -147,15 +147,17 @@ int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, con
 // and the tile sort's digit counts.
 int64_t tile_marks_bytes(int H, int W);
 int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
-                       cudaStream_t s);
+                       int* has_order, cudaStream_t s);
+bool tile_order_available(int H, int W);  // whether launch_tile_layout leaves the tile order for this image size
 int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
 int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);
 
 int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
-                         float* image, float* final_T, int32_t* final_idx, float* depth, cudaStream_t s);
+                         float* image, float* final_T, int32_t* final_idx, float* depth, const int32_t* tile_order,
+                         cudaStream_t s);
 int launch_blend_backward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
                           const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
-                          float* grad_acc, cudaStream_t s);
+                          float* grad_acc, const int32_t* tile_order, cudaStream_t s);
 int launch_geometry_backward(const CamParams& cp, int n, const float* means, const float* scales, const float* rots,
                              const float* records, const float* cov3d, const int32_t* radii, const float* grad_acc,
                              float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opac,

@@ -164,13 +164,13 @@ class ViewRenderer:
         """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
         capi, lib, p = self._capi, self.lib, self.p
         c, keep, cam = self._last_cam
-        image, final_t, final_idx, ranges, _marks = self._image_buffers(cam.H, cam.W)
+        image, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
         g = grads.views
         capi.check(lib.dsb_backward(
             C.byref(c), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
             self.records.data_ptr(), self.cov3d.data_ptr(), self.radii.data_ptr(), self.pairs[0].data_ptr(),
             ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
-            self.grad_acc.data_ptr(),
+            tile_marks.data_ptr(), self.grad_acc.data_ptr(),
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 

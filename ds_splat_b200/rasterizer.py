@@ -164,7 +164,7 @@ class DsRasterizerFunction(torch.autograd.Function):
                    cov_3d_precomp is not None)
         ctx.save_for_backward(means_3d, scales if scales is not None else means_3d.new_empty(0),
                               rotations if rotations is not None else means_3d.new_empty(0), records, cov3d, radii,
-                              sorted_pairs, ranges, final_t, final_idx)
+                              sorted_pairs, ranges, final_t, final_idx, tile_marks)
         ctx.mark_non_differentiable(radii)
         if raster_settings.channels_first:
             image = image.permute(2, 0, 1)
@@ -175,7 +175,8 @@ class DsRasterizerFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, rendered_img_grad, _radii_grad, depth_grad=None):
         lib = _capi.lib()
-        (means_3d, scales, rotations, records, cov3d, radii, sorted_pairs, ranges, final_t, final_idx) = ctx.saved_tensors
+        (means_3d, scales, rotations, records, cov3d, radii, sorted_pairs, ranges, final_t, final_idx,
+         tile_order) = ctx.saved_tensors
         settings = ctx.raster_settings
         had_shs, had_colors, had_scales, had_rots, had_cov = ctx.had
         dev = means_3d.device
@@ -204,7 +205,8 @@ class DsRasterizerFunction(torch.autograd.Function):
             _capi.check(lib.dsb_backward(
                 C.byref(cam), n, means_3d.data_ptr(), _capi.ptr(scales), _capi.ptr(rotations), records.data_ptr(),
                 cov3d.data_ptr(), radii.data_ptr(), _capi.ptr(sorted_pairs), ranges.data_ptr(), final_t.data_ptr(),
-                final_idx.data_ptr(), v_image.data_ptr(), _capi.ptr(v_depth), grad_acc.data_ptr(), _capi.ptr(v_means3d),
+                final_idx.data_ptr(), v_image.data_ptr(), _capi.ptr(v_depth), tile_order.data_ptr(), grad_acc.data_ptr(),
+                _capi.ptr(v_means3d),
                 _capi.ptr(v_means2d),
                 _capi.ptr(v_shs), _capi.ptr(v_colors), _capi.ptr(v_opac), _capi.ptr(v_scales), _capi.ptr(v_rots),
                 _capi.ptr(v_cov3d), 0, _capi.stream_ptr()))

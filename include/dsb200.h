@@ -199,7 +199,8 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
  *                      from tile_marks -- a small grid in which dsb_forward_plan's preprocess kernel marked the
  *                      corners of every splat's tile rectangle and whose 2-D prefix sum is the number of pairs
  *                      per tile -- instead of passes over the pairs.  tile_marks (dsb_tile_marks_bytes) is
- *                      written by dsb_forward_plan and consumed (destroyed) by dsb_forward_render;
+ *                      written by dsb_forward_plan and consumed by dsb_forward_render, which leaves in it the
+ *                      tile order (tile ids by falling pair count) that dsb_backward accepts as tile_order;
  *                      workspace: dsb_sort_workspace_bytes(k)
  * dsb_backward       = dsb_blend_backward + dsb_geometry_backward (rasterizer_backward_deepsense,
  *                      cpp/rasterizer_torch.cu:263-316); grad_acc is zeroed inside. */
@@ -218,6 +219,7 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,
                  const int32_t* final_idx, const float* v_image, const float* v_depth /* may be NULL */,
+                 const int32_t* tile_order /* tile_marks as dsb_forward_render left it, or NULL */,
                  float* grad_acc, float* v_means3d,
                  float* v_means2d, float* v_shs, float* v_colors, float* v_opacities, float* v_scales,
                  float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
