@@ -62,29 +62,41 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
             if (lane >= off) wi += t;
         }
         s_wsum[lane] = wi - w;  // exclusive prefix of the warps
-        if (lane == 31) {
-            const u64 block_total = wi;
-            volatile u64* mine = lookback + tile;
-            u64 earlier = 0;
-            if (tile == 0) {
-                *mine = block_total | kScanInclusive;
-            } else {
-                *mine = block_total | kScanAggregate;
-                int p = (int)tile - 1;
-                u32 polls = 0;
-                while (p >= 0) {
-                    const u64 v = *(volatile const u64*)(lookback + p);
-                    if ((v >> 62) == 0) {
-                        if (++polls > kSpinLimit) { atomicExch(&tail->status, DSB_ERR_DEVICE_WAIT_EXPIRED); break; }
-                        __nanosleep(40);
-                        continue;
+        const u64 block_total = __shfl_sync(0xffffffffu, wi, 31);
+        volatile u64* mine = lookback + tile;
+        if (lane == 0) *mine = block_total | (tile == 0 ? kScanInclusive : kScanAggregate);
+        // Look-back by the whole warp: lane l reads the status of tile (p - l); the leading run of published
+        // tiles, up to and including the first inclusive one, is summed at once.
+        u64 earlier = 0;
+        if (tile > 0) {
+            int p = (int)tile - 1;
+            u32 polls = 0;
+            bool done = false;
+            while (!done) {
+                const int idx = p - lane;
+                const u64 v = idx >= 0 ? *(volatile const u64*)(lookback + idx) : kScanInclusive;  // before tile 0: zero
+                const u32 ready = __ballot_sync(0xffffffffu, (v >> 62) != 0);
+                const u32 incl = __ballot_sync(0xffffffffu, (v & kScanInclusive) != 0);
+                const int n_ready = ready == 0xffffffffu ? 32 : __ffs(~ready) - 1;
+                const u32 incl_in = n_ready == 32 ? incl : (incl & ((1u << n_ready) - 1u));
+                const int take = incl_in ? __ffs(incl_in) : n_ready;
+                u64 part = lane < take ? (v & kScanValue) : 0ull;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                earlier += part;
+                p -= take;
+                done = incl_in != 0;
+                if (!done && take < 32) {  // met a tile that has not published yet
+                    if (++polls > kSpinLimit) {
+                        if (lane == 0) atomicExch(&tail->status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                        break;
                     }
-                    earlier += v & kScanValue;
-                    if (v & kScanInclusive) break;
-                    --p;
+                    __nanosleep(40);
                 }
-                *mine = ((earlier + block_total) & kScanValue) | kScanInclusive;
             }
+            if (lane == 0) *mine = ((earlier + block_total) & kScanValue) | kScanInclusive;
+        }
+        if (lane == 0) {
             s_prefix = earlier;
             if ((int)tile == (n + kScanThreads - 1) / kScanThreads - 1) tail->total = earlier + block_total;
         }

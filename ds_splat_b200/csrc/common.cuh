@@ -107,6 +107,7 @@ struct SortPlan {
     int bits[kMaxSortPasses];   // digit width of the pass, 1..8
     u32 mask[kMaxSortPasses];
     u32 flip[kMaxSortPasses];
+    int tile_items;             // items per block; 0 = chosen from the list length
 };
 __device__ __forceinline__ u32 sort_digit(u64 key, int shift, u32 mask, u32 flip) {
     return ((u32)(key >> shift) & mask) ^ flip;
@@ -131,7 +132,7 @@ SortPlan make_sort_plan(int begin_bit, int end_bit, bool signed_top);
 int64_t sort_workspace_bytes(int64_t k);
 int64_t sort_status_offset();  // byte offset of the int status word inside a sort workspace
 int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
-                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s);
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only = false);
 // Two-step form for producers that count the digits themselves while writing the items:
 // sort_begin clears the workspace and returns the histogram to fill, sort_passes runs the passes.
 int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s);

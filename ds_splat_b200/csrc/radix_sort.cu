@@ -32,8 +32,18 @@ constexpr int kWarps = kThreads / 32;
 #ifndef DSB_SORT_ITEMS
 #define DSB_SORT_ITEMS 16
 #endif
-constexpr int kItems = DSB_SORT_ITEMS;          // items per thread (multiple of 4)
+#define DSB_SORT_MIN_BLOCKS_HINT 4  // resident blocks per SM the passes are built for
+constexpr int kItems = DSB_SORT_ITEMS;          // items per thread of the large tile (multiple of 4)
 constexpr int kTileItems = kThreads * kItems;   // 4096 items per block
+// Lists that would not fill the GPU with large tiles are cut into half-size tiles: a pass over such a list
+// is one wave of blocks, its duration is one block's chain of dependent steps, and half the items per
+// thread shortens that chain.
+constexpr int kSmallItems = kItems / 2;
+constexpr int kSmallTileItems = kThreads * kSmallItems;
+constexpr int64_t kSmallListLimit = (int64_t)148 * DSB_SORT_MIN_BLOCKS_HINT * kSmallTileItems;  // one wave of small tiles
+__host__ __device__ constexpr int tile_items_for(int64_t k, bool force_large) {
+    return (!force_large && k <= kSmallListLimit) ? kSmallTileItems : kTileItems;
+}
 constexpr int kRadix = 256;
 constexpr u32 kFlagAggregate = 1u << 30;        // status word holds this block's own count
 constexpr u32 kFlagInclusive = 1u << 31;        // status word holds the count of this and all earlier blocks
@@ -132,25 +142,25 @@ struct SweepShared {
 };
 
 // One block-sized tile of one pass.  FULL: the tile holds kTileItems items, so no bounds checks.
-template <bool HAS_VALS, int NB, bool FULL>
+template <bool HAS_VALS, int NB, int ITEMS, bool FULL>
 __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin,
                                            u32* __restrict__ vout, const u32 n, const DigitSpec ds,
                                            const u32* __restrict__ hist, u32* __restrict__ lookback, int* __restrict__ status,
                                            const u32 tile, const SweepShared sh) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const u32 tile_base = tile * (u32)kTileItems;
-    const u32 tile_n = FULL ? (u32)kTileItems : n - tile_base;
-    const u32 wbase = tile_base + (u32)warp * (32 * kItems);
+    const u32 tile_base = tile * (u32)(kThreads * ITEMS);
+    const u32 tile_n = FULL ? (u32)(kThreads * ITEMS) : n - tile_base;
+    const u32 wbase = tile_base + (u32)warp * (32 * ITEMS);
     u32* my_wcnt = sh.wcnt + warp * kRadix;
 
     // Load: item i of lane l sits at wbase + 32 i + l, so (i, l) order is memory order.
-    u64 key[kItems];
-    u32 val[kItems];
+    u64 key[ITEMS];
+    u32 val[ITEMS];
     {
         const u64* src = kin + wbase + lane;
         const u32* vsrc = HAS_VALS ? vin + wbase + lane : nullptr;
 #pragma unroll
-        for (int i = 0; i < kItems; ++i) {
+        for (int i = 0; i < ITEMS; ++i) {
             const bool ok = FULL || wbase + 32 * i + lane < n;
             key[i] = ok ? src[32 * i] : ~0ull;
             if (HAS_VALS) val[i] = ok ? vsrc[32 * i] : 0u;
@@ -163,11 +173,11 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     // peer masks, then the atomics in item order (a warp barrier between two of them keeps that order), and
     // only then the broadcasts of the old values -- so no item waits for the previous item's round trip.
     // rd[i] packs the item's rank among equal digits of its warp (low 16 bits) with its digit (bits 16..23).
-    u32 rd[kItems];
+    u32 rd[ITEMS];
     const u32 lanemask_lt = (1u << lane) - 1u;
     constexpr int kGroup = DSB_SORT_GROUP;
 #pragma unroll
-    for (int i0 = 0; i0 < kItems; i0 += kGroup) {
+    for (int i0 = 0; i0 < ITEMS; i0 += kGroup) {
         u32 m[kGroup], d[kGroup], before[kGroup];
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
@@ -213,7 +223,8 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
         }
     }
 
-    // Decoupled look-back over earlier tiles for this digit.
+    // Decoupled look-back over earlier tiles for this digit.  (Requesting the status words of several
+    // predecessors at once was measured and is slower here: the extra registers spill.)
     u32 earlier = 0;
     if (tile > 0 && owner) {
         int p = (int)tile - 1;
@@ -237,7 +248,7 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     // Scatter into block-sorted order in shared memory, then stream out: consecutive slots of one
     // digit are consecutive in global memory, so the stores coalesce.
 #pragma unroll
-    for (int i = 0; i < kItems; ++i) {
+    for (int i = 0; i < ITEMS; ++i) {
         if (FULL || wbase + 32 * i + lane < n) {
             const u32 slot = my_wcnt[rd[i] >> 16] + (rd[i] & 0xffffu);
             sh.keys[slot] = key[i];
@@ -246,7 +257,7 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < kItems; ++j) {
+    for (int j = 0; j < ITEMS; ++j) {
         const u32 slot = j * kThreads + tid;
         if (FULL || slot < tile_n) {
             const u64 k = sh.keys[slot];
@@ -257,7 +268,7 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     }
 }
 
-template <bool HAS_VALS, int NB>
+template <bool HAS_VALS, int NB, int ITEMS>
 __global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
 onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
                 const u32 n, const DigitSpec ds, const u32* __restrict__ hist, u32* __restrict__ tile_counter,
@@ -269,7 +280,7 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
     __shared__ u32 s_tile;
     SweepShared sh;
     sh.keys = reinterpret_cast<u64*>(dyn);
-    sh.vals = reinterpret_cast<u32*>(dyn + kTileItems * sizeof(u64));
+    sh.vals = reinterpret_cast<u32*>(dyn + kThreads * ITEMS * sizeof(u64));
     sh.wcnt = s_wcnt;
     sh.glob = s_glob;
     sh.wsum = s_wsum;
@@ -279,20 +290,20 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
     for (int k = tid; k < kWarps * kRadix; k += kThreads) s_wcnt[k] = 0;
     __syncthreads();
     const u32 tile = s_tile;
-    if (n - tile * (u32)kTileItems >= (u32)kTileItems)
-        sweep_tile<HAS_VALS, NB, true>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+    if (n - tile * (u32)(kThreads * ITEMS) >= (u32)(kThreads * ITEMS))
+        sweep_tile<HAS_VALS, NB, ITEMS, true>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
     else
-        sweep_tile<HAS_VALS, NB, false>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+        sweep_tile<HAS_VALS, NB, ITEMS, false>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
 }
 
-template <bool HAS_VALS, int NB>
+template <bool HAS_VALS, int NB, int ITEMS>
 int launch_sweep(const u64* src, u64* dst, const u32* vsrc, u32* vdst, u32 n, const DigitSpec& ds, const u32* hist,
                  u32* tile_counter, u32* lookback, int* status, int64_t tiles, size_t dyn, cudaStream_t s) {
     // Keys alone fit the default 48 KB of shared memory per block; with values the block opts in to more.  The
     // attribute belongs to the current device's context, so it is set at every launch rather than cached.
     if (HAS_VALS || dyn + 10 * 1024 > 48 * 1024)
-        DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<HAS_VALS, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    onesweep_kernel<HAS_VALS, NB><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, n, ds, hist, tile_counter,
+        DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<HAS_VALS, NB, ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    onesweep_kernel<HAS_VALS, NB, ITEMS><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, n, ds, hist, tile_counter,
                                                                          lookback, status);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
@@ -300,8 +311,18 @@ int launch_sweep(const u64* src, u64* dst, const u32* vsrc, u32* vdst, u32 n, co
 
 }  // namespace
 
+// Tiles of a k-item list under the plan's tile size (0 = chosen from k).
+static int64_t tiles_of(int64_t k, const SortPlan& plan) {
+    const int t = plan.tile_items ? plan.tile_items : tile_items_for(k, false);
+    return (k + t - 1) / t;
+}
+
+// Enough for any list of at most k items, whichever tile size it ends up with.
 int64_t sort_workspace_bytes(int64_t k) {
-    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int64_t small_k = k < kSmallListLimit ? k : kSmallListLimit;
+    const int64_t tiles_small = (small_k + kSmallTileItems - 1) / kSmallTileItems;
+    const int64_t tiles_large = (k + kTileItems - 1) / kTileItems;
+    const int64_t tiles = tiles_small > tiles_large ? tiles_small : tiles_large;
     return (int64_t)sizeof(SortHeader) + (int64_t)kMaxSortPasses * tiles * kRadix * (int64_t)sizeof(u32);
 }
 
@@ -344,7 +365,7 @@ static int check_sort_args(const void* items, const void* items_alt, const void*
 int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s) {
     *hist_out = nullptr;
     if (k <= 1) return DSB_OK;
-    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int64_t tiles = tiles_of(k, plan);
     const int64_t need = (int64_t)sizeof(SortHeader) + (int64_t)plan.npass * tiles * kRadix * (int64_t)sizeof(u32);
     if (ws_bytes < need) {
         set_error("sort: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
@@ -360,10 +381,11 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
                 int* in_alt, cudaStream_t s) {
     if (in_alt) *in_alt = 0;
     if (k <= 1) return DSB_OK;
-    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int64_t tiles = tiles_of(k, plan);
+    const bool small = (plan.tile_items ? plan.tile_items : tile_items_for(k, false)) == kSmallTileItems;
     SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
     u32* lookback = reinterpret_cast<u32*>(hdr + 1);
-    const size_t dyn = kTileItems * (sizeof(u64) + (vals ? sizeof(u32) : 0));
+    const size_t dyn = (small ? kSmallTileItems : kTileItems) * (sizeof(u64) + (vals ? sizeof(u32) : 0));
     u64 *src = items, *dst = items_alt;
     u32 *vsrc = vals, *vdst = vals_alt;
     for (int p = 0; p < plan.npass; ++p) {
@@ -375,8 +397,11 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
         ds.flip = plan.flip[p];
         const int nb = plan.bits[p] <= 5 ? 5 : plan.bits[p];
         int rc;
-#define DSB_SWEEP(V, NB) launch_sweep<V, NB>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb, \
-                                             &hdr->status, tiles, dyn, s)
+#define DSB_SWEEP(V, NB)                                                                                              \
+    (small ? launch_sweep<V, NB, kSmallItems>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb,  \
+                                              &hdr->status, tiles, dyn, s)                                                \
+           : launch_sweep<V, NB, kItems>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb,       \
+                                         &hdr->status, tiles, dyn, s))
         if (vals) rc = nb == 5 ? DSB_SWEEP(true, 5) : nb == 6 ? DSB_SWEEP(true, 6) : nb == 7 ? DSB_SWEEP(true, 7) : DSB_SWEEP(true, 8);
         else rc = nb == 5 ? DSB_SWEEP(false, 5) : nb == 6 ? DSB_SWEEP(false, 6) : nb == 7 ? DSB_SWEEP(false, 7) : DSB_SWEEP(false, 8);
 #undef DSB_SWEEP
@@ -390,17 +415,18 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
 
 // Sorts k items on bits [begin_bit, end_bit).  vals may be null.  *in_alt tells where the result is.
 int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
-                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s) {
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only) {
     if (in_alt) *in_alt = 0;
     int rc = check_sort_args(items, items_alt, ws, k, begin_bit, end_bit);
     if (rc != DSB_OK) return rc;
     if (k <= 1) return DSB_OK;
     DSB_REQUIRE(!vals == !vals_alt, "sort: values and alternate values must both be given or both be null");
-    const SortPlan plan = make_sort_plan(begin_bit, end_bit, end_bit == 64 && vals != nullptr);  // signed keys in the pair interface
+    SortPlan plan = make_sort_plan(begin_bit, end_bit, end_bit == 64 && vals != nullptr);  // signed keys in the pair interface
+    if (large_tiles_only) plan.tile_items = kTileItems;
     u32* hist = nullptr;
     rc = sort_begin(k, plan, ws, ws_bytes, &hist, s);
     if (rc != DSB_OK) return rc;
-    const int64_t tiles = (k + kTileItems - 1) / kTileItems;
+    const int64_t tiles = tiles_of(k, plan);
     const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
     radix_histogram_kernel<<<hist_blocks, kThreads, 0, s>>>(items, (u32)k, plan, hist);
     DSB_LAUNCH_CHECK();
@@ -460,7 +486,8 @@ extern "C" int dsb_sort_pairs_static(uint64_t* items, uint64_t* items_alt, int64
     // launch_sort clears the part of the scratch it is about to use, so whatever the previous call left
     // behind does not matter; it issues memset + kernels only, nothing that allocates.
     const int rc2 = launch_sort(reinterpret_cast<u64*>(items), reinterpret_cast<u64*>(items_alt), nullptr, nullptr, k,
-                                begin_bit, end_bit, scratch, (int64_t)kStaticSortScratchBytes, &in_alt, (cudaStream_t)stream);
+                                begin_bit, end_bit, scratch, (int64_t)kStaticSortScratchBytes, &in_alt, (cudaStream_t)stream,
+                                /*large_tiles_only=*/true);  // the scratch is sized for 4096-item tiles
     if (sorted_in_alt_host) *sorted_in_alt_host = in_alt;
     return rc2;
 }
