@@ -174,7 +174,7 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
 // to start their longest lists first so that no long list is left running alone at the end of the launch.
 constexpr int kLayoutThreads = 1024;
 __global__ void __launch_bounds__(kLayoutThreads)
-tile_layout_kernel(int* __restrict__ marks, const int tiles_x, const int tiles_y, const SortPlan plan,
+tile_layout_kernel(int* __restrict__ marks, const int copy_ints, const int tiles_x, const int tiles_y, const SortPlan plan,
                    u32* __restrict__ hist, int32_t* __restrict__ ranges, const int use_smem) {
     extern __shared__ int s_grid[];
     __shared__ u32 s_hist[4][256];
@@ -184,10 +184,12 @@ tile_layout_kernel(int* __restrict__ marks, const int tiles_x, const int tiles_y
     const int stride = tiles_x + 1, rows = tiles_y + 1;
     for (int i = tid; i < 4 * 256; i += kLayoutThreads) (&s_hist[0][0])[i] = 0;
     // The grid is worked on in shared memory when it fits (up to about 4K images), else in place.
-    int* diff = marks;
-    if (use_smem) {
-        for (int i = tid; i < rows * stride; i += kLayoutThreads) s_grid[i] = marks[i];
-        diff = s_grid;
+    int* diff = use_smem ? s_grid : marks;
+    for (int i = tid; i < rows * stride; i += kLayoutThreads) {  // add up the copies
+        int v = 0;
+#pragma unroll
+        for (int c = 0; c < kMarkCopies; ++c) v += marks[(size_t)c * copy_ints + i];
+        diff[i] = v;
     }
     __syncthreads();
     // along x: one warp per row, 32 columns at a time with a running carry
@@ -403,10 +405,12 @@ int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, con
     return DSB_OK;
 }
 
-int64_t tile_marks_bytes(int H, int W) {
+int64_t tile_marks_copy_ints(int H, int W) {
     const int64_t tx = (W + kTile - 1) / kTile, ty = (H + kTile - 1) / kTile;
-    return align256((tx + 1) * (ty + 1) * 4);
+    return align256((tx + 1) * (ty + 1) * 4) / 4;
 }
+
+int64_t tile_marks_bytes(int H, int W) { return tile_marks_copy_ints(H, W) * 4 * kMarkCopies; }
 
 // tile_marks: the grid the preprocess kernel filled (destroyed here); hist: the tile sort's digit counters
 // (plan.npass rows of 256, may be null when there is nothing to sort); ranges: [tiles + 1].
@@ -425,8 +429,9 @@ int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& pla
     if (has_order) *has_order = use_smem;
     if (use_smem && grid_bytes > 40 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
-    tile_layout_kernel<<<1, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(tile_marks, cp.tiles_x, cp.tiles_y, plan, hist,
-                                                                           ranges, use_smem);
+    tile_layout_kernel<<<1, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(tile_marks, (int)tile_marks_copy_ints(cp.H, cp.W),
+                                                                           cp.tiles_x, cp.tiles_y, plan, hist, ranges,
+                                                                           use_smem);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

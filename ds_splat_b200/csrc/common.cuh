@@ -146,7 +146,14 @@ int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, con
                 const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s);
 // Grid of rectangle corner marks filled by the preprocess kernel; launch_tile_layout turns it into tile ranges
 // and the tile sort's digit counts.
+// The grid is kept in kMarkCopies copies, one per residue of the marking block's index, so that the marks of
+// splats that share a tile corner do not all queue up on one L2 word; the layout kernel adds the copies.
+#ifndef DSB_MARK_COPIES
+#define DSB_MARK_COPIES 4
+#endif
+constexpr int kMarkCopies = DSB_MARK_COPIES;
 int64_t tile_marks_bytes(int H, int W);
+int64_t tile_marks_copy_ints(int H, int W);   // distance between two copies, in ints
 int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
                        int* has_order, cudaStream_t s);
 bool tile_order_available(int H, int W);  // whether launch_tile_layout leaves the tile order for this image size

@@ -21,7 +21,10 @@ namespace dsb {
 
 namespace {
 
-constexpr int kThreads = 128;
+#ifndef DSB_GEO_THREADS
+#define DSB_GEO_THREADS 128
+#endif
+constexpr int kThreads = DSB_GEO_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kShStride = 49;  // odd stride: conflict-free row-per-lane writes
 

@@ -17,7 +17,10 @@ namespace dsb {
 
 namespace {
 
-constexpr int kThreads = 256;
+#ifndef DSB_PRE_THREADS
+#define DSB_PRE_THREADS 256
+#endif
+constexpr int kThreads = DSB_PRE_THREADS;
 constexpr int kShRow4 = 13;  // padded SH row in float4 units (12 used): conflict-free 16-byte shared loads
 
 __device__ __forceinline__ float sh_channel(const float* f, int ch, int degree, float x, float y, float z) {
@@ -48,13 +51,13 @@ __device__ __forceinline__ void stage_floats(float* dst, const float* src, int c
     for (int k = tid; k < count; k += kThreads) dst[k] = src[k];
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 512 / kThreads)
 preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ means, const float* __restrict__ shs,
                   const float* __restrict__ colors_precomp, const float* __restrict__ opac,
                   const float* __restrict__ scales, const float* __restrict__ rots,
                   const float* __restrict__ cov3d_precomp, float4* __restrict__ records, int32_t* __restrict__ radii,
                   int32_t* __restrict__ tiles, float* __restrict__ cov3d, u64* __restrict__ depth_keys,
-                  const int sh_vec4, const int use_bulk, int* __restrict__ tile_marks) {
+                  const int sh_vec4, const int use_bulk, int* __restrict__ tile_marks, const int marks_copy_ints) {
     extern __shared__ __align__(16) float4 dyn4[];
     __shared__ float s_cam[31];      // view rows 0..2 (12), projection (16), camera centre (3)
     __shared__ __align__(16) float s_means[kThreads * 3];
@@ -74,6 +77,22 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
     // its own 192-byte SH row (into the padded row layout), one thread asks for the block's 3 KB of means
     // and of scales, and one mbarrier counts the bytes in.  No registers or load instructions are spent on
     // the 54 KB a block brings in.  The wait is bounded; if it ever expires the ordinary loads below run.
+    // While this block works, the inputs of the block that will follow it on the GPU (about one wave of
+    // resident blocks later) are requested into L2, so that block's copies find them there instead of
+    // starting DRAM reads only when it begins.
+#ifndef DSB_PRE_PREFETCH_BLOCKS
+#define DSB_PRE_PREFETCH_BLOCKS (148 * 3)
+#endif
+    if (use_bulk && DSB_PRE_PREFETCH_BLOCKS > 0 && tid == 0) {
+        const long long nb = (long long)blockIdx.x + DSB_PRE_PREFETCH_BLOCKS;
+        if ((nb + 1) * kThreads <= n) {
+            const size_t first = (size_t)nb * kThreads;
+            bulk_prefetch_l2(shs + first * 48, kThreads * 192u);
+            bulk_prefetch_l2(means + first * 3, kThreads * 12u);
+            bulk_prefetch_l2(scales + first * 3, kThreads * 12u);
+            bulk_prefetch_l2(rots + first * 4, kThreads * 16u);
+        }
+    }
     bool staged = false;
     if (use_bulk && cnt == kThreads) {
         if (tid == 0) mbar_init(&s_bar, 1);
@@ -250,10 +269,11 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
         // kernel's memory traffic.
         if (tile_marks && count > 0 && !(cp.drop_last && i == n - 1)) {
             const int stride = cp.tiles_x + 1;
-            atomicAdd(tile_marks + y0 * stride + x0, 1);
-            atomicAdd(tile_marks + y0 * stride + x1, -1);
-            atomicAdd(tile_marks + y1 * stride + x0, -1);
-            atomicAdd(tile_marks + y1 * stride + x1, 1);
+            int* m = tile_marks + (size_t)(blockIdx.x % kMarkCopies) * marks_copy_ints;
+            atomicAdd(m + y0 * stride + x0, 1);
+            atomicAdd(m + y0 * stride + x1, -1);
+            atomicAdd(m + y1 * stride + x0, -1);
+            atomicAdd(m + y1 * stride + x1, 1);
         }
 
         // Conic = inverse of the dilated 2-D covariance.
@@ -312,7 +332,7 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
     const int blocks = (n + kThreads - 1) / kThreads;
     preprocess_kernel<<<blocks, kThreads, dyn, s>>>(cp, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp,
                                                    reinterpret_cast<float4*>(records), radii, tiles, cov3d, depth_keys,
-                                                   sh_vec4, use_bulk, tile_marks);
+                                                   sh_vec4, use_bulk, tile_marks, (int)tile_marks_copy_ints(cp.H, cp.W));
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
