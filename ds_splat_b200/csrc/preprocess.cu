@@ -77,22 +77,6 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
     // its own 192-byte SH row (into the padded row layout), one thread asks for the block's 3 KB of means
     // and of scales, and one mbarrier counts the bytes in.  No registers or load instructions are spent on
     // the 54 KB a block brings in.  The wait is bounded; if it ever expires the ordinary loads below run.
-    // While this block works, the inputs of the block that will follow it on the GPU (about one wave of
-    // resident blocks later) are requested into L2, so that block's copies find them there instead of
-    // starting DRAM reads only when it begins.
-#ifndef DSB_PRE_PREFETCH_BLOCKS
-#define DSB_PRE_PREFETCH_BLOCKS (148 * 3)
-#endif
-    if (use_bulk && DSB_PRE_PREFETCH_BLOCKS > 0 && tid == 0) {
-        const long long nb = (long long)blockIdx.x + DSB_PRE_PREFETCH_BLOCKS;
-        if ((nb + 1) * kThreads <= n) {
-            const size_t first = (size_t)nb * kThreads;
-            bulk_prefetch_l2(shs + first * 48, kThreads * 192u);
-            bulk_prefetch_l2(means + first * 3, kThreads * 12u);
-            bulk_prefetch_l2(scales + first * 3, kThreads * 12u);
-            bulk_prefetch_l2(rots + first * 4, kThreads * 16u);
-        }
-    }
     bool staged = false;
     if (use_bulk && cnt == kThreads) {
         if (tid == 0) mbar_init(&s_bar, 1);

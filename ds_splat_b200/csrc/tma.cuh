@@ -50,10 +50,4 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                  : "memory");
 }
 
-// Asks the copy engine to bring `bytes` (multiple of 16, 16-byte aligned) of global memory into L2; nothing
-// waits on it and nothing breaks if the lines are evicted again before they are used.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, const uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
-}
-
 }  // namespace dsb
