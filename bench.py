@@ -266,7 +266,9 @@ def main():
     torch.cuda.synchronize()
     stage_raw = _capi.read_stage_timings()
     _capi.stage_timing(False)
-    stages_ms = {name: round(ms / max(calls, 1), 5) for name, (ms, calls) in stage_raw.items() if calls}
+    # per view: the per-splat backward runs once for all views of a step, every other stage once per view
+    timed_views = min(args.steps, 40) * vpr
+    stages_ms = {name: round(ms / timed_views, 5) for name, (ms, calls) in stage_raw.items() if calls}
 
     # ---- end to end through the public operator, host buffers -----------------------------------------
     e2e = None

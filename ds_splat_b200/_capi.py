@@ -18,13 +18,15 @@ LIB_PATH = os.environ.get("DSB200_LIBRARY") or os.path.join(_HERE, "libdsb200.so
 DSB_FLAG_DROP_LAST_SPLAT = 1
 RECORD_FLOATS = 12
 GRAD_FLOATS = 12
+MAX_BATCH_VIEWS = 8
 MAX_PAIRS = 1 << 30
 
 EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
-    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_export_reference_lists",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_backward_blend", "dsb_geometry_backward_views",
+    "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
     "dsb_sort_pairs_static", "dsb_tile_marks_bytes",
 )
@@ -84,6 +86,8 @@ def lib():
             "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
             "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
+            "dsb_backward_blend": [CAM, I32] + [P] * 10,
+            "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
         }
         for name, argtypes in sig.items():

@@ -309,6 +309,46 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
                                     v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d, accumulate, s);
 }
 
+int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
+                       const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
+                       const float* v_depth, const int32_t* tile_order, float* grad_acc, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    if (n == 0) return DSB_OK;
+    DSB_REQUIRE(grad_acc, "backward_blend: grad_acc is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    StageScope scope(kStageBlendBackward, s);
+    DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
+    return launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
+                                 v_image, v_depth, grad_acc,
+#ifdef DSB_NO_TILE_ORDER
+                                 nullptr, s);
+#else
+                                 tile_order && tile_order_available(cp.H, cp.W) ? tile_order : nullptr, s);
+#endif
+}
+
+int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                                const float* scales, const float* rotations, const float* cov3d,
+                                const float* const* records, const int32_t* const* radii, const float* const* grad_acc,
+                                float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
+                                float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
+    DSB_REQUIRE(cams && num_views >= 0 && num_views <= DSB_MAX_BATCH_VIEWS,
+                "geometry_backward_views: between 0 and %d views per call", DSB_MAX_BATCH_VIEWS);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    if (n == 0 || num_views == 0) return DSB_OK;
+    CamParams cps[DSB_MAX_BATCH_VIEWS];
+    for (int v = 0; v < num_views; ++v) {
+        const int rc = make_cam_params(&cams[v], &cps[v]);
+        if (rc != DSB_OK) return rc;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    StageScope scope(kStageGeometryBackward, s);
+    return launch_geometry_backward_views(cps, num_views, n, means3d, scales, rotations, cov3d, records, radii, grad_acc,
+                                          v_means3d, v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d,
+                                          accumulate, s);
+}
+
 int dsb_export_reference_lists(const uint64_t* sorted_pairs, int64_t k, const float* records, int64_t* keys, int32_t* ids,
                                void* stream) {
     DSB_REQUIRE(k >= 0, "k must be non-negative");

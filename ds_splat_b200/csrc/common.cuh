@@ -171,4 +171,10 @@ int launch_geometry_backward(const CamParams& cp, int n, const float* means, con
                              float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opac,
                              float* v_scales, float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
 
+int launch_geometry_backward_views(const CamParams* cps, int count, int n, const float* means, const float* scales,
+                                   const float* rots, const float* cov3d, const float* const* records,
+                                   const int32_t* const* radii, const float* const* grad_acc, float* v_means3d,
+                                   float* v_means2d, float* v_shs, float* v_colors, float* v_opac, float* v_scales,
+                                   float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
+
 }  // namespace dsb

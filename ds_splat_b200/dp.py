@@ -14,6 +14,11 @@ Layout choices:
     no per-tensor collectives.
   * ``ViewRenderer`` bypasses autograd and calls the fused C-ABI entry points with buffers that are
     allocated once and reused across views and steps (only the pair list grows with the largest K seen).
+  * A step renders its views one after the other (forward, then the backward blend, per view) but runs the
+    per-splat part of the backward ONCE for up to eight views (``dsb_geometry_backward_views``): the splat
+    parameters are read once and the 236 bytes of gradients per splat are written once per step instead of
+    being read and rewritten for every view.  Each view of a batch keeps its own records, radii and
+    accumulator rows (100 bytes per splat and view) until that call.
 
 Everything that is not a kernel launch (sharding, buffer layout, the collective) works on CPU tensors
 too, which is how the world_size-2 gloo tests exercise it.
@@ -90,7 +95,8 @@ class CameraTensors:
 class ViewRenderer:
     """Forward + backward of one view at a time through the fused C-ABI calls, with reusable buffers."""
 
-    def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True):
+    def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True,
+                 batch_views: int = 8):
         from . import _capi
         self._capi = _capi
         self.lib = _capi.lib()
@@ -103,15 +109,20 @@ class ViewRenderer:
         self.strict = strict_reference
         n, dev = self.n, self.dev
         f32 = dict(dtype=torch.float32, device=dev)
-        self.records = torch.empty((n, _capi.RECORD_FLOATS), **f32)
-        self.radii = torch.empty(n, dtype=torch.int32, device=dev)
+        self.batch_views = max(1, min(int(batch_views), _capi.MAX_BATCH_VIEWS))
+        # slot 0 exists from the start; the other slots of a batch are allocated when a step first uses them
+        self.slot_records = [torch.empty((n, _capi.RECORD_FLOATS), **f32)]
+        self.slot_radii = [torch.empty(n, dtype=torch.int32, device=dev)]
+        self.slot_grad = [torch.empty((n, _capi.GRAD_FLOATS), **f32)]
+        self.slot_cam = [None]
+        self.records, self.radii = self.slot_records[0], self.slot_radii[0]
         self.tiles = torch.empty(n, dtype=torch.int32, device=dev)
         self.cov3d = torch.empty((n, 6), **f32)
         self.depth_keys = torch.empty((2, n), dtype=torch.int64, device=dev)
         self.offsets = torch.empty(n, dtype=torch.int32, device=dev)
         self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes(n))
         self.plan_ws = torch.empty(self.plan_bytes, dtype=torch.uint8, device=dev)
-        self.grad_acc = torch.empty((n, _capi.GRAD_FLOATS), **f32)
+        self.grad_acc = self.slot_grad[0]
         self.pairs = None
         self.sort_ws = None
         self.sort_bytes = 0
@@ -133,9 +144,20 @@ class ViewRenderer:
         return self._capi.make_camera(cam.H, cam.W, cam.tanfovx, cam.tanfovy, cam.viewmatrix, cam.projmatrix, cam.campos,
                                       cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict)
 
-    def forward(self, cam: CameraTensors):
-        """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size)."""
+    def _slot(self, j: int):
+        while len(self.slot_records) <= j:
+            f32 = dict(dtype=torch.float32, device=self.dev)
+            self.slot_records.append(torch.empty((self.n, self._capi.RECORD_FLOATS), **f32))
+            self.slot_radii.append(torch.empty(self.n, dtype=torch.int32, device=self.dev))
+            self.slot_grad.append(torch.empty((self.n, self._capi.GRAD_FLOATS), **f32))
+            self.slot_cam.append(None)
+        return self.slot_records[j], self.slot_radii[j], self.slot_grad[j]
+
+    def forward(self, cam: CameraTensors, slot: int = 0):
+        """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size).
+        ``slot`` selects which of the batch's record / radii buffers the view's per-splat data goes to."""
         capi, lib, p = self._capi, self.lib, self.p
+        self.records, self.radii, self.grad_acc = self._slot(slot)
         c, keep = self._camera(cam)
         stream = capi.stream_ptr()
         k = C.c_int64(0)
@@ -158,6 +180,7 @@ class ViewRenderer:
             final_idx.data_ptr(), None, stream))
         self.last_k = k
         self._last_cam = (c, keep, cam)
+        self.slot_cam[slot] = (c, keep)
         return image
 
     def backward(self, v_image: torch.Tensor, grads: GradientBuffer, accumulate: bool = True):
@@ -174,16 +197,41 @@ class ViewRenderer:
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 
+    def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False):
+        """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
+        contents when ``accumulate``).  Views are taken in batches of ``batch_views``: per view the forward and the
+        backward blend, per batch one per-splat backward over all its views."""
+        capi, lib, p = self._capi, self.lib, self.p
+        g = grads.views
+        for b0 in range(0, len(cameras), self.batch_views):
+            batch = range(b0, min(b0 + self.batch_views, len(cameras)))
+            for j, idx in enumerate(batch):
+                cam = cameras[idx]
+                image = self.forward(cam, slot=j)
+                v_image = image_grads(idx, image) if callable(image_grads) else image_grads[idx]
+                c, keep = self.slot_cam[j]
+                _img, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
+                capi.check(lib.dsb_backward_blend(
+                    C.byref(c), self.n, self.records.data_ptr(), self.pairs[0].data_ptr(), ranges.data_ptr(),
+                    final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None, tile_marks.data_ptr(),
+                    self.grad_acc.data_ptr(), capi.stream_ptr()))
+            nv = len(batch)
+            cams = (capi.DsbCamera * nv)(*[self.slot_cam[j][0] for j in range(nv)])
+            ptrs = lambda ts: (C.c_void_p * nv)(*[t.data_ptr() for t in ts[:nv]])
+            capi.check(lib.dsb_geometry_backward_views(
+                cams, nv, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
+                self.cov3d.data_ptr(), ptrs(self.slot_records), ptrs(self.slot_radii), ptrs(self.slot_grad),
+                g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
+                g["rotations"].data_ptr(), None, 1 if (accumulate or b0 > 0) else 0, capi.stream_ptr()))
 
-def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads: Sequence[torch.Tensor],
+
+def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads,
                        grads: GradientBuffer, group=None) -> None:
-    """One step of the multi-view batch on this rank: for each local camera forward + backward (gradients
-    accumulated in ``grads``), then the all-reduce.  ``cameras`` / ``image_grads`` are this rank's shard."""
-    first = True
-    for cam, v_image in zip(cameras, image_grads):
-        renderer.forward(cam)
-        renderer.backward(v_image, grads, accumulate=not first)
-        first = False
-    if first:
+    """One step of the multi-view batch on this rank: forward + backward of each local camera (gradients
+    summed into ``grads``), then the all-reduce.  ``cameras`` is this rank's shard; ``image_grads`` is the
+    matching sequence of dL/dimage tensors, or a callable ``(index, image) -> dL/dimage`` (the loss)."""
+    if len(cameras) == 0:
         grads.zero_()  # a rank without views still takes part in the collective
+    else:
+        renderer.render_views(cameras, image_grads, grads, accumulate=False)
     allreduce_gradients(grads, group)

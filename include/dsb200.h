@@ -33,6 +33,7 @@ extern "C" {
 #define DSB_FLAG_DROP_LAST_SPLAT 1
 
 #define DSB_RECORD_FLOATS 12  /* packed per-splat record: 3 x float4, see DsbCamera notes below   */
+#define DSB_MAX_BATCH_VIEWS 8 /* views one dsb_geometry_backward_views call takes                  */
 #define DSB_GRAD_FLOATS 12    /* per-splat accumulator row written by dsb_blend_backward          */
 #define DSB_MAX_PAIRS ((int64_t)1 << 30)
 
@@ -223,6 +224,29 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
                  float* grad_acc, float* v_means3d,
                  float* v_means2d, float* v_shs, float* v_colors, float* v_opacities, float* v_scales,
                  float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
+
+/* ---- multi-view step ----------------------------------------------------------------------------
+ * A training step renders several cameras against the same splats and needs the SUM of their gradients
+ * (no reference counterpart: the reference is called once per camera and autograd adds the results).
+ * Splitting dsb_backward lets the per-splat part run once per step instead of once per view:
+ *   per view:   dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
+ *   per step:   dsb_geometry_backward_views   over up to DSB_MAX_BATCH_VIEWS views at a time
+ * records, radii and grad_acc are HOST arrays of num_views device pointers (one buffer per view, all of the
+ * layouts dsb_preprocess / dsb_blend_backward use); cams is a host array of num_views cameras that must
+ * share sh_degree, max_sh_degree and scale_modifier; cov3d is the splats' own (any view's).  The outputs
+ * receive the sum over the views (added to their contents when accumulate != 0); v_means2d, too, is the
+ * sum over views.  Results equal num_views calls of dsb_geometry_backward with accumulate, up to
+ * floating-point summation order. */
+int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
+                       const int32_t* ranges, const float* final_T, const int32_t* final_idx,
+                       const float* v_image, const float* v_depth /* may be NULL */,
+                       const int32_t* tile_order /* may be NULL */, float* grad_acc, void* stream);
+int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                                const float* scales, const float* rotations, const float* cov3d,
+                                const float* const* records, const int32_t* const* radii,
+                                const float* const* grad_acc, float* v_means3d, float* v_means2d, float* v_shs,
+                                float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
+                                float* v_cov3d, int32_t accumulate, void* stream);
 
 /* Test/export helper: rebuild the reference-format sorted lists from this library's packed pairs:
  * keys[i] = (tile << 32) | sign-extended depth bits of the splat, ids[i] = splat id

@@ -22,7 +22,8 @@ def _free_port():
 
 
 class OracleRenderer:
-    """Stands in for ViewRenderer on CPU: same forward/backward protocol, gradients from the CPU checker."""
+    """Stands in for ViewRenderer on CPU: same forward / backward / render_views protocol, gradients from the
+    CPU checker."""
 
     def __init__(self, scene):
         from oracle import oracle as O
@@ -46,6 +47,12 @@ class OracleRenderer:
                 grads.views[dst] += g
             else:
                 grads.views[dst].copy_(g)
+
+    def render_views(self, cameras, image_grads, grads, accumulate=False):
+        for idx, view in enumerate(cameras):
+            image = self.forward(view)
+            v_image = image_grads(idx, image) if callable(image_grads) else image_grads[idx]
+            self.backward(v_image, grads, accumulate=accumulate or idx > 0)
 
 
 def _scene():

@@ -214,3 +214,33 @@ def test_return_depth_is_differentiable_and_leaves_the_image_alone():
     assert _rel(p["means"].grad.cpu().numpy(), bwd["v_means3d"]) < 1e-2
     assert _rel(p["opacities"].grad.cpu().numpy(), bwd["v_opacities"]) < 1e-2
     assert _rel(p["scales"].grad.cpu().numpy(), bwd["v_scales"]) < 1e-2
+
+
+def test_batched_views_equal_one_view_at_a_time():
+    """render_views sums the per-splat backward of up to eight views in one kernel; eleven views (two batches,
+    the loss given as a callable) must give what eleven single-view backward calls with accumulation give."""
+    sc = scenes.headline(n=15_000, seed=92, W=256, H=160, focal=180.0, views=11)
+    t = scene_tensors(sc)
+    cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
+    vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
+    batched = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    g_b = GradientBuffer(sc.n, "cuda")
+    g_b.flat.fill_(3.0)
+    seen = []
+    batched.render_views(cams, lambda i, image: (seen.append((i, tuple(image.shape))), vimgs[i])[1], g_b, accumulate=False)
+    assert [i for i, _ in seen] == list(range(11)) and all(s == (160, 256, 3) for _, s in seen)
+    single = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    g_s = GradientBuffer(sc.n, "cuda")
+    for i, cam in enumerate(cams):
+        single.forward(cam)
+        single.backward(vimgs[i], g_s, accumulate=i > 0)
+    torch.cuda.synchronize()
+    for key in ("means3d", "shs", "opacities", "scales", "rotations"):
+        a, b = g_b.views[key].cpu().numpy(), g_s.views[key].cpu().numpy()
+        assert _rel(a, b) < 1e-4, key
+    # accumulate=True adds on top of what the buffer holds
+    batched.render_views(cams[:2], vimgs[:2], g_b, accumulate=True)
+    single.forward(cams[0]); single.backward(vimgs[0], g_s, accumulate=True)
+    single.forward(cams[1]); single.backward(vimgs[1], g_s, accumulate=True)
+    torch.cuda.synchronize()
+    assert _rel(g_b.views["shs"].cpu().numpy(), g_s.views["shs"].cpu().numpy()) < 1e-4
