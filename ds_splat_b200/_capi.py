@@ -25,7 +25,8 @@ EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
-    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_backward_blend", "dsb_geometry_backward_views",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_backward_blend",
+    "dsb_geometry_backward_views",
     "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
     "dsb_sort_pairs_static", "dsb_tile_marks_bytes",
@@ -86,6 +87,7 @@ def lib():
             "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
             "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
+            "dsb_preprocess_views": [P, I32, I32] + [P] * 14,
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
@@ -180,6 +182,25 @@ def preprocess(cam, means3d, shs, opacities, scales, rotations, colors_precomp=N
                                ptr(rotations), ptr(cov3d_precomp), ptr(records), ptr(radii), ptr(tiles), ptr(cov3d),
                                ptr(depth_keys), stream_ptr()))
     return records, radii, tiles, cov3d, depth_keys
+
+
+def preprocess_views(cams, means3d, shs, opacities, scales, rotations):
+    """One preprocess launch for several cameras of one image size; returns a list of per-view
+    (records, radii, tiles, depth_keys, tile_marks) and the shared cov3d."""
+    n, dev, nv = means3d.shape[0], means3d.device, len(cams)
+    h, w = cams[0].image_height, cams[0].image_width
+    out = []
+    for _ in range(nv):
+        out.append((torch.empty((n, RECORD_FLOATS), dtype=torch.float32, device=dev),
+                    torch.empty(n, dtype=torch.int32, device=dev), torch.empty(n, dtype=torch.int32, device=dev),
+                    torch.empty(n, dtype=torch.int64, device=dev),
+                    torch.empty(int(lib().dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=dev)))
+    cov3d = torch.empty((n, 6), dtype=torch.float32, device=dev)
+    arr = lambda i: (C.c_void_p * nv)(*[o[i].data_ptr() for o in out])
+    check(lib().dsb_preprocess_views((DsbCamera * nv)(*cams), nv, n, ptr(means3d), ptr(shs), None, ptr(opacities),
+                                     ptr(scales), ptr(rotations), None, arr(0), arr(1), arr(2), ptr(cov3d), arr(3), arr(4),
+                                     stream_ptr()))
+    return out, cov3d
 
 
 def plan_pairs(cam, tiles, depth_keys):

@@ -309,6 +309,31 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
                                     v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d, accumulate, s);
 }
 
+int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d, const float* shs,
+                         const float* colors_precomp, const float* opacities, const float* scales, const float* rotations,
+                         const float* cov3d_precomp, float* const* records, int32_t* const* radii,
+                         int32_t* const* tiles_touched, float* cov3d, uint64_t* const* depth_keys,
+                         int32_t* const* tile_marks, void* stream) {
+    DSB_REQUIRE(cams && num_views >= 0 && num_views <= DSB_MAX_BATCH_VIEWS,
+                "preprocess_views: between 0 and %d views per call", DSB_MAX_BATCH_VIEWS);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    if (num_views == 0) return DSB_OK;
+    DSB_REQUIRE(records && radii && tiles_touched && depth_keys && tile_marks, "preprocess_views: null pointer array");
+    CamParams cps[DSB_MAX_BATCH_VIEWS];
+    u64* keys[DSB_MAX_BATCH_VIEWS];
+    cudaStream_t s = (cudaStream_t)stream;
+    StageScope scope(kStagePreprocess, s);
+    for (int v = 0; v < num_views; ++v) {
+        const int rc = make_cam_params(&cams[v], &cps[v]);
+        if (rc != DSB_OK) return rc;
+        DSB_REQUIRE(tile_marks[v], "preprocess_views: tile_marks of view %d is null", v);
+        DSB_CUDA_CHECK(cudaMemsetAsync(tile_marks[v], 0, (size_t)tile_marks_bytes(cps[v].H, cps[v].W), s));
+        keys[v] = reinterpret_cast<u64*>(depth_keys[v]);
+    }
+    return launch_preprocess_views(cps, num_views, n, means3d, shs, colors_precomp, opacities, scales, rotations,
+                                   cov3d_precomp, records, radii, tiles_touched, cov3d, keys, tile_marks, s);
+}
+
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
                        const float* v_depth, const int32_t* tile_order, float* grad_acc, void* stream) {

@@ -99,6 +99,12 @@ int launch_preprocess(const CamParams& cp, int n, const float* means, const floa
                       float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, int* tile_marks,
                       cudaStream_t s);
 
+int launch_preprocess_views(const CamParams* cps, int count, int n, const float* means, const float* shs,
+                            const float* colors_precomp, const float* opac, const float* scales, const float* rots,
+                            const float* cov3d_precomp, float* const* records, int32_t* const* radii,
+                            int32_t* const* tiles, float* cov3d, u64* const* depth_keys, int* const* tile_marks,
+                            cudaStream_t s);
+
 // Radix-sort pass layout: which bits each pass looks at.  flip is XORed into the digit (sign bit of signed keys).
 constexpr int kMaxSortPasses = 8;
 struct SortPlan {

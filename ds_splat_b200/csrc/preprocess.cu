@@ -51,27 +51,44 @@ __device__ __forceinline__ void stage_floats(float* dst, const float* src, int c
     for (int k = tid; k < count; k += kThreads) dst[k] = src[k];
 }
 
-__global__ void __launch_bounds__(kThreads, 512 / kThreads)
-preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ means, const float* __restrict__ shs,
+// Per-view part of one launch: camera and output buffers.  All views share the splat parameters, which a block
+// brings into shared memory once; the 3-D covariance, too, is computed once.
+struct PreViews {
+    int count;
+    CamParams cam[DSB_MAX_BATCH_VIEWS];
+    float4* records[DSB_MAX_BATCH_VIEWS];
+    int32_t* radii[DSB_MAX_BATCH_VIEWS];
+    int32_t* tiles[DSB_MAX_BATCH_VIEWS];
+    u64* depth_keys[DSB_MAX_BATCH_VIEWS];
+    int* tile_marks[DSB_MAX_BATCH_VIEWS];   // may be null
+};
+
+__global__ void __launch_bounds__(kThreads, 768 / kThreads)
+preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ means, const float* __restrict__ shs,
                   const float* __restrict__ colors_precomp, const float* __restrict__ opac,
                   const float* __restrict__ scales, const float* __restrict__ rots,
-                  const float* __restrict__ cov3d_precomp, float4* __restrict__ records, int32_t* __restrict__ radii,
-                  int32_t* __restrict__ tiles, float* __restrict__ cov3d, u64* __restrict__ depth_keys,
-                  const int sh_vec4, const int use_bulk, int* __restrict__ tile_marks, const int marks_copy_ints) {
+                  const float* __restrict__ cov3d_precomp, float* __restrict__ cov3d, const int sh_vec4, const int use_bulk,
+                  const int marks_copy_ints) {
     extern __shared__ __align__(16) float4 dyn4[];
-    __shared__ float s_cam[31];      // view rows 0..2 (12), projection (16), camera centre (3)
+    __shared__ float s_cams[DSB_MAX_BATCH_VIEWS][32];   // per view: view rows 0..2 (12), projection (16), camera centre (3)
     __shared__ __align__(16) float s_means[kThreads * 3];
     __shared__ __align__(16) float s_scales[kThreads * 3];
+    __shared__ __align__(16) float4 s_rec[kThreads * 3];   // output rows of the view being written
     __shared__ __align__(8) uint64_t s_bar;
+    const CamParams& cp = pv.cam[0];   // SH degree, coefficient count and scale modifier are common to the views
 
     const int tid = threadIdx.x;
     const int base = blockIdx.x * kThreads;
     const int cnt = min(kThreads, n - base);
     const int i = base + tid;
 
-    if (tid < 12) s_cam[tid] = mat_at(cp.view, tid >> 2, tid & 3, cp.transposed);
-    else if (tid < 28) s_cam[tid] = mat_at(cp.proj, (tid - 12) >> 2, (tid - 12) & 3, cp.transposed);
-    else if (tid < 31) s_cam[tid] = cp.campos[tid - 28];
+    for (int k = tid; k < pv.count * 32; k += kThreads) {
+        const int v = k >> 5, e = k & 31;
+        const CamParams& c = pv.cam[v];
+        s_cams[v][e] = e < 12 ? mat_at(c.view, e >> 2, e & 3, c.transposed)
+                     : e < 28 ? mat_at(c.proj, (e - 12) >> 2, (e - 12) & 3, c.transposed)
+                     : e < 31 ? c.campos[e - 28] : 0.f;
+    }
 
     // Full blocks with 16-byte aligned inputs are staged by the bulk copy engine (TMA): every thread asks for
     // its own 192-byte SH row (into the padded row layout), one thread asks for the block's 3 KB of means
@@ -121,16 +138,12 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
     }
     __syncthreads();
 
-    float4 q0 = make_float4(0, 0, 0, 0), q1 = q0, q2 = q0;
     float S[6] = {0, 0, 0, 0, 0, 0};
-    int radius = 0, count = 0;
-    float tz = 0.0f;
-
-    if (tid < cnt) {
-        const float* V = s_cam;
-        const float* P = s_cam + 12;
-        const float mx = s_means[3 * tid], my = s_means[3 * tid + 1], mz = s_means[3 * tid + 2];
-
+    float mx = 0.f, my = 0.f, mz = 0.f, opacity = 0.f;
+    const bool live = tid < cnt;
+    if (live) {
+        mx = s_means[3 * tid]; my = s_means[3 * tid + 1]; mz = s_means[3 * tid + 2];
+        opacity = opac[i];
         // 3-D covariance from scale and rotation (or taken as given).
         if (cov3d_precomp) {
 #pragma unroll
@@ -156,132 +169,145 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
             S[5] = m20 * m20 + m21 * m21 + m22 * m22;
         }
 
-        // Colour.
-        float cr, cg, cb;
-        if (colors_precomp) {
-            cr = colors_precomp[(size_t)i * 3]; cg = colors_precomp[(size_t)i * 3 + 1]; cb = colors_precomp[(size_t)i * 3 + 2];
-        } else if (cp.sh_degree > 3) {
-            cr = cg = cb = 0.0f;
-        } else {
-            float dx = mx - s_cam[28], dy = my - s_cam[29], dz = mz - s_cam[30];
-            const float inv_norm = rsqrtf(dx * dx + dy * dy + dz * dz);
-            dx = dx * inv_norm; dy = dy * inv_norm; dz = dz * inv_norm;
-            float f[48];
-            if (sh_vec4) {
-                const float4* row = dyn4 + tid * kShRow4;
-#pragma unroll
-                for (int j = 0; j < 12; ++j) {
-                    const float4 v = row[j];
-                    f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
-                }
-            } else {
-                const float* row = s_sh + tid * (row_floats | 1);
-                const int have = min(row_floats, 3 * (cp.sh_degree + 1) * (cp.sh_degree + 1));
-#pragma unroll
-                for (int j = 0; j < 48; ++j) f[j] = j < have ? row[j] : 0.0f;
-            }
-            cr = sh_channel(f, 0, cp.sh_degree, dx, dy, dz);
-            cg = sh_channel(f, 1, cp.sh_degree, dx, dy, dz);
-            cb = sh_channel(f, 2, cp.sh_degree, dx, dy, dz);
-        }
-
-        // Frustum test on the projected centre (strict bounds, z_ndc > 0.1).
-        const float inv_w = 1.f / (P[12] * mx + P[13] * my + P[14] * mz + P[15]);
-        const float ndc_x = inv_w * (P[0] * mx + P[1] * my + P[2] * mz + P[3]);
-        const float ndc_y = inv_w * (P[4] * mx + P[5] * my + P[6] * mz + P[7]);
-        const float ndc_z = inv_w * (P[8] * mx + P[9] * my + P[10] * mz + P[11]);
-        const int in_frustum = ndc_x > -1.f && ndc_x < 1.f && ndc_y > -1.f && ndc_y < 1.f && ndc_z > 0.1f;
-
-        // View-space centre.
-        const float tx = V[0] * mx + V[1] * my + V[2] * mz + V[3];
-        const float ty = V[4] * mx + V[5] * my + V[6] * mz + V[7];
-        tz = V[8] * mx + V[9] * my + V[10] * mz + V[11];
-
-        // EWA projection of the covariance: cov2d = (W J^T)^T Sigma (W J^T), W = view rotation columns.
-        const float limx = 1.3f * cp.tanfovx, limy = 1.3f * cp.tanfovy;
-        const float txtz = tx / tz, tytz = ty / tz;
-        const float t0 = min(limx, max(-limx, txtz)) * tz, t1 = min(limy, max(-limy, tytz)) * tz, t2 = tz;
-        const float J[3][3] = {{cp.fx / t2, 0, -(cp.fx * t0) / (t2 * t2)}, {0, cp.fy / t2, -(cp.fy * t1) / (t2 * t2)}, {0, 0, 0}};
-        const float Wc[3][3] = {{V[0], V[4], V[8]}, {V[1], V[5], V[9]}, {V[2], V[6], V[10]}};
-        float Tm[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
-#pragma unroll
-        for (int a = 0; a < 3; ++a)
-#pragma unroll
-            for (int b = 0; b < 3; ++b)
-#pragma unroll
-                for (int k = 0; k < 3; ++k) Tm[a][b] += Wc[a][k] * J[b][k];
-        const float Sm[3][3] = {{S[0], S[1], S[2]}, {S[1], S[3], S[4]}, {S[2], S[4], S[5]}};
-        float half[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
-#pragma unroll
-        for (int a = 0; a < 3; ++a)
-#pragma unroll
-            for (int b = 0; b < 3; ++b)
-#pragma unroll
-                for (int k = 0; k < 3; ++k) half[a][b] += Tm[k][a] * Sm[k][b];
-        float c2[2][2] = {{0, 0}, {0, 0}};
-#pragma unroll
-        for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int k = 0; k < 3; ++k) c2[a][b] += half[a][k] * Tm[k][b];
-        const float ca = c2[0][0] + 0.3f, cb2 = c2[0][1], cc = c2[1][1] + 0.3f;
-
-        // Pixel centre.
-        const float z_inv = 1.f / (tz + 1e-6f);
-        const float px = cp.fx * tx * z_inv + cp.cx, py = cp.fy * ty * z_inv + cp.cy;
-
-        // Radius from the larger eigenvalue, 3 sigma, rounded up.
-        const float det = ca * cc - cb2 * cb2;
-        const float mid = 0.5f * (ca + cc);
-        const float diff = mid * mid - det;
-        const float lambda1 = mid + sqrtf(max(0.1f, diff));
-        const float lambda2 = mid - sqrtf(max(0.1f, diff));
-        radius = ceilf(3 * sqrtf(max(lambda1, lambda2))) * (det > 1e-6f && in_frustum > 0);
-
-        // Tile rectangle (float -> int conversion truncates toward zero) and its size.
-        const float cxt = px / kTile, cyt = py / kTile, dt = radius / (float)kTile;
-        const int x0 = min(max(0, (int)(cxt - dt)), cp.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cp.tiles_x);
-        const int y0 = min(max(0, (int)(cyt - dt)), cp.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cp.tiles_y);
-        // A centre behind the camera can pass the frustum test (w < 0 flips both signs).  The reference
-        // still reports its radius but, because the negative depth bits spill over the tile id of its
-        // keys, never draws it; here it simply gets no pairs.
-        count = (x1 - x0) * (y1 - y0) * (radius > 0 && tz > 0.f);
-        // Corner marks of the tile rectangle (+1, -1, -1, +1) in a (tiles_y + 1) x (tiles_x + 1) grid: its 2-D
-        // prefix sum is the number of (tile, splat) pairs per tile, from which tile ranges and the tile sort's
-        // digit counts follow without a pass over the pairs.  Fire-and-forget reductions, hidden behind the
-        // kernel's memory traffic.
-        if (tile_marks && count > 0 && !(cp.drop_last && i == n - 1)) {
-            const int stride = cp.tiles_x + 1;
-            int* m = tile_marks + (size_t)(blockIdx.x % kMarkCopies) * marks_copy_ints;
-            atomicAdd(m + y0 * stride + x0, 1);
-            atomicAdd(m + y0 * stride + x1, -1);
-            atomicAdd(m + y1 * stride + x0, -1);
-            atomicAdd(m + y1 * stride + x1, 1);
-        }
-
-        // Conic = inverse of the dilated 2-D covariance.
-        const float det_inv = 1.0f / (det + 1e-6f);
-        q0 = make_float4(px, py, cc * det_inv, -cb2 * det_inv);
-        q1 = make_float4(ca * det_inv, opac[i], cr, cg);
-        q2 = make_float4(cb, tz, __uint_as_float(pack_rect(x0, x1)), __uint_as_float(pack_rect(y0, y1)));
-
-        radii[i] = radius;
-        tiles[i] = count;
-        depth_keys[i] = ((u64)__float_as_uint(tz) << 32) | (u32)i;
     }
 
-    // Outputs leave through shared memory so that global stores are contiguous 16-byte lanes.
-    __syncthreads();
-    float4* s_rec = dyn4;                                   // [256][3]
-    float* s_cov = reinterpret_cast<float*>(dyn4 + kThreads * 3);  // [256][6]
-    s_rec[tid * 3] = q0; s_rec[tid * 3 + 1] = q1; s_rec[tid * 3 + 2] = q2;
+    for (int view = 0; view < pv.count; ++view) {
+        const CamParams& cv = pv.cam[view];
+        const float* s_cam = s_cams[view];
+        float4 q0 = make_float4(0, 0, 0, 0), q1 = q0, q2 = q0;
+        if (live) {
+            const float* V = s_cam;
+            const float* P = s_cam + 12;
+            int radius = 0, count = 0;
+            float tz = 0.0f;
+            // Colour.
+            float cr, cg, cb;
+            if (colors_precomp) {
+                cr = colors_precomp[(size_t)i * 3]; cg = colors_precomp[(size_t)i * 3 + 1]; cb = colors_precomp[(size_t)i * 3 + 2];
+            } else if (cp.sh_degree > 3) {
+                cr = cg = cb = 0.0f;
+            } else {
+                float dx = mx - s_cam[28], dy = my - s_cam[29], dz = mz - s_cam[30];
+                const float inv_norm = rsqrtf(dx * dx + dy * dy + dz * dz);
+                dx = dx * inv_norm; dy = dy * inv_norm; dz = dz * inv_norm;
+                float f[48];
+                if (sh_vec4) {
+                    const float4* row = dyn4 + tid * kShRow4;
+    #pragma unroll
+                    for (int j = 0; j < 12; ++j) {
+                        const float4 v = row[j];
+                        f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
+                    }
+                } else {
+                    const float* row = s_sh + tid * (row_floats | 1);
+                    const int have = min(row_floats, 3 * (cp.sh_degree + 1) * (cp.sh_degree + 1));
+    #pragma unroll
+                    for (int j = 0; j < 48; ++j) f[j] = j < have ? row[j] : 0.0f;
+                }
+                cr = sh_channel(f, 0, cp.sh_degree, dx, dy, dz);
+                cg = sh_channel(f, 1, cp.sh_degree, dx, dy, dz);
+                cb = sh_channel(f, 2, cp.sh_degree, dx, dy, dz);
+            }
+
+            // Frustum test on the projected centre (strict bounds, z_ndc > 0.1).
+            const float inv_w = 1.f / (P[12] * mx + P[13] * my + P[14] * mz + P[15]);
+            const float ndc_x = inv_w * (P[0] * mx + P[1] * my + P[2] * mz + P[3]);
+            const float ndc_y = inv_w * (P[4] * mx + P[5] * my + P[6] * mz + P[7]);
+            const float ndc_z = inv_w * (P[8] * mx + P[9] * my + P[10] * mz + P[11]);
+            const int in_frustum = ndc_x > -1.f && ndc_x < 1.f && ndc_y > -1.f && ndc_y < 1.f && ndc_z > 0.1f;
+
+            // View-space centre.
+            const float tx = V[0] * mx + V[1] * my + V[2] * mz + V[3];
+            const float ty = V[4] * mx + V[5] * my + V[6] * mz + V[7];
+            tz = V[8] * mx + V[9] * my + V[10] * mz + V[11];
+
+            // EWA projection of the covariance: cov2d = (W J^T)^T Sigma (W J^T), W = view rotation columns.
+            const float limx = 1.3f * cv.tanfovx, limy = 1.3f * cv.tanfovy;
+            const float txtz = tx / tz, tytz = ty / tz;
+            const float t0 = min(limx, max(-limx, txtz)) * tz, t1 = min(limy, max(-limy, tytz)) * tz, t2 = tz;
+            const float J[3][3] = {{cv.fx / t2, 0, -(cv.fx * t0) / (t2 * t2)}, {0, cv.fy / t2, -(cv.fy * t1) / (t2 * t2)}, {0, 0, 0}};
+            const float Wc[3][3] = {{V[0], V[4], V[8]}, {V[1], V[5], V[9]}, {V[2], V[6], V[10]}};
+            float Tm[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    #pragma unroll
+            for (int a = 0; a < 3; ++a)
+    #pragma unroll
+                for (int b = 0; b < 3; ++b)
+    #pragma unroll
+                    for (int k = 0; k < 3; ++k) Tm[a][b] += Wc[a][k] * J[b][k];
+            const float Sm[3][3] = {{S[0], S[1], S[2]}, {S[1], S[3], S[4]}, {S[2], S[4], S[5]}};
+            float half[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    #pragma unroll
+            for (int a = 0; a < 3; ++a)
+    #pragma unroll
+                for (int b = 0; b < 3; ++b)
+    #pragma unroll
+                    for (int k = 0; k < 3; ++k) half[a][b] += Tm[k][a] * Sm[k][b];
+            float c2[2][2] = {{0, 0}, {0, 0}};
+    #pragma unroll
+            for (int a = 0; a < 2; ++a)
+    #pragma unroll
+                for (int b = 0; b < 2; ++b)
+    #pragma unroll
+                    for (int k = 0; k < 3; ++k) c2[a][b] += half[a][k] * Tm[k][b];
+            const float ca = c2[0][0] + 0.3f, cb2 = c2[0][1], cc = c2[1][1] + 0.3f;
+
+            // Pixel centre.
+            const float z_inv = 1.f / (tz + 1e-6f);
+            const float px = cv.fx * tx * z_inv + cv.cx, py = cv.fy * ty * z_inv + cv.cy;
+
+            // Radius from the larger eigenvalue, 3 sigma, rounded up.
+            const float det = ca * cc - cb2 * cb2;
+            const float mid = 0.5f * (ca + cc);
+            const float diff = mid * mid - det;
+            const float lambda1 = mid + sqrtf(max(0.1f, diff));
+            const float lambda2 = mid - sqrtf(max(0.1f, diff));
+            radius = ceilf(3 * sqrtf(max(lambda1, lambda2))) * (det > 1e-6f && in_frustum > 0);
+
+            // Tile rectangle (float -> int conversion truncates toward zero) and its size.
+            const float cxt = px / kTile, cyt = py / kTile, dt = radius / (float)kTile;
+            const int x0 = min(max(0, (int)(cxt - dt)), cv.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cv.tiles_x);
+            const int y0 = min(max(0, (int)(cyt - dt)), cv.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cv.tiles_y);
+            // A centre behind the camera can pass the frustum test (w < 0 flips both signs).  The reference
+            // still reports its radius but, because the negative depth bits spill over the tile id of its
+            // keys, never draws it; here it simply gets no pairs.
+            count = (x1 - x0) * (y1 - y0) * (radius > 0 && tz > 0.f);
+            // Corner marks of the tile rectangle (+1, -1, -1, +1) in a (tiles_y + 1) x (tiles_x + 1) grid: its 2-D
+            // prefix sum is the number of (tile, splat) pairs per tile, from which tile ranges and the tile sort's
+            // digit counts follow without a pass over the pairs.  Fire-and-forget reductions, hidden behind the
+            // kernel's memory traffic.
+            if (pv.tile_marks[view] && count > 0 && !(cv.drop_last && i == n - 1)) {
+                const int stride = cv.tiles_x + 1;
+                int* m = pv.tile_marks[view] + (size_t)(blockIdx.x % kMarkCopies) * marks_copy_ints;
+                atomicAdd(m + y0 * stride + x0, 1);
+                atomicAdd(m + y0 * stride + x1, -1);
+                atomicAdd(m + y1 * stride + x0, -1);
+                atomicAdd(m + y1 * stride + x1, 1);
+            }
+
+            // Conic = inverse of the dilated 2-D covariance.
+            const float det_inv = 1.0f / (det + 1e-6f);
+            q0 = make_float4(px, py, cc * det_inv, -cb2 * det_inv);
+            q1 = make_float4(ca * det_inv, opacity, cr, cg);
+            q2 = make_float4(cb, tz, __uint_as_float(pack_rect(x0, x1)), __uint_as_float(pack_rect(y0, y1)));
+
+            pv.radii[view][i] = radius;
+            pv.tiles[view][i] = count;
+            pv.depth_keys[view][i] = ((u64)__float_as_uint(tz) << 32) | (u32)i;
+        }
+
+        // Records leave through shared memory so that global stores are contiguous 16-byte lanes.
+        s_rec[tid * 3] = q0; s_rec[tid * 3 + 1] = q1; s_rec[tid * 3 + 2] = q2;
+        __syncthreads();
+        float4* grec = pv.records[view] + (size_t)base * 3;
+        for (int k = tid; k < cnt * 3; k += kThreads) grec[k] = s_rec[k];
+        __syncthreads();   // s_rec is reused by the next view
+    }
+
+    if (cov3d && !cov3d_precomp) {   // the covariance does not depend on the view: written once
+        float* s_cov = reinterpret_cast<float*>(s_rec);  // [256][6]
 #pragma unroll
-    for (int k = 0; k < 6; ++k) s_cov[tid * 6 + k] = S[k];
-    __syncthreads();
-    float4* grec = records + (size_t)base * 3;
-    for (int k = tid; k < cnt * 3; k += kThreads) grec[k] = s_rec[k];
-    if (cov3d && !cov3d_precomp) {
+        for (int k = 0; k < 6; ++k) s_cov[tid * 6 + k] = S[k];
+        __syncthreads();
         float* gcov = cov3d + (size_t)base * 6;
         for (int k = tid; k < cnt * 6; k += kThreads) gcov[k] = s_cov[k];
     }
@@ -289,36 +315,58 @@ preprocess_kernel(const CamParams cp, const int n, const float* __restrict__ mea
 
 }  // namespace
 
-int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
-                      const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
-                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, int* tile_marks,
-                      cudaStream_t s) {
-    if (n == 0) return DSB_OK;
+// views: `count` cameras with their output buffers (count <= DSB_MAX_BATCH_VIEWS); cov3d is written once.
+int launch_preprocess_views(const CamParams* cps, int count, int n, const float* means, const float* shs,
+                            const float* colors_precomp, const float* opac, const float* scales, const float* rots,
+                            const float* cov3d_precomp, float* const* records, int32_t* const* radii,
+                            int32_t* const* tiles, float* cov3d, u64* const* depth_keys, int* const* tile_marks,
+                            cudaStream_t s) {
+    if (n == 0 || count == 0) return DSB_OK;
+    DSB_REQUIRE(count > 0 && count <= DSB_MAX_BATCH_VIEWS, "preprocess: %d views in one call (at most %d)", count,
+                DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(means && opac && records && radii && tiles && depth_keys, "preprocess: null required pointer");
     DSB_REQUIRE(colors_precomp || shs, "preprocess: need shs or colors_precomp");
     DSB_REQUIRE(cov3d_precomp || (scales && rots), "preprocess: need scales and rotations, or cov3d_precomp");
-    DSB_REQUIRE(((uintptr_t)records & 15) == 0, "preprocess: records must be 16-byte aligned");
     DSB_REQUIRE(!rots || ((uintptr_t)rots & 15) == 0, "preprocess: rotations must be 16-byte aligned");
+    const CamParams& cp = cps[0];
+    PreViews pv;
+    pv.count = count;
+    for (int v = 0; v < count; ++v) {
+        DSB_REQUIRE(records[v] && radii[v] && tiles[v] && depth_keys[v], "preprocess: null output pointer for view %d", v);
+        DSB_REQUIRE(((uintptr_t)records[v] & 15) == 0, "preprocess: records must be 16-byte aligned");
+        DSB_REQUIRE(cps[v].max_coeff == cp.max_coeff && cps[v].sh_degree == cp.sh_degree &&
+                        cps[v].scale_modifier == cp.scale_modifier,
+                    "preprocess: the views of one call must share SH degree and scale modifier");
+        DSB_REQUIRE(cps[v].H == cp.H && cps[v].W == cp.W, "preprocess: the views of one call must share the image size");
+        pv.cam[v] = cps[v];
+        pv.records[v] = reinterpret_cast<float4*>(records[v]);
+        pv.radii[v] = radii[v];
+        pv.tiles[v] = tiles[v];
+        pv.depth_keys[v] = depth_keys[v];
+        pv.tile_marks[v] = tile_marks ? tile_marks[v] : nullptr;
+    }
     const int sh_vec4 = shs && cp.max_coeff == 16 && ((uintptr_t)shs & 15) == 0;
     // bulk-copy staging needs every streamed input 16-byte aligned and the default input form
     const int use_bulk = sh_vec4 && !colors_precomp && !cov3d_precomp && scales && ((uintptr_t)means & 15) == 0 &&
                          ((uintptr_t)scales & 15) == 0;
-    // dynamic shared memory: padded SH rows on the way in, record + covariance rows on the way out
-    const size_t sh_bytes = sh_vec4 ? (size_t)kThreads * kShRow4 * 16 : (size_t)kThreads * ((3 * cp.max_coeff) | 1) * 4;
-    const size_t out_bytes = (size_t)kThreads * (3 * 16 + 6 * 4);
-    const size_t dyn = sh_bytes > out_bytes ? sh_bytes : out_bytes;
-    static bool attr_set = false;
-    if (!attr_set) {
-        DSB_CUDA_CHECK(cudaFuncSetAttribute(preprocess_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        attr_set = true;
-    }
+    // dynamic shared memory: the padded SH rows
+    const size_t dyn = sh_vec4 ? (size_t)kThreads * kShRow4 * 16 : (size_t)kThreads * ((3 * cp.max_coeff) | 1) * 4;
     DSB_REQUIRE(dyn <= 64 * 1024, "preprocess: SH layout too large for shared memory");
+    // the attribute belongs to the current device's context, so it is set at every launch rather than cached
+    DSB_CUDA_CHECK(cudaFuncSetAttribute(preprocess_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
     const int blocks = (n + kThreads - 1) / kThreads;
-    preprocess_kernel<<<blocks, kThreads, dyn, s>>>(cp, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp,
-                                                   reinterpret_cast<float4*>(records), radii, tiles, cov3d, depth_keys,
-                                                   sh_vec4, use_bulk, tile_marks, (int)tile_marks_copy_ints(cp.H, cp.W));
+    preprocess_kernel<<<blocks, kThreads, dyn, s>>>(pv, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp, cov3d,
+                                                   sh_vec4, use_bulk, (int)tile_marks_copy_ints(cp.H, cp.W));
     DSB_LAUNCH_CHECK();
     return DSB_OK;
+}
+
+int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
+                      const float* opac, const float* scales, const float* rots, const float* cov3d_precomp,
+                      float* records, int32_t* radii, int32_t* tiles, float* cov3d, u64* depth_keys, int* tile_marks,
+                      cudaStream_t s) {
+    return launch_preprocess_views(&cp, 1, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp, &records, &radii,
+                                   &tiles, cov3d, &depth_keys, tile_marks ? &tile_marks : nullptr, s);
 }
 
 }  // namespace dsb

@@ -92,8 +92,25 @@ class CameraTensors:
                              t(np.ascontiguousarray(view.campos)), torch.zeros(3, device=device))
 
 
+class _Slot:
+    """Per-view buffers that must survive until the batch's per-splat backward: 124 bytes per splat."""
+
+    def __init__(self, n, dev, capi):
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.records = torch.empty((n, capi.RECORD_FLOATS), **f32)
+        self.radii = torch.empty(n, dtype=torch.int32, device=dev)
+        self.tiles = torch.empty(n, dtype=torch.int32, device=dev)
+        self.depth_keys = torch.empty(n, dtype=torch.int64, device=dev)
+        self.grad_acc = torch.empty((n, capi.GRAD_FLOATS), **f32)
+        self.marks = {}     # (H, W) -> tile-mark grid, later the tile order
+        self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
+
+
 class ViewRenderer:
-    """Forward + backward of one view at a time through the fused C-ABI calls, with reusable buffers."""
+    """Forward + backward of views of one splat cloud through the fused C-ABI calls, with reusable buffers.
+
+    ``forward`` / ``backward`` handle one view at a time; ``render_views`` handles a whole step (see the module
+    docstring) and is what ``data_parallel_step`` uses."""
 
     def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True,
                  batch_views: int = 8):
@@ -108,26 +125,24 @@ class ViewRenderer:
         self.coeffs = shs.shape[1]
         self.strict = strict_reference
         n, dev = self.n, self.dev
-        f32 = dict(dtype=torch.float32, device=dev)
         self.batch_views = max(1, min(int(batch_views), _capi.MAX_BATCH_VIEWS))
-        # slot 0 exists from the start; the other slots of a batch are allocated when a step first uses them
-        self.slot_records = [torch.empty((n, _capi.RECORD_FLOATS), **f32)]
-        self.slot_radii = [torch.empty(n, dtype=torch.int32, device=dev)]
-        self.slot_grad = [torch.empty((n, _capi.GRAD_FLOATS), **f32)]
-        self.slot_cam = [None]
-        self.records, self.radii = self.slot_records[0], self.slot_radii[0]
-        self.tiles = torch.empty(n, dtype=torch.int32, device=dev)
-        self.cov3d = torch.empty((n, 6), **f32)
-        self.depth_keys = torch.empty((2, n), dtype=torch.int64, device=dev)
+        self.slots = [_Slot(n, dev, _capi)]   # further slots are allocated when a step first needs them
+        self.cur = self.slots[0]
+        self.cov3d = torch.empty((n, 6), dtype=torch.float32, device=dev)
+        self.depth_keys_alt = torch.empty(n, dtype=torch.int64, device=dev)
         self.offsets = torch.empty(n, dtype=torch.int32, device=dev)
         self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes(n))
         self.plan_ws = torch.empty(self.plan_bytes, dtype=torch.uint8, device=dev)
-        self.grad_acc = self.slot_grad[0]
         self.pairs = None
         self.sort_ws = None
         self.sort_bytes = 0
         self.img = {}
         self.last_k = 0
+
+    # buffers of the view rendered last (kept as attributes for callers that inspect them)
+    records = property(lambda self: self.cur.records)
+    radii = property(lambda self: self.cur.radii)
+    grad_acc = property(lambda self: self.cur.grad_acc)
 
     def _image_buffers(self, h, w):
         key = (h, w)
@@ -135,94 +150,123 @@ class ViewRenderer:
             f32 = dict(dtype=torch.float32, device=self.dev)
             self.img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
                              torch.empty((h, w), dtype=torch.int32, device=self.dev),
-                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev),
-                             torch.empty(int(self.lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=self.dev))
+                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev))
         return self.img[key]
+
+    def _marks(self, slot: _Slot, h, w):
+        key = (h, w)
+        if key not in slot.marks:
+            slot.marks[key] = torch.empty(int(self.lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=self.dev)
+        return slot.marks[key]
 
     def _camera(self, cam: CameraTensors):
         max_deg = {1: 0, 4: 1, 9: 2, 16: 3}[self.coeffs]
         return self._capi.make_camera(cam.H, cam.W, cam.tanfovx, cam.tanfovy, cam.viewmatrix, cam.projmatrix, cam.campos,
                                       cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict)
 
-    def _slot(self, j: int):
-        while len(self.slot_records) <= j:
-            f32 = dict(dtype=torch.float32, device=self.dev)
-            self.slot_records.append(torch.empty((self.n, self._capi.RECORD_FLOATS), **f32))
-            self.slot_radii.append(torch.empty(self.n, dtype=torch.int32, device=self.dev))
-            self.slot_grad.append(torch.empty((self.n, self._capi.GRAD_FLOATS), **f32))
-            self.slot_cam.append(None)
-        return self.slot_records[j], self.slot_radii[j], self.slot_grad[j]
+    def _slot(self, j: int) -> _Slot:
+        while len(self.slots) <= j:
+            self.slots.append(_Slot(self.n, self.dev, self._capi))
+        return self.slots[j]
 
-    def forward(self, cam: CameraTensors, slot: int = 0):
-        """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size).
-        ``slot`` selects which of the batch's record / radii buffers the view's per-splat data goes to."""
-        capi, lib, p = self._capi, self.lib, self.p
-        self.records, self.radii, self.grad_acc = self._slot(slot)
-        c, keep = self._camera(cam)
-        stream = capi.stream_ptr()
-        k = C.c_int64(0)
-        image, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
-        capi.check(lib.dsb_forward_plan(
-            C.byref(c), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
-            p["scales"].data_ptr(), p["rotations"].data_ptr(), None, self.records.data_ptr(), self.radii.data_ptr(),
-            self.tiles.data_ptr(), self.cov3d.data_ptr(), self.depth_keys[0].data_ptr(), self.depth_keys[1].data_ptr(),
-            self.offsets.data_ptr(), tile_marks.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes, C.byref(k), stream))
-        k = int(k.value)
+    def _pair_buffers(self, k: int):
         if self.pairs is None or self.pairs.shape[1] < k:
             cap = max(int(k * 1.25), 1024)
             self.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
-            self.sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
+            self.sort_bytes = int(self.lib.dsb_sort_workspace_bytes(cap))
             self.sort_ws = torch.empty(self.sort_bytes, dtype=torch.uint8, device=self.dev)
+
+    def _render(self, slot: _Slot, cam: CameraTensors, k: int):
+        """Second half of a forward: pairs, tile layout, tile sort, blend.  Returns the image buffer."""
+        capi, lib = self._capi, self.lib
+        c, _keep = slot.cam
+        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        self._pair_buffers(k)
         capi.check(lib.dsb_forward_render(
-            C.byref(c), self.n, k, self.records.data_ptr(), self.tiles.data_ptr(), self.depth_keys[0].data_ptr(),
-            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(), tile_marks.data_ptr(),
-            self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(), image.data_ptr(), final_t.data_ptr(),
-            final_idx.data_ptr(), None, stream))
+            C.byref(c), self.n, k, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
+            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(),
+            self._marks(slot, cam.H, cam.W).data_ptr(), self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(),
+            image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None, capi.stream_ptr()))
         self.last_k = k
-        self._last_cam = (c, keep, cam)
-        self.slot_cam[slot] = (c, keep)
+        self.cur = slot
+        self._last_cam = cam
         return image
+
+    def forward(self, cam: CameraTensors, slot: int = 0):
+        """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size)."""
+        capi, lib, p = self._capi, self.lib, self.p
+        sl = self._slot(slot)
+        sl.cam = self._camera(cam)
+        k = C.c_int64(0)
+        capi.check(lib.dsb_forward_plan(
+            C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
+            p["scales"].data_ptr(), p["rotations"].data_ptr(), None, sl.records.data_ptr(), sl.radii.data_ptr(),
+            sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_keys_alt.data_ptr(),
+            self.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
+            C.byref(k), capi.stream_ptr()))
+        return self._render(sl, cam, int(k.value))
 
     def backward(self, v_image: torch.Tensor, grads: GradientBuffer, accumulate: bool = True):
         """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
         capi, lib, p = self._capi, self.lib, self.p
-        c, keep, cam = self._last_cam
-        image, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
+        sl, cam = self.cur, self._last_cam
+        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
         g = grads.views
         capi.check(lib.dsb_backward(
-            C.byref(c), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
-            self.records.data_ptr(), self.cov3d.data_ptr(), self.radii.data_ptr(), self.pairs[0].data_ptr(),
+            C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
+            sl.records.data_ptr(), self.cov3d.data_ptr(), sl.radii.data_ptr(), self.pairs[0].data_ptr(),
             ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
-            tile_marks.data_ptr(), self.grad_acc.data_ptr(),
+            self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(),
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 
     def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False):
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
-        contents when ``accumulate``).  Views are taken in batches of ``batch_views``: per view the forward and the
-        backward blend, per batch one per-splat backward over all its views."""
+        contents when ``accumulate``).  ``image_grads`` is a sequence of dL/dimage tensors or a callable
+        ``(index, image) -> dL/dimage``.  Views are taken in batches of up to ``batch_views`` of one image size:
+        one preprocess launch for the batch, then per view the rest of the forward and the backward blend, then
+        one per-splat backward for the batch."""
         capi, lib, p = self._capi, self.lib, self.p
         g = grads.views
-        for b0 in range(0, len(cameras), self.batch_views):
-            batch = range(b0, min(b0 + self.batch_views, len(cameras)))
-            for j, idx in enumerate(batch):
-                cam = cameras[idx]
-                image = self.forward(cam, slot=j)
-                v_image = image_grads(idx, image) if callable(image_grads) else image_grads[idx]
-                c, keep = self.slot_cam[j]
-                _img, final_t, final_idx, ranges, tile_marks = self._image_buffers(cam.H, cam.W)
+        b0, first = 0, True
+        while b0 < len(cameras):
+            size = (cameras[b0].H, cameras[b0].W)
+            b1 = b0 + 1
+            while b1 < len(cameras) and b1 - b0 < self.batch_views and (cameras[b1].H, cameras[b1].W) == size:
+                b1 += 1
+            nv = b1 - b0
+            slots = [self._slot(j) for j in range(nv)]
+            for j, sl in enumerate(slots):
+                sl.cam = self._camera(cameras[b0 + j])
+            cams = (capi.DsbCamera * nv)(*[sl.cam[0] for sl in slots])
+            ptrs = lambda ts: (C.c_void_p * nv)(*[t.data_ptr() for t in ts])
+            capi.check(lib.dsb_preprocess_views(
+                cams, nv, self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
+                p["scales"].data_ptr(), p["rotations"].data_ptr(), None, ptrs([sl.records for sl in slots]),
+                ptrs([sl.radii for sl in slots]), ptrs([sl.tiles for sl in slots]), self.cov3d.data_ptr(),
+                ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]), capi.stream_ptr()))
+            for j, sl in enumerate(slots):
+                cam = cameras[b0 + j]
+                k = C.c_int64(0)
+                capi.check(lib.dsb_plan_pairs(
+                    C.byref(sl.cam[0]), self.n, sl.tiles.data_ptr(), sl.depth_keys.data_ptr(),
+                    self.depth_keys_alt.data_ptr(), self.offsets.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
+                    C.byref(k), capi.stream_ptr()))
+                image = self._render(sl, cam, int(k.value))
+                v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
+                _img, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
                 capi.check(lib.dsb_backward_blend(
-                    C.byref(c), self.n, self.records.data_ptr(), self.pairs[0].data_ptr(), ranges.data_ptr(),
-                    final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None, tile_marks.data_ptr(),
-                    self.grad_acc.data_ptr(), capi.stream_ptr()))
-            nv = len(batch)
-            cams = (capi.DsbCamera * nv)(*[self.slot_cam[j][0] for j in range(nv)])
-            ptrs = lambda ts: (C.c_void_p * nv)(*[t.data_ptr() for t in ts[:nv]])
+                    C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), self.pairs[0].data_ptr(), ranges.data_ptr(),
+                    final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
+                    self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
             capi.check(lib.dsb_geometry_backward_views(
                 cams, nv, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
-                self.cov3d.data_ptr(), ptrs(self.slot_records), ptrs(self.slot_radii), ptrs(self.slot_grad),
-                g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
-                g["rotations"].data_ptr(), None, 1 if (accumulate or b0 > 0) else 0, capi.stream_ptr()))
+                self.cov3d.data_ptr(), ptrs([sl.records for sl in slots]), ptrs([sl.radii for sl in slots]),
+                ptrs([sl.grad_acc for sl in slots]), g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None,
+                g["opacities"].data_ptr(), g["scales"].data_ptr(), g["rotations"].data_ptr(), None,
+                1 if (accumulate or not first) else 0, capi.stream_ptr()))
+            first = False
+            b0 = b1
 
 
 def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads,

@@ -229,14 +229,25 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
  * A training step renders several cameras against the same splats and needs the SUM of their gradients
  * (no reference counterpart: the reference is called once per camera and autograd adds the results).
  * Splitting dsb_backward lets the per-splat part run once per step instead of once per view:
- *   per view:   dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
+ *   per step:   dsb_preprocess_views          (= the preprocess half of dsb_forward_plan for up to
+ *                                              DSB_MAX_BATCH_VIEWS cameras: the splat parameters are read once,
+ *                                              the 3-D covariance computed once; clears and fills each
+ *                                              view's tile_marks)
+ *   per view:   dsb_plan_pairs, dsb_forward_render, then
+ *               dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
  *   per step:   dsb_geometry_backward_views   over up to DSB_MAX_BATCH_VIEWS views at a time
- * records, radii and grad_acc are HOST arrays of num_views device pointers (one buffer per view, all of the
+ * records, radii, tiles_touched, depth_keys, tile_marks and grad_acc are HOST arrays of num_views device pointers (one buffer per view, all of the
  * layouts dsb_preprocess / dsb_blend_backward use); cams is a host array of num_views cameras that must
- * share sh_degree, max_sh_degree and scale_modifier; cov3d is the splats' own (any view's).  The outputs
+ * share sh_degree, max_sh_degree and scale_modifier (and, for dsb_preprocess_views, the image size); cov3d is
+ * the splats' own (any view's).  The outputs
  * receive the sum over the views (added to their contents when accumulate != 0); v_means2d, too, is the
  * sum over views.  Results equal num_views calls of dsb_geometry_backward with accumulate, up to
  * floating-point summation order. */
+int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                         const float* shs, const float* colors_precomp, const float* opacities,
+                         const float* scales, const float* rotations, const float* cov3d_precomp,
+                         float* const* records, int32_t* const* radii, int32_t* const* tiles_touched,
+                         float* cov3d, uint64_t* const* depth_keys, int32_t* const* tile_marks, void* stream);
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
                        const float* v_image, const float* v_depth /* may be NULL */,

@@ -174,7 +174,7 @@ def test_fused_render_matches_stage_calls():
     image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
     k = r.last_k
     fused_pairs = r.pairs[0][:k].clone()
-    _, _, _, fused_ranges, _ = r._image_buffers(view.H, view.W)
+    _, _, _, fused_ranges = r._image_buffers(view.H, view.W)
     from conftest import capi_camera
     cam, keep = capi_camera(view)
     records, radii, tiles, cov3d, dk = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
@@ -244,3 +244,18 @@ def test_batched_views_equal_one_view_at_a_time():
     single.forward(cams[1]); single.backward(vimgs[1], g_s, accumulate=True)
     torch.cuda.synchronize()
     assert _rel(g_b.views["shs"].cpu().numpy(), g_s.views["shs"].cpu().numpy()) < 1e-4
+
+
+def test_preprocess_of_several_views_is_bit_identical_to_one_at_a_time():
+    from conftest import capi_camera
+    sc = scenes.headline(n=30_000, seed=94, W=400, H=240, focal=260.0, views=5)
+    t = scene_tensors(sc)
+    cams, keep = zip(*[capi_camera(v) for v in sc.views])
+    outs, cov3d = _capi.preprocess_views(list(cams), t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    torch.cuda.synchronize()
+    for cam, (records, radii, tiles, dkeys, _marks) in zip(cams, outs):
+        r1, ra1, t1, c1, d1 = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+        assert torch.equal(records.view(torch.int32), r1.view(torch.int32))
+        assert torch.equal(radii, ra1) and torch.equal(tiles, t1) and torch.equal(dkeys, d1)
+        assert torch.equal(cov3d, c1)
+    assert int(outs[0][1].max()) > 0 and not torch.equal(outs[0][0], outs[1][0])
