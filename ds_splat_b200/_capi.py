@@ -25,7 +25,8 @@ EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
-    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_backward_blend",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_pairs_views",
+    "dsb_backward_blend",
     "dsb_geometry_backward_views",
     "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
@@ -64,6 +65,8 @@ def lib():
         l.dsb_launch_count.restype = C.c_int64
         l.dsb_plan_workspace_bytes.restype = C.c_int64
         l.dsb_plan_workspace_bytes.argtypes = [C.c_int32]
+        l.dsb_plan_workspace_bytes_views.restype = C.c_int64
+        l.dsb_plan_workspace_bytes_views.argtypes = [C.c_int32, C.c_int32]
         l.dsb_sort_workspace_bytes.restype = C.c_int64
         l.dsb_sort_workspace_bytes.argtypes = [C.c_int64]
         l.dsb_tile_marks_bytes.restype = C.c_int64
@@ -88,6 +91,7 @@ def lib():
             "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
             "dsb_preprocess_views": [P, I32, I32] + [P] * 14,
+            "dsb_plan_pairs_views": [CAM, I32, I32, I64, P, P, P, P, P, I64, P, P],
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],

@@ -30,8 +30,12 @@ struct PlanTail {       // lives after the sort workspace
 // Single-pass exclusive scan of tiles_touched taken in depth order.
 __global__ void __launch_bounds__(kScanThreads)
 scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __restrict__ tiles, const int n,
-                   const int drop_last, u32* __restrict__ offsets, u64* __restrict__ lookback, PlanTail* __restrict__ tail) {
+                   const int drop_last, u32* __restrict__ offsets, u64* __restrict__ lookback, PlanTail* __restrict__ tail,
+                   const long long item_stride, const long long lookback_stride) {
     __shared__ u32 s_wsum[32];
+    // blockIdx.y: which view of the batch (each with its own keys, counts, offsets, look-back row and tail)
+    depth_keys_sorted += blockIdx.y * item_stride; tiles += blockIdx.y * item_stride; offsets += blockIdx.y * item_stride;
+    lookback += blockIdx.y * lookback_stride; tail += blockIdx.y;
     __shared__ u32 s_tile;
     __shared__ u64 s_prefix;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -336,61 +340,90 @@ inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 
 }  // namespace
 
-int64_t plan_workspace_bytes(int n) {
-    const int64_t scan_tiles = (n + kScanThreads - 1) / kScanThreads;
-    return align256(sort_workspace_bytes(n)) + align256(scan_tiles * 8) + align256(sizeof(PlanTail));
+// Workspace of a batch of `views` plans: per view a sort slice, then per view a scan look-back row, then the tails.
+static int64_t plan_scan_row_bytes(int n) { return align256(((int64_t)n + kScanThreads - 1) / kScanThreads * 8); }
+int64_t plan_workspace_bytes_views(int n, int views) {
+    return (int64_t)views * (sort_batch_stride_bytes(n) + plan_scan_row_bytes(n)) + align256((int64_t)views * sizeof(PlanTail));
 }
+int64_t plan_workspace_bytes(int n) { return plan_workspace_bytes_views(n, 1); }
 
-int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
-                void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
+// Depth order and pair offsets of `views` views in the same launches.  tiles, depth_keys, depth_keys_alt and
+// offsets hold one row of `n` entries per view, `item_stride` entries apart; k_host receives one total per view.
+int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
+                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
     DSB_REQUIRE(k_host, "plan: k_host is null");
-    *k_host = 0;
+    DSB_REQUIRE(views >= 1 && views <= DSB_MAX_BATCH_VIEWS, "plan: between 1 and %d views per call", DSB_MAX_BATCH_VIEWS);
+    for (int v = 0; v < views; ++v) k_host[v] = 0;
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(tiles && depth_keys && depth_keys_alt && offsets && ws, "plan: null pointer");
-    const int64_t need = plan_workspace_bytes(n);
+    DSB_REQUIRE(views == 1 || item_stride >= n, "plan: rows of the views overlap");
+    const int64_t need = plan_workspace_bytes_views(n, views);
     if (ws_bytes < need) {
         set_error("plan: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
         return DSB_ERR_WORKSPACE_TOO_SMALL;
     }
     DSB_REQUIRE(((uintptr_t)ws & 255) == 0, "plan: workspace must be 256-byte aligned");
     unsigned char* base = reinterpret_cast<unsigned char*>(ws);
-    const int64_t sort_bytes = align256(sort_workspace_bytes(n));
-    const int64_t scan_tiles = (n + kScanThreads - 1) / kScanThreads;
+    const int64_t sort_stride = sort_batch_stride_bytes(n), sort_bytes = (int64_t)views * sort_stride;
+    const int64_t scan_row = plan_scan_row_bytes(n);
+    const int64_t scan_tiles = ((int64_t)n + kScanThreads - 1) / kScanThreads;
     u64* lookback = reinterpret_cast<u64*>(base + sort_bytes);
-    PlanTail* tail = reinterpret_cast<PlanTail*>(base + sort_bytes + align256(scan_tiles * 8));
+    PlanTail* tail = reinterpret_cast<PlanTail*>(base + sort_bytes + (int64_t)views * scan_row);
 
+    // everything, including the sort slices: a list of one item or none is not sorted and leaves its slice untouched
     DSB_CUDA_CHECK(cudaMemsetAsync(ws, 0, (size_t)need, s));
 
     // (depth, id) order: sort the packed (depth bits << 32 | id) words on their depth bits; ids are already ascending.
     int in_alt = 0;
     {
         StageScope scope(kStageDepthSort, s);
-        int rc = launch_sort(depth_keys, depth_keys_alt, nullptr, nullptr, n, 32, 64, ws, sort_bytes, &in_alt, s);
+        int rc = launch_sort(depth_keys, depth_keys_alt, nullptr, nullptr, n, 32, 64, ws, sort_bytes, &in_alt, s, false, views,
+                             item_stride);
         if (rc != DSB_OK) return rc;
-        if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(depth_keys, depth_keys_alt, (size_t)n * 8, cudaMemcpyDeviceToDevice, s));
+        if (in_alt) {
+            if (views == 1 || item_stride == n) {
+                DSB_CUDA_CHECK(cudaMemcpyAsync(depth_keys, depth_keys_alt, (size_t)(item_stride * (views - 1) + n) * 8,
+                                               cudaMemcpyDeviceToDevice, s));
+            } else {
+                DSB_CUDA_CHECK(cudaMemcpy2DAsync(depth_keys, (size_t)item_stride * 8, depth_keys_alt, (size_t)item_stride * 8,
+                                                 (size_t)n * 8, (size_t)views, cudaMemcpyDeviceToDevice, s));
+            }
+        }
     }
     {
         StageScope scope(kStageScan, s);
-        scan_counts_kernel<<<(unsigned)scan_tiles, kScanThreads, 0, s>>>(depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail);
+        scan_counts_kernel<<<dim3((unsigned)scan_tiles, (unsigned)views), kScanThreads, 0, s>>>(
+            depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8);
         DSB_LAUNCH_CHECK();
     }
 
-    struct { u64 total; u32 counter; int status; } host_tail;
-    int sort_status = 0;
-    DSB_CUDA_CHECK(cudaMemcpyAsync(&host_tail, tail, sizeof(host_tail), cudaMemcpyDeviceToHost, s));
-    DSB_CUDA_CHECK(cudaMemcpyAsync(&sort_status, base + sort_status_offset(), sizeof(int), cudaMemcpyDeviceToHost, s));
+    struct HostTail { u64 total; u32 counter; int status; } host_tail[DSB_MAX_BATCH_VIEWS];
+    int sort_status[DSB_MAX_BATCH_VIEWS] = {};
+    static_assert(sizeof(HostTail) == sizeof(PlanTail), "host mirror of the plan tail");
+    DSB_CUDA_CHECK(cudaMemcpyAsync(host_tail, tail, sizeof(HostTail) * views, cudaMemcpyDeviceToHost, s));
+    DSB_CUDA_CHECK(cudaMemcpy2DAsync(sort_status, sizeof(int), base + sort_status_offset(), (size_t)sort_stride, sizeof(int),
+                                     (size_t)views, cudaMemcpyDeviceToHost, s));
     DSB_CUDA_CHECK(cudaStreamSynchronize(s));
-    if (host_tail.status != 0 || sort_status != 0) {
-        set_error("plan: a device-side wait expired (scan %d, sort %d)", host_tail.status, sort_status);
-        return DSB_ERR_DEVICE_WAIT_EXPIRED;
+    for (int v = 0; v < views; ++v) {
+        if (host_tail[v].status != 0 || sort_status[v] != 0) {
+            set_error("plan: a device-side wait expired (view %d: scan %d, sort %d)", v, host_tail[v].status, sort_status[v]);
+            return DSB_ERR_DEVICE_WAIT_EXPIRED;
+        }
+        k_host[v] = (int64_t)host_tail[v].total;
     }
-    if (host_tail.total >= (u64)DSB_MAX_PAIRS) {
-        set_error("plan: %llu (tile, splat) pairs exceed the supported maximum of 2^30 - 1", (unsigned long long)host_tail.total);
-        *k_host = (int64_t)host_tail.total;
-        return DSB_ERR_TOO_MANY_PAIRS;
+    for (int v = 0; v < views; ++v) {
+        if (host_tail[v].total >= (u64)DSB_MAX_PAIRS) {
+            set_error("plan: %llu (tile, splat) pairs exceed the supported maximum of 2^30 - 1",
+                      (unsigned long long)host_tail[v].total);
+            return DSB_ERR_TOO_MANY_PAIRS;
+        }
     }
-    *k_host = (int64_t)host_tail.total;
     return DSB_OK;
+}
+
+int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
+                void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
+    return launch_plan_views(cp, 1, n, n, tiles, depth_keys, depth_keys_alt, offsets, ws, ws_bytes, k_host, s);
 }
 
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,

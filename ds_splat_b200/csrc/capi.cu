@@ -149,6 +149,20 @@ int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched
                        offsets, workspace, workspace_bytes, k_host, (cudaStream_t)stream);
 }
 
+int64_t dsb_plan_workspace_bytes_views(int32_t n, int32_t num_views) {
+    return (n >= 0 && num_views >= 1 && num_views <= DSB_MAX_BATCH_VIEWS) ? plan_workspace_bytes_views(n, num_views) : 0;
+}
+
+int dsb_plan_pairs_views(const DsbCamera* cam, int32_t num_views, int32_t n, int64_t row_stride,
+                         const int32_t* tiles_touched, uint64_t* depth_keys, uint64_t* depth_keys_alt, uint32_t* offsets,
+                         void* workspace, int64_t workspace_bytes, int64_t* k_host, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    return launch_plan_views(cp, num_views, n, row_stride, tiles_touched, reinterpret_cast<u64*>(depth_keys),
+                             reinterpret_cast<u64*>(depth_keys_alt), offsets, workspace, workspace_bytes, k_host,
+                             (cudaStream_t)stream);
+}
+
 int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
                    const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, void* stream) {
     CAM_OR_RETURN(cam, cp);

@@ -138,14 +138,19 @@ SortPlan make_sort_plan(int begin_bit, int end_bit, bool signed_top);
 int64_t sort_workspace_bytes(int64_t k);
 int64_t sort_status_offset();  // byte offset of the int status word inside a sort workspace
 int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
-                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only = false);
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only = false, int batch = 1,
+                int64_t item_stride = 0);
+int64_t sort_batch_stride_bytes(int64_t k);  // workspace slice per list when `batch` lists are sorted together
 // Two-step form for producers that count the digits themselves while writing the items:
 // sort_begin clears the workspace and returns the histogram to fill, sort_passes runs the passes.
-int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s);
+int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s, int batch = 1);
 int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, const SortPlan& plan, void* ws,
-                int* in_alt, cudaStream_t s);
+                int* in_alt, cudaStream_t s, int batch = 1, int64_t item_stride = 0);
 
 int64_t plan_workspace_bytes(int n);
+int64_t plan_workspace_bytes_views(int n, int views);
+int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
+                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,

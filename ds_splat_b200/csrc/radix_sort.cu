@@ -60,8 +60,11 @@ struct SortHeader {                  // start of the workspace, zeroed before ev
 // the shared-memory atomics to one per distinct digit per warp, which matters when a digit is nearly
 // constant (the exponent byte of depth keys, the high tile bits).
 __global__ void __launch_bounds__(kThreads)
-radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan plan, u32* __restrict__ hist) {
+radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan plan, u32* __restrict__ hist,
+                       const long long item_stride, const long long ws_stride_u32) {
     __shared__ u32 s_hist[kMaxSortPasses][kRadix];
+    keys += blockIdx.y * item_stride;     // blockIdx.y: which of the batch's independent lists
+    hist += blockIdx.y * ws_stride_u32;
     for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
     __syncthreads();
     const u32 lane = threadIdx.x & 31;
@@ -272,8 +275,14 @@ template <bool HAS_VALS, int NB, int ITEMS>
 __global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
 onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
                 const u32 n, const DigitSpec ds, const u32* __restrict__ hist, u32* __restrict__ tile_counter,
-                u32* __restrict__ lookback, int* __restrict__ status) {
+                u32* __restrict__ lookback, int* __restrict__ status, const long long item_stride,
+                const long long ws_stride_u32) {
     extern __shared__ __align__(16) unsigned char dyn[];
+    // blockIdx.y: which of the batch's independent lists (each with its own workspace slice)
+    kin += blockIdx.y * item_stride; kout += blockIdx.y * item_stride;
+    if (HAS_VALS) { vin += blockIdx.y * item_stride; vout += blockIdx.y * item_stride; }
+    hist += blockIdx.y * ws_stride_u32; tile_counter += blockIdx.y * ws_stride_u32;
+    lookback += blockIdx.y * ws_stride_u32; status += blockIdx.y * ws_stride_u32;
     __shared__ u32 s_wcnt[kWarps * kRadix];
     __shared__ u32 s_glob[kRadix];
     __shared__ u32 s_wsum[kWarps];
@@ -298,13 +307,14 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
 
 template <bool HAS_VALS, int NB, int ITEMS>
 int launch_sweep(const u64* src, u64* dst, const u32* vsrc, u32* vdst, u32 n, const DigitSpec& ds, const u32* hist,
-                 u32* tile_counter, u32* lookback, int* status, int64_t tiles, size_t dyn, cudaStream_t s) {
+                 u32* tile_counter, u32* lookback, int* status, int64_t tiles, size_t dyn, int batch, long long item_stride,
+                 long long ws_stride_u32, cudaStream_t s) {
     // Keys alone fit the default 48 KB of shared memory per block; with values the block opts in to more.  The
     // attribute belongs to the current device's context, so it is set at every launch rather than cached.
     if (HAS_VALS || dyn + 10 * 1024 > 48 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<HAS_VALS, NB, ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    onesweep_kernel<HAS_VALS, NB, ITEMS><<<(unsigned)tiles, kThreads, dyn, s>>>(src, dst, vsrc, vdst, n, ds, hist, tile_counter,
-                                                                         lookback, status);
+    onesweep_kernel<HAS_VALS, NB, ITEMS><<<dim3((unsigned)tiles, (unsigned)batch), kThreads, dyn, s>>>(
+        src, dst, vsrc, vdst, n, ds, hist, tile_counter, lookback, status, item_stride, ws_stride_u32);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
@@ -360,13 +370,18 @@ static int check_sort_args(const void* items, const void* items_alt, const void*
     return DSB_OK;
 }
 
+// A batch of `batch` equally long lists is sorted by the same launches (grid dimension y); list b uses the
+// workspace slice that starts b * sort_batch_stride_bytes(k) into the workspace.
+int64_t sort_batch_stride_bytes(int64_t k) { return (sort_workspace_bytes(k) + 255) / 256 * 256; }
+
 // Step 1 of a sort whose digit counts come from the producer of the items: clears the workspace and hands
 // back the histogram the producer has to fill (plan.npass rows of 256 counters).
-int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s) {
+int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32** hist_out, cudaStream_t s, int batch) {
     *hist_out = nullptr;
     if (k <= 1) return DSB_OK;
     const int64_t tiles = tiles_of(k, plan);
-    const int64_t need = (int64_t)sizeof(SortHeader) + (int64_t)plan.npass * tiles * kRadix * (int64_t)sizeof(u32);
+    const int64_t one = (int64_t)sizeof(SortHeader) + (int64_t)plan.npass * tiles * kRadix * (int64_t)sizeof(u32);
+    const int64_t need = batch > 1 ? (int64_t)(batch - 1) * sort_batch_stride_bytes(k) + one : one;
     if (ws_bytes < need) {
         set_error("sort: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
         return DSB_ERR_WORKSPACE_TOO_SMALL;
@@ -378,7 +393,7 @@ int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32*
 
 // Step 2: the onesweep passes, given a filled histogram.
 int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, const SortPlan& plan, void* ws,
-                int* in_alt, cudaStream_t s) {
+                int* in_alt, cudaStream_t s, int batch, int64_t item_stride) {
     if (in_alt) *in_alt = 0;
     if (k <= 1) return DSB_OK;
     const int64_t tiles = tiles_of(k, plan);
@@ -386,6 +401,7 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
     u32* lookback = reinterpret_cast<u32*>(hdr + 1);
     const size_t dyn = (small ? kSmallTileItems : kTileItems) * (sizeof(u64) + (vals ? sizeof(u32) : 0));
+    const long long ws_stride_u32 = batch > 1 ? sort_batch_stride_bytes(k) / 4 : 0;
     u64 *src = items, *dst = items_alt;
     u32 *vsrc = vals, *vdst = vals_alt;
     for (int p = 0; p < plan.npass; ++p) {
@@ -399,9 +415,9 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
         int rc;
 #define DSB_SWEEP(V, NB)                                                                                              \
     (small ? launch_sweep<V, NB, kSmallItems>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb,  \
-                                              &hdr->status, tiles, dyn, s)                                                \
+                                              &hdr->status, tiles, dyn, batch, item_stride, ws_stride_u32, s)             \
            : launch_sweep<V, NB, kItems>(src, dst, vsrc, vdst, (u32)k, ds, hdr->hist[p], &hdr->tile_counter[p], lb,       \
-                                         &hdr->status, tiles, dyn, s))
+                                         &hdr->status, tiles, dyn, batch, item_stride, ws_stride_u32, s))
         if (vals) rc = nb == 5 ? DSB_SWEEP(true, 5) : nb == 6 ? DSB_SWEEP(true, 6) : nb == 7 ? DSB_SWEEP(true, 7) : DSB_SWEEP(true, 8);
         else rc = nb == 5 ? DSB_SWEEP(false, 5) : nb == 6 ? DSB_SWEEP(false, 6) : nb == 7 ? DSB_SWEEP(false, 7) : DSB_SWEEP(false, 8);
 #undef DSB_SWEEP
@@ -415,7 +431,8 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
 
 // Sorts k items on bits [begin_bit, end_bit).  vals may be null.  *in_alt tells where the result is.
 int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, int begin_bit, int end_bit,
-                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only) {
+                void* ws, int64_t ws_bytes, int* in_alt, cudaStream_t s, bool large_tiles_only, int batch,
+                int64_t item_stride) {
     if (in_alt) *in_alt = 0;
     int rc = check_sort_args(items, items_alt, ws, k, begin_bit, end_bit);
     if (rc != DSB_OK) return rc;
@@ -424,13 +441,15 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     SortPlan plan = make_sort_plan(begin_bit, end_bit, end_bit == 64 && vals != nullptr);  // signed keys in the pair interface
     if (large_tiles_only) plan.tile_items = kTileItems;
     u32* hist = nullptr;
-    rc = sort_begin(k, plan, ws, ws_bytes, &hist, s);
+    DSB_REQUIRE(batch >= 1 && (batch == 1 || item_stride >= k), "sort: bad batch layout");
+    rc = sort_begin(k, plan, ws, ws_bytes, &hist, s, batch);
     if (rc != DSB_OK) return rc;
     const int64_t tiles = tiles_of(k, plan);
     const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
-    radix_histogram_kernel<<<hist_blocks, kThreads, 0, s>>>(items, (u32)k, plan, hist);
+    radix_histogram_kernel<<<dim3((unsigned)hist_blocks, (unsigned)batch), kThreads, 0, s>>>(
+        items, (u32)k, plan, hist, item_stride, batch > 1 ? sort_batch_stride_bytes(k) / 4 : 0);
     DSB_LAUNCH_CHECK();
-    return sort_passes(items, items_alt, vals, vals_alt, k, plan, ws, in_alt, s);
+    return sort_passes(items, items_alt, vals, vals_alt, k, plan, ws, in_alt, s, batch, item_stride);
 }
 
 // ---- sort without any allocation ------------------------------------------------------------------

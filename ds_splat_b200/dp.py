@@ -93,14 +93,14 @@ class CameraTensors:
 
 
 class _Slot:
-    """Per-view buffers that must survive until the batch's per-splat backward: 124 bytes per splat."""
+    """Per-view buffers that must survive until the batch's per-splat backward: 128 bytes per splat.  tiles,
+    depth_keys and offsets are rows of tensors shared by the slots, because the batch's plan takes them as rows."""
 
-    def __init__(self, n, dev, capi):
+    def __init__(self, n, dev, capi, tiles, depth_keys, offsets):
         f32 = dict(dtype=torch.float32, device=dev)
         self.records = torch.empty((n, capi.RECORD_FLOATS), **f32)
         self.radii = torch.empty(n, dtype=torch.int32, device=dev)
-        self.tiles = torch.empty(n, dtype=torch.int32, device=dev)
-        self.depth_keys = torch.empty(n, dtype=torch.int64, device=dev)
+        self.tiles, self.depth_keys, self.offsets = tiles, depth_keys, offsets
         self.grad_acc = torch.empty((n, capi.GRAD_FLOATS), **f32)
         self.marks = {}     # (H, W) -> tile-mark grid, later the tile order
         self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
@@ -126,12 +126,14 @@ class ViewRenderer:
         self.strict = strict_reference
         n, dev = self.n, self.dev
         self.batch_views = max(1, min(int(batch_views), _capi.MAX_BATCH_VIEWS))
-        self.slots = [_Slot(n, dev, _capi)]   # further slots are allocated when a step first needs them
-        self.cur = self.slots[0]
+        bv = self.batch_views
+        self.tiles_rows = torch.empty((bv, n), dtype=torch.int32, device=dev)
+        self.depth_rows = torch.empty((2, bv, n), dtype=torch.int64, device=dev)   # [1] is the sort's other buffer
+        self.offset_rows = torch.empty((bv, n), dtype=torch.int32, device=dev)
+        self.slots = []                      # the slots' large buffers are allocated when a step first needs them
+        self.cur = self._slot(0)
         self.cov3d = torch.empty((n, 6), dtype=torch.float32, device=dev)
-        self.depth_keys_alt = torch.empty(n, dtype=torch.int64, device=dev)
-        self.offsets = torch.empty(n, dtype=torch.int32, device=dev)
-        self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes(n))
+        self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes_views(n, bv))
         self.plan_ws = torch.empty(self.plan_bytes, dtype=torch.uint8, device=dev)
         self.pairs = None
         self.sort_ws = None
@@ -166,7 +168,9 @@ class ViewRenderer:
 
     def _slot(self, j: int) -> _Slot:
         while len(self.slots) <= j:
-            self.slots.append(_Slot(self.n, self.dev, self._capi))
+            i = len(self.slots)
+            self.slots.append(_Slot(self.n, self.dev, self._capi, self.tiles_rows[i], self.depth_rows[0, i],
+                                    self.offset_rows[i]))
         return self.slots[j]
 
     def _pair_buffers(self, k: int):
@@ -184,7 +188,7 @@ class ViewRenderer:
         self._pair_buffers(k)
         capi.check(lib.dsb_forward_render(
             C.byref(c), self.n, k, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
-            self.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(),
+            slot.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(),
             self._marks(slot, cam.H, cam.W).data_ptr(), self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(),
             image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None, capi.stream_ptr()))
         self.last_k = k
@@ -201,8 +205,8 @@ class ViewRenderer:
         capi.check(lib.dsb_forward_plan(
             C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
             p["scales"].data_ptr(), p["rotations"].data_ptr(), None, sl.records.data_ptr(), sl.radii.data_ptr(),
-            sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_keys_alt.data_ptr(),
-            self.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
+            sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_rows[1, slot].data_ptr(),
+            sl.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
             C.byref(k), capi.stream_ptr()))
         return self._render(sl, cam, int(k.value))
 
@@ -224,8 +228,9 @@ class ViewRenderer:
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
         contents when ``accumulate``).  ``image_grads`` is a sequence of dL/dimage tensors or a callable
         ``(index, image) -> dL/dimage``.  Views are taken in batches of up to ``batch_views`` of one image size:
-        one preprocess launch for the batch, then per view the rest of the forward and the backward blend, then
-        one per-splat backward for the batch."""
+        one preprocess launch and one plan (depth sorts, offset scans, a single read-back of the pair counts) for
+        the batch, then per view the rest of the forward and the backward blend, then one per-splat backward for
+        the batch."""
         capi, lib, p = self._capi, self.lib, self.p
         g = grads.views
         b0, first = 0, True
@@ -245,14 +250,14 @@ class ViewRenderer:
                 p["scales"].data_ptr(), p["rotations"].data_ptr(), None, ptrs([sl.records for sl in slots]),
                 ptrs([sl.radii for sl in slots]), ptrs([sl.tiles for sl in slots]), self.cov3d.data_ptr(),
                 ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]), capi.stream_ptr()))
+            ks = (C.c_int64 * nv)()
+            capi.check(lib.dsb_plan_pairs_views(     # depth order and pair offsets of all views, one host sync
+                C.byref(slots[0].cam[0]), nv, self.n, self.n, self.tiles_rows.data_ptr(), self.depth_rows[0].data_ptr(),
+                self.depth_rows[1].data_ptr(), self.offset_rows.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
+                ks, capi.stream_ptr()))
             for j, sl in enumerate(slots):
                 cam = cameras[b0 + j]
-                k = C.c_int64(0)
-                capi.check(lib.dsb_plan_pairs(
-                    C.byref(sl.cam[0]), self.n, sl.tiles.data_ptr(), sl.depth_keys.data_ptr(),
-                    self.depth_keys_alt.data_ptr(), self.offsets.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
-                    C.byref(k), capi.stream_ptr()))
-                image = self._render(sl, cam, int(k.value))
+                image = self._render(sl, cam, int(ks[j]))
                 v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
                 _img, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
                 capi.check(lib.dsb_backward_blend(

@@ -233,7 +233,12 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
  *                                              DSB_MAX_BATCH_VIEWS cameras: the splat parameters are read once,
  *                                              the 3-D covariance computed once; clears and fills each
  *                                              view's tile_marks)
- *   per view:   dsb_plan_pairs, dsb_forward_render, then
+ *               dsb_plan_pairs_views          (= dsb_plan_pairs for all those views in the same launches and
+ *                                              with ONE host synchronisation: tiles_touched, depth_keys,
+ *                                              depth_keys_alt and offsets hold one row of n entries per
+ *                                              view, row_stride entries apart; k_host receives num_views
+ *                                              totals; workspace: dsb_plan_workspace_bytes_views)
+ *   per view:   dsb_forward_render, then
  *               dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
  *   per step:   dsb_geometry_backward_views   over up to DSB_MAX_BATCH_VIEWS views at a time
  * records, radii, tiles_touched, depth_keys, tile_marks and grad_acc are HOST arrays of num_views device pointers (one buffer per view, all of the
@@ -248,6 +253,11 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
                          const float* scales, const float* rotations, const float* cov3d_precomp,
                          float* const* records, int32_t* const* radii, int32_t* const* tiles_touched,
                          float* cov3d, uint64_t* const* depth_keys, int32_t* const* tile_marks, void* stream);
+int64_t dsb_plan_workspace_bytes_views(int32_t n, int32_t num_views);
+int dsb_plan_pairs_views(const DsbCamera* cam /* any of the views: only its flags are used */, int32_t num_views,
+                         int32_t n, int64_t row_stride, const int32_t* tiles_touched, uint64_t* depth_keys,
+                         uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
+                         int64_t* k_host, void* stream);
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
                        const float* v_image, const float* v_depth /* may be NULL */,
