@@ -16,7 +16,9 @@ namespace dsb {
 
 namespace {
 
-constexpr int kScanThreads = 1024;
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 4;                      // consecutive items per thread: four gathers in flight
+constexpr int kScanTile = kScanThreads * kScanItems;
 constexpr u64 kScanAggregate = 1ull << 62;
 constexpr u64 kScanInclusive = 1ull << 63;
 constexpr u64 kScanValue = (1ull << 62) - 1;
@@ -42,14 +44,18 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
     if (tid == 0) s_tile = atomicAdd(&tail->tile_counter, 1u);
     __syncthreads();
     const u32 tile = s_tile;
-    const int j = (int)tile * kScanThreads + tid;
-    u32 c = 0;
-    if (j < n) {
-        const u32 id = (u32)depth_keys_sorted[j];
-        c = (u32)tiles[id];
-        if (drop_last && id == (u32)(n - 1)) c = 0;  // the reference never emits pairs for the last splat
+    const int j0 = (int)tile * kScanTile + tid * kScanItems;
+    u32 id[kScanItems], c[kScanItems];
+#pragma unroll
+    for (int q = 0; q < kScanItems; ++q) id[q] = j0 + q < n ? (u32)depth_keys_sorted[j0 + q] : 0u;
+    u32 mine = 0;
+#pragma unroll
+    for (int q = 0; q < kScanItems; ++q) {
+        c[q] = j0 + q < n ? (u32)tiles[id[q]] : 0u;
+        if (drop_last && id[q] == (u32)(n - 1)) c[q] = 0;  // the reference never emits pairs for the last splat
+        mine += c[q];
     }
-    u32 incl = c;
+    u32 incl = mine;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
         const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
@@ -58,7 +64,7 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
     if (lane == 31) s_wsum[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-        u32 w = s_wsum[lane];
+        u32 w = lane < kScanThreads / 32 ? s_wsum[lane] : 0u;
         u32 wi = w;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
@@ -102,13 +108,15 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
         }
         if (lane == 0) {
             s_prefix = earlier;
-            if ((int)tile == (n + kScanThreads - 1) / kScanThreads - 1) tail->total = earlier + block_total;
+            if ((int)tile == (n + kScanTile - 1) / kScanTile - 1) tail->total = earlier + block_total;
         }
     }
     __syncthreads();
-    if (j < n) {
-        const u64 off = s_prefix + s_wsum[warp] + (incl - c);
-        offsets[j] = off > 0xffffffffull ? 0xffffffffu : (u32)off;
+    u64 off = s_prefix + s_wsum[warp] + (incl - mine);
+#pragma unroll
+    for (int q = 0; q < kScanItems; ++q) {
+        if (j0 + q < n) offsets[j0 + q] = off > 0xffffffffull ? 0xffffffffu : (u32)off;
+        off += c[q];
     }
 }
 
@@ -341,7 +349,7 @@ inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 }  // namespace
 
 // Workspace of a batch of `views` plans: per view a sort slice, then per view a scan look-back row, then the tails.
-static int64_t plan_scan_row_bytes(int n) { return align256(((int64_t)n + kScanThreads - 1) / kScanThreads * 8); }
+static int64_t plan_scan_row_bytes(int n) { return align256(((int64_t)n + kScanTile - 1) / kScanTile * 8); }
 int64_t plan_workspace_bytes_views(int n, int views) {
     return (int64_t)views * (sort_batch_stride_bytes(n) + plan_scan_row_bytes(n)) + align256((int64_t)views * sizeof(PlanTail));
 }
@@ -366,7 +374,7 @@ int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride
     unsigned char* base = reinterpret_cast<unsigned char*>(ws);
     const int64_t sort_stride = sort_batch_stride_bytes(n), sort_bytes = (int64_t)views * sort_stride;
     const int64_t scan_row = plan_scan_row_bytes(n);
-    const int64_t scan_tiles = ((int64_t)n + kScanThreads - 1) / kScanThreads;
+    const int64_t scan_tiles = ((int64_t)n + kScanTile - 1) / kScanTile;
     u64* lookback = reinterpret_cast<u64*>(base + sort_bytes);
     PlanTail* tail = reinterpret_cast<PlanTail*>(base + sort_bytes + (int64_t)views * scan_row);
 

@@ -68,14 +68,25 @@ radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan
     for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
     __syncthreads();
     const u32 lane = threadIdx.x & 31;
-    const u32 n_round = (n + 31u) & ~31u;  // whole warps stay converged for the ballots
-    for (u32 i = blockIdx.x * kThreads + threadIdx.x; i < n_round; i += gridDim.x * kThreads) {
-        const bool valid = i < n;
-        const u64 key = valid ? keys[i] : 0ull;
-        for (int p = 0; p < plan.npass; ++p) {
-            const u32 d = sort_digit(key, plan.shift[p], plan.mask[p], plan.flip[p]);
-            const u32 m = warp_peers(d, valid, plan.bits[p]);
-            if (valid && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[p][d], (u32)__popc(m));
+    // Four keys per thread and trip, loaded before any of them is counted, so that four loads are in flight;
+    // whole warps stay converged for the ballots.
+    constexpr u32 kUnroll = 4;
+    const u32 chunk = kThreads * kUnroll;
+    for (u32 base = blockIdx.x * chunk; base < n; base += gridDim.x * chunk) {
+        u64 key[kUnroll];
+#pragma unroll
+        for (u32 q = 0; q < kUnroll; ++q) {
+            const u32 i = base + q * kThreads + threadIdx.x;
+            key[q] = i < n ? keys[i] : 0ull;
+        }
+#pragma unroll
+        for (u32 q = 0; q < kUnroll; ++q) {
+            const bool valid = base + q * kThreads + threadIdx.x < n;
+            for (int p = 0; p < plan.npass; ++p) {
+                const u32 d = sort_digit(key[q], plan.shift[p], plan.mask[p], plan.flip[p]);
+                const u32 m = warp_peers(d, valid, plan.bits[p]);
+                if (valid && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[p][d], (u32)__popc(m));
+            }
         }
     }
     __syncthreads();
@@ -444,8 +455,8 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     DSB_REQUIRE(batch >= 1 && (batch == 1 || item_stride >= k), "sort: bad batch layout");
     rc = sort_begin(k, plan, ws, ws_bytes, &hist, s, batch);
     if (rc != DSB_OK) return rc;
-    const int64_t tiles = tiles_of(k, plan);
-    const int hist_blocks = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
+    const int64_t chunks = (k + kThreads * 4 - 1) / (kThreads * 4);   // four keys per thread and trip
+    const int hist_blocks = (int)(chunks < 148 * 8 ? chunks : 148 * 8);
     radix_histogram_kernel<<<dim3((unsigned)hist_blocks, (unsigned)batch), kThreads, 0, s>>>(
         items, (u32)k, plan, hist, item_stride, batch > 1 ? sort_batch_stride_bytes(k) / 4 : 0);
     DSB_LAUNCH_CHECK();
