@@ -88,9 +88,9 @@ def lib():
             "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P, P],
             "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
             "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
-            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 6,
+            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 7,
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
-            "dsb_preprocess_views": [P, I32, I32] + [P] * 14,
+            "dsb_preprocess_views": [P, I32, I32] + [P] * 16,
             "dsb_plan_pairs_views": [CAM, I32, I32, I64, P, P, P, P, P, I64, P, P],
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
@@ -203,7 +203,7 @@ def preprocess_views(cams, means3d, shs, opacities, scales, rotations):
     arr = lambda i: (C.c_void_p * nv)(*[o[i].data_ptr() for o in out])
     check(lib().dsb_preprocess_views((DsbCamera * nv)(*cams), nv, n, ptr(means3d), ptr(shs), None, ptr(opacities),
                                      ptr(scales), ptr(rotations), None, arr(0), arr(1), arr(2), ptr(cov3d), arr(3), arr(4),
-                                     stream_ptr()))
+                                     None, None, stream_ptr()))
     return out, cov3d
 
 

@@ -185,10 +185,18 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
 // order: the tile ids sorted by falling pair count (in 256 logarithmic classes), which the blend kernels use
 // to start their longest lists first so that no long list is left running alone at the end of the launch.
 constexpr int kLayoutThreads = 1024;
+struct LayoutViews {       // one block per view
+    int* marks[DSB_MAX_BATCH_VIEWS];
+    u32* hist[DSB_MAX_BATCH_VIEWS];
+    int32_t* ranges[DSB_MAX_BATCH_VIEWS];
+};
 __global__ void __launch_bounds__(kLayoutThreads)
-tile_layout_kernel(int* __restrict__ marks, const int copy_ints, const int tiles_x, const int tiles_y, const SortPlan plan,
-                   u32* __restrict__ hist, int32_t* __restrict__ ranges, const int use_smem) {
+tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x, const int tiles_y, const SortPlan plan,
+                   const int use_smem) {
     extern __shared__ int s_grid[];
+    int* __restrict__ marks = lv.marks[blockIdx.x];
+    u32* __restrict__ hist = lv.hist[blockIdx.x];
+    int32_t* __restrict__ ranges = lv.ranges[blockIdx.x];
     __shared__ u32 s_hist[4][256];
     __shared__ u32 s_wsum[32];
     __shared__ u32 s_carry;
@@ -460,21 +468,38 @@ bool tile_order_available(int H, int W) {
     return (size_t)(tx + 1) * (ty + 1) * sizeof(int) <= 200 * 1024;
 }
 
-// *has_order tells whether tile_marks[0 .. tiles) holds the tile order afterwards.
-int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
-                       int* has_order, cudaStream_t s) {
-    DSB_REQUIRE(tile_marks && ranges, "tile_layout: null pointer");
-    DSB_REQUIRE(!hist || plan.npass <= 4, "tile_layout: at most 4 digit passes");
+// *has_order tells whether tile_marks[0 .. tiles) holds the tile order afterwards.  One block per view.
+int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_marks, const SortPlan& plan, u32* const* hist,
+                             int32_t* const* ranges, int* has_order, cudaStream_t s) {
+    DSB_REQUIRE(count >= 1 && count <= DSB_MAX_BATCH_VIEWS, "tile_layout: between 1 and %d views", DSB_MAX_BATCH_VIEWS);
+    DSB_REQUIRE(plan.npass <= 4, "tile_layout: at most 4 digit passes");
+    LayoutViews lv;
+    for (int v = 0; v < count; ++v) {
+        DSB_REQUIRE(tile_marks[v] && ranges[v], "tile_layout: null pointer");
+        lv.marks[v] = tile_marks[v];
+        lv.hist[v] = hist ? hist[v] : nullptr;
+        lv.ranges[v] = ranges[v];
+    }
     const size_t grid_bytes = (size_t)(cp.tiles_x + 1) * (cp.tiles_y + 1) * sizeof(int);
     const int use_smem = tile_order_available(cp.H, cp.W);
     if (has_order) *has_order = use_smem;
     if (use_smem && grid_bytes > 40 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
-    tile_layout_kernel<<<1, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(tile_marks, (int)tile_marks_copy_ints(cp.H, cp.W),
-                                                                           cp.tiles_x, cp.tiles_y, plan, hist, ranges,
-                                                                           use_smem);
+    tile_layout_kernel<<<count, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(lv, (int)tile_marks_copy_ints(cp.H, cp.W),
+                                                                               cp.tiles_x, cp.tiles_y, plan, use_smem);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
+}
+
+int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
+                       int* has_order, cudaStream_t s) {
+    return launch_tile_layout_views(cp, 1, &tile_marks, plan, hist ? &hist : nullptr, &ranges, has_order, s);
+}
+
+SortPlan tile_sort_plan(const CamParams& cp) {   // only the tile id is sorted: ceil(log2(tiles)) live bits above bit 32
+    int tile_bits = 1;
+    while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
+    return make_sort_plan(32, 32 + tile_bits, false);
 }
 
 int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s) {

@@ -251,18 +251,16 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
 int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
                        const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, uint64_t* pairs_alt,
                        int32_t* tile_marks, void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image,
-                       float* final_T, int32_t* final_idx, float* depth, void* stream) {
+                       float* final_T, int32_t* final_idx, float* depth, const uint32_t* layout_hist, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
     // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The preprocess kernel marked
     // every splat's tile rectangle in a small grid; one block turns that grid into the tile ranges and the sort's
     // digit counts, so nothing reads the K pairs except the sort passes themselves.
-    int tile_bits = 1;
-    while ((1 << tile_bits) < cp.tiles_x * cp.tiles_y) ++tile_bits;
     DSB_REQUIRE(k < DSB_MAX_PAIRS, "too many pairs");
     DSB_REQUIRE(tile_marks && ranges, "forward_render: null tile_marks or ranges");
     DSB_REQUIRE(k <= 1 || (pairs && pairs_alt && workspace), "forward_render: null pair buffers or workspace");
-    const SortPlan plan = make_sort_plan(32, 32 + tile_bits, false);
+    const SortPlan plan = tile_sort_plan(cp);
     int has_order = 0;
     u32* hist = nullptr;
     int rc;
@@ -274,13 +272,17 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                          reinterpret_cast<u64*>(pairs), s);
     }
     if (rc != DSB_OK) return rc;
-    {
+    if (layout_hist) {   // the layout of this view was made by dsb_preprocess_views: ranges and tile order are in place
+        has_order = tile_order_available(cp.H, cp.W);
+        if (hist)
+            DSB_CUDA_CHECK(cudaMemcpyAsync(hist, layout_hist, (size_t)plan.npass * 256 * sizeof(u32), cudaMemcpyDeviceToDevice, s));
+    } else {
         StageScope scope(kStageRanges, s);
         rc = launch_tile_layout(cp, tile_marks, plan, hist, ranges, &has_order, s);
-#ifdef DSB_NO_TILE_ORDER
-        has_order = 0;
-#endif
     }
+#ifdef DSB_NO_TILE_ORDER
+    has_order = 0;
+#endif
     if (rc != DSB_OK) return rc;
     int in_alt = 0;
     {
@@ -327,7 +329,7 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
                          const float* colors_precomp, const float* opacities, const float* scales, const float* rotations,
                          const float* cov3d_precomp, float* const* records, int32_t* const* radii,
                          int32_t* const* tiles_touched, float* cov3d, uint64_t* const* depth_keys,
-                         int32_t* const* tile_marks, void* stream) {
+                         int32_t* const* tile_marks, int32_t* const* ranges, uint32_t* const* layout_hist, void* stream) {
     DSB_REQUIRE(cams && num_views >= 0 && num_views <= DSB_MAX_BATCH_VIEWS,
                 "preprocess_views: between 0 and %d views per call", DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
@@ -336,7 +338,6 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
     CamParams cps[DSB_MAX_BATCH_VIEWS];
     u64* keys[DSB_MAX_BATCH_VIEWS];
     cudaStream_t s = (cudaStream_t)stream;
-    StageScope scope(kStagePreprocess, s);
     for (int v = 0; v < num_views; ++v) {
         const int rc = make_cam_params(&cams[v], &cps[v]);
         if (rc != DSB_OK) return rc;
@@ -344,8 +345,17 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
         DSB_CUDA_CHECK(cudaMemsetAsync(tile_marks[v], 0, (size_t)tile_marks_bytes(cps[v].H, cps[v].W), s));
         keys[v] = reinterpret_cast<u64*>(depth_keys[v]);
     }
-    return launch_preprocess_views(cps, num_views, n, means3d, shs, colors_precomp, opacities, scales, rotations,
-                                   cov3d_precomp, records, radii, tiles_touched, cov3d, keys, tile_marks, s);
+    DSB_REQUIRE(!ranges == !layout_hist, "preprocess_views: ranges and layout_hist go together");
+    {
+        StageScope scope(kStagePreprocess, s);
+        const int rc = launch_preprocess_views(cps, num_views, n, means3d, shs, colors_precomp, opacities, scales, rotations,
+                                               cov3d_precomp, records, radii, tiles_touched, cov3d, keys, tile_marks, s);
+        if (rc != DSB_OK || !ranges) return rc;
+    }
+    // tile layout of all views at once (one block each): ranges, the tile sort's digit counts, the tile order
+    StageScope scope(kStageRanges, s);
+    int has_order = 0;
+    return launch_tile_layout_views(cps[0], num_views, tile_marks, tile_sort_plan(cps[0]), layout_hist, ranges, &has_order, s);
 }
 
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,

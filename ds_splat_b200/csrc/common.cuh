@@ -167,6 +167,9 @@ int64_t tile_marks_bytes(int H, int W);
 int64_t tile_marks_copy_ints(int H, int W);   // distance between two copies, in ints
 int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
                        int* has_order, cudaStream_t s);
+int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_marks, const SortPlan& plan, u32* const* hist,
+                             int32_t* const* ranges, int* has_order, cudaStream_t s);
+SortPlan tile_sort_plan(const CamParams& cp);
 bool tile_order_available(int H, int W);  // whether launch_tile_layout leaves the tile order for this image size
 int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
 int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);

@@ -103,6 +103,8 @@ class _Slot:
         self.tiles, self.depth_keys, self.offsets = tiles, depth_keys, offsets
         self.grad_acc = torch.empty((n, capi.GRAD_FLOATS), **f32)
         self.marks = {}     # (H, W) -> tile-mark grid, later the tile order
+        self.ranges = {}    # (H, W) -> tile ranges of the view
+        self.layout_hist = torch.empty(1024, dtype=torch.int32, device=dev)   # the tile sort's digit counts
         self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
 
 
@@ -151,9 +153,14 @@ class ViewRenderer:
         if key not in self.img:
             f32 = dict(dtype=torch.float32, device=self.dev)
             self.img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
-                             torch.empty((h, w), dtype=torch.int32, device=self.dev),
-                             torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev))
+                             torch.empty((h, w), dtype=torch.int32, device=self.dev))
         return self.img[key]
+
+    def _ranges(self, slot: _Slot, h, w):
+        key = (h, w)
+        if key not in slot.ranges:
+            slot.ranges[key] = torch.empty(self._capi.num_tiles(h, w) + 1, dtype=torch.int32, device=self.dev)
+        return slot.ranges[key]
 
     def _marks(self, slot: _Slot, h, w):
         key = (h, w)
@@ -180,17 +187,20 @@ class ViewRenderer:
             self.sort_bytes = int(self.lib.dsb_sort_workspace_bytes(cap))
             self.sort_ws = torch.empty(self.sort_bytes, dtype=torch.uint8, device=self.dev)
 
-    def _render(self, slot: _Slot, cam: CameraTensors, k: int):
-        """Second half of a forward: pairs, tile layout, tile sort, blend.  Returns the image buffer."""
+    def _render(self, slot: _Slot, cam: CameraTensors, k: int, layout_done: bool = False):
+        """Second half of a forward: pairs, tile layout (unless the batch made it already), tile sort, blend.
+        Returns the image buffer."""
         capi, lib = self._capi, self.lib
         c, _keep = slot.cam
-        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        image, final_t, final_idx = self._image_buffers(cam.H, cam.W)
+        ranges = self._ranges(slot, cam.H, cam.W)
         self._pair_buffers(k)
         capi.check(lib.dsb_forward_render(
             C.byref(c), self.n, k, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
             slot.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(),
             self._marks(slot, cam.H, cam.W).data_ptr(), self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(),
-            image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None, capi.stream_ptr()))
+            image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None,
+            slot.layout_hist.data_ptr() if layout_done else None, capi.stream_ptr()))
         self.last_k = k
         self.cur = slot
         self._last_cam = cam
@@ -214,7 +224,8 @@ class ViewRenderer:
         """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
         capi, lib, p = self._capi, self.lib, self.p
         sl, cam = self.cur, self._last_cam
-        image, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+        image, final_t, final_idx = self._image_buffers(cam.H, cam.W)
+        ranges = self._ranges(sl, cam.H, cam.W)
         g = grads.views
         capi.check(lib.dsb_backward(
             C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
@@ -228,8 +239,8 @@ class ViewRenderer:
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
         contents when ``accumulate``).  ``image_grads`` is a sequence of dL/dimage tensors or a callable
         ``(index, image) -> dL/dimage``.  Views are taken in batches of up to ``batch_views`` of one image size:
-        one preprocess launch and one plan (depth sorts, offset scans, a single read-back of the pair counts) for
-        the batch, then per view the rest of the forward and the backward blend, then one per-splat backward for
+        one preprocess launch (with the tile layout of every view) and one plan (depth sorts, offset scans, a
+        single read-back of the pair counts) for the batch, then per view the rest of the forward and the backward blend, then one per-splat backward for
         the batch."""
         capi, lib, p = self._capi, self.lib, self.p
         g = grads.views
@@ -249,7 +260,8 @@ class ViewRenderer:
                 cams, nv, self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
                 p["scales"].data_ptr(), p["rotations"].data_ptr(), None, ptrs([sl.records for sl in slots]),
                 ptrs([sl.radii for sl in slots]), ptrs([sl.tiles for sl in slots]), self.cov3d.data_ptr(),
-                ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]), capi.stream_ptr()))
+                ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]),
+                ptrs([self._ranges(sl, *size) for sl in slots]), ptrs([sl.layout_hist for sl in slots]), capi.stream_ptr()))
             ks = (C.c_int64 * nv)()
             capi.check(lib.dsb_plan_pairs_views(     # depth order and pair offsets of all views, one host sync
                 C.byref(slots[0].cam[0]), nv, self.n, self.n, self.tiles_rows.data_ptr(), self.depth_rows[0].data_ptr(),
@@ -257,9 +269,10 @@ class ViewRenderer:
                 ks, capi.stream_ptr()))
             for j, sl in enumerate(slots):
                 cam = cameras[b0 + j]
-                image = self._render(sl, cam, int(ks[j]))
+                image = self._render(sl, cam, int(ks[j]), layout_done=True)
                 v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
-                _img, final_t, final_idx, ranges = self._image_buffers(cam.H, cam.W)
+                _img, final_t, final_idx = self._image_buffers(cam.H, cam.W)
+                ranges = self._ranges(sl, cam.H, cam.W)
                 capi.check(lib.dsb_backward_blend(
                     C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), self.pairs[0].data_ptr(), ranges.data_ptr(),
                     final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,

@@ -155,7 +155,7 @@ class DsRasterizerFunction(torch.autograd.Function):
                 C.byref(cam), n, k, records.data_ptr(), tiles.data_ptr(), depth_keys[0].data_ptr(), offsets.data_ptr(),
                 pairs[0].data_ptr(), pairs[1].data_ptr(), tile_marks.data_ptr(), sort_ws.data_ptr(), sort_bytes,
                 ranges.data_ptr(),
-                image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), _capi.ptr(depth), stream))
+                image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), _capi.ptr(depth), None, stream))
             sorted_pairs = pairs[0][:k]
 
         ctx.raster_settings = raster_settings

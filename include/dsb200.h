@@ -215,7 +215,9 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                        const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
                        uint64_t* pairs, uint64_t* pairs_alt, int32_t* tile_marks, void* workspace,
                        int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T, int32_t* final_idx,
-                       float* depth /* may be NULL */, void* stream);
+                       float* depth /* may be NULL */,
+                       const uint32_t* layout_hist /* NULL, or this view's layout_hist from dsb_preprocess_views */,
+                       void* stream);
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,
@@ -232,7 +234,10 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
  *   per step:   dsb_preprocess_views          (= the preprocess half of dsb_forward_plan for up to
  *                                              DSB_MAX_BATCH_VIEWS cameras: the splat parameters are read once,
  *                                              the 3-D covariance computed once; clears and fills each
- *                                              view's tile_marks)
+ *                                              view's tile_marks; when ranges and layout_hist (1024
+ *                                              uint32 per view) are given it also makes every view's tile
+ *                                              layout, and dsb_forward_render is then told so by passing
+ *                                              the view's layout_hist)
  *               dsb_plan_pairs_views          (= dsb_plan_pairs for all those views in the same launches and
  *                                              with ONE host synchronisation: tiles_touched, depth_keys,
  *                                              depth_keys_alt and offsets hold one row of n entries per
@@ -252,7 +257,9 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
                          const float* shs, const float* colors_precomp, const float* opacities,
                          const float* scales, const float* rotations, const float* cov3d_precomp,
                          float* const* records, int32_t* const* radii, int32_t* const* tiles_touched,
-                         float* cov3d, uint64_t* const* depth_keys, int32_t* const* tile_marks, void* stream);
+                         float* cov3d, uint64_t* const* depth_keys, int32_t* const* tile_marks,
+                         int32_t* const* ranges /* may be NULL */, uint32_t* const* layout_hist /* may be NULL */,
+                         void* stream);
 int64_t dsb_plan_workspace_bytes_views(int32_t n, int32_t num_views);
 int dsb_plan_pairs_views(const DsbCamera* cam /* any of the views: only its flags are used */, int32_t num_views,
                          int32_t n, int64_t row_stride, const int32_t* tiles_touched, uint64_t* depth_keys,

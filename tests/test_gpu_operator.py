@@ -174,7 +174,7 @@ def test_fused_render_matches_stage_calls():
     image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
     k = r.last_k
     fused_pairs = r.pairs[0][:k].clone()
-    _, _, _, fused_ranges = r._image_buffers(view.H, view.W)
+    fused_ranges = r._ranges(r.cur, view.H, view.W)
     from conftest import capi_camera
     cam, keep = capi_camera(view)
     records, radii, tiles, cov3d, dk = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
