@@ -398,6 +398,72 @@ int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_
                                           accumulate, s);
 }
 
+// Torch-free forward with the argument list of the reference's rasterizer_forward_core_deepsense
+// (cpp/ds_cuda_rasterizer/rasterizer_cuda.hpp:4-9): device pointers in, device image out, every intermediate
+// taken from and returned to the stream-ordered allocator inside the call.
+int dsb_forward_core(const float* means3d, const float* shs, const float* opacities, const float* scales,
+                     const float* rotations, int32_t n, const float* view_matrix, const float* proj_matrix,
+                     const float* camera_position, int32_t image_width, int32_t image_height, float tan_fovx,
+                     float tan_fovy, float scale_modifier, int32_t max_sh_degree, int32_t sh_degree, float* output_image,
+                     void* stream) {
+    DSB_REQUIRE(n >= 0 && output_image, "forward_core: bad arguments");
+    DsbCamera cam = {};
+    cam.image_height = image_height; cam.image_width = image_width;
+    cam.tanfovx = tan_fovx; cam.tanfovy = tan_fovy; cam.scale_modifier = scale_modifier;
+    cam.sh_degree = sh_degree; cam.max_sh_degree = max_sh_degree;
+    cam.matrices_transposed = 0;                 // row-major [R|t] and P*V, as the reference's C++ entry takes them
+    cam.flags = DSB_FLAG_DROP_LAST_SPLAT;        // what the reference's pair count does (cpp/rasterizer_torch.cu:97-104)
+    cam.viewmatrix = view_matrix; cam.projmatrix = proj_matrix; cam.campos = camera_position; cam.bg = nullptr;
+    CAM_OR_RETURN(&cam, cp);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t pixels = (size_t)image_height * image_width;
+    if (n == 0) {
+        DSB_CUDA_CHECK(cudaMemsetAsync(output_image, 0, pixels * 3 * sizeof(float), s));
+        return DSB_OK;
+    }
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    const size_t nn = (size_t)n;
+    const size_t b_records = up(nn * 48), b_i32 = up(nn * 4), b_cov = up(nn * 24), b_keys = up(nn * 8);
+    const size_t b_marks = up((size_t)tile_marks_bytes(cp.H, cp.W)), b_plan = up((size_t)plan_workspace_bytes(n));
+    const size_t b_ranges = up(((size_t)cp.tiles_x * cp.tiles_y + 1) * 4), b_pix = up(pixels * 4);
+    unsigned char* a = nullptr;   // arena 1: everything whose size is known before the pair count
+    const size_t bytes1 = b_records + 3 * b_i32 + b_cov + 2 * b_keys + b_marks + b_plan + b_ranges + 2 * b_pix;
+    DSB_CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&a), bytes1, s));
+    unsigned char* p = a;
+    auto take = [&p](size_t b) { unsigned char* r = p; p += b; return r; };
+    float* records = reinterpret_cast<float*>(take(b_records));
+    int32_t* radii = reinterpret_cast<int32_t*>(take(b_i32));
+    int32_t* tiles = reinterpret_cast<int32_t*>(take(b_i32));
+    uint32_t* offsets = reinterpret_cast<uint32_t*>(take(b_i32));
+    float* cov3d = reinterpret_cast<float*>(take(b_cov));
+    uint64_t* keys = reinterpret_cast<uint64_t*>(take(b_keys));
+    uint64_t* keys_alt = reinterpret_cast<uint64_t*>(take(b_keys));
+    int32_t* marks = reinterpret_cast<int32_t*>(take(b_marks));
+    void* plan_ws = take(b_plan);
+    int32_t* ranges = reinterpret_cast<int32_t*>(take(b_ranges));
+    float* final_T = reinterpret_cast<float*>(take(b_pix));
+    int32_t* final_idx = reinterpret_cast<int32_t*>(take(b_pix));
+    int64_t k = 0;
+    int rc = dsb_forward_plan(&cam, n, means3d, shs, nullptr, opacities, scales, rotations, nullptr, records, radii, tiles, cov3d,
+                              keys, keys_alt, offsets, marks, plan_ws, (int64_t)b_plan, &k, stream);
+    unsigned char* b = nullptr;   // arena 2: pair list and sort workspace
+    if (rc == DSB_OK) {
+        const size_t b_pairs = up((size_t)(k > 0 ? k : 1) * 8), b_sort = up((size_t)sort_workspace_bytes(k));
+        const cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&b), 2 * b_pairs + b_sort, s);
+        if (e != cudaSuccess) {
+            set_error("forward_core: cudaMallocAsync of the pair list failed: %s", cudaGetErrorString(e));
+            rc = DSB_ERR_CUDA;
+        } else {
+            rc = dsb_forward_render(&cam, n, k, records, tiles, keys, offsets, reinterpret_cast<uint64_t*>(b),
+                                    reinterpret_cast<uint64_t*>(b + b_pairs), marks, b + 2 * b_pairs, (int64_t)b_sort, ranges,
+                                    output_image, final_T, final_idx, nullptr, nullptr, stream);
+        }
+    }
+    if (b) cudaFreeAsync(b, s);
+    cudaFreeAsync(a, s);
+    return rc;
+}
+
 int dsb_export_reference_lists(const uint64_t* sorted_pairs, int64_t k, const float* records, int64_t* keys, int32_t* ids,
                                void* stream) {
     DSB_REQUIRE(k >= 0, "k must be non-negative");

@@ -276,6 +276,19 @@ int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_
                                 float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
                                 float* v_cov3d, int32_t accumulate, void* stream);
 
+/* ---- torch-free forward ---------------------------------------------------------------------------
+ * Same argument list as the reference's C++ entry rasterizer_forward_core_deepsense
+ * (cpp/ds_cuda_rasterizer/rasterizer_cuda.hpp:4-9, cpp/rasterizer_cuda.cu:128-158) plus the stream: all
+ * pointers are device pointers, view_matrix is the row-major [R|t], proj_matrix the row-major P*V,
+ * output_image [H][W][3].  Intermediates come from the stream-ordered allocator (cudaMallocAsync) and
+ * are returned to it before the call ends; the call synchronises the stream once (pair count).
+ * include/dsb200.hpp wraps it under the reference's own function name. */
+int dsb_forward_core(const float* means3d, const float* shs, const float* opacities, const float* scales,
+                     const float* rotations, int32_t n, const float* view_matrix, const float* proj_matrix,
+                     const float* camera_position, int32_t image_width, int32_t image_height, float tan_fovx,
+                     float tan_fovy, float scale_modifier, int32_t max_sh_degree, int32_t sh_degree,
+                     float* output_image, void* stream);
+
 /* Test/export helper: rebuild the reference-format sorted lists from this library's packed pairs:
  * keys[i] = (tile << 32) | sign-extended depth bits of the splat, ids[i] = splat id
  * (the layout cpp/rasterizer_kernels.cu:283,299-301 produces and thrust sorts). */

@@ -259,3 +259,30 @@ def test_preprocess_of_several_views_is_bit_identical_to_one_at_a_time():
         assert torch.equal(radii, ra1) and torch.equal(tiles, t1) and torch.equal(dkeys, d1)
         assert torch.equal(cov3d, c1)
     assert int(outs[0][1].max()) > 0 and not torch.equal(outs[0][0], outs[1][0])
+
+
+def test_torch_free_forward_equals_the_operator_image():
+    """dsb_forward_core takes the argument list of the reference's C++ entry (row-major matrices, device pointers,
+    no caller-side scratch) and must render what the operator renders."""
+    import ctypes as C
+    sc = scenes.tiny(n=9000, seed=61, W=336, H=208, focal=260.0)
+    view = sc.views[0]
+    _, _, image, _ = _run_operator(sc, view)
+    t = scene_tensors(sc)
+    vm = torch.from_numpy(np.ascontiguousarray(view.view, dtype=np.float32)).cuda()    # row-major [R|t]
+    pm = torch.from_numpy(np.ascontiguousarray(view.proj, dtype=np.float32)).cuda()    # row-major P*V
+    cp = torch.from_numpy(np.ascontiguousarray(view.campos, dtype=np.float32)).cuda()
+    out = torch.full((view.H, view.W, 3), -1.0, device="cuda")
+    lib = _capi.lib()
+    _capi.check(lib.dsb_forward_core(t["means"].data_ptr(), t["shs"].data_ptr(), t["opacities"].data_ptr(),
+                                     t["scales"].data_ptr(), t["rotations"].data_ptr(), sc.n, vm.data_ptr(), pm.data_ptr(),
+                                     cp.data_ptr(), view.W, view.H, C.c_float(view.tanfovx), C.c_float(view.tanfovy),
+                                     C.c_float(1.0), 3, 3, out.data_ptr(), _capi.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out, image.detach())
+    # no splats: a black image, no error
+    _capi.check(lib.dsb_forward_core(None, None, None, None, None, 0, vm.data_ptr(), pm.data_ptr(), cp.data_ptr(), view.W,
+                                     view.H, C.c_float(view.tanfovx), C.c_float(view.tanfovy), C.c_float(1.0), 3, 3,
+                                     out.data_ptr(), _capi.stream_ptr()))
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) == 0.0
