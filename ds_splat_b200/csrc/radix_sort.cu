@@ -39,6 +39,7 @@ constexpr int kTileItems = kThreads * kItems;   // 4096 items per block
 // is one wave of blocks, its duration is one block's chain of dependent steps, and half the items per
 // thread shortens that chain.
 constexpr int kSmallItems = kItems / 2;
+static_assert(kThreads == 256, "the pass kernels are validated for 256 threads (digit owners, shared-memory budget)");
 constexpr int kSmallTileItems = kThreads * kSmallItems;
 constexpr int64_t kSmallListLimit = (int64_t)148 * DSB_SORT_MIN_BLOCKS_HINT * kSmallTileItems;  // one wave of small tiles
 __host__ __device__ constexpr int tile_items_for(int64_t k, bool force_large) {
@@ -120,6 +121,9 @@ __device__ __forceinline__ u32 block_exclusive_scan_256(u32 v, u32* s_warp_sums,
 #ifndef DSB_SORT_MIN_BLOCKS
 #define DSB_SORT_MIN_BLOCKS 4
 #endif
+// the ranking loop walks a thread's items in whole groups, for both tile sizes
+static_assert(DSB_SORT_ITEMS % DSB_SORT_GROUP == 0 && (DSB_SORT_ITEMS / 2) % DSB_SORT_GROUP == 0,
+              "items per thread (and half of it, for short lists) must be a multiple of the ranking group");
 
 // Where a pass finds its digit inside the 64-bit item.  A digit never straddles more than the two 32-bit
 // halves, so one funnel shift (or a plain shift of the high half) replaces 64-bit shifting.
