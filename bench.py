@@ -257,7 +257,15 @@ def main():
     elapsed_ms = float(tmax.item())
     ms_per_step = elapsed_ms / args.steps
     views_per_s = world * vpr * args.steps / (elapsed_ms * 1e-3)
-    K = renderer.last_k
+    K_emitted = renderer.last_k
+    # Pair count of the reference's own list for the same view (the renderer pairs a splat only with the tiles it can
+    # contribute to, a subset with identical results): the algorithmic figures below are those of the reference's list.
+    ref_lists = ViewRenderer(**params, sh_degree=scene.sh_degree, batch_views=1, tight_tiles=False)
+    ref_lists.forward(cams[-1])
+    torch.cuda.synchronize()
+    K = ref_lists.last_k
+    del ref_lists
+    torch.cuda.empty_cache()
 
     # ---- per-stage timing of the same steps (events recorded by the library around each stage) ---------
     _capi.stage_timing(True)
@@ -389,7 +397,7 @@ def main():
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{scene.name}: {scene.n} splats SH-3, {W}x{H}, {vpr} view(s) per rank per step, fwd+bwd"
                                    + (", gradient all-reduce of 59 floats/splat" if world > 1 else ""),
-                       "pairs_K": int(K), "tiles": view.num_tiles, "l2": "inputs larger than L2 (236 MB of parameters + "
+                       "pairs_K": int(K), "pairs_emitted": int(K_emitted), "tiles": view.num_tiles, "l2": "inputs larger than L2 (236 MB of parameters + "
                        "88 MB pair list per view; no explicit flush)", "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
             "clocks": clocks, "gpu_launches": int(launches), "stages_ms": stages_ms, "roofline": roofline,
             "roofline_fp32": roofline_fp32, "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda,

@@ -73,6 +73,7 @@ int make_cam_params(const DsbCamera* cam, CamParams* out) {
     p.max_coeff = (cam->max_sh_degree + 1) * (cam->max_sh_degree + 1);
     p.transposed = cam->matrices_transposed != 0;
     p.drop_last = (cam->flags & DSB_FLAG_DROP_LAST_SPLAT) != 0;
+    p.tight_tiles = (cam->flags & DSB_FLAG_TIGHT_TILES) != 0;
     *out = p;
     return DSB_OK;
 }

@@ -74,6 +74,7 @@ struct CamParams {
     int sh_degree, max_coeff;
     int transposed;              // matrices still in the caller's transposed layout
     int drop_last;
+    int tight_tiles;             // tile rectangles shrunk to where the splat can contribute
 };
 
 int make_cam_params(const DsbCamera* cam, CamParams* out);

@@ -265,8 +265,30 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
 
             // Tile rectangle (float -> int conversion truncates toward zero) and its size.
             const float cxt = px / kTile, cyt = py / kTile, dt = radius / (float)kTile;
-            const int x0 = min(max(0, (int)(cxt - dt)), cv.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cv.tiles_x);
-            const int y0 = min(max(0, (int)(cyt - dt)), cv.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cv.tiles_y);
+            int x0 = min(max(0, (int)(cxt - dt)), cv.tiles_x), x1 = min(max(0, (int)(cxt + dt + 1)), cv.tiles_x);
+            int y0 = min(max(0, (int)(cyt - dt)), cv.tiles_y), y1 = min(max(0, (int)(cyt + dt + 1)), cv.tiles_y);
+            if (cv.tight_tiles) {
+                // A pixel blends the splat only if opacity * exp(-q) >= 1/255, q = 0.5 d^T conic d, i.e. inside the
+                // ellipse q <= ln(255 opacity).  Its bounding box has half-widths sqrt(2 tau cov_xx), sqrt(2 tau cov_yy)
+                // with cov the dilated 2-D covariance; tau carries the margin of the blend kernels' cull, the factor
+                // (det + 1e-6) / det undoes the shrink the conic gets from its regularised inverse, and half a pixel
+                // is added on every side, so the box can only be too large.  Tile t holds pixel centres
+                // 16 t + 0.5 .. 16 t + 15.5; tiles outside the box are dropped from the rectangle.
+                const float tau = __logf(255.0f * opacity) + 0.02f;
+                if (!(tau > 0.f)) {
+                    x1 = x0; y1 = y0;   // too faint to reach 1/255 anywhere
+                } else if (det > 1e-6f) {
+                    const float grow = 2.0f * tau * (1.0f + 1e-6f / det) * 1.001f;
+                    const float wx = sqrtf(grow * ca) + 0.5f, wy = sqrtf(grow * cc) + 0.5f;
+                    const float fx0 = floorf((px - wx - 15.5f) * (1.0f / kTile)) + 1.0f, fx1 = floorf((px + wx - 0.5f) * (1.0f / kTile)) + 1.0f;
+                    const float fy0 = floorf((py - wy - 15.5f) * (1.0f / kTile)) + 1.0f, fy1 = floorf((py + wy - 0.5f) * (1.0f / kTile)) + 1.0f;
+                    // compare as floats first: a huge splat must not overflow the conversion
+                    if (fx0 > (float)x0) x0 = min((int)fx0, x1);
+                    if (fx1 < (float)x1) x1 = max((int)fx1, x0);
+                    if (fy0 > (float)y0) y0 = min((int)fy0, y1);
+                    if (fy1 < (float)y1) y1 = max((int)fy1, y0);
+                }
+            }
             // A centre behind the camera can pass the frustum test (w < 0 flips both signs).  The reference
             // still reports its radius but, because the negative depth bits spill over the tile id of its
             // keys, never draws it; here it simply gets no pairs.

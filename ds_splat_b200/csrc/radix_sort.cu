@@ -27,7 +27,7 @@ namespace {
 #ifndef DSB_SORT_THREADS
 #define DSB_SORT_THREADS 256
 #endif
-constexpr int kThreads = DSB_SORT_THREADS;   // 256 or 512; the first 256 threads also own one digit each
+constexpr int kThreads = DSB_SORT_THREADS;   // 256: thread d also owns digit d in the block-level steps
 constexpr int kWarps = kThreads / 32;
 #ifndef DSB_SORT_ITEMS
 #define DSB_SORT_ITEMS 16

@@ -115,7 +115,7 @@ class ViewRenderer:
     docstring) and is what ``data_parallel_step`` uses."""
 
     def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True,
-                 batch_views: int = 8):
+                 batch_views: int = 8, tight_tiles: bool = True):
         from . import _capi
         self._capi = _capi
         self.lib = _capi.lib()
@@ -126,6 +126,7 @@ class ViewRenderer:
         self.sh_degree = sh_degree
         self.coeffs = shs.shape[1]
         self.strict = strict_reference
+        self.tight_tiles = tight_tiles   # pairs only for tiles a splat can contribute to: same results, shorter lists
         n, dev = self.n, self.dev
         self.batch_views = max(1, min(int(batch_views), _capi.MAX_BATCH_VIEWS))
         bv = self.batch_views
@@ -171,7 +172,8 @@ class ViewRenderer:
     def _camera(self, cam: CameraTensors):
         max_deg = {1: 0, 4: 1, 9: 2, 16: 3}[self.coeffs]
         return self._capi.make_camera(cam.H, cam.W, cam.tanfovx, cam.tanfovy, cam.viewmatrix, cam.projmatrix, cam.campos,
-                                      cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict)
+                                      cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict,
+                                      tight_tiles=self.tight_tiles)
 
     def _slot(self, j: int) -> _Slot:
         while len(self.slots) <= j:

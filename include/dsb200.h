@@ -31,6 +31,14 @@ extern "C" {
  * exclusive prefix of the last splat as the pair total (cpp/rasterizer_torch.cu:97-104).  With this
  * flag set the library reproduces that, which bit-exact parity of the sorted lists needs. */
 #define DSB_FLAG_DROP_LAST_SPLAT 1
+/* Pairs only for the tiles a splat can contribute to.  The reference pairs a splat with every tile of the
+ * square around its 3-sigma circle (cpp/rasterizer_kernels.cu:233-250); most of those pairs end in the
+ * per-pixel "alpha < 1/255" skip.  With this flag the tile rectangle kept in the record and counted in
+ * tiles_touched is the square intersected with the bounding box of the region where opacity * exp(-q) can
+ * reach 1/255, so the pair list, K and the ranges are those of a SUBSET of the reference's list; image, radii
+ * and gradients are unchanged (the dropped pairs never pass the per-pixel test).  Off: lists, counts and
+ * ranges are exactly the reference's. */
+#define DSB_FLAG_TIGHT_TILES 2
 
 #define DSB_RECORD_FLOATS 12  /* packed per-splat record: 3 x float4, see DsbCamera notes below   */
 #define DSB_MAX_BATCH_VIEWS 8 /* views one dsb_geometry_backward_views call takes                  */

@@ -170,7 +170,7 @@ def test_fused_render_matches_stage_calls():
     sc = scenes.headline(n=60_000, seed=93, W=500, H=297, focal=300.0)
     view = sc.views[0]
     t = scene_tensors(sc)
-    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], tight_tiles=False)
     image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
     k = r.last_k
     fused_pairs = r.pairs[0][:k].clone()
@@ -286,3 +286,27 @@ def test_torch_free_forward_equals_the_operator_image():
                                      out.data_ptr(), _capi.stream_ptr()))
     torch.cuda.synchronize()
     assert float(out.abs().max()) == 0.0
+
+
+def test_tight_tiles_change_the_pair_list_but_not_the_results():
+    """DSB_FLAG_TIGHT_TILES drops the (tile, splat) pairs of tiles a splat cannot contribute to.  The pair count must
+    fall, image and final transmittance must stay bit-identical, gradients equal up to atomic summation order."""
+    for sc in (scenes.headline(n=120_000, seed=95, W=960, H=544, focal=560.0), scenes.stress(n=4_000, seed=96, W=640, H=368, focal=400.0)):
+        view = sc.views[0]
+        t = scene_tensors(sc)
+        cam = CameraTensors.from_view(view, "cuda")
+        v = torch.from_numpy(sc.image_grad()).cuda()
+        out = {}
+        for tight in (False, True):
+            r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], tight_tiles=tight)
+            image = r.forward(cam).clone()
+            final_t = r._image_buffers(view.H, view.W)[1].clone()
+            g = GradientBuffer(sc.n, "cuda")
+            r.backward(v, g, accumulate=False)
+            torch.cuda.synchronize()
+            out[tight] = (r.last_k, image, final_t, g.flat.clone(), r.radii.clone())
+        k_ref, img_ref, ft_ref, g_ref, radii_ref = out[False]
+        k_tight, img_t, ft_t, g_t, radii_t = out[True]
+        assert 0 < k_tight < 0.85 * k_ref
+        assert torch.equal(img_t, img_ref) and torch.equal(ft_t, ft_ref) and torch.equal(radii_t, radii_ref)
+        assert float((g_t - g_ref).abs().max()) <= 1e-5 * float(g_ref.abs().max())
