@@ -374,9 +374,9 @@ def main():
         alg_bytes = K * (8 + 48 + 36) + 20 * H * W + 48 * scene.n
         achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
         # DRAM bytes of one blend_backward_kernel launch from the ncu capture summarised in
-        # profiles/blend_backward_c1.md (90,752,768 read + 4,090,624 written at K = 10,957,444); it is dominated
+        # profiles/blend_backward_c1.md (83,103,232 read + 4,211,712 written at config 1); it is dominated
         # by the pair list and the gathered records, so other workloads scale it by their pair count.
-        traffic = int(94_843_392 * (K / 10_957_444))
+        traffic = int(87_314_944 * (K / 10_957_444))
         roofline = {"kernel": dom, "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                     "frac": round(achieved / peak, 4), "traffic": traffic,
                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on config 1, scaled by pairs",

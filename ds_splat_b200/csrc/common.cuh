@@ -119,21 +119,6 @@ struct SortPlan {
 __device__ __forceinline__ u32 sort_digit(u64 key, int shift, u32 mask, u32 flip) {
     return ((u32)(key >> shift) & mask) ^ flip;
 }
-// Lanes of the warp that are valid and hold the same nbits-wide digit as the calling lane: one ballot per
-// digit bit.  (match.any gives the same answer but its latency grows with the number of distinct values in
-// the warp, which is the common case for the low digits of tile ids and depth keys.)
-__device__ __forceinline__ u32 warp_peers(const u32 d, const bool valid, const int nbits) {
-    u32 peers = __ballot_sync(0xffffffffu, valid);
-#pragma unroll
-    for (int b = 0; b < 8; ++b) {
-        if (b < nbits) {
-            const bool bit = (d >> b) & 1u;
-            const u32 vote = __ballot_sync(0xffffffffu, bit);
-            peers &= bit ? vote : ~vote;
-        }
-    }
-    return peers;
-}
 SortPlan make_sort_plan(int begin_bit, int end_bit, bool signed_top);
 
 int64_t sort_workspace_bytes(int64_t k);

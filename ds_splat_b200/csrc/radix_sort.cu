@@ -57,9 +57,8 @@ struct SortHeader {                  // start of the workspace, zeroed before ev
     int pad[7];
 };
 
-// Counts all digits of all passes in one read of the keys.  Per-warp aggregation (warp_peers) keeps
-// the shared-memory atomics to one per distinct digit per warp, which matters when a digit is nearly
-// constant (the exponent byte of depth keys, the high tile bits).
+// Counts all digits of all passes in one read of the keys, into per-block shared-memory counters that are
+// added to the global ones at the end.
 __global__ void __launch_bounds__(kThreads)
 radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan plan, u32* __restrict__ hist,
                        const long long item_stride, const long long ws_stride_u32) {
@@ -68,7 +67,6 @@ radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan
     hist += blockIdx.y * ws_stride_u32;
     for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
     __syncthreads();
-    const u32 lane = threadIdx.x & 31;
     // Four keys per thread and trip, loaded before any of them is counted, so that four loads are in flight;
     // whole warps stay converged for the ballots.
     constexpr u32 kUnroll = 4;
@@ -84,9 +82,10 @@ radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan
         for (u32 q = 0; q < kUnroll; ++q) {
             const bool valid = base + q * kThreads + threadIdx.x < n;
             for (int p = 0; p < plan.npass; ++p) {
+                // one shared-memory atomic per key and pass: lanes that share a digit are serialised by the hardware,
+                // which costs less than finding them with ballots first
                 const u32 d = sort_digit(key[q], plan.shift[p], plan.mask[p], plan.flip[p]);
-                const u32 m = warp_peers(d, valid, plan.bits[p]);
-                if (valid && (m & ((1u << lane) - 1u)) == 0) atomicAdd(&s_hist[p][d], (u32)__popc(m));
+                if (valid) atomicAdd(&s_hist[p][d], 1u);
             }
         }
     }
@@ -459,8 +458,12 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     DSB_REQUIRE(batch >= 1 && (batch == 1 || item_stride >= k), "sort: bad batch layout");
     rc = sort_begin(k, plan, ws, ws_bytes, &hist, s, batch);
     if (rc != DSB_OK) return rc;
-    const int64_t chunks = (k + kThreads * 4 - 1) / (kThreads * 4);   // four keys per thread and trip
-    const int hist_blocks = (int)(chunks < 148 * 8 ? chunks : 148 * 8);
+    // Four keys per thread and trip.  Every block ends by adding its 256 counters per pass to the global ones, so
+    // the grid is kept to about eight blocks per SM over the whole batch: more blocks would spend the time in
+    // those atomics, fewer would leave loads uncovered.
+    const int64_t chunks = (k + kThreads * 4 - 1) / (kThreads * 4);
+    const int64_t per_list = (148 * 8 + batch - 1) / batch;
+    const int hist_blocks = (int)(chunks < per_list ? chunks : per_list);
     radix_histogram_kernel<<<dim3((unsigned)hist_blocks, (unsigned)batch), kThreads, 0, s>>>(
         items, (u32)k, plan, hist, item_stride, batch > 1 ? sort_batch_stride_bytes(k) / 4 : 0);
     DSB_LAUNCH_CHECK();
