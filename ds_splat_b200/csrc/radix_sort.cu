@@ -67,8 +67,7 @@ radix_histogram_kernel(const u64* __restrict__ keys, const u32 n, const SortPlan
     hist += blockIdx.y * ws_stride_u32;
     for (int k = threadIdx.x; k < plan.npass * kRadix; k += kThreads) (&s_hist[0][0])[k] = 0;
     __syncthreads();
-    // Four keys per thread and trip, loaded before any of them is counted, so that four loads are in flight;
-    // whole warps stay converged for the ballots.
+    // Four keys per thread and trip, loaded before any of them is counted, so that four loads are in flight.
     constexpr u32 kUnroll = 4;
     const u32 chunk = kThreads * kUnroll;
     for (u32 base = blockIdx.x * chunk; base < n; base += gridDim.x * chunk) {
