@@ -124,6 +124,7 @@ blend_backward_kernel(const int W, const int H, const int tiles_x, const int num
     if (slot >= num_tiles) return;                         // whole warps only; no block-wide barrier below
     const int sub = wb - slot * kBlocksPerTile;
     const int tile = tile_order ? tile_order[slot] : slot; // longest lists first when the order is known
+    if ((unsigned)tile >= (unsigned)num_tiles) return;     // a caller's stale order must not index outside the ranges
     const int tile_x = tile % tiles_x, tile_y = tile / tiles_x;
     const int bx = tile_x * kTile + (sub % kBlocksPerTileX) * kBlockW, by = tile_y * kTile + (sub / kBlocksPerTileX) * kBlockH;
     const int x = bx + (lane % kBlockW), y0 = by + (lane / kBlockW);

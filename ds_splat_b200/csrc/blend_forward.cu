@@ -75,6 +75,7 @@ blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_
     const int slot = wb / kWarpsPerTile;
     if (slot >= num_tiles) return;               // whole warps only; no block-wide barrier below
     const int tile = tile_order ? tile_order[slot] : slot;   // longest lists first when the order is known
+    if ((unsigned)tile >= (unsigned)num_tiles) return;       // a caller's stale order must not index outside the ranges
     const WarpPixels wp = warp_pixels(tile % tiles_x, tile / tiles_x, wb % kWarpsPerTile, lane);
     const int x = wp.x, y = wp.y;
     const bool inside = x < W && y < H;
