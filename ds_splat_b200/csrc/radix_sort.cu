@@ -169,19 +169,24 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     const u32 wbase = tile_base + (u32)warp * (32 * ITEMS);
     u32* my_wcnt = sh.wcnt + warp * kRadix;
 
-    // Load: item i of lane l sits at wbase + 32 i + l, so (i, l) order is memory order.
+    // Load: item i of lane l sits at wbase + 32 i + l, so (i, l) order is memory order.  Only the digits are kept
+    // (rd[i], later joined by the rank): the keys are read again, from L2, when they are moved -- sixteen 64-bit
+    // keys held in registers across the ranking cost more in spills and occupancy than the second read.
+#ifndef DSB_SORT_RELOAD
+#define DSB_SORT_RELOAD 1
+#endif
+    constexpr bool kReload = DSB_SORT_RELOAD != 0;
     u64 key[ITEMS];
-    u32 val[ITEMS];
-    {
-        const u64* src = kin + wbase + lane;
-        const u32* vsrc = HAS_VALS ? vin + wbase + lane : nullptr;
+    u32 rd[ITEMS];
+    const u64* src = kin + wbase + lane;
+    const u32* vsrc = HAS_VALS ? vin + wbase + lane : nullptr;
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const bool ok = FULL || wbase + 32 * i + lane < n;
-            key[i] = ok ? src[32 * i] : ~0ull;
-            if (HAS_VALS) val[i] = ok ? vsrc[32 * i] : 0u;
-        }
+    for (int i = 0; i < ITEMS; ++i) {
+        const bool ok = FULL || wbase + 32 * i + lane < n;
+        key[i] = ok ? src[32 * i] : ~0ull;
     }
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) rd[i] = digit_of(key[i], ds);
 
     // Rank inside the warp: lanes holding the same digit find each other (peers_of); the lowest of them
     // bumps the warp's counter for that digit by the group size with a shared-memory atomic, whose old value
@@ -189,7 +194,6 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     // peer masks, then the atomics in item order (a warp barrier between two of them keeps that order), and
     // only then the broadcasts of the old values -- so no item waits for the previous item's round trip.
     // rd[i] packs the item's rank among equal digits of its warp (low 16 bits) with its digit (bits 16..23).
-    u32 rd[ITEMS];
     const u32 lanemask_lt = (1u << lane) - 1u;
     constexpr int kGroup = DSB_SORT_GROUP;
 #pragma unroll
@@ -198,7 +202,7 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
             const bool valid = FULL || wbase + 32 * (i0 + j) + lane < n;
-            d[j] = digit_of(key[i0 + j], ds);
+            d[j] = rd[i0 + j];
             m[j] = peers_of<NB, FULL>(d[j], valid);
         }
 #pragma unroll
@@ -267,8 +271,8 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     for (int i = 0; i < ITEMS; ++i) {
         if (FULL || wbase + 32 * i + lane < n) {
             const u32 slot = my_wcnt[rd[i] >> 16] + (rd[i] & 0xffffu);
-            sh.keys[slot] = key[i];
-            if (HAS_VALS) sh.vals[slot] = val[i];
+            sh.keys[slot] = kReload ? src[32 * i] : key[i];
+            if (HAS_VALS) sh.vals[slot] = vsrc[32 * i];
         }
     }
     __syncthreads();
