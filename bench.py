@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-reference-cuda", action="store_true")
+    ap.add_argument("--skip-optimizer", action="store_true")
     return ap.parse_args()
 
 
@@ -278,6 +279,28 @@ def main():
     timed_views = min(args.steps, 40) * vpr
     stages_ms = {name: round(ms / timed_views, 5) for name, (ms, calls) in stage_raw.items() if calls}
 
+    # ---- the optimizer step that follows a training step (not part of the metric; reported beside it) ---------
+    optimizer = None
+    if world == 1 and not args.skip_optimizer:
+        from ds_splat_b200.dp import FlatAdam
+        scratch = {k: v.clone() for k, v in renderer.p.items()}   # the timed steps must not move the benchmark's scene
+        opt = FlatAdam(scratch, dict(means3d=1.6e-4, shs=2.5e-3, opacities=5e-2, scales=5e-3, rotations=1e-3))
+        for _ in range(3):
+            opt.step(grads, grad_scale=1.0 / vpr)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(20):
+            opt.step(grads, grad_scale=1.0 / vpr)
+        ev1.record()
+        torch.cuda.synchronize()
+        adam_ms = ev0.elapsed_time(ev1) / 20
+        adam_bytes = 28 * grads.flat.numel()   # read p, g, m, v; write p, m, v
+        optimizer = {"kernel": "adam_kernel (5 launches, one per parameter tensor)", "ms_per_step": round(adam_ms, 4),
+                     "achieved_GBps": round(adam_bytes / (adam_ms * 1e-3) / 1e9, 1), "algorithmic_bytes": int(adam_bytes)}
+        del scratch, opt
+        torch.cuda.empty_cache()
+
     # ---- end to end through the public operator, host buffers -----------------------------------------
     e2e = None
     if not args.skip_e2e:
@@ -364,6 +387,8 @@ def main():
     reference_cuda = reference_cuda_numbers(scene, view, v_images_host[0]) if world == 1 and not args.skip_reference_cuda else None
 
     peak, peak_src = measured_peaks()
+    if optimizer:
+        optimizer["frac_of_hbm_peak"] = round(optimizer["achieved_GBps"] / peak, 4)
     dom = "blend_backward"
     dom_ms = stages_ms.get(dom)
     roofline, roofline_fp32 = None, None
@@ -401,6 +426,7 @@ def main():
                        "88 MB pair list per view; no explicit flush)", "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
             "clocks": clocks, "gpu_launches": int(launches), "stages_ms": stages_ms, "roofline": roofline,
             "roofline_fp32": roofline_fp32, "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda,
+            "optimizer": optimizer,
             "pairs_evaluated": {"forward_per_pixel": pairs_fwd, "backward_per_pixel": pairs_bwd}}
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -465,6 +465,11 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
     return rc;
 }
 
+int dsb_adam_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr,
+                  double beta1, double beta2, double eps, int32_t step, double grad_scale, void* stream) {
+    return launch_adam(params, grads, exp_avg, exp_avg_sq, count, lr, beta1, beta2, eps, step, grad_scale, (cudaStream_t)stream);
+}
+
 int dsb_export_reference_lists(const uint64_t* sorted_pairs, int64_t k, const float* records, int64_t* keys, int32_t* ids,
                                void* stream) {
     DSB_REQUIRE(k >= 0, "k must be non-negative");

@@ -177,4 +177,7 @@ int launch_geometry_backward_views(const CamParams* cps, int count, int n, const
                                    float* v_means2d, float* v_shs, float* v_colors, float* v_opac, float* v_scales,
                                    float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
 
+int launch_adam(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr, double beta1,
+                double beta2, double eps, int step, double grad_scale, cudaStream_t s);
+
 }  // namespace dsb

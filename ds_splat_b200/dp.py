@@ -289,6 +289,34 @@ class ViewRenderer:
             b0 = b1
 
 
+class FlatAdam:
+    """Adam over the five parameter tensors of a splat cloud, fed from a ``GradientBuffer``: one fused kernel launch
+    per tensor (``dsb_adam_step``), each with its own learning rate as 3DGS training uses them, moments kept in one
+    flat allocation laid out like the gradient block.  The update is torch.optim.Adam's (no weight decay, no
+    amsgrad); ``grad_scale`` turns the summed gradient of a multi-view, multi-rank step into a mean on the fly."""
+
+    def __init__(self, params: Dict[str, torch.Tensor], lrs: Dict[str, float], betas=(0.9, 0.999), eps: float = 1e-15):
+        from . import _capi
+        self._capi, self.lib = _capi, _capi.lib()
+        self.params, self.lrs, self.betas, self.eps = params, dict(lrs), betas, eps
+        self.step_count = 0
+        n = params["means3d"].shape[0]
+        dev = params["means3d"].device
+        self.m = GradientBuffer(n, dev, sh_coeffs=params["shs"].shape[1])
+        self.v = GradientBuffer(n, dev, sh_coeffs=params["shs"].shape[1])
+
+    def step(self, grads: GradientBuffer, grad_scale: float = 1.0):
+        self.step_count += 1
+        for name, _ in SEGMENTS:
+            p, g = self.params[name], grads.views[name]
+            if not p.is_contiguous() or p.numel() != g.numel():
+                raise ValueError(f"{name}: parameter and gradient layouts differ")
+            self._capi.check(self.lib.dsb_adam_step(
+                p.data_ptr(), g.data_ptr(), self.m.views[name].data_ptr(), self.v.views[name].data_ptr(), p.numel(),
+                float(self.lrs[name]), float(self.betas[0]), float(self.betas[1]), float(self.eps), self.step_count,
+                float(grad_scale), self._capi.stream_ptr()))
+
+
 def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads,
                        grads: GradientBuffer, group=None) -> None:
     """One step of the multi-view batch on this rank: forward + backward of each local camera (gradients

@@ -297,6 +297,17 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
                      float tan_fovy, float scale_modifier, int32_t max_sh_degree, int32_t sh_degree,
                      float* output_image, void* stream);
 
+/* ---- the step after the operator -------------------------------------------------------------------
+ * Adam on one parameter tensor (no reference counterpart: users of the reference call torch.optim.Adam;
+ * this is that update -- no weight decay, no amsgrad -- in one pass over memory):
+ *     g' = grad_scale * g;  m <- b1 m + (1-b1) g';  v <- b2 v + (1-b2) g'^2
+ *     p <- p - lr / (1 - b1^step) * m / (sqrt(v) / sqrt(1 - b2^step) + eps)
+ * params, exp_avg and exp_avg_sq are float tensors updated in place; step counts from 1.  The hyper-parameters are
+ * doubles and are combined in double before rounding (1 - beta, the bias corrections), as torch does.  grad_scale lets the caller
+ * turn the summed gradient of a multi-view step into a mean without another pass. */
+int dsb_adam_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr,
+                  double beta1, double beta2, double eps, int32_t step, double grad_scale, void* stream);
+
 /* Test/export helper: rebuild the reference-format sorted lists from this library's packed pairs:
  * keys[i] = (tile << 32) | sign-extended depth bits of the splat, ids[i] = splat id
  * (the layout cpp/rasterizer_kernels.cu:283,299-301 produces and thrust sorts). */

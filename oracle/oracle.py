@@ -254,3 +254,18 @@ def backward(cam: Camera, fwd, means, shs, opacities, scales, rots, v_image, v_d
     v_means2d = np.concatenate([v_xy, np.zeros((n, 1), np.float32)], axis=1)
     return dict(v_means3d=v_mean, v_means2d=v_means2d, v_shs=v_sh, v_colors=v_rgb, v_opacities=v_op.reshape(n, 1),
                 v_scales=v_scale, v_rotations=v_rot, v_cov3d=v_cov3d, v_conic=v_conic, pairs_bwd=pairs)
+
+
+def adam_step(param, grad, exp_avg, exp_avg_sq, lr, beta1=0.9, beta2=0.999, eps=1e-8, step=1, grad_scale=1.0):
+    """Checker for the optimizer step that follows the operator in a training loop.  No reference file to cite: the
+    reference's users call torch.optim.Adam; this restates that update (Kingma & Ba, algorithm 1, in the form
+    torch applies it without weight decay or amsgrad) in float32 numpy, returning new (param, exp_avg, exp_avg_sq).
+    tests/test_oracle.py pins it against torch.optim.Adam itself."""
+    f = np.float32
+    g = (_f32(grad) * f(grad_scale)).astype(np.float32)
+    m = (f(beta1) * _f32(exp_avg) + f(1.0 - beta1) * g).astype(np.float32)
+    v = (f(beta2) * _f32(exp_avg_sq) + f(1.0 - beta2) * g * g).astype(np.float32)
+    bias1, bias2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    denom = (np.sqrt(v) / f(np.sqrt(bias2)) + f(eps)).astype(np.float32)
+    p = (_f32(param) - f(lr / bias1) * (m / denom)).astype(np.float32)
+    return p, m, v

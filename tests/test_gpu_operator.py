@@ -377,3 +377,40 @@ def test_plan_of_several_views_equals_one_at_a_time():
     with pytest.raises(_capi.DsbError):
         _capi.check(lib.dsb_plan_pairs_views(C.byref(cams[0]), nv, n, n, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
                                              offsets.data_ptr(), ws.data_ptr(), 1024, ks, _capi.stream_ptr()))
+
+
+def test_adam_step_matches_the_checker_and_a_training_step_lowers_the_loss():
+    from ds_splat_b200.dp import FlatAdam
+    rng = np.random.default_rng(21)
+    # the kernel alone: odd length (scalar tail) and an unaligned view (scalar path), three steps
+    for count, offset in ((100_003, 0), (4_099, 1)):
+        p0 = rng.normal(0, 1, count + offset).astype(np.float32)
+        p = torch.from_numpy(p0.copy()).cuda()[offset:]
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        po, mo, vo = p0[offset:].copy(), np.zeros(count, np.float32), np.zeros(count, np.float32)
+        for step in (1, 2, 3):
+            g = (rng.normal(0, 1e-2, count) * 10.0 ** rng.integers(-2, 2)).astype(np.float32)
+            gt = torch.from_numpy(g).cuda()
+            _capi.check(_capi.lib().dsb_adam_step(p.data_ptr(), gt.data_ptr(), m.data_ptr(), v.data_ptr(), count,
+                                                  1e-3, 0.9, 0.999, 1e-15, step, 0.5, _capi.stream_ptr()))
+            po, mo, vo = O.adam_step(po, g, mo, vo, lr=1e-3, eps=1e-15, step=step, grad_scale=0.5)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(p.cpu().numpy(), po, rtol=2e-6, atol=1e-8)
+        np.testing.assert_allclose(m.cpu().numpy(), mo, rtol=1e-5, atol=1e-6 * float(np.abs(mo).max()))
+        np.testing.assert_allclose(v.cpu().numpy(), vo, rtol=1e-5, atol=1e-6 * float(vo.max()))
+    # a few optimisation steps towards a target image lower an L2 loss
+    sc = scenes.tiny(n=5000, seed=41, W=192, H=128, focal=180.0)
+    t = scene_tensors(sc)
+    cam = CameraTensors.from_view(sc.views[0], "cuda")
+    target = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"]).forward(cam).clone()
+    params = dict(means3d=t["means"].clone(), shs=(t["shs"] * 0.5).contiguous(), opacities=t["opacities"].clone(),
+                  scales=t["scales"].clone(), rotations=t["rotations"].clone())
+    opt = FlatAdam(params, dict(means3d=0.0, shs=2.5e-2, opacities=0.0, scales=0.0, rotations=0.0))
+    grads = GradientBuffer(sc.n, "cuda")
+    losses = []
+    for _ in range(6):
+        r = ViewRenderer(params["means3d"], params["shs"], params["opacities"], params["scales"], params["rotations"])
+        r.render_views([cam], lambda i, image: (losses.append(float(((image - target) ** 2).sum())), 2.0 * (image - target))[1],
+                       grads)
+        opt.step(grads)
+    assert losses[-1] < 0.5 * losses[0]

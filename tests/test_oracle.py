@@ -153,3 +153,23 @@ def test_depth_map_is_a_fourth_colour_channel(small):
     V = np.asarray(sc.views[0].view, np.float32).reshape(4, 4)
     np.testing.assert_allclose(vm[vis], b[5][vis, None] * V[2, :3][None, :], rtol=1e-6, atol=1e-12)
     assert np.abs(vm[~vis]).max() == 0
+
+
+def test_adam_checker_equals_torch_optim_adam():
+    """The optimizer-step checker has no reference source to follow; pin it against torch.optim.Adam itself."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(12)
+    p0 = rng.normal(0, 1, 5000).astype(np.float32)
+    grads = [(rng.normal(0, 1e-2, 5000) * (10.0 ** rng.integers(-3, 2))).astype(np.float32) for _ in range(4)]
+    tp = torch.nn.Parameter(torch.from_numpy(p0.copy()))
+    opt = torch.optim.Adam([tp], lr=1.6e-4, betas=(0.9, 0.999), eps=1e-15)
+    p, m, v = p0.copy(), np.zeros_like(p0), np.zeros_like(p0)
+    for step, g in enumerate(grads, start=1):
+        tp.grad = torch.from_numpy(g.copy())
+        opt.step()
+        p, m, v = O.adam_step(p, g, m, v, lr=1.6e-4, beta1=0.9, beta2=0.999, eps=1e-15, step=step)
+        np.testing.assert_allclose(p, tp.detach().numpy(), rtol=2e-6, atol=1e-9)
+    st = opt.state[tp]
+    # moments: sums of terms of mixed sign, so the tolerance is relative to the largest entry
+    np.testing.assert_allclose(m, st["exp_avg"].numpy(), rtol=1e-5, atol=1e-6 * float(np.abs(m).max()))
+    np.testing.assert_allclose(v, st["exp_avg_sq"].numpy(), rtol=1e-5, atol=1e-6 * float(v.max()))
