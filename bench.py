@@ -299,6 +299,25 @@ def main():
         optimizer = {"kernel": "adam_kernel (5 launches, one per parameter tensor)", "ms_per_step": round(adam_ms, 4),
                      "achieved_GBps": round(adam_bytes / (adam_ms * 1e-3) / 1e9, 1), "algorithmic_bytes": int(adam_bytes)}
         del scratch, opt
+        # ... and the photometric loss between forward and backward (L1 + D-SSIM and its gradient, two launches)
+        from ds_splat_b200.dp import ImageLoss
+        loss_fn = ImageLoss(lambda_dssim=0.2)
+        img = renderer.forward(cams[-1]).clone()
+        tgt = torch.rand_like(img)
+        for _ in range(3):
+            loss_fn.gradient(img, tgt)
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(20):
+            loss_fn.gradient(img, tgt)
+        ev1.record()
+        torch.cuda.synchronize()
+        loss_ms = ev0.elapsed_time(ev1) / 20
+        loss_bytes = 4 * 3 * H * W * (2 + 3 + 3 + 2 + 1)   # read x, y; write 3 maps; read 3 maps, x, y; write dL/dx
+        optimizer["image_loss"] = {"kernels": "ssim_moments_kernel + ssim_gradient_kernel", "ms_per_view": round(loss_ms, 4),
+                                   "achieved_GBps": round(loss_bytes / (loss_ms * 1e-3) / 1e9, 1),
+                                   "algorithmic_bytes": int(loss_bytes)}
+        del loss_fn, img, tgt
         torch.cuda.empty_cache()
 
     # ---- end to end through the public operator, host buffers -----------------------------------------

@@ -465,6 +465,17 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
     return rc;
 }
 
+int64_t dsb_image_loss_workspace_bytes(int32_t image_height, int32_t image_width) {
+    return (image_height > 0 && image_width > 0) ? image_loss_workspace_bytes(image_height, image_width) : 0;
+}
+
+int dsb_image_loss_backward(const float* image, const float* target, int32_t image_height, int32_t image_width,
+                            float lambda_dssim, void* workspace, int64_t workspace_bytes, float* v_image, float* loss,
+                            void* stream) {
+    return launch_image_loss(image, target, image_height, image_width, lambda_dssim, workspace, workspace_bytes, v_image, loss,
+                             (cudaStream_t)stream);
+}
+
 int dsb_adam_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr,
                   double beta1, double beta2, double eps, int32_t step, double grad_scale, void* stream) {
     return launch_adam(params, grads, exp_avg, exp_avg_sq, count, lr, beta1, beta2, eps, step, grad_scale, (cudaStream_t)stream);

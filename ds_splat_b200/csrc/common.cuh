@@ -177,6 +177,9 @@ int launch_geometry_backward_views(const CamParams* cps, int count, int n, const
                                    float* v_means2d, float* v_shs, float* v_colors, float* v_opac, float* v_scales,
                                    float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
 
+int64_t image_loss_workspace_bytes(int H, int W);
+int launch_image_loss(const float* image, const float* target, int H, int W, float lambda_dssim, void* workspace,
+                      int64_t workspace_bytes, float* v_image, float* loss, cudaStream_t s);
 int launch_adam(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr, double beta1,
                 double beta2, double eps, int step, double grad_scale, cudaStream_t s);
 

@@ -1,0 +1,195 @@
+// The step before the operator's backward in a training loop: the photometric loss of 3-D Gaussian Splatting
+// training and its gradient with respect to the rendered image, in two launches.
+//
+//     L = (1 - lambda) * mean |x - y|  +  lambda * (1 - mean SSIM(x, y))
+//
+// x the rendered image, y the target, both [H][W][3]; SSIM per channel with an 11x11 Gaussian window (sigma 1.5),
+// zero padding, C1 = 0.01^2, C2 = 0.03^2 (Wang et al., "Image quality assessment: from error visibility to
+// structural similarity", 2004, in the form 3DGS training code uses).  Not part of the reference, whose users
+// build this loss from ~20 torch operations and let autograd differentiate them.
+//
+// With w the window, m1 = w*x, m2 = w*y, e11 = w*x^2, e22 = w*y^2, e12 = w*(xy) (* = zero-padded correlation):
+//     s11 = e11 - m1^2, s22 = e22 - m2^2, s12 = e12 - m1 m2
+//     A1 = 2 m1 m2 + C1, A2 = 2 s12 + C2, B1 = m1^2 + m2^2 + C1, B2 = s11 + s22 + C2, S = A1 A2 / (B1 B2)
+// S depends on x through m1, e11 and e12; the window is symmetric, so
+//     dL/dx = w*(g dS/dm1) + 2 x . w*(g dS/de11) + y . w*(g dS/de12) + (1 - lambda)/(3HW) sign(x - y),  g = -lambda/(3HW)
+//     dS/dm1  = [2 m2 (A2 - A1) B1 B2 - A1 A2 2 m1 (B2 - B1)] / (B1 B2)^2
+//     dS/de11 = -A1 A2 / (B1 B2^2)          dS/de12 = 2 A1 / (B1 B2)
+// Kernel 1 computes the five windowed moments per pixel (separable, through shared memory), the loss sums and the
+// three maps g dS/d.; kernel 2 correlates the maps with the window again and assembles dL/dx.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace dsb {
+
+namespace {
+
+constexpr int kWin = 11, kHalf = 5;
+constexpr int kTileW = 16, kTileH = 16;
+constexpr int kPadW = kTileW + 2 * kHalf, kPadH = kTileH + 2 * kHalf;   // 26 x 26 with the halo
+
+struct Window { float w[kWin]; };
+
+__device__ __forceinline__ float block_sum(float v, float* s_red) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int tid = threadIdx.y * kTileW + threadIdx.x;
+    if ((tid & 31) == 0) s_red[tid >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+    if (tid == 0)
+        for (int k = 0; k < kTileW * kTileH / 32; ++k) total += s_red[k];
+    __syncthreads();
+    return total;   // valid in thread 0
+}
+
+// maps: [3][H][W][3] (g dS/dm1, g dS/de11, g dS/de12); sums: [0] += sum |x - y|, [1] += sum SSIM
+__global__ void __launch_bounds__(kTileW * kTileH)
+ssim_moments_kernel(const float* __restrict__ x, const float* __restrict__ y, const int H, const int W, const Window win,
+                    const float g, float* __restrict__ maps, float* __restrict__ sums) {
+    __shared__ float s_x[kPadH][kPadW], s_y[kPadH][kPadW];
+    __shared__ float s_h[5][kPadH][kTileW];   // horizontally filtered x, y, x^2, y^2, xy
+    __shared__ float s_red[kTileW * kTileH / 32];
+    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kTileW + tx;
+    const int x0 = blockIdx.x * kTileW, y0 = blockIdx.y * kTileH;
+    const int px = x0 + tx, py = y0 + ty;
+    const bool inside = px < W && py < H;
+    const size_t plane = (size_t)H * W * 3;
+    float l1_sum = 0.f, ssim_sum = 0.f;
+    for (int c = 0; c < 3; ++c) {
+        for (int k = tid; k < kPadH * kPadW; k += kTileW * kTileH) {
+            const int ry = k / kPadW, rx = k - ry * kPadW;
+            const int gy = y0 + ry - kHalf, gx = x0 + rx - kHalf;
+            const bool ok = gy >= 0 && gy < H && gx >= 0 && gx < W;   // zero padding outside the image
+            const size_t idx = ((size_t)gy * W + gx) * 3 + c;
+            s_x[ry][rx] = ok ? x[idx] : 0.f;
+            s_y[ry][rx] = ok ? y[idx] : 0.f;
+        }
+        __syncthreads();
+        for (int k = tid; k < kPadH * kTileW; k += kTileW * kTileH) {
+            const int ry = k / kTileW, cx = k - ry * kTileW;
+            float a = 0.f, b = 0.f, aa = 0.f, bb = 0.f, ab = 0.f;
+#pragma unroll
+            for (int t = 0; t < kWin; ++t) {
+                const float xv = s_x[ry][cx + t], yv = s_y[ry][cx + t], wt = win.w[t];
+                a += wt * xv; b += wt * yv; aa += wt * xv * xv; bb += wt * yv * yv; ab += wt * xv * yv;
+            }
+            s_h[0][ry][cx] = a; s_h[1][ry][cx] = b; s_h[2][ry][cx] = aa; s_h[3][ry][cx] = bb; s_h[4][ry][cx] = ab;
+        }
+        __syncthreads();
+        float m1 = 0.f, m2 = 0.f, e11 = 0.f, e22 = 0.f, e12 = 0.f;
+#pragma unroll
+        for (int t = 0; t < kWin; ++t) {
+            const float wt = win.w[t];
+            m1 += wt * s_h[0][ty + t][tx]; m2 += wt * s_h[1][ty + t][tx]; e11 += wt * s_h[2][ty + t][tx];
+            e22 += wt * s_h[3][ty + t][tx]; e12 += wt * s_h[4][ty + t][tx];
+        }
+        if (inside) {
+            const float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
+            const float s11 = e11 - m1 * m1, s22 = e22 - m2 * m2, s12 = e12 - m1 * m2;
+            const float A1 = 2.f * m1 * m2 + C1, A2 = 2.f * s12 + C2, B1 = m1 * m1 + m2 * m2 + C1, B2 = s11 + s22 + C2;
+            const float inv = 1.f / (B1 * B2);
+            const float S = A1 * A2 * inv;
+            const float dS_dm1 = (2.f * m2 * (A2 - A1) * B1 * B2 - A1 * A2 * 2.f * m1 * (B2 - B1)) * inv * inv;
+            const float dS_de11 = -A1 * A2 * inv / B2;
+            const float dS_de12 = 2.f * A1 * inv;
+            const size_t idx = ((size_t)py * W + px) * 3 + c;
+            maps[idx] = g * dS_dm1; maps[plane + idx] = g * dS_de11; maps[2 * plane + idx] = g * dS_de12;
+            ssim_sum += S;
+            l1_sum += fabsf(s_x[ty + kHalf][tx + kHalf] - s_y[ty + kHalf][tx + kHalf]);
+        }
+        __syncthreads();   // the tiles are reloaded for the next channel
+    }
+    const float l1_total = block_sum(l1_sum, s_red);
+    const float ssim_total = block_sum(ssim_sum, s_red);
+    if (tid == 0) { atomicAdd(sums, l1_total); atomicAdd(sums + 1, ssim_total); }
+}
+
+__global__ void __launch_bounds__(kTileW * kTileH)
+ssim_gradient_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ maps, const int H,
+                     const int W, const Window win, const float l1_weight, float* __restrict__ v_image) {
+    __shared__ float s_m[3][kPadH][kPadW];
+    __shared__ float s_h[3][kPadH][kTileW];
+    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kTileW + tx;
+    const int x0 = blockIdx.x * kTileW, y0 = blockIdx.y * kTileH;
+    const int px = x0 + tx, py = y0 + ty;
+    const size_t plane = (size_t)H * W * 3;
+    for (int c = 0; c < 3; ++c) {
+        for (int k = tid; k < kPadH * kPadW; k += kTileW * kTileH) {
+            const int ry = k / kPadW, rx = k - ry * kPadW;
+            const int gy = y0 + ry - kHalf, gx = x0 + rx - kHalf;
+            const bool ok = gy >= 0 && gy < H && gx >= 0 && gx < W;
+            const size_t idx = ((size_t)gy * W + gx) * 3 + c;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) s_m[q][ry][rx] = ok ? maps[q * plane + idx] : 0.f;
+        }
+        __syncthreads();
+        for (int k = tid; k < kPadH * kTileW; k += kTileW * kTileH) {
+            const int ry = k / kTileW, cx = k - ry * kTileW;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+#pragma unroll
+            for (int t = 0; t < kWin; ++t) {
+                const float wt = win.w[t];
+                a0 += wt * s_m[0][ry][cx + t]; a1 += wt * s_m[1][ry][cx + t]; a2 += wt * s_m[2][ry][cx + t];
+            }
+            s_h[0][ry][cx] = a0; s_h[1][ry][cx] = a1; s_h[2][ry][cx] = a2;
+        }
+        __syncthreads();
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int t = 0; t < kWin; ++t) {
+            const float wt = win.w[t];
+            c0 += wt * s_h[0][ty + t][tx]; c1 += wt * s_h[1][ty + t][tx]; c2 += wt * s_h[2][ty + t][tx];
+        }
+        if (px < W && py < H) {
+            const size_t idx = ((size_t)py * W + px) * 3 + c;
+            const float xv = x[idx], yv = y[idx];
+            const float d = xv - yv;
+            const float sign = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
+            v_image[idx] = c0 + 2.f * xv * c1 + yv * c2 + l1_weight * sign;
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void finish_loss_kernel(const float* __restrict__ sums, const float inv_count, const float lambda, float* __restrict__ loss) {
+    loss[0] = (1.f - lambda) * sums[0] * inv_count + lambda * (1.f - sums[1] * inv_count);
+}
+
+}  // namespace
+
+int64_t image_loss_workspace_bytes(int H, int W) { return ((int64_t)H * W * 3 * 3 + 2) * (int64_t)sizeof(float); }
+
+// workspace: image_loss_workspace_bytes(H, W); loss: one float on the device (may be null); v_image: [H][W][3].
+int launch_image_loss(const float* image, const float* target, int H, int W, float lambda_dssim, void* workspace,
+                      int64_t workspace_bytes, float* v_image, float* loss, cudaStream_t s) {
+    DSB_REQUIRE(H > 0 && W > 0, "image_loss: bad image size");
+    DSB_REQUIRE(image && target && v_image && workspace, "image_loss: null pointer");
+    DSB_REQUIRE(lambda_dssim >= 0.f && lambda_dssim <= 1.f, "image_loss: lambda must lie in [0, 1]");
+    const int64_t need = image_loss_workspace_bytes(H, W);
+    if (workspace_bytes < need) {
+        set_error("image_loss: workspace of %lld bytes is smaller than the %lld needed", (long long)workspace_bytes, (long long)need);
+        return DSB_ERR_WORKSPACE_TOO_SMALL;
+    }
+    Window win;
+    double sum = 0.0, raw[kWin];
+    for (int t = 0; t < kWin; ++t) { raw[t] = std::exp(-(double)((t - kHalf) * (t - kHalf)) / (2.0 * 1.5 * 1.5)); sum += raw[t]; }
+    for (int t = 0; t < kWin; ++t) win.w[t] = (float)(raw[t] / sum);
+    float* maps = reinterpret_cast<float*>(workspace);
+    float* sums = maps + (size_t)H * W * 3 * 3;
+    DSB_CUDA_CHECK(cudaMemsetAsync(sums, 0, 2 * sizeof(float), s));
+    const float count = (float)((double)H * W * 3);
+    const dim3 grid((W + kTileW - 1) / kTileW, (H + kTileH - 1) / kTileH), block(kTileW, kTileH);
+    ssim_moments_kernel<<<grid, block, 0, s>>>(image, target, H, W, win, -lambda_dssim / count, maps, sums);
+    DSB_LAUNCH_CHECK();
+    ssim_gradient_kernel<<<grid, block, 0, s>>>(image, target, maps, H, W, win, (1.f - lambda_dssim) / count, v_image);
+    DSB_LAUNCH_CHECK();
+    if (loss) {
+        finish_loss_kernel<<<1, 1, 0, s>>>(sums, 1.f / count, lambda_dssim, loss);
+        DSB_LAUNCH_CHECK();
+    }
+    return DSB_OK;
+}
+
+}  // namespace dsb

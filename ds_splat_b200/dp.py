@@ -289,6 +289,40 @@ class ViewRenderer:
             b0 = b1
 
 
+class ImageLoss:
+    """L = (1 - lambda) * mean|image - target| + lambda * (1 - mean SSIM(image, target)) and dL/dimage in two kernel
+    launches (``dsb_image_loss_backward``), with buffers that are reused from call to call.  ``__call__`` returns
+    (dL/dimage [H, W, 3], loss as a one-element device tensor -- reading it is the caller's synchronisation);
+    it has the ``(index, image)`` form ``ViewRenderer.render_views`` expects of its ``image_grads`` argument when
+    built with a list of target images."""
+
+    def __init__(self, targets=None, lambda_dssim: float = 0.2):
+        from . import _capi
+        self._capi, self.lib = _capi, _capi.lib()
+        self.targets, self.lam = targets, float(lambda_dssim)
+        self.buf = {}
+        self.losses = []
+
+    def gradient(self, image: torch.Tensor, target: torch.Tensor):
+        h, w = image.shape[0], image.shape[1]
+        key = (h, w, image.device)
+        if key not in self.buf:
+            nbytes = int(self.lib.dsb_image_loss_workspace_bytes(h, w))
+            self.buf[key] = (torch.empty(nbytes, dtype=torch.uint8, device=image.device), torch.empty_like(image))
+        ws, v_image = self.buf[key]
+        loss = torch.empty(1, dtype=torch.float32, device=image.device)
+        image, target = image.contiguous(), target.contiguous()
+        self._capi.check(self.lib.dsb_image_loss_backward(image.data_ptr(), target.data_ptr(), h, w, self.lam, ws.data_ptr(),
+                                                          ws.numel(), v_image.data_ptr(), loss.data_ptr(),
+                                                          self._capi.stream_ptr()))
+        return v_image, loss
+
+    def __call__(self, index: int, image: torch.Tensor):
+        v_image, loss = self.gradient(image, self.targets[index])
+        self.losses.append(loss)
+        return v_image
+
+
 class FlatAdam:
     """Adam over the five parameter tensors of a splat cloud, fed from a ``GradientBuffer``: one fused kernel launch
     per tensor (``dsb_adam_step``), each with its own learning rate as 3DGS training uses them, moments kept in one

@@ -297,6 +297,19 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
                      float tan_fovy, float scale_modifier, int32_t max_sh_degree, int32_t sh_degree,
                      float* output_image, void* stream);
 
+/* ---- the step before the operator's backward ----------------------------------------------------------
+ * Photometric loss of 3-D Gaussian Splatting training and its gradient with respect to the rendered image
+ * (no reference counterpart: users of the reference compose it from torch operations and autograd):
+ *     L = (1 - lambda) * mean|image - target| + lambda * (1 - mean SSIM(image, target))
+ * SSIM per channel, 11x11 Gaussian window (sigma 1.5), zero padding, C1 = 0.01^2, C2 = 0.03^2.
+ * image, target, v_image: [H][W][3] floats on the device; v_image receives dL/dimage, ready to be passed to
+ * dsb_backward / dsb_backward_blend; loss (may be NULL) receives L as one float on the device (no host
+ * synchronisation).  workspace: dsb_image_loss_workspace_bytes(H, W). */
+int64_t dsb_image_loss_workspace_bytes(int32_t image_height, int32_t image_width);
+int dsb_image_loss_backward(const float* image, const float* target, int32_t image_height, int32_t image_width,
+                            float lambda_dssim, void* workspace, int64_t workspace_bytes, float* v_image, float* loss,
+                            void* stream);
+
 /* ---- the step after the operator -------------------------------------------------------------------
  * Adam on one parameter tensor (no reference counterpart: users of the reference call torch.optim.Adam;
  * this is that update -- no weight decay, no amsgrad -- in one pass over memory):

@@ -414,3 +414,38 @@ def test_adam_step_matches_the_checker_and_a_training_step_lowers_the_loss():
                        grads)
         opt.step(grads)
     assert losses[-1] < 0.9 * losses[0] and all(np.isfinite(losses))
+
+
+def test_image_loss_gradient_matches_the_autograd_checker():
+    """dsb_image_loss_backward against oracle/loss_oracle.py (torch autograd in float64 on the CPU): ragged sizes that
+    exercise the zero padding and partial tiles, both terms of the loss, and its use as the loss of render_views."""
+    from ds_splat_b200.dp import ImageLoss
+    from oracle import loss_oracle as L
+    rng = np.random.default_rng(8)
+    for (h, w), lam in (((37, 53), 0.2), ((64, 48), 1.0), ((19, 16), 0.0), ((130, 97), 0.2)):
+        img = rng.uniform(0, 1, (h, w, 3)).astype(np.float32)
+        tgt = np.clip(img + rng.normal(0, 0.1, img.shape), 0, 1).astype(np.float32)
+        loss_o, grad_o = L.image_loss_and_grad(img, tgt, lam)
+        v, loss = ImageLoss(lambda_dssim=lam).gradient(torch.from_numpy(img).cuda(), torch.from_numpy(tgt).cuda())
+        torch.cuda.synchronize()
+        assert abs(float(loss) - loss_o) <= 1e-5 * max(abs(loss_o), 1e-3)
+        scale = float(np.abs(grad_o).max())
+        assert float(np.abs(v.cpu().numpy() - grad_o).max()) <= 2e-4 * scale, (h, w, lam)
+    # as the loss of a multi-view step: the gradients equal those of a step fed with the checker's dL/dimage
+    sc = scenes.headline(n=10_000, seed=99, W=240, H=144, focal=170.0, views=3)
+    t = scene_tensors(sc)
+    cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
+    targets = [torch.from_numpy(rng.uniform(0, 1, (144, 240, 3)).astype(np.float32)).cuda() for _ in cams]
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    loss_fn = ImageLoss(targets)
+    g_fused = GradientBuffer(sc.n, "cuda")
+    r.render_views(cams, loss_fn, g_fused)
+    def checker_grad(i, image):
+        _, g = L.image_loss_and_grad(image.cpu().numpy(), targets[i].cpu().numpy(), 0.2)
+        return torch.from_numpy(g).cuda()
+    g_check = GradientBuffer(sc.n, "cuda")
+    r.render_views(cams, checker_grad, g_check)
+    torch.cuda.synchronize()
+    assert len(loss_fn.losses) == 3 and all(0.0 < float(l) < 1.5 for l in loss_fn.losses)
+    assert _rel(g_fused.views["shs"].cpu().numpy(), g_check.views["shs"].cpu().numpy()) < 1e-3
+    assert _rel(g_fused.views["means3d"].cpu().numpy(), g_check.views["means3d"].cpu().numpy()) < 1e-3

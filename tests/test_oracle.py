@@ -173,3 +173,26 @@ def test_adam_checker_equals_torch_optim_adam():
     # moments: sums of terms of mixed sign, so the tolerance is relative to the largest entry
     np.testing.assert_allclose(m, st["exp_avg"].numpy(), rtol=1e-5, atol=1e-6 * float(np.abs(m).max()))
     np.testing.assert_allclose(v, st["exp_avg_sq"].numpy(), rtol=1e-5, atol=1e-6 * float(v.max()))
+
+
+def test_image_loss_checker_properties():
+    """The loss checker is autograd over plain torch operations; pin the formula through cases with known answers."""
+    torch = pytest.importorskip("torch")
+    from oracle import loss_oracle as L
+    rng = np.random.default_rng(3)
+    img = rng.uniform(0, 1, (23, 31, 3)).astype(np.float32)
+    loss_same, grad_same = L.image_loss_and_grad(img, img.copy())
+    assert abs(loss_same) < 1e-12                       # identical images: L1 = 0 and SSIM = 1 everywhere
+    assert np.abs(grad_same).max() < 1e-9               # ... and that is a stationary point (sign(0) = 0)
+    other = rng.uniform(0, 1, img.shape).astype(np.float32)
+    l_l1, _ = L.image_loss_and_grad(img, other, lambda_dssim=0.0)
+    assert abs(l_l1 - float(np.abs(img.astype(np.float64) - other).mean())) < 1e-9
+    l_full, g_full = L.image_loss_and_grad(img, other, lambda_dssim=0.2)
+    assert 0.0 < l_full < 1.2 and g_full.shape == img.shape and np.isfinite(g_full).all()
+    # SSIM of a constant image against another constant: only the luminance term is left, (2ab + C1) / (a^2 + b^2 + C1),
+    # in the interior, where the window does not reach the zero padding
+    a, b = 0.3, 0.6
+    xa, xb = torch.full((400, 400, 3), a), torch.full((400, 400, 3), b)
+    l_const = float(L.image_loss(xa, xb, lambda_dssim=1.0))
+    inner = (2 * a * b + 1e-4) / (a * a + b * b + 1e-4)
+    assert abs((1.0 - l_const) - inner) < 0.02          # the 5-pixel border changes the mean a little
