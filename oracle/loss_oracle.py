@@ -37,4 +37,4 @@ def image_loss_and_grad(image: np.ndarray, target: np.ndarray, lambda_dssim: flo
     y = torch.from_numpy(np.ascontiguousarray(target, dtype=np.float32)).double()
     loss = image_loss(x, y, lambda_dssim)
     loss.backward()
-    return float(loss), x.grad.numpy().astype(np.float32)
+    return float(loss.detach()), x.grad.numpy().astype(np.float32)
