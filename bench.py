@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"])
     ap.add_argument("--views-per-rank", type=int, default=8,
                     help="views each rank renders per step before the gradient all-reduce (64-view batch on 8 GPUs)")
+    ap.add_argument("--view-streams", type=int, default=2,
+                    help="streams the per-view stages of a step's views are dealt over (1 = one after the other)")
     ap.add_argument("--splats", type=int, default=0, help="override the workload's splat count (debugging)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -224,7 +226,7 @@ def main():
     v_images_host = [scene.image_grad(v, seed=7 + rank * vpr + j) for j, v in enumerate(view_ids)]
     view = scene.views[view_ids[0]]
     v_images = [t(v) for v in v_images_host]
-    renderer = ViewRenderer(**params, sh_degree=scene.sh_degree)
+    renderer = ViewRenderer(**params, sh_degree=scene.sh_degree, view_streams=args.view_streams)
     grads = GradientBuffer(scene.n, dev)
 
     def barrier():
@@ -441,7 +443,7 @@ def main():
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{scene.name}: {scene.n} splats SH-3, {W}x{H}, {vpr} view(s) per rank per step, fwd+bwd"
                                    + (", gradient all-reduce of 59 floats/splat" if world > 1 else ""),
-                       "pairs_K": int(K), "pairs_emitted": int(K_emitted), "tiles": view.num_tiles, "l2": "inputs larger than L2 (236 MB of parameters + "
+                       "pairs_K": int(K), "pairs_emitted": int(K_emitted), "tiles": view.num_tiles, "view_streams": int(min(args.view_streams, vpr)), "l2": "inputs larger than L2 (236 MB of parameters + "
                        "88 MB pair list per view; no explicit flush)", "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
             "clocks": clocks, "gpu_launches": int(launches), "stages_ms": stages_ms, "roofline": roofline,
             "roofline_fp32": roofline_fp32, "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda,

@@ -14,7 +14,8 @@ Layout choices:
     no per-tensor collectives.
   * ``ViewRenderer`` bypasses autograd and calls the fused C-ABI entry points with buffers that are
     allocated once and reused across views and steps (only the pair list grows with the largest K seen).
-  * A step renders its views one after the other (forward, then the backward blend, per view) but runs the
+  * A step deals its views over two streams (forward, then the backward blend, per view; one view's pair sort,
+    which waits on memory, runs beside another view's blend, which waits on instruction issue) but runs the
     per-splat part of the backward ONCE for up to eight views (``dsb_geometry_backward_views``): the splat
     parameters are read once and the 236 bytes of gradients per splat are written once per step instead of
     being read and rewritten for every view.  Each view of a batch keeps its own records, radii and
@@ -108,6 +109,20 @@ class _Slot:
         self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
 
 
+class _Lane:
+    """Buffers of the per-view stages (pair list and its sort, image, transmittance, last contributor) and the stream
+    they run on.  Lane 0 runs on the caller's stream; ``render_views`` adds lanes with streams of their own so that
+    one view's latency-bound pair sort runs beside another view's issue-bound blend."""
+
+    def __init__(self, stream=None):
+        self.stream = stream    # None: whatever stream is current
+        self.pairs = None
+        self.sort_ws = None
+        self.sort_bytes = 0
+        self.img = {}
+        self.done = None        # event after the lane's last launch of a batch
+
+
 class ViewRenderer:
     """Forward + backward of views of one splat cloud through the fused C-ABI calls, with reusable buffers.
 
@@ -115,7 +130,7 @@ class ViewRenderer:
     docstring) and is what ``data_parallel_step`` uses."""
 
     def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True,
-                 batch_views: int = 8, tight_tiles: bool = True):
+                 batch_views: int = 8, tight_tiles: bool = True, view_streams: int = 2):
         from . import _capi
         self._capi = _capi
         self.lib = _capi.lib()
@@ -138,24 +153,29 @@ class ViewRenderer:
         self.cov3d = torch.empty((n, 6), dtype=torch.float32, device=dev)
         self.plan_bytes = int(self.lib.dsb_plan_workspace_bytes_views(n, bv))
         self.plan_ws = torch.empty(self.plan_bytes, dtype=torch.uint8, device=dev)
-        self.pairs = None
-        self.sort_ws = None
-        self.sort_bytes = 0
-        self.img = {}
+        self.view_streams = max(1, int(view_streams))   # lanes render_views spreads a batch's views over
+        self.lanes = [_Lane()]
         self.last_k = 0
 
     # buffers of the view rendered last (kept as attributes for callers that inspect them)
     records = property(lambda self: self.cur.records)
     radii = property(lambda self: self.cur.radii)
     grad_acc = property(lambda self: self.cur.grad_acc)
+    pairs = property(lambda self: self.lanes[0].pairs)
 
-    def _image_buffers(self, h, w):
+    def _image_buffers(self, h, w, lane: int = 0):
+        img = self.lanes[lane].img
         key = (h, w)
-        if key not in self.img:
+        if key not in img:
             f32 = dict(dtype=torch.float32, device=self.dev)
-            self.img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
-                             torch.empty((h, w), dtype=torch.int32, device=self.dev))
-        return self.img[key]
+            img[key] = (torch.empty((h, w, 3), **f32), torch.empty((h, w), **f32),
+                        torch.empty((h, w), dtype=torch.int32, device=self.dev))
+        return img[key]
+
+    def _lane(self, i: int) -> _Lane:
+        while len(self.lanes) <= i:
+            self.lanes.append(_Lane(torch.cuda.Stream(device=self.dev)))
+        return self.lanes[i]
 
     def _ranges(self, slot: _Slot, h, w):
         key = (h, w)
@@ -182,25 +202,29 @@ class ViewRenderer:
                                     self.offset_rows[i]))
         return self.slots[j]
 
-    def _pair_buffers(self, k: int):
-        if self.pairs is None or self.pairs.shape[1] < k:
+    def _pair_buffers(self, k: int, lane: int = 0) -> _Lane:
+        ln = self.lanes[lane]
+        if ln.pairs is None or ln.pairs.shape[1] < k:
             cap = max(int(k * 1.25), 1024)
-            self.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
-            self.sort_bytes = int(self.lib.dsb_sort_workspace_bytes(cap))
-            self.sort_ws = torch.empty(self.sort_bytes, dtype=torch.uint8, device=self.dev)
+            if ln.pairs is not None and ln.stream is not None:
+                ln.stream.synchronize()   # the old buffers go back to the allocator of another stream
+            ln.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
+            ln.sort_bytes = int(self.lib.dsb_sort_workspace_bytes(cap))
+            ln.sort_ws = torch.empty(ln.sort_bytes, dtype=torch.uint8, device=self.dev)
+        return ln
 
-    def _render(self, slot: _Slot, cam: CameraTensors, k: int, layout_done: bool = False):
-        """Second half of a forward: pairs, tile layout (unless the batch made it already), tile sort, blend.
-        Returns the image buffer."""
+    def _render(self, slot: _Slot, cam: CameraTensors, k: int, layout_done: bool = False, lane: int = 0):
+        """Second half of a forward: pairs, tile layout (unless the batch made it already), tile sort, blend, on
+        the current stream with the buffers of ``lane``.  Returns the image buffer."""
         capi, lib = self._capi, self.lib
         c, _keep = slot.cam
-        image, final_t, final_idx = self._image_buffers(cam.H, cam.W)
+        image, final_t, final_idx = self._image_buffers(cam.H, cam.W, lane)
         ranges = self._ranges(slot, cam.H, cam.W)
-        self._pair_buffers(k)
+        ln = self._pair_buffers(k, lane)
         capi.check(lib.dsb_forward_render(
             C.byref(c), self.n, k, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
-            slot.offsets.data_ptr(), self.pairs[0].data_ptr(), self.pairs[1].data_ptr(),
-            self._marks(slot, cam.H, cam.W).data_ptr(), self.sort_ws.data_ptr(), self.sort_bytes, ranges.data_ptr(),
+            slot.offsets.data_ptr(), ln.pairs[0].data_ptr(), ln.pairs[1].data_ptr(),
+            self._marks(slot, cam.H, cam.W).data_ptr(), ln.sort_ws.data_ptr(), ln.sort_bytes, ranges.data_ptr(),
             image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None,
             slot.layout_hist.data_ptr() if layout_done else None, capi.stream_ptr()))
         self.last_k = k
@@ -269,16 +293,33 @@ class ViewRenderer:
                 C.byref(slots[0].cam[0]), nv, self.n, self.n, self.tiles_rows.data_ptr(), self.depth_rows[0].data_ptr(),
                 self.depth_rows[1].data_ptr(), self.offset_rows.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
                 ks, capi.stream_ptr()))
+            # The K-sized stages of the views, dealt over the lanes: lane 0 is the caller's stream, the others wait for
+            # the batch's plan, and the caller's stream waits for them before the per-splat backward.
+            main = torch.cuda.current_stream(self.dev)
+            nl = min(self.view_streams, nv)
+            lanes = [self._lane(i) for i in range(nl)]
+            if nl > 1:
+                planned = torch.cuda.Event()
+                planned.record(main)
+                for ln in lanes[1:]:
+                    ln.stream.wait_event(planned)
             for j, sl in enumerate(slots):
                 cam = cameras[b0 + j]
-                image = self._render(sl, cam, int(ks[j]), layout_done=True)
-                v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
-                _img, final_t, final_idx = self._image_buffers(cam.H, cam.W)
-                ranges = self._ranges(sl, cam.H, cam.W)
-                capi.check(lib.dsb_backward_blend(
-                    C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), self.pairs[0].data_ptr(), ranges.data_ptr(),
-                    final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
-                    self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
+                li = j % nl
+                with torch.cuda.stream(lanes[li].stream if li else main):
+                    image = self._render(sl, cam, int(ks[j]), layout_done=True, lane=li)
+                    v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
+                    _img, final_t, final_idx = self._image_buffers(cam.H, cam.W, li)
+                    ranges = self._ranges(sl, cam.H, cam.W)
+                    capi.check(lib.dsb_backward_blend(
+                        C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), lanes[li].pairs[0].data_ptr(),
+                        ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
+                        self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
+                    if li:
+                        lanes[li].done = torch.cuda.Event()
+                        lanes[li].done.record(lanes[li].stream)
+            for ln in lanes[1:]:
+                main.wait_event(ln.done)
             capi.check(lib.dsb_geometry_backward_views(
                 cams, nv, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
                 self.cov3d.data_ptr(), ptrs([sl.records for sl in slots]), ptrs([sl.radii for sl in slots]),
