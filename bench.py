@@ -208,8 +208,13 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the rasterizer has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    json_out = sys.stdout
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout for the one JSON line
+        # Libraries below write to file descriptor 1 (NCCL prints its version there): keep a private copy of it
+        # for the one JSON line and point descriptor 1 at stderr for everything else.
+        sys.stdout.flush()
+        json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     _capi.lib()  # fail loudly if the library is missing
 
@@ -449,7 +454,7 @@ def main():
             "roofline_fp32": roofline_fp32, "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda,
             "optimizer": optimizer,
             "pairs_evaluated": {"forward_per_pixel": pairs_fwd, "backward_per_pixel": pairs_bwd}}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=json_out, flush=True)
     if world > 1:
         dist.destroy_process_group()
 

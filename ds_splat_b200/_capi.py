@@ -28,7 +28,7 @@ EXPORTS = (
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
     "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_pairs_views",
     "dsb_backward_blend",
-    "dsb_geometry_backward_views",
+    "dsb_geometry_backward_views", "dsb_geometry_backward_views_stats",
     "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_adam_step",
     "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
@@ -98,6 +98,7 @@ def lib():
             "dsb_plan_pairs_views": [CAM, I32, I32, I64, P, P, P, P, P, I64, P, P],
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
+            "dsb_geometry_backward_views_stats": [P, I32, I32] + [P] * 15 + [I32, C.c_float, C.c_float, P, P, P, P],
             "dsb_forward_core": [P, P, P, P, P, I32, P, P, P, I32, I32, C.c_float, C.c_float, C.c_float, I32, I32, P, P],
             "dsb_image_loss_backward": [P, P, I32, I32, C.c_float, P, I64, P, P, P],
             "dsb_adam_step": [P, P, P, P, I64, C.c_double, C.c_double, C.c_double, C.c_double, I32, C.c_double, P],

@@ -378,11 +378,12 @@ int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, co
 #endif
 }
 
-int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
-                                const float* scales, const float* rotations, const float* cov3d,
-                                const float* const* records, const int32_t* const* radii, const float* const* grad_acc,
-                                float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
-                                float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
+namespace {
+int geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d, const float* scales,
+                            const float* rotations, const float* cov3d, const float* const* records,
+                            const int32_t* const* radii, const float* const* grad_acc, float* v_means3d, float* v_means2d,
+                            float* v_shs, float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
+                            float* v_cov3d, int32_t accumulate, const DensifyStats* stats, void* stream) {
     DSB_REQUIRE(cams && num_views >= 0 && num_views <= DSB_MAX_BATCH_VIEWS,
                 "geometry_backward_views: between 0 and %d views per call", DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
@@ -396,7 +397,34 @@ int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_
     StageScope scope(kStageGeometryBackward, s);
     return launch_geometry_backward_views(cps, num_views, n, means3d, scales, rotations, cov3d, records, radii, grad_acc,
                                           v_means3d, v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d,
-                                          accumulate, s);
+                                          accumulate, s, stats);
+}
+}  // namespace
+
+int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                                const float* scales, const float* rotations, const float* cov3d,
+                                const float* const* records, const int32_t* const* radii, const float* const* grad_acc,
+                                float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opacities,
+                                float* v_scales, float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream) {
+    return geometry_backward_views(cams, num_views, n, means3d, scales, rotations, cov3d, records, radii, grad_acc,
+                                   v_means3d, v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d,
+                                   accumulate, nullptr, stream);
+}
+
+int dsb_geometry_backward_views_stats(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                                      const float* scales, const float* rotations, const float* cov3d,
+                                      const float* const* records, const int32_t* const* radii,
+                                      const float* const* grad_acc, float* v_means3d, float* v_means2d, float* v_shs,
+                                      float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
+                                      float* v_cov3d, int32_t accumulate, float norm_scale_x, float norm_scale_y,
+                                      float* grad_norm_sum, float* visible_count, float* max_radius, void* stream) {
+    DSB_REQUIRE(grad_norm_sum && visible_count && max_radius, "geometry_backward_views_stats: null statistics array");
+    DensifyStats st;
+    st.grad_norm_sum = grad_norm_sum; st.visible_count = visible_count; st.max_radius = max_radius;
+    st.scale_x = norm_scale_x; st.scale_y = norm_scale_y;
+    return geometry_backward_views(cams, num_views, n, means3d, scales, rotations, cov3d, records, radii, grad_acc,
+                                   v_means3d, v_means2d, v_shs, v_colors, v_opacities, v_scales, v_rotations, v_cov3d,
+                                   accumulate, &st, stream);
 }
 
 // Torch-free forward with the argument list of the reference's rasterizer_forward_core_deepsense

@@ -171,11 +171,23 @@ int launch_geometry_backward(const CamParams& cp, int n, const float* means, con
                              float* v_means3d, float* v_means2d, float* v_shs, float* v_colors, float* v_opac,
                              float* v_scales, float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
 
+// Per-splat statistics a training loop keeps between two densification rounds; the per-splat backward adds a
+// step's views to them when the pointers are set.  For every view in which splat i has radius > 0:
+//   grad_norm_sum[i] += sqrt((scale_x * v_x)^2 + (scale_y * v_y)^2)   (v_x, v_y: that view's pixel-mean gradient)
+//   visible_count[i] += 1,   max_radius[i] = max(max_radius[i], radius)
+struct DensifyStats {
+    float* grad_norm_sum = nullptr;
+    float* visible_count = nullptr;
+    float* max_radius = nullptr;
+    float scale_x = 1.f, scale_y = 1.f;
+};
+
 int launch_geometry_backward_views(const CamParams* cps, int count, int n, const float* means, const float* scales,
                                    const float* rots, const float* cov3d, const float* const* records,
                                    const int32_t* const* radii, const float* const* grad_acc, float* v_means3d,
                                    float* v_means2d, float* v_shs, float* v_colors, float* v_opac, float* v_scales,
-                                   float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s);
+                                   float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s,
+                                   const DensifyStats* stats = nullptr);
 
 int64_t image_loss_workspace_bytes(int H, int W);
 int launch_image_loss(const float* image, const float* target, int H, int W, float lambda_dssim, void* workspace,

@@ -53,7 +53,7 @@ geometry_backward_kernel(const GeoViews gv, const int n, const float* __restrict
                          const float* __restrict__ rots, const float* __restrict__ cov3d, float* __restrict__ v_means3d,
                          float* __restrict__ v_means2d, float* __restrict__ v_shs, float* __restrict__ v_colors,
                          float* __restrict__ v_opac, float* __restrict__ v_scales, float* __restrict__ v_rots,
-                         float* __restrict__ v_cov3d, const int accumulate) {
+                         float* __restrict__ v_cov3d, const int accumulate, const DensifyStats st) {
     __shared__ float s_sh[kWarps][32 * kShStride];
     __shared__ float s_cam[DSB_MAX_BATCH_VIEWS][16];  // per view: view rows 0..2 (12) + camera centre (3)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -83,6 +83,7 @@ geometry_backward_kernel(const GeoViews gv, const int n, const float* __restrict
     float vc[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float m2x = 0.f, m2y = 0.f, col_r = 0.f, col_g = 0.f, col_b = 0.f, vop = 0.f;
     bool any_geometry = false;
+    float st_norm = 0.f, st_seen = 0.f, st_radius = 0.f;
 
     for (int view = 0; view < gv.count; ++view) {
         const float* V = s_cam[view];
@@ -150,6 +151,12 @@ geometry_backward_kernel(const GeoViews gv, const int n, const float* __restrict
         // ---- geometry of this view
         if (live && radius > 0) {
             any_geometry = true;
+            {
+                const float sx = st.scale_x * g0.x, sy = st.scale_y * g0.y;
+                st_norm += sqrtf(sx * sx + sy * sy);
+                st_seen += 1.f;
+                st_radius = fmaxf(st_radius, (float)radius);
+            }
             const float fx = gv.cam[view].fx_bwd, fy = gv.cam[view].fy_bwd;
             const float tx = V[0] * mx + V[1] * my + V[2] * mz + V[3];
             const float ty = V[4] * mx + V[5] * my + V[6] * mz + V[7];
@@ -252,6 +259,11 @@ geometry_backward_kernel(const GeoViews gv, const int n, const float* __restrict
         vq3 = 2.f * (x * (vR[2][0] + vR[0][2]) + y * (vR[2][1] + vR[1][2]) - 2.f * z * (vR[0][0] + vR[1][1]) + w * (vR[1][0] - vR[0][1]));
     }
 
+    if (live && st.grad_norm_sum && st_seen > 0.f) {   // always added: the caller clears them when it densifies
+        st.grad_norm_sum[i] += st_norm;
+        st.visible_count[i] += st_seen;
+        st.max_radius[i] = fmaxf(st.max_radius[i], st_radius);
+    }
     if (live) {
         if (v_means3d) { float* p = v_means3d + (size_t)i * 3; put(p, vm0, accumulate); put(p + 1, vm1, accumulate); put(p + 2, vm2, accumulate); }
         if (v_means2d) { float* p = v_means2d + (size_t)i * 3; put(p, m2x, accumulate); put(p + 1, m2y, accumulate); put(p + 2, 0.f, accumulate); }
@@ -299,8 +311,15 @@ int launch_geometry_backward_views(const CamParams* cps, int count, int n, const
                                    const float* rots, const float* cov3d, const float* const* records,
                                    const int32_t* const* radii, const float* const* grad_acc, float* v_means3d,
                                    float* v_means2d, float* v_shs, float* v_colors, float* v_opac, float* v_scales,
-                                   float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s) {
+                                   float* v_rots, float* v_cov3d, int accumulate, cudaStream_t s,
+                                   const DensifyStats* stats) {
     if (n == 0 || count == 0) return DSB_OK;
+    DensifyStats st;
+    if (stats) {
+        st = *stats;
+        DSB_REQUIRE(st.grad_norm_sum && st.visible_count && st.max_radius,
+                    "geometry_backward: the three statistics arrays come together");
+    }
     DSB_REQUIRE(count > 0 && count <= DSB_MAX_BATCH_VIEWS, "geometry_backward: %d views in one call (at most %d)", count,
                 DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(means && cov3d && records && radii && grad_acc, "geometry_backward: null required pointer");
@@ -321,7 +340,7 @@ int launch_geometry_backward_views(const CamParams* cps, int count, int n, const
     }
     geometry_backward_kernel<<<(n + kThreads - 1) / kThreads, kThreads, 0, s>>>(gv, n, means, scales, rots, cov3d, v_means3d,
                                                                               v_means2d, v_shs, v_colors, v_opac, v_scales,
-                                                                              v_rots, v_cov3d, accumulate);
+                                                                              v_rots, v_cov3d, accumulate, st);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

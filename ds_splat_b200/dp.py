@@ -109,6 +109,46 @@ class _Slot:
         self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
 
 
+class DensifyStats:
+    """The per-splat statistics a 3-D Gaussian Splatting training loop consults when it densifies, kept by the
+    per-splat backward itself (``dsb_geometry_backward_views_stats``): for every view in which a splat is visible
+    (radius > 0) ``grad_norm_sum`` grows by the norm of that view's pixel-mean gradient, ``visible_count`` by one,
+    and ``max_radius`` becomes the larger of itself and the view's radius.  ``ndc_units`` scales the gradient by
+    (W/2, H/2) first, the units of loops written for the original 3DGS rasterizer; otherwise pixel units, as the
+    reference's v_means2d.  The caller clears them with ``zero_()`` when it has densified."""
+
+    def __init__(self, n: int, device, ndc_units: bool = False):
+        self.flat = torch.zeros((3, n), dtype=torch.float32, device=device)
+        self.grad_norm_sum, self.visible_count, self.max_radius = self.flat[0], self.flat[1], self.flat[2]
+        self.ndc_units = ndc_units
+
+    def zero_(self):
+        self.flat.zero_()
+
+    def add_view(self, v_means2d: torch.Tensor, radii: torch.Tensor, height: int, width: int) -> None:
+        """The same update from one view's v_means2d and radii as tensors (what a loop around the single-view
+        operator has in hand)."""
+        sx, sy = (0.5 * width, 0.5 * height) if self.ndc_units else (1.0, 1.0)
+        seen = radii > 0
+        norm = torch.sqrt((sx * v_means2d[:, 0]) ** 2 + (sy * v_means2d[:, 1]) ** 2)
+        self.grad_norm_sum += torch.where(seen, norm, torch.zeros_like(norm))
+        self.visible_count += seen.to(torch.float32)
+        torch.maximum(self.max_radius, torch.where(seen, radii.to(torch.float32), self.max_radius), out=self.max_radius)
+
+    def allreduce(self, group=None) -> None:
+        """Combines the ranks' statistics (sums of the first two, maximum of the third).  Called once, just before
+        the ranks densify: each rank's arrays only cover the views it rendered itself."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.flat[:2], op=dist.ReduceOp.SUM, group=group)
+            dist.all_reduce(self.flat[2], op=dist.ReduceOp.MAX, group=group)
+
+    def mean_grad_norm(self) -> torch.Tensor:
+        """grad_norm_sum / visible_count, zero where a splat was never visible."""
+        return torch.where(self.visible_count > 0, self.grad_norm_sum / self.visible_count.clamp(min=1),
+                           torch.zeros_like(self.grad_norm_sum))
+
+
 class _Lane:
     """Buffers of the per-view stages (pair list and its sort, image, transmittance, last contributor) and the stream
     they run on.  Lane 0 runs on the caller's stream; ``render_views`` adds lanes with streams of their own so that
@@ -261,13 +301,14 @@ class ViewRenderer:
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 
-    def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False):
+    def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False,
+                     stats: Optional[DensifyStats] = None):
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
         contents when ``accumulate``).  ``image_grads`` is a sequence of dL/dimage tensors or a callable
         ``(index, image) -> dL/dimage``.  Views are taken in batches of up to ``batch_views`` of one image size:
         one preprocess launch (with the tile layout of every view) and one plan (depth sorts, offset scans, a
         single read-back of the pair counts) for the batch, then per view the rest of the forward and the backward blend, then one per-splat backward for
-        the batch."""
+        the batch, which also updates ``stats`` (a ``DensifyStats``) when given."""
         capi, lib, p = self._capi, self.lib, self.p
         g = grads.views
         b0, first = 0, True
@@ -320,12 +361,19 @@ class ViewRenderer:
                         lanes[li].done.record(lanes[li].stream)
             for ln in lanes[1:]:
                 main.wait_event(ln.done)
-            capi.check(lib.dsb_geometry_backward_views(
+            geo_args = (
                 cams, nv, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
                 self.cov3d.data_ptr(), ptrs([sl.records for sl in slots]), ptrs([sl.radii for sl in slots]),
                 ptrs([sl.grad_acc for sl in slots]), g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None,
                 g["opacities"].data_ptr(), g["scales"].data_ptr(), g["rotations"].data_ptr(), None,
-                1 if (accumulate or not first) else 0, capi.stream_ptr()))
+                1 if (accumulate or not first) else 0)
+            if stats is None:
+                capi.check(lib.dsb_geometry_backward_views(*geo_args, capi.stream_ptr()))
+            else:
+                sx, sy = (0.5 * size[1], 0.5 * size[0]) if stats.ndc_units else (1.0, 1.0)
+                capi.check(lib.dsb_geometry_backward_views_stats(
+                    *geo_args, sx, sy, stats.grad_norm_sum.data_ptr(), stats.visible_count.data_ptr(),
+                    stats.max_radius.data_ptr(), capi.stream_ptr()))
             first = False
             b0 = b1
 
@@ -393,12 +441,12 @@ class FlatAdam:
 
 
 def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads,
-                       grads: GradientBuffer, group=None) -> None:
+                       grads: GradientBuffer, group=None, stats: Optional[DensifyStats] = None) -> None:
     """One step of the multi-view batch on this rank: forward + backward of each local camera (gradients
     summed into ``grads``), then the all-reduce.  ``cameras`` is this rank's shard; ``image_grads`` is the
     matching sequence of dL/dimage tensors, or a callable ``(index, image) -> dL/dimage`` (the loss)."""
     if len(cameras) == 0:
         grads.zero_()  # a rank without views still takes part in the collective
     else:
-        renderer.render_views(cameras, image_grads, grads, accumulate=False)
+        renderer.render_views(cameras, image_grads, grads, accumulate=False, stats=stats)
     allreduce_gradients(grads, group)

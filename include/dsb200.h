@@ -283,6 +283,25 @@ int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_
                                 const float* const* grad_acc, float* v_means3d, float* v_means2d, float* v_shs,
                                 float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
                                 float* v_cov3d, int32_t accumulate, void* stream);
+/* The same call, which also keeps the per-splat statistics a 3-D Gaussian Splatting training loop consults when it
+ * densifies (clone / split / prune), so that the loop does not read radii and v_means2d again after every view.
+ * For every view of the call in which splat i has radius > 0:
+ *     grad_norm_sum[i] += sqrt((norm_scale_x * v_x)^2 + (norm_scale_y * v_y)^2)
+ *     visible_count[i] += 1
+ *     max_radius[i]     = max(max_radius[i], radius)
+ * with (v_x, v_y) THAT view's gradient of the pixel mean (the first two columns of the v_means2d a single-view
+ * backward returns; the reference returns it in pixel units, cpp/rasterizer_torch.cu:287-315).
+ * norm_scale = (1, 1) keeps pixel units; (W/2, H/2) gives the normalised-device-coordinate units of training
+ * loops written for the original 3DGS rasterizer.  The three arrays are float[n], are always added to (never
+ * overwritten, whatever `accumulate` says) and are cleared by the caller when it densifies.  Not part of the
+ * reference. */
+int dsb_geometry_backward_views_stats(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
+                                      const float* scales, const float* rotations, const float* cov3d,
+                                      const float* const* records, const int32_t* const* radii,
+                                      const float* const* grad_acc, float* v_means3d, float* v_means2d, float* v_shs,
+                                      float* v_colors, float* v_opacities, float* v_scales, float* v_rotations,
+                                      float* v_cov3d, int32_t accumulate, float norm_scale_x, float norm_scale_y,
+                                      float* grad_norm_sum, float* visible_count, float* max_radius, void* stream);
 
 /* ---- torch-free forward ---------------------------------------------------------------------------
  * Same argument list as the reference's C++ entry rasterizer_forward_core_deepsense

@@ -36,9 +36,11 @@ class OracleRenderer:
         self.fwd = O.forward(self.cam, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations)
         return self.fwd["image"]
 
-    def backward(self, v_image, grads, accumulate=True):
+    def backward(self, v_image, grads, accumulate=True, stats=None):
         sc = self.sc
         b = self.O.backward(self.cam, self.fwd, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image.numpy())
+        if stats is not None:
+            stats.add_view(torch.from_numpy(b["v_means2d"]), torch.from_numpy(self.fwd["pre"]["radii"]), self.cam.H, self.cam.W)
         pairs = (("means3d", "v_means3d"), ("shs", "v_shs"), ("opacities", "v_opacities"), ("scales", "v_scales"),
                  ("rotations", "v_rotations"))
         for dst, src in pairs:
@@ -48,11 +50,11 @@ class OracleRenderer:
             else:
                 grads.views[dst].copy_(g)
 
-    def render_views(self, cameras, image_grads, grads, accumulate=False):
+    def render_views(self, cameras, image_grads, grads, accumulate=False, stats=None):
         for idx, view in enumerate(cameras):
             image = self.forward(view)
             v_image = image_grads(idx, image) if callable(image_grads) else image_grads[idx]
-            self.backward(v_image, grads, accumulate=accumulate or idx > 0)
+            self.backward(v_image, grads, accumulate=accumulate or idx > 0, stats=stats)
 
 
 def _scene():
@@ -66,10 +68,13 @@ def _worker(rank, world, port, out):
     mine = dp.shard_views(len(sc.views), rank, world)
     grads = dp.GradientBuffer(sc.n, "cpu")
     grads.flat.fill_(123.0)  # stale contents must not leak into the result
+    stats = dp.DensifyStats(sc.n, "cpu", ndc_units=True)
     dp.data_parallel_step(OracleRenderer(sc), [sc.views[i] for i in mine],
-                          [torch.from_numpy(sc.image_grad(i)) for i in mine], grads)
+                          [torch.from_numpy(sc.image_grad(i)) for i in mine], grads, stats=stats)
+    stats.allreduce()   # what the ranks do once before they densify
     if rank == 0:
         np.save(out, grads.flat.numpy())
+        np.save(out + ".stats.npy", stats.flat.numpy())
     dist.destroy_process_group()
 
 
@@ -97,9 +102,16 @@ def test_two_rank_step_equals_serial_sum(tmp_path):
     got = np.load(out)
     sc = _scene()
     serial = dp.GradientBuffer(sc.n, "cpu")
+    serial_stats = dp.DensifyStats(sc.n, "cpu", ndc_units=True)
     r = OracleRenderer(sc)
     for i, v in enumerate(sc.views):
         r.forward(v)
-        r.backward(torch.from_numpy(sc.image_grad(i)), serial, accumulate=i > 0)
+        r.backward(torch.from_numpy(sc.image_grad(i)), serial, accumulate=i > 0, stats=serial_stats)
     np.testing.assert_allclose(got, serial.flat.numpy(), rtol=1e-5, atol=1e-9)
     assert np.abs(got).max() > 0
+    # densification statistics: sums and visibility counts add over ranks, the largest radius is a maximum
+    got_stats = np.load(out + ".stats.npy")
+    np.testing.assert_allclose(got_stats, serial_stats.flat.numpy(), rtol=1e-5, atol=1e-9)
+    assert got_stats[1].max() >= 2 and got_stats[2].max() > 0 and got_stats[0].max() > 0
+    mean = serial_stats.mean_grad_norm().numpy()
+    assert np.all(mean[got_stats[1] == 0] == 0) and np.isfinite(mean).all()

@@ -10,7 +10,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 from ds_splat_b200 import GaussianRasterizer, _capi, scenes  # noqa: E402
-from ds_splat_b200.dp import CameraTensors, GradientBuffer, ViewRenderer, data_parallel_step  # noqa: E402
+from ds_splat_b200.dp import CameraTensors, DensifyStats, GradientBuffer, ViewRenderer, data_parallel_step  # noqa: E402
 from oracle import oracle as O  # noqa: E402
 
 
@@ -244,6 +244,35 @@ def test_batched_views_equal_one_view_at_a_time():
     single.forward(cams[1]); single.backward(vimgs[1], g_s, accumulate=True)
     torch.cuda.synchronize()
     assert _rel(g_b.views["shs"].cpu().numpy(), g_s.views["shs"].cpu().numpy()) < 1e-4
+
+
+@pytest.mark.parametrize("ndc_units", [False, True])
+def test_densification_statistics_equal_what_a_loop_around_the_operator_collects(ndc_units):
+    """The per-splat backward of a step keeps gradient-norm sums, visibility counts and largest radii; a training
+    loop around the single-view operator builds the same numbers from v_means2d and radii of every view."""
+    sc = scenes.headline(n=12_000, seed=97, W=256, H=160, focal=180.0, views=10)
+    t = scene_tensors(sc)
+    cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
+    vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
+    stats = DensifyStats(sc.n, "cuda", ndc_units=ndc_units)
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
+    g = GradientBuffer(sc.n, "cuda")
+    r.render_views(cams, vimgs, g, accumulate=False, stats=stats)      # two batches: 8 + 2 views
+    r.render_views(cams[:3], vimgs[:3], g, accumulate=False, stats=stats)  # statistics keep adding across steps
+    want = DensifyStats(sc.n, "cuda", ndc_units=ndc_units)
+    for i in list(range(10)) + [0, 1, 2]:
+        p, m2, image, radii = _run_operator(sc, sc.views[i])
+        image.backward(vimgs[i])
+        want.add_view(m2.grad, radii, sc.views[i].H, sc.views[i].W)
+    torch.cuda.synchronize()
+    assert torch.equal(stats.visible_count, want.visible_count) and float(stats.visible_count.max()) == 13.0
+    assert torch.equal(stats.max_radius, want.max_radius) and float(stats.max_radius.max()) > 0
+    scale = float(want.grad_norm_sum.max())
+    assert scale > 0 and float((stats.grad_norm_sum - want.grad_norm_sum).abs().max()) <= 1e-4 * scale
+    never = stats.visible_count == 0
+    assert bool(never.any()) and float(stats.grad_norm_sum[never].abs().max()) == 0.0
+    stats.zero_()
+    assert float(stats.flat.abs().max()) == 0.0
 
 
 def test_preprocess_of_several_views_is_bit_identical_to_one_at_a_time():
