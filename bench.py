@@ -276,12 +276,17 @@ def main():
     torch.cuda.empty_cache()
 
     # ---- per-stage timing of the same steps (events recorded by the library around each stage) ---------
+    # The stages are timed with the views one after the other on one stream: with two views in flight the events
+    # around one view's stage also cover the other view's kernels.
+    lanes_used = renderer.view_streams
+    renderer.view_streams = 1
     _capi.stage_timing(True)
     for _ in range(min(args.steps, 40)):
         step()
     torch.cuda.synchronize()
     stage_raw = _capi.read_stage_timings()
     _capi.stage_timing(False)
+    renderer.view_streams = lanes_used
     # per view: the per-splat backward runs once for all views of a step, every other stage once per view
     timed_views = min(args.steps, 40) * vpr
     stages_ms = {name: round(ms / timed_views, 5) for name, (ms, calls) in stage_raw.items() if calls}

@@ -26,40 +26,60 @@ namespace dsb {
 namespace {
 
 constexpr int kWin = 11, kHalf = 5;
-constexpr int kTileW = 16, kTileH = 16;
-constexpr int kPadW = kTileW + 2 * kHalf, kPadH = kTileH + 2 * kHalf;   // 26 x 26 with the halo
+// A block of 256 threads produces a 32 x 32 pixel tile of one channel at a time.  Both passes of the separable window
+// slide over registers: a thread of the horizontal pass turns 14 neighbouring values of a row into 4 neighbouring
+// outputs, a thread of the vertical pass 14 values of a column into 4 outputs, so a value is read from shared memory
+// 1.2 times per tap instead of once per tap and output.  Row strides are odd, which keeps the row-major work items of
+// the horizontal pass (consecutive lanes = consecutive rows) and the column-major threads of the vertical pass free of
+// bank conflicts.
+constexpr int kPatch = 32, kLossThreads = 256, kOut = 4;
+constexpr int kPad = kPatch + 2 * kHalf;          // 42 rows / columns with the halo
+constexpr int kInStride = kPad + 1;              // 43
+constexpr int kHStride = kPatch + 1;              // 33
+constexpr int kGroups = kPatch / kOut;            // 8 four-column groups per row
+constexpr int kSpan = kOut + kWin - 1;           // 14 inputs for 4 outputs
+static_assert(kLossThreads == kPatch * (kPatch / kOut), "the vertical pass gives every thread one column and four rows");
 
 struct Window { float w[kWin]; };
+
+// acc[j] += w[k - j] * v for the outputs j that input k of the span reaches (k is a compile-time constant after unrolling)
+__device__ __forceinline__ void slide(float (&acc)[kOut], const float v, const int k, const Window& win) {
+#pragma unroll
+    for (int j = 0; j < kOut; ++j) {
+        const int t = k - j;
+        if (t >= 0 && t < kWin) acc[j] = fmaf(win.w[t], v, acc[j]);
+    }
+}
 
 __device__ __forceinline__ float block_sum(float v, float* s_red) {
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    const int tid = threadIdx.y * kTileW + threadIdx.x;
+    const int tid = threadIdx.x;
     if ((tid & 31) == 0) s_red[tid >> 5] = v;
     __syncthreads();
     float total = 0.f;
     if (tid == 0)
-        for (int k = 0; k < kTileW * kTileH / 32; ++k) total += s_red[k];
+        for (int k = 0; k < kLossThreads / 32; ++k) total += s_red[k];
     __syncthreads();
     return total;   // valid in thread 0
 }
 
 // maps: [3][H][W][3] (g dS/dm1, g dS/de11, g dS/de12); sums: [0] += sum |x - y|, [1] += sum SSIM
-__global__ void __launch_bounds__(kTileW * kTileH)
+__global__ void __launch_bounds__(kLossThreads)
 ssim_moments_kernel(const float* __restrict__ x, const float* __restrict__ y, const int H, const int W, const Window win,
                     const float g, float* __restrict__ maps, float* __restrict__ sums) {
-    __shared__ float s_x[kPadH][kPadW], s_y[kPadH][kPadW];
-    __shared__ float s_h[5][kPadH][kTileW];   // horizontally filtered x, y, x^2, y^2, xy
-    __shared__ float s_red[kTileW * kTileH / 32];
-    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kTileW + tx;
-    const int x0 = blockIdx.x * kTileW, y0 = blockIdx.y * kTileH;
-    const int px = x0 + tx, py = y0 + ty;
-    const bool inside = px < W && py < H;
+    __shared__ float s_x[kPad][kInStride], s_y[kPad][kInStride];
+    __shared__ float s_h[5][kPad][kHStride];   // horizontally filtered x, y, x^2, y^2, xy
+    __shared__ float s_red[kLossThreads / 32];
+    const int tid = threadIdx.x;
+    const int x0 = blockIdx.x * kPatch, y0 = blockIdx.y * kPatch;
+    const int tx = tid % kPatch, r0 = (tid / kPatch) * kOut;   // the vertical pass: column tx, rows r0 .. r0 + 3
+    const int px = x0 + tx;
     const size_t plane = (size_t)H * W * 3;
     float l1_sum = 0.f, ssim_sum = 0.f;
     for (int c = 0; c < 3; ++c) {
-        for (int k = tid; k < kPadH * kPadW; k += kTileW * kTileH) {
-            const int ry = k / kPadW, rx = k - ry * kPadW;
+        for (int k = tid; k < kPad * kPad; k += kLossThreads) {
+            const int ry = k / kPad, rx = k - ry * kPad;
             const int gy = y0 + ry - kHalf, gx = x0 + rx - kHalf;
             const bool ok = gy >= 0 && gy < H && gx >= 0 && gx < W;   // zero padding outside the image
             const size_t idx = ((size_t)gy * W + gx) * 3 + c;
@@ -67,37 +87,47 @@ ssim_moments_kernel(const float* __restrict__ x, const float* __restrict__ y, co
             s_y[ry][rx] = ok ? y[idx] : 0.f;
         }
         __syncthreads();
-        for (int k = tid; k < kPadH * kTileW; k += kTileW * kTileH) {
-            const int ry = k / kTileW, cx = k - ry * kTileW;
-            float a = 0.f, b = 0.f, aa = 0.f, bb = 0.f, ab = 0.f;
+        for (int item = tid; item < kPad * kGroups; item += kLossThreads) {
+            const int ry = item % kPad, cx = (item / kPad) * kOut;
+            float a[kOut] = {}, b[kOut] = {}, aa[kOut] = {}, bb[kOut] = {}, ab[kOut] = {};
 #pragma unroll
-            for (int t = 0; t < kWin; ++t) {
-                const float xv = s_x[ry][cx + t], yv = s_y[ry][cx + t], wt = win.w[t];
-                a += wt * xv; b += wt * yv; aa += wt * xv * xv; bb += wt * yv * yv; ab += wt * xv * yv;
+            for (int k = 0; k < kSpan; ++k) {
+                const float xv = s_x[ry][cx + k], yv = s_y[ry][cx + k];
+                slide(a, xv, k, win); slide(b, yv, k, win);
+                slide(aa, xv * xv, k, win); slide(bb, yv * yv, k, win); slide(ab, xv * yv, k, win);
             }
-            s_h[0][ry][cx] = a; s_h[1][ry][cx] = b; s_h[2][ry][cx] = aa; s_h[3][ry][cx] = bb; s_h[4][ry][cx] = ab;
+#pragma unroll
+            for (int j = 0; j < kOut; ++j) {
+                s_h[0][ry][cx + j] = a[j]; s_h[1][ry][cx + j] = b[j]; s_h[2][ry][cx + j] = aa[j];
+                s_h[3][ry][cx + j] = bb[j]; s_h[4][ry][cx + j] = ab[j];
+            }
         }
         __syncthreads();
-        float m1 = 0.f, m2 = 0.f, e11 = 0.f, e22 = 0.f, e12 = 0.f;
+        float m1[kOut] = {}, m2[kOut] = {}, e11[kOut] = {}, e22[kOut] = {}, e12[kOut] = {};
 #pragma unroll
-        for (int t = 0; t < kWin; ++t) {
-            const float wt = win.w[t];
-            m1 += wt * s_h[0][ty + t][tx]; m2 += wt * s_h[1][ty + t][tx]; e11 += wt * s_h[2][ty + t][tx];
-            e22 += wt * s_h[3][ty + t][tx]; e12 += wt * s_h[4][ty + t][tx];
+        for (int k = 0; k < kSpan; ++k) {
+            slide(m1, s_h[0][r0 + k][tx], k, win); slide(m2, s_h[1][r0 + k][tx], k, win);
+            slide(e11, s_h[2][r0 + k][tx], k, win); slide(e22, s_h[3][r0 + k][tx], k, win);
+            slide(e12, s_h[4][r0 + k][tx], k, win);
         }
-        if (inside) {
-            const float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
-            const float s11 = e11 - m1 * m1, s22 = e22 - m2 * m2, s12 = e12 - m1 * m2;
-            const float A1 = 2.f * m1 * m2 + C1, A2 = 2.f * s12 + C2, B1 = m1 * m1 + m2 * m2 + C1, B2 = s11 + s22 + C2;
-            const float inv = 1.f / (B1 * B2);
-            const float S = A1 * A2 * inv;
-            const float dS_dm1 = (2.f * m2 * (A2 - A1) * B1 * B2 - A1 * A2 * 2.f * m1 * (B2 - B1)) * inv * inv;
-            const float dS_de11 = -A1 * A2 * inv / B2;
-            const float dS_de12 = 2.f * A1 * inv;
-            const size_t idx = ((size_t)py * W + px) * 3 + c;
-            maps[idx] = g * dS_dm1; maps[plane + idx] = g * dS_de11; maps[2 * plane + idx] = g * dS_de12;
-            ssim_sum += S;
-            l1_sum += fabsf(s_x[ty + kHalf][tx + kHalf] - s_y[ty + kHalf][tx + kHalf]);
+#pragma unroll
+        for (int j = 0; j < kOut; ++j) {
+            const int py = y0 + r0 + j;
+            if (px < W && py < H) {
+                const float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
+                const float s11 = e11[j] - m1[j] * m1[j], s22 = e22[j] - m2[j] * m2[j], s12 = e12[j] - m1[j] * m2[j];
+                const float A1 = 2.f * m1[j] * m2[j] + C1, A2 = 2.f * s12 + C2;
+                const float B1 = m1[j] * m1[j] + m2[j] * m2[j] + C1, B2 = s11 + s22 + C2;
+                const float inv = 1.f / (B1 * B2);
+                const float S = A1 * A2 * inv;
+                const float dS_dm1 = (2.f * m2[j] * (A2 - A1) * B1 * B2 - A1 * A2 * 2.f * m1[j] * (B2 - B1)) * inv * inv;
+                const float dS_de11 = -A1 * A2 * inv / B2;
+                const float dS_de12 = 2.f * A1 * inv;
+                const size_t idx = ((size_t)py * W + px) * 3 + c;
+                maps[idx] = g * dS_dm1; maps[plane + idx] = g * dS_de11; maps[2 * plane + idx] = g * dS_de12;
+                ssim_sum += S;
+                l1_sum += fabsf(s_x[r0 + j + kHalf][tx + kHalf] - s_y[r0 + j + kHalf][tx + kHalf]);
+            }
         }
         __syncthreads();   // the tiles are reloaded for the next channel
     }
@@ -106,18 +136,19 @@ ssim_moments_kernel(const float* __restrict__ x, const float* __restrict__ y, co
     if (tid == 0) { atomicAdd(sums, l1_total); atomicAdd(sums + 1, ssim_total); }
 }
 
-__global__ void __launch_bounds__(kTileW * kTileH)
+__global__ void __launch_bounds__(kLossThreads)
 ssim_gradient_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ maps, const int H,
                      const int W, const Window win, const float l1_weight, float* __restrict__ v_image) {
-    __shared__ float s_m[3][kPadH][kPadW];
-    __shared__ float s_h[3][kPadH][kTileW];
-    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kTileW + tx;
-    const int x0 = blockIdx.x * kTileW, y0 = blockIdx.y * kTileH;
-    const int px = x0 + tx, py = y0 + ty;
+    __shared__ float s_m[3][kPad][kInStride];
+    __shared__ float s_h[3][kPad][kHStride];
+    const int tid = threadIdx.x;
+    const int x0 = blockIdx.x * kPatch, y0 = blockIdx.y * kPatch;
+    const int tx = tid % kPatch, r0 = (tid / kPatch) * kOut;
+    const int px = x0 + tx;
     const size_t plane = (size_t)H * W * 3;
     for (int c = 0; c < 3; ++c) {
-        for (int k = tid; k < kPadH * kPadW; k += kTileW * kTileH) {
-            const int ry = k / kPadW, rx = k - ry * kPadW;
+        for (int k = tid; k < kPad * kPad; k += kLossThreads) {
+            const int ry = k / kPad, rx = k - ry * kPad;
             const int gy = y0 + ry - kHalf, gx = x0 + rx - kHalf;
             const bool ok = gy >= 0 && gy < H && gx >= 0 && gx < W;
             const size_t idx = ((size_t)gy * W + gx) * 3 + c;
@@ -125,29 +156,34 @@ ssim_gradient_kernel(const float* __restrict__ x, const float* __restrict__ y, c
             for (int q = 0; q < 3; ++q) s_m[q][ry][rx] = ok ? maps[q * plane + idx] : 0.f;
         }
         __syncthreads();
-        for (int k = tid; k < kPadH * kTileW; k += kTileW * kTileH) {
-            const int ry = k / kTileW, cx = k - ry * kTileW;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+        for (int item = tid; item < kPad * kGroups; item += kLossThreads) {
+            const int ry = item % kPad, cx = (item / kPad) * kOut;
+            float a0[kOut] = {}, a1[kOut] = {}, a2[kOut] = {};
 #pragma unroll
-            for (int t = 0; t < kWin; ++t) {
-                const float wt = win.w[t];
-                a0 += wt * s_m[0][ry][cx + t]; a1 += wt * s_m[1][ry][cx + t]; a2 += wt * s_m[2][ry][cx + t];
+            for (int k = 0; k < kSpan; ++k) {
+                slide(a0, s_m[0][ry][cx + k], k, win); slide(a1, s_m[1][ry][cx + k], k, win);
+                slide(a2, s_m[2][ry][cx + k], k, win);
             }
-            s_h[0][ry][cx] = a0; s_h[1][ry][cx] = a1; s_h[2][ry][cx] = a2;
+#pragma unroll
+            for (int j = 0; j < kOut; ++j) { s_h[0][ry][cx + j] = a0[j]; s_h[1][ry][cx + j] = a1[j]; s_h[2][ry][cx + j] = a2[j]; }
         }
         __syncthreads();
-        float c0 = 0.f, c1 = 0.f, c2 = 0.f;
+        float c0[kOut] = {}, c1[kOut] = {}, c2[kOut] = {};
 #pragma unroll
-        for (int t = 0; t < kWin; ++t) {
-            const float wt = win.w[t];
-            c0 += wt * s_h[0][ty + t][tx]; c1 += wt * s_h[1][ty + t][tx]; c2 += wt * s_h[2][ty + t][tx];
+        for (int k = 0; k < kSpan; ++k) {
+            slide(c0, s_h[0][r0 + k][tx], k, win); slide(c1, s_h[1][r0 + k][tx], k, win);
+            slide(c2, s_h[2][r0 + k][tx], k, win);
         }
-        if (px < W && py < H) {
-            const size_t idx = ((size_t)py * W + px) * 3 + c;
-            const float xv = x[idx], yv = y[idx];
-            const float d = xv - yv;
-            const float sign = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
-            v_image[idx] = c0 + 2.f * xv * c1 + yv * c2 + l1_weight * sign;
+#pragma unroll
+        for (int j = 0; j < kOut; ++j) {
+            const int py = y0 + r0 + j;
+            if (px < W && py < H) {
+                const size_t idx = ((size_t)py * W + px) * 3 + c;
+                const float xv = x[idx], yv = y[idx];
+                const float d = xv - yv;
+                const float sign = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
+                v_image[idx] = c0[j] + 2.f * xv * c1[j] + yv * c2[j] + l1_weight * sign;
+            }
         }
         __syncthreads();
     }
@@ -180,7 +216,7 @@ int launch_image_loss(const float* image, const float* target, int H, int W, flo
     float* sums = maps + (size_t)H * W * 3 * 3;
     DSB_CUDA_CHECK(cudaMemsetAsync(sums, 0, 2 * sizeof(float), s));
     const float count = (float)((double)H * W * 3);
-    const dim3 grid((W + kTileW - 1) / kTileW, (H + kTileH - 1) / kTileH), block(kTileW, kTileH);
+    const dim3 grid((W + kPatch - 1) / kPatch, (H + kPatch - 1) / kPatch), block(kLossThreads);
     ssim_moments_kernel<<<grid, block, 0, s>>>(image, target, H, W, win, -lambda_dssim / count, maps, sums);
     DSB_LAUNCH_CHECK();
     ssim_gradient_kernel<<<grid, block, 0, s>>>(image, target, maps, H, W, win, (1.f - lambda_dssim) / count, v_image);
