@@ -26,7 +26,7 @@ EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
-    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_pairs_views",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_pairs_views", "dsb_plan_totals_views",
     "dsb_backward_blend",
     "dsb_geometry_backward_views", "dsb_geometry_backward_views_stats",
     "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_adam_step",
@@ -96,6 +96,7 @@ def lib():
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
             "dsb_preprocess_views": [P, I32, I32] + [P] * 16,
             "dsb_plan_pairs_views": [CAM, I32, I32, I64, P, P, P, P, P, I64, P, P],
+            "dsb_plan_totals_views": [I32, I32, P, I64, P, P],
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_geometry_backward_views_stats": [P, I32, I32] + [P] * 15 + [I32, C.c_float, C.c_float, P, P, P, P],

@@ -365,11 +365,12 @@ int64_t plan_workspace_bytes(int n) { return plan_workspace_bytes_views(n, 1); }
 
 // Depth order and pair offsets of `views` views in the same launches.  tiles, depth_keys, depth_keys_alt and
 // offsets hold one row of `n` entries per view, `item_stride` entries apart; k_host receives one total per view.
+// k_host == nullptr: only the launches; read_plan_totals_views() fetches the totals later.
 int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
                       u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
-    DSB_REQUIRE(k_host, "plan: k_host is null");
     DSB_REQUIRE(views >= 1 && views <= DSB_MAX_BATCH_VIEWS, "plan: between 1 and %d views per call", DSB_MAX_BATCH_VIEWS);
-    for (int v = 0; v < views; ++v) k_host[v] = 0;
+    if (k_host)
+        for (int v = 0; v < views; ++v) k_host[v] = 0;
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(tiles && depth_keys && depth_keys_alt && offsets && ws, "plan: null pointer");
     DSB_REQUIRE(views == 1 || item_stride >= n, "plan: rows of the views overlap");
@@ -413,6 +414,21 @@ int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride
         DSB_LAUNCH_CHECK();
     }
 
+    if (!k_host) return DSB_OK;
+    return read_plan_totals_views(views, n, ws, ws_bytes, k_host, s);
+}
+
+// The pair totals of a plan launched before on stream s (one host synchronisation), and the status words of its
+// bounded waits.
+int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
+    DSB_REQUIRE(k_host, "plan: k_host is null");
+    DSB_REQUIRE(views >= 1 && views <= DSB_MAX_BATCH_VIEWS, "plan: between 1 and %d views per call", DSB_MAX_BATCH_VIEWS);
+    for (int v = 0; v < views; ++v) k_host[v] = 0;
+    if (n == 0) return DSB_OK;
+    DSB_REQUIRE(ws && ws_bytes >= plan_workspace_bytes_views(n, views), "plan: not the workspace the plan was launched with");
+    const unsigned char* base = reinterpret_cast<const unsigned char*>(ws);
+    const int64_t sort_stride = sort_batch_stride_bytes(n), sort_bytes = (int64_t)views * sort_stride;
+    const PlanTail* tail = reinterpret_cast<const PlanTail*>(base + sort_bytes + (int64_t)views * plan_scan_row_bytes(n));
     struct HostTail { u64 total; u32 counter; int status; } host_tail[DSB_MAX_BATCH_VIEWS];
     int sort_status[DSB_MAX_BATCH_VIEWS] = {};
     static_assert(sizeof(HostTail) == sizeof(PlanTail), "host mirror of the plan tail");

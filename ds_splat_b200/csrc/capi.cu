@@ -146,6 +146,7 @@ int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched
                    int64_t* k_host, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
+    DSB_REQUIRE(k_host, "plan: k_host is null");
     return launch_plan(cp, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
                        offsets, workspace, workspace_bytes, k_host, (cudaStream_t)stream);
 }
@@ -162,6 +163,12 @@ int dsb_plan_pairs_views(const DsbCamera* cam, int32_t num_views, int32_t n, int
     return launch_plan_views(cp, num_views, n, row_stride, tiles_touched, reinterpret_cast<u64*>(depth_keys),
                              reinterpret_cast<u64*>(depth_keys_alt), offsets, workspace, workspace_bytes, k_host,
                              (cudaStream_t)stream);
+}
+
+int dsb_plan_totals_views(int32_t num_views, int32_t n, const void* workspace, int64_t workspace_bytes, int64_t* k_host,
+                          void* stream) {
+    DSB_REQUIRE(n >= 0, "n must be non-negative");
+    return read_plan_totals_views(num_views, n, workspace, workspace_bytes, k_host, (cudaStream_t)stream);
 }
 
 int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
@@ -236,6 +243,7 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
     DSB_REQUIRE(tile_marks, "forward_plan: tile_marks is null");
+    DSB_REQUIRE(k_host, "forward_plan: k_host is null");
     cudaStream_t s = (cudaStream_t)stream;
     {
         StageScope scope(kStagePreprocess, s);

@@ -137,6 +137,7 @@ int64_t plan_workspace_bytes(int n);
 int64_t plan_workspace_bytes_views(int n, int views);
 int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
                       u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
+int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,

@@ -160,7 +160,6 @@ class _Lane:
         self.sort_ws = None
         self.sort_bytes = 0
         self.img = {}
-        self.done = None        # event after the lane's last launch of a batch
 
 
 class ViewRenderer:
@@ -322,31 +321,32 @@ class ViewRenderer:
             for j, sl in enumerate(slots):
                 sl.cam = self._camera(cameras[b0 + j])
             cams = (capi.DsbCamera * nv)(*[sl.cam[0] for sl in slots])
-            ptrs = lambda ts: (C.c_void_p * nv)(*[t.data_ptr() for t in ts])
+            ptrs = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+            main = torch.cuda.current_stream(self.dev)
+            nl = min(self.view_streams, nv)
+            lanes = [self._lane(i) for i in range(nl)]
             capi.check(lib.dsb_preprocess_views(
                 cams, nv, self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
                 p["scales"].data_ptr(), p["rotations"].data_ptr(), None, ptrs([sl.records for sl in slots]),
                 ptrs([sl.radii for sl in slots]), ptrs([sl.tiles for sl in slots]), self.cov3d.data_ptr(),
                 ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]),
                 ptrs([self._ranges(sl, *size) for sl in slots]), ptrs([sl.layout_hist for sl in slots]), capi.stream_ptr()))
-            ks = (C.c_int64 * nv)()
-            capi.check(lib.dsb_plan_pairs_views(     # depth order and pair offsets of all views, one host sync
+            # depth order and pair offsets of all views: launched without a host wait, then ONE read-back of the totals
+            capi.check(lib.dsb_plan_pairs_views(
                 C.byref(slots[0].cam[0]), nv, self.n, self.n, self.tiles_rows.data_ptr(), self.depth_rows[0].data_ptr(),
                 self.depth_rows[1].data_ptr(), self.offset_rows.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
-                ks, capi.stream_ptr()))
+                None, capi.stream_ptr()))
+            ks = (C.c_int64 * nv)()
+            capi.check(lib.dsb_plan_totals_views(nv, self.n, self.plan_ws.data_ptr(), self.plan_bytes, ks,
+                                                 capi.stream_ptr()))
             # The K-sized stages of the views, dealt over the lanes: lane 0 is the caller's stream, the others wait for
             # the batch's plan, and the caller's stream waits for them before the per-splat backward.
-            main = torch.cuda.current_stream(self.dev)
-            nl = min(self.view_streams, nv)
-            lanes = [self._lane(i) for i in range(nl)]
-            if nl > 1:
-                planned = torch.cuda.Event()
-                planned.record(main)
-                for ln in lanes[1:]:
-                    ln.stream.wait_event(planned)
+            planned = torch.cuda.Event()
+            planned.record(main)
+            for ln in lanes[1:]:
+                ln.stream.wait_event(planned)
             for j, sl in enumerate(slots):
-                cam = cameras[b0 + j]
-                li = j % nl
+                cam, li = cameras[b0 + j], j % nl
                 with torch.cuda.stream(lanes[li].stream if li else main):
                     image = self._render(sl, cam, int(ks[j]), layout_done=True, lane=li)
                     v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
@@ -356,11 +356,10 @@ class ViewRenderer:
                         C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), lanes[li].pairs[0].data_ptr(),
                         ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
                         self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
-                    if li:
-                        lanes[li].done = torch.cuda.Event()
-                        lanes[li].done.record(lanes[li].stream)
             for ln in lanes[1:]:
-                main.wait_event(ln.done)
+                done = torch.cuda.Event()
+                done.record(ln.stream)
+                main.wait_event(done)
             geo_args = (
                 cams, nv, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
                 self.cov3d.data_ptr(), ptrs([sl.records for sl in slots]), ptrs([sl.radii for sl in slots]),

@@ -273,6 +273,12 @@ int dsb_plan_pairs_views(const DsbCamera* cam /* any of the views: only its flag
                          int32_t n, int64_t row_stride, const int32_t* tiles_touched, uint64_t* depth_keys,
                          uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
                          int64_t* k_host, void* stream);
+/* dsb_plan_pairs_views with k_host == NULL only launches (no host synchronisation); dsb_plan_totals_views then
+ * fetches the totals of that plan from the same workspace on the same stream (one synchronisation of that stream) and
+ * reports an expired device-side wait.  Lets a caller queue other work, or a second batch on another stream, between
+ * the two. */
+int dsb_plan_totals_views(int32_t num_views, int32_t n, const void* workspace, int64_t workspace_bytes,
+                          int64_t* k_host, void* stream);
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
                        const float* v_image, const float* v_depth /* may be NULL */,
