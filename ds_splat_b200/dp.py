@@ -304,7 +304,9 @@ class ViewRenderer:
                      stats: Optional[DensifyStats] = None):
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
         contents when ``accumulate``).  ``image_grads`` is a sequence of dL/dimage tensors or a callable
-        ``(index, image) -> dL/dimage``.  Views are taken in batches of up to ``batch_views`` of one image size:
+        ``(index, image) -> dL/dimage``; it is called under the stream its view runs on (``view_streams`` of them
+        take turns), so buffers it reuses from call to call must be per stream, as ``ImageLoss`` keeps them.  Views are
+        taken in batches of up to ``batch_views`` of one image size:
         one preprocess launch (with the tile layout of every view) and one plan (depth sorts, offset scans, a
         single read-back of the pair counts) for the batch, then per view the rest of the forward and the backward blend, then one per-splat backward for
         the batch, which also updates ``stats`` (a ``DensifyStats``) when given."""
@@ -393,7 +395,10 @@ class ImageLoss:
 
     def gradient(self, image: torch.Tensor, target: torch.Tensor):
         h, w = image.shape[0], image.shape[1]
-        key = (h, w, image.device)
+        # one set of buffers per stream: render_views calls this under the stream of the view's lane, and a buffer
+        # shared by two lanes would be rewritten while the other lane's backward still reads it
+        stream = torch.cuda.current_stream(image.device).cuda_stream if image.is_cuda else 0
+        key = (h, w, image.device, stream)
         if key not in self.buf:
             nbytes = int(self.lib.dsb_image_loss_workspace_bytes(h, w))
             self.buf[key] = (torch.empty(nbytes, dtype=torch.uint8, device=image.device), torch.empty_like(image))

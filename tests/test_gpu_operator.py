@@ -476,5 +476,12 @@ def test_image_loss_gradient_matches_the_autograd_checker():
     r.render_views(cams, checker_grad, g_check)
     torch.cuda.synchronize()
     assert len(loss_fn.losses) == 3 and all(0.0 < float(l) < 1.5 for l in loss_fn.losses)
+    # render_views runs neighbouring views on different streams: the loss keeps one set of buffers per stream
+    side = torch.cuda.Stream()
+    v_main, _ = loss_fn.gradient(targets[0], targets[1])
+    with torch.cuda.stream(side):
+        v_side, _ = loss_fn.gradient(targets[0], targets[1])
+    side.synchronize()
+    assert v_main.data_ptr() != v_side.data_ptr() and torch.equal(v_main, v_side)
     assert _rel(g_fused.views["shs"].cpu().numpy(), g_check.views["shs"].cpu().numpy()) < 1e-3
     assert _rel(g_fused.views["means3d"].cpu().numpy(), g_check.views["means3d"].cpu().numpy()) < 1e-3
