@@ -1,26 +1,38 @@
 #!/usr/bin/env python3
-"""Benchmark of the splat rasterizer hot path: forward + backward of one 1920x1080 view of 1M degree-3
-splats (config 1 of BASELINE.json), reported as whole-job views/s (``fwd_bwd_ms_per_view`` is fwd+bwd ms/iter).
+"""Benchmark of the splat rasterizer hot path: training steps over 1920x1080 views of 1M degree-3 splats
+(config 1 of BASELINE.json), reported as whole-job views/s, with the literal "fwd+bwd ms/iter" beside it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1]
 
-One process per GPU (torchrun for N > 1).  Each step every rank renders ``--views-per-rank`` views of
-the replicated cloud (forward, backward with gradient accumulation into one flat 59-float-per-splat
-buffer) and, for N > 1, all ranks sum that buffer with one NCCL all-reduce: weak scaling, per-GPU work
-fixed.  Rank 0 prints ONE JSON line.
+One process per GPU (torchrun for N > 1).  A step on every rank: forward + backward of ``--views-per-rank``
+distinct cameras of the replicated cloud (gradients summed into one flat 59-float-per-splat block), then the
+optimizer step with the gradient sum folded in -- reduce-scatter of the block over NCCL, Adam on the rank's 1/N
+slice, all-gather of the parameters (plain Adam in a single process).  Weak scaling: per-GPU work is fixed.
+Rank 0 prints ONE JSON line.
 
-  value      device-timed throughput (CUDA events, barrier + synchronize on both sides, max over ranks)
-             of the fused C-ABI calls with all inputs resident in HBM;
-  e2e        the same step through the public Python operator (GaussianRasterizer + autograd) with the
-             step's inputs (camera, upstream image gradient) copied from pinned host memory and the
-             rendered image + radii copied back inside the timed region;
-  roofline   the dominant kernel (backward blend), timed live with cudaEvent pairs the library records
-             around each stage while the same steps run again;
-  cpu_baseline  the C++/OpenMP restatement of the reference's algorithm (oracle/), one full view, all
-             host threads -- a reported baseline, not the target;
-  --impl reference  times that CPU restatement as the reference arm (the reference ships no CPU path
-             and cannot be pip-installed here; its own CUDA kernels, built under oracle/_ref, are
-             reported beside it as ``reference_cuda`` when that library is present).
+  value            device-timed throughput of those steps (CUDA events, barrier + synchronize on both sides, max
+                   over ranks), all inputs resident in HBM; ``step_breakdown_ms`` splits a step into render,
+                   gradient reduce-scatter, Adam and parameter all-gather;
+  single_view_ms   the literal metric "fwd+bwd ms/iter @1M": ONE view per iteration through the fused single-view
+                   calls (dsb_forward / dsb_backward), median over the iterations, for the default pair lists and
+                   for ``strict_lists`` (tiles-touched counts, pair list and tile ranges bit-identical to the
+                   reference's; the default pairs a splat only with tiles it can contribute to, a subset with
+                   identical image, radii and gradients);
+  strict_lists     the multi-view step again with the reference-identical lists;
+  e2e              one view per step through the public Python operator (GaussianRasterizer + autograd) with the
+                   step's inputs (camera, upstream image gradient) copied from pinned host memory and the
+                   rendered image + radii copied back inside the timed region;
+  roofline         the dominant kernel (backward blend) on the configuration's own camera against the FP32 pipe
+                   (148 SMs x 128 lanes x 2 flop x sampled SM clock), timed live with the cudaEvent pairs the
+                   library records around each stage; ``roofline_hbm`` is the same launch against the measured
+                   copy bandwidth;
+  c3               config 3 (6M splats, 8 of its 64 ring cameras per rank and step, 1.416 GB of gradients) for a
+                   few steps, so that the scaling curve of the configuration the multi-GPU metric names is on record;
+  cpu_baseline     the C++/OpenMP restatement of the reference's algorithm (oracle/), one full view, all host
+                   threads -- a reported baseline, not the target;
+  --impl reference times that CPU restatement as the reference arm (the reference ships no CPU path and cannot be
+                   pip-installed here; its own CUDA kernels, built under oracle/_ref, are reported beside it as
+                   ``reference_cuda`` when that library is present).
 """
 from __future__ import annotations
 
@@ -37,8 +49,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-METRIC = "training views/s (fwd+bwd), 1M splats SH-3 @1920x1080 (fwd_bwd_ms_per_view = fwd+bwd ms/iter)"
+METRIC = "training views/s (fwd+bwd+optimizer step), 1M splats SH-3 @1920x1080 (single_view_ms = fwd+bwd ms/iter)"
 UNIT = "views/s"
+LRS = dict(means3d=1.6e-4, shs=2.5e-3, opacities=5e-2, scales=5e-3, rotations=1e-3)
 
 
 def parse_args():
@@ -47,16 +60,22 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"])
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4", "flythrough"])
     ap.add_argument("--views-per-rank", type=int, default=8,
-                    help="views each rank renders per step before the gradient all-reduce (64-view batch on 8 GPUs)")
+                    help="views each rank renders per step before the gradient reduction (64-view batch on 8 GPUs)")
     ap.add_argument("--view-streams", type=int, default=2,
                     help="streams the per-view stages of a step's views are dealt over (1 = one after the other)")
     ap.add_argument("--splats", type=int, default=0, help="override the workload's splat count (debugging)")
+    ap.add_argument("--reduce", default="sharded", choices=["sharded", "allreduce"],
+                    help="sharded: reduce-scatter + Adam on 1/N + all-gather; allreduce: all-reduce + Adam over everything")
+    ap.add_argument("--no-nccl-registration", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-reference-cuda", action="store_true")
-    ap.add_argument("--skip-optimizer", action="store_true")
+    ap.add_argument("--skip-optimizer", action="store_true", help="skip the separate Adam / image-loss kernel timings")
+    ap.add_argument("--skip-c3", action="store_true")
+    ap.add_argument("--skip-strict", action="store_true")
+    ap.add_argument("--frames", type=int, default=120, help="frames of the fly-through workload")
     return ap.parse_args()
 
 
@@ -111,12 +130,15 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def load_scene(args):
+def load_scene(args, views: int = 1):
     from ds_splat_b200 import scenes
     kw = {}
     if args.splats:
         kw["n"] = args.splats
-    return scenes.CONFIGS[args.workload](**kw)
+    name = "c1" if args.workload == "flythrough" else args.workload
+    if name == "c1":
+        kw["views"] = views   # view 0 is the configuration's camera, the others are turned +-5 degrees away from it
+    return scenes.CONFIGS[name](**kw)
 
 
 def measured_peaks():
@@ -161,6 +183,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     from oracle import oracle as O
+    cores = O.use_all_host_threads()   # torchrun exports OMP_NUM_THREADS=1 to its workers
     scene = load_scene(args)
     view = scene.views[0]
     v_image = scene.image_grad()
@@ -170,12 +193,12 @@ def run_reference_arm(args):
     times = [oracle_one_view(scene, view, v_image)[0] for _ in range(steps)]
     sec = sum(times) / len(times)
     value = 1.0 / sec
-    cores = O.num_threads()
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": UNIT, "n_gpus": args.gpus,
             "steps": steps, "warmup": warmup, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{scene.name}: {scene.n} splats SH-3, {view.W}x{view.H}, one view fwd+bwd",
-                       "note": "the reference has no CPU path; this is the C++/OpenMP restatement of its algorithm (oracle/)"},
+                       "note": "the reference has no CPU path; this is the C++/OpenMP restatement of its algorithm (oracle/), "
+                               "which has no optimizer step"},
             "cpu_baseline": {"value": round(value, 5), "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{steps} full views of the workload (steps clamped to 5)"},
             "e2e": {"value": round(value, 5), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -189,17 +212,215 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+class Timed:
+    """CUDA-event timing of a callable on the current stream: barrier + synchronize on both sides, max over ranks."""
+
+    def __init__(self, world, dev):
+        self.world, self.dev = world, dev
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms: float) -> float:
+        import torch
+        import torch.distributed as dist
+        if self.world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=self.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def run(self, fn, steps, warmup):
+        import torch
+        from ds_splat_b200 import _capi
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = _capi.launch_count()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        self.launches = _capi.launch_count() - launches0   # kernels of this library launched inside the timed region
+        self.barrier()
+        return self.max_over_ranks(ev0.elapsed_time(ev1))
+
+
+def build_training(scene, cams, v_images, dev, args, world, tight_tiles=True):
+    """Parameter block, renderer on its views, gradient block and optimizer of one training configuration."""
+    import numpy as np
+    import torch
+    from ds_splat_b200.dp import GradientBuffer, ParameterBuffer, ShardedAdam, ViewRenderer, register_with_nccl
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    host = dict(means3d=scene.means, shs=scene.shs, opacities=scene.opacities, scales=scene.scales, rotations=scene.rotations)
+
+    def make():
+        return (ParameterBuffer(scene.n, dev, shards=world), GradientBuffer(scene.n, dev, shards=world))
+
+    if world > 1 and not args.no_nccl_registration:
+        (params, grads), pool = register_with_nccl(make)
+    else:
+        (params, grads), pool = make(), None
+    for name, arr in host.items():
+        params.views[name].copy_(t(arr).reshape(params.views[name].shape))
+    renderer = ViewRenderer(**params.views, sh_degree=scene.sh_degree, view_streams=args.view_streams, tight_tiles=tight_tiles)
+    # Learning rate zero: the kernel reads and writes exactly what it does in training (parameters, gradients, both
+    # moments), but the cloud stays the configuration's cloud over hundreds of timed steps.  (Adam's normalised
+    # update would otherwise move every scale by lr per step whatever the gradient, and 300 steps destroy the scene.)
+    opt = ShardedAdam(params, {k: 0.0 for k in LRS})
+    return params, grads, renderer, opt, pool
+
+
+def timed_training(timer, renderer, cams, v_images, grads, opt, args, world, steps, warmup):
+    """Times `steps` training steps; returns (ms per step, per-phase ms)."""
+    import torch
+    import torch.distributed as dist
+    vpr = len(cams)
+    marks = []
+
+    def step(record=False):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
+        if record:
+            ev[0].record()
+        renderer.render_views(cams, v_images, grads, accumulate=False)
+        if record:
+            ev[1].record()
+        g_slice = grads.storage[opt.lo:opt.hi]
+        opt.step_count += 1
+        if world > 1:
+            dist.reduce_scatter_tensor(g_slice, grads.storage, op=dist.ReduceOp.SUM)
+        if record:
+            ev[2].record()
+        for name, a, b in opt.pieces:
+            opt.update(opt.params.storage[a:b], grads.storage[a:b], opt.m[a - opt.lo:b - opt.lo], opt.v[a - opt.lo:b - opt.lo],
+                       opt.lrs[name], opt.betas[0], opt.betas[1], opt.eps, opt.step_count, 1.0 / (vpr * world))
+        if record:
+            ev[3].record()
+        if world > 1:
+            dist.all_gather_into_tensor(opt.params.storage, opt.params.storage[opt.lo:opt.hi])
+        if record:
+            ev[4].record()
+            marks.append(ev)
+
+    ms = timer.run(step, steps, warmup) / steps
+    launches = timer.launches
+    # the phases of a step, from a few extra steps with events between them (not part of the timed region above)
+    for _ in range(min(steps, 10)):
+        step(record=True)
+    torch.cuda.synchronize()
+    names = ("render", "reduce_scatter", "adam", "all_gather")
+    phases = {n: round(timer.max_over_ranks(sum(e[i].elapsed_time(e[i + 1]) for e in marks) / len(marks)), 4)
+              for i, n in enumerate(names)}
+    timer.launches = launches
+    return ms, phases
+
+
+def timed_allreduce_form(timer, renderer, cams, v_images, grads, params, args, world, steps, warmup):
+    """The replicated form for comparison: all-reduce of the gradient block, Adam over everything on every rank."""
+    import torch
+    from ds_splat_b200.dp import FlatAdam, allreduce_gradients
+    opt = FlatAdam(params.views, {k: 0.0 for k in LRS})
+    vpr = len(cams)
+
+    def step():
+        renderer.render_views(cams, v_images, grads, accumulate=False)
+        allreduce_gradients(grads)
+        opt.step(grads, grad_scale=1.0 / (vpr * world))
+
+    ms = timer.run(step, steps, warmup) / steps
+    del opt
+    torch.cuda.empty_cache()
+    return ms
+
+
+def single_view_timing(renderer_cls, params_views, scene, cam, v_image, grads, tight_tiles, iters, warmup, capi):
+    """Median device time of ONE forward+backward through the fused single-view calls, and the stage times of it."""
+    import torch
+    r = renderer_cls(**params_views, sh_degree=scene.sh_degree, batch_views=1, tight_tiles=tight_tiles, view_streams=1)
+    for _ in range(warmup):
+        r.forward(cam)
+        r.backward(v_image, grads, accumulate=False)
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r.forward(cam)
+        r.backward(v_image, grads, accumulate=False)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = sorted(a.elapsed_time(b) for a, b in evs)
+    k = r.last_k
+    capi.stage_timing(True)
+    for _ in range(min(iters, 20)):
+        r.forward(cam)
+        r.backward(v_image, grads, accumulate=False)
+    torch.cuda.synchronize()
+    raw = capi.read_stage_timings()
+    capi.stage_timing(False)
+    stages = {name: round(ms / calls, 5) for name, (ms, calls) in raw.items() if calls}
+    del r
+    return {"median_ms": round(statistics.median(times), 4), "min_ms": round(times[0], 4), "iters": iters,
+            "pairs": int(k), "stages_ms": stages}
+
+
+def run_flythrough(args):
+    """The reference README's protocol on a synthetic cloud: 120 frames of a camera that backs away from the scene,
+    forward only, milliseconds per frame (README.md:199-204 of the reference plots such series for trained scenes)."""
+    import numpy as np
+    import torch
+    from ds_splat_b200 import _capi, scene_io
+    from ds_splat_b200.dp import CameraTensors, ViewRenderer
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    _capi.lib()
+    scene = load_scene(args)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    r = ViewRenderer(t(scene.means), t(scene.shs), t(scene.opacities), t(scene.scales), t(scene.rotations),
+                     sh_degree=scene.sh_degree, batch_views=1, view_streams=1)
+    v0 = scene.views[0]
+    views = scene_io.zoom_out_path(args.frames, start_distance=3.0, end_distance=12.0, W=v0.W, H=v0.H,
+                                   focal=v0.W / (2.0 * v0.tanfovx))
+    cams = [CameraTensors.from_view(v, dev) for v in views]
+    for c in cams[:3]:
+        r.forward(c)
+    torch.cuda.synchronize()
+    ms, pairs = [], []
+    for c in cams:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r.forward(c)
+        b.record()
+        b.synchronize()
+        ms.append(round(a.elapsed_time(b), 4))
+        pairs.append(int(r.last_k))
+    line = {"metric": "forward ms per frame, 120-frame zoom-out fly-through", "value": round(statistics.mean(ms), 4), "unit": "ms",
+            "n_gpus": 1, "steps": len(ms), "warmup": 3, "higher_is_better": False, "data": "synthetic", "dtype": "f32",
+            "config": {"workload": f"flythrough over {scene.name}: {scene.n} splats, {v0.W}x{v0.H}, camera distance 3 -> 12"},
+            "frame_ms": ms, "frame_pairs": pairs, "median_ms": round(statistics.median(ms), 4), "max_ms": max(ms)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "flythrough":
+        run_flythrough(args)
         return
 
     import numpy as np
     import torch
     import torch.distributed as dist
     from ds_splat_b200 import GaussianRasterizationSettings, GaussianRasterizer, _capi
-    from ds_splat_b200.dp import CameraTensors, GradientBuffer, ViewRenderer, data_parallel_step
+    from ds_splat_b200.dp import CameraTensors, ViewRenderer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -217,63 +438,55 @@ def main():
         os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     _capi.lib()  # fail loudly if the library is missing
-
-    scene = load_scene(args)
-    view = scene.views[0]
-    H, W = view.H, view.W
+    timer = Timed(world, dev)
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
-    params = dict(means3d=t(scene.means), shs=t(scene.shs), opacities=t(scene.opacities), scales=t(scene.scales),
-                  rotations=t(scene.rotations))
+
     vpr = max(1, args.views_per_rank)
-    # Cameras are dealt to ranks in blocks of vpr; a scene with a single camera (config 1) gives every rank that one.
+    scene = load_scene(args, views=world * vpr)
+    H, W = scene.views[0].H, scene.views[0].W
+    # Cameras are dealt to ranks in blocks of vpr: every view of a step, on every rank, is a different camera.
     view_ids = [(rank * vpr + j) % len(scene.views) for j in range(vpr)]
     cams = [CameraTensors.from_view(scene.views[v], dev) for v in view_ids]
-    v_images_host = [scene.image_grad(v, seed=7 + rank * vpr + j) for j, v in enumerate(view_ids)]
-    view = scene.views[view_ids[0]]
+    v_images_host = [scene.image_grad(v, seed=7 + v) for v in view_ids]
     v_images = [t(v) for v in v_images_host]
-    renderer = ViewRenderer(**params, sh_degree=scene.sh_degree, view_streams=args.view_streams)
-    grads = GradientBuffer(scene.n, dev)
+    params, grads, renderer, opt, pool = build_training(scene, cams, v_images, dev, args, world)
+    warmup = max(args.warmup, 3)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def step():
-        data_parallel_step(renderer, cams, v_images, grads)
-
-    # ---- device-timed throughput ------------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    # ---- device-timed training steps ------------------------------------------------------------------
+    for _ in range(warmup):   # allocator and pair buffers reach their steady state before the clocks are sampled
+        renderer.render_views(cams, v_images, grads, accumulate=False)
+    timer.barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    launches0 = _capi.launch_count()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    elapsed_ms = ev0.elapsed_time(ev1)
-    launches = _capi.launch_count() - launches0
+    ms_per_step, phases = timed_training(timer, renderer, cams, v_images, grads, opt, args, world, args.steps, warmup)
+    launches = timer.launches
     clocks = sampler.stop()
-    tmax = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+    if world > 1 and args.reduce == "allreduce":
+        ms_per_step = timed_allreduce_form(timer, renderer, cams, v_images, grads, params, args, world, args.steps, 3)
+        launches = timer.launches
+    views_per_s = world * vpr / (ms_per_step * 1e-3)
+    ks = [int(k) for k in renderer.last_ks]
+    kt = torch.tensor([min(ks), max(ks), sum(ks)], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(tmax.item())
-    ms_per_step = elapsed_ms / args.steps
-    views_per_s = world * vpr * args.steps / (elapsed_ms * 1e-3)
-    K_emitted = renderer.last_k
-    # Pair count of the reference's own list for the same view (the renderer pairs a splat only with the tiles it can
-    # contribute to, a subset with identical results): the algorithmic figures below are those of the reference's list.
-    ref_lists = ViewRenderer(**params, sh_degree=scene.sh_degree, batch_views=1, tight_tiles=False)
-    ref_lists.forward(cams[-1])
-    torch.cuda.synchronize()
-    K = ref_lists.last_k
-    del ref_lists
-    torch.cuda.empty_cache()
+        kmin, kmax, ksum = kt[0:1].clone(), kt[1:2].clone(), kt[2:3].clone()
+        dist.all_reduce(kmin, op=dist.ReduceOp.MIN); dist.all_reduce(kmax, op=dist.ReduceOp.MAX); dist.all_reduce(ksum)
+        kt = torch.cat([kmin, kmax, ksum])
+    pairs_emitted = {"min": int(kt[0].item()), "max": int(kt[1].item()), "mean": int(kt[2].item() / (world * vpr))}
+    allreduce_form_ms = None
+    if world > 1 and args.reduce == "sharded":
+        allreduce_form_ms = timed_allreduce_form(timer, renderer, cams, v_images, grads, params, args, world,
+                                                 min(args.steps, 40), 3)
+
+    # ---- the same step with the reference-identical pair lists ------------------------------------------
+    strict = None
+    if not args.skip_strict:
+        renderer.tight_tiles = False
+        s_steps = min(args.steps, 60)
+        s_ms, _ = timed_training(timer, renderer, cams, v_images, grads, opt, args, world, s_steps, 3)
+        strict = {"ms_per_view": round(s_ms / vpr, 4), "views_per_s": round(world * vpr / (s_ms * 1e-3), 3), "steps": s_steps,
+                  "pairs_mean": int(sum(renderer.last_ks) / vpr),
+                  "note": "tight_tiles off: tiles-touched counts, pair list and tile ranges are bit-identical to the reference's"}
+        renderer.tight_tiles = True
 
     # ---- per-stage timing of the same steps (events recorded by the library around each stage) ---------
     # The stages are timed with the views one after the other on one stream: with two views in flight the events
@@ -281,183 +494,222 @@ def main():
     lanes_used = renderer.view_streams
     renderer.view_streams = 1
     _capi.stage_timing(True)
-    for _ in range(min(args.steps, 40)):
-        step()
+    stage_steps = min(args.steps, 40)
+    for _ in range(stage_steps):
+        renderer.render_views(cams, v_images, grads, accumulate=False)
     torch.cuda.synchronize()
     stage_raw = _capi.read_stage_timings()
     _capi.stage_timing(False)
     renderer.view_streams = lanes_used
     # per view: the per-splat backward runs once for all views of a step, every other stage once per view
-    timed_views = min(args.steps, 40) * vpr
-    stages_ms = {name: round(ms / timed_views, 5) for name, (ms, calls) in stage_raw.items() if calls}
+    stages_ms = {name: round(ms / (stage_steps * vpr), 5) for name, (ms, calls) in stage_raw.items() if calls}
 
-    # ---- the optimizer step that follows a training step (not part of the metric; reported beside it) ---------
+    # ---- the literal metric: one view per iteration through the fused single-view calls, configuration's camera ----
+    single = None
+    if world == 1 or rank == 0:
+        cam0 = CameraTensors.from_view(scene.views[0], dev)
+        v0 = t(scene.image_grad(0, seed=7))
+        iters = max(20, min(args.steps, 100))
+        single = {"tight_tiles": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, True, iters, 5, _capi),
+                  "strict_lists": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, False, iters, 5, _capi)}
+        del cam0, v0
+    timer.barrier()
+
+    # ---- the kernels either side of the operator in a training loop (reported beside the metric) ---------
     optimizer = None
     if world == 1 and not args.skip_optimizer:
-        from ds_splat_b200.dp import FlatAdam
-        scratch = {k: v.clone() for k, v in renderer.p.items()}   # the timed steps must not move the benchmark's scene
-        opt = FlatAdam(scratch, dict(means3d=1.6e-4, shs=2.5e-3, opacities=5e-2, scales=5e-3, rotations=1e-3))
-        for _ in range(3):
-            opt.step(grads, grad_scale=1.0 / vpr)
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        ev0.record()
-        for _ in range(20):
-            opt.step(grads, grad_scale=1.0 / vpr)
-        ev1.record()
-        torch.cuda.synchronize()
-        adam_ms = ev0.elapsed_time(ev1) / 20
+        adam_ms = phases["adam"]
         adam_bytes = 28 * grads.flat.numel()   # read p, g, m, v; write p, m, v
-        optimizer = {"kernel": "adam_kernel (5 launches, one per parameter tensor)", "ms_per_step": round(adam_ms, 4),
+        optimizer = {"kernel": "adam_kernel (one launch per parameter tensor)", "ms_per_step": round(adam_ms, 4),
                      "achieved_GBps": round(adam_bytes / (adam_ms * 1e-3) / 1e9, 1), "algorithmic_bytes": int(adam_bytes)}
-        del scratch, opt
-        # ... and the photometric loss between forward and backward (L1 + D-SSIM and its gradient, two launches)
         from ds_splat_b200.dp import ImageLoss
         loss_fn = ImageLoss(lambda_dssim=0.2)
         img = renderer.forward(cams[-1]).clone()
         tgt = torch.rand_like(img)
-        for _ in range(3):
-            loss_fn.gradient(img, tgt)
-        torch.cuda.synchronize()
-        ev0.record()
-        for _ in range(20):
-            loss_fn.gradient(img, tgt)
-        ev1.record()
-        torch.cuda.synchronize()
-        loss_ms = ev0.elapsed_time(ev1) / 20
+        loss_ms = timer.run(lambda: loss_fn.gradient(img, tgt), 20, 3) / 20
         loss_bytes = 4 * 3 * H * W * (2 + 3 + 3 + 2 + 1)   # read x, y; write 3 maps; read 3 maps, x, y; write dL/dx
         optimizer["image_loss"] = {"kernels": "ssim_moments_kernel + ssim_gradient_kernel", "ms_per_view": round(loss_ms, 4),
                                    "achieved_GBps": round(loss_bytes / (loss_ms * 1e-3) / 1e9, 1),
                                    "algorithmic_bytes": int(loss_bytes)}
         del loss_fn, img, tgt
-        torch.cuda.empty_cache()
 
     # ---- end to end through the public operator, host buffers -----------------------------------------
     e2e = None
     if not args.skip_e2e:
+        view = scene.views[view_ids[0]]
         pinned_grad = torch.from_numpy(v_images_host[0]).pin_memory()
         pinned_view = torch.from_numpy(view.viewmatrix_t).pin_memory()
         pinned_proj = torch.from_numpy(view.projmatrix_t).pin_memory()
         pinned_pos = torch.from_numpy(np.ascontiguousarray(view.campos)).pin_memory()
         out_image = torch.empty((H, W, 3), dtype=torch.float32).pin_memory()
         out_radii = torch.empty(scene.n, dtype=torch.int32).pin_memory()
-        leaves = {k: v.clone().requires_grad_(True) for k, v in params.items()}
+        leaves = {k: v.detach().clone().requires_grad_(True) for k, v in params.views.items()}
         means2d = torch.zeros_like(leaves["means3d"], requires_grad=True)
         bg = torch.zeros(3, device=dev)
+        vm, pm, cp = (torch.empty_like(x, device=dev) for x in (pinned_view, pinned_proj, pinned_pos))
+        vg = torch.empty((H, W, 3), dtype=torch.float32, device=dev)
+        settings = GaussianRasterizationSettings(H, W, view.tanfovx, view.tanfovy, bg, 1.0, vm, pm, scene.sh_degree, 3, cp,
+                                                 False, False)
+        rasterizer = GaussianRasterizer(settings)
         h2d = pinned_grad.numel() * 4 + (16 + 16 + 3) * 4
         d2h = out_image.numel() * 4 + out_radii.numel() * 4
-
         copy_stream = torch.cuda.Stream(device=dev)
+        main_stream = torch.cuda.current_stream()
+        grad_ready, rendered, copied = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
 
         def e2e_step():
-            # A training loop's usual overlap: the image gradient travels to the device while the forward
-            # runs, the rendered image travels back while the backward runs (second stream, events).
-            main = torch.cuda.current_stream()
-            vm = pinned_view.to(dev, non_blocking=True)
-            pm = pinned_proj.to(dev, non_blocking=True)
-            cp = pinned_pos.to(dev, non_blocking=True)
+            # A training loop's usual overlap: the image gradient travels to the device while the forward runs, the
+            # rendered image travels back while the backward runs (second stream, events).  The device-side
+            # destinations are the step's own buffers, reused from step to step as a loop's batch buffers are.
+            vm.copy_(pinned_view, non_blocking=True)
+            pm.copy_(pinned_proj, non_blocking=True)
+            cp.copy_(pinned_pos, non_blocking=True)
+            copy_stream.wait_event(copied)   # the previous step's backward has read vg (event recorded after it)
             with torch.cuda.stream(copy_stream):
-                vg = pinned_grad.to(dev, non_blocking=True)
-                grad_ready = torch.cuda.Event()
+                vg.copy_(pinned_grad, non_blocking=True)
                 grad_ready.record(copy_stream)
-            settings = GaussianRasterizationSettings(H, W, view.tanfovx, view.tanfovy, bg, 1.0, vm, pm, scene.sh_degree, 3,
-                                                     cp, False, False)
-            for leaf in list(leaves.values()) + [means2d]:
+            for leaf in leaves.values():
                 leaf.grad = None
-            image, radii = GaussianRasterizer(settings)(leaves["means3d"], means2d, leaves["shs"], None, leaves["opacities"],
-                                                        leaves["scales"], leaves["rotations"], None)
-            rendered = torch.cuda.Event()
-            rendered.record(main)
+            means2d.grad = None
+            image, radii = rasterizer(leaves["means3d"], means2d, leaves["shs"], None, leaves["opacities"],
+                                      leaves["scales"], leaves["rotations"], None)
+            rendered.record(main_stream)
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(rendered)
                 out_image.copy_(image.detach(), non_blocking=True)
                 out_radii.copy_(radii, non_blocking=True)
             image.record_stream(copy_stream)
             radii.record_stream(copy_stream)
-            main.wait_event(grad_ready)
-            vg.record_stream(main)
+            main_stream.wait_event(grad_ready)
             image.backward(vg)
+            copied.record(main_stream)
             torch.cuda.synchronize()  # the caller reads the result on the host every step
 
-        for _ in range(max(args.warmup, 3)):
+        copied.record(main_stream)
+        for _ in range(warmup):
             e2e_step()
-        barrier()
+        timer.barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall0 = time.perf_counter()
         a.record()
         for _ in range(args.steps):
             e2e_step()
         b.record()
-        barrier()
+        timer.barrier()
         wall = time.perf_counter() - wall0
-        e_ms = max(a.elapsed_time(b), wall * 1e3)  # host work between kernels counts: take the slower clock
-        tm = torch.tensor([e_ms], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-        e2e = {"value": round(world * args.steps / (float(tm.item()) * 1e-3), 3), "unit": UNIT,
+        e_ms = timer.max_over_ranks(max(a.elapsed_time(b), wall * 1e3))  # host work between kernels counts: the slower clock
+        e2e = {"value": round(world * args.steps / (e_ms * 1e-3), 3), "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": round(float(tm.item()) / args.steps, 4),
-               "note": "GaussianRasterizer + autograd; per step H2D camera + dL/dimage from pinned memory, D2H image + radii; "
-                       "splat parameters are model state resident on the device"}
-        del leaves, means2d
+               "ms_per_step": round(e_ms / args.steps, 4),
+               "note": "GaussianRasterizer + autograd, one view per step; per step H2D camera + dL/dimage from pinned memory, "
+                       "D2H image + radii; splat parameters are model state resident on the device"
+                       + ("; per-rank rendering with no collective in it (N independent render loops)" if world > 1 else "")}
+        del leaves, means2d, rasterizer
 
+    nccl_registered = pool is not None
+    # ---- config 3 beside it: 6M splats, 8 of the 64 ring cameras per rank and step, 1.416 GB of gradients ----------
+    c3 = None
+    if not args.skip_c3 and args.workload == "c1" and not args.splats:
+        del renderer, opt, params, grads, cams, v_images, pool
+        torch.cuda.empty_cache()
+        from ds_splat_b200 import scenes
+        sc3 = scenes.multiview()
+        ids3 = [(rank * vpr + j) % len(sc3.views) for j in range(vpr)]
+        cams3 = [CameraTensors.from_view(sc3.views[v], dev) for v in ids3]
+        vim3 = [t(sc3.image_grad(v, seed=7 + v)) for v in ids3]
+        params3, grads3, renderer3, opt3, pool3 = build_training(sc3, cams3, vim3, dev, args, world)
+        ms3, phases3 = timed_training(timer, renderer3, cams3, vim3, grads3, opt3, args, world, 8, 3)
+        c3 = {"workload": f"{sc3.name}: {sc3.n} splats SH-3, {W}x{H}, {vpr} of {len(sc3.views)} ring cameras per rank per step",
+              "views_per_s": round(world * vpr / (ms3 * 1e-3), 3), "ms_per_step": round(ms3, 4), "steps": 8, "warmup": 3,
+              "step_breakdown_ms": phases3, "gradient_bytes": int(grads3.nbytes()),
+              "pairs_emitted_mean": int(sum(renderer3.last_ks) / vpr), "nccl_registered_buffers": pool3 is not None}
+        del renderer3, opt3, params3, grads3, cams3, vim3, sc3, pool3
+        torch.cuda.empty_cache()
+
+    # ---- CPU baseline (rank 0; the other ranks wait at the barrier below) -------------------------------
+    view0 = scene.views[0]
+    v_image0 = scene.image_grad(0, seed=7)
+    cpu_baseline, pairs_bwd, pairs_fwd, K_ref = None, None, None, None
+    if rank == 0 and not args.skip_cpu_baseline:
+        from oracle import oracle as O
+        cores = O.use_all_host_threads()   # torchrun exports OMP_NUM_THREADS=1 to its workers
+        sec, fwd_o, bwd_o = oracle_one_view(scene, view0, v_image0)
+        pairs_fwd, pairs_bwd, K_ref = fwd_o["pairs_fwd"], bwd_o["pairs_bwd"], fwd_o["K"]
+        # timed at every N (it also counts the pairs the roofline needs), reported as the baseline at N = 1 only
+        if world == 1:
+            cpu_baseline = {"value": round(1.0 / sec, 5), "unit": UNIT, "cores": cores, "kind": "port",
+                            "sample": "one full view of the workload (forward + backward, no optimizer step), C++/OpenMP "
+                                      "restatement in oracle/", "ms_per_view": round(sec * 1e3, 1)}
+    timer.barrier()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-
-    # ---- CPU baseline + roofline (rank 0) -----------------------------------------------------------
-    cpu_baseline, pairs_bwd, pairs_fwd = None, None, None
-    if world == 1 and not args.skip_cpu_baseline:
-        from oracle import oracle as O
-        sec, fwd_o, bwd_o = oracle_one_view(scene, view, v_images_host[0])
-        pairs_fwd, pairs_bwd = fwd_o["pairs_fwd"], bwd_o["pairs_bwd"]
-        cpu_baseline = {"value": round(1.0 / sec, 5), "unit": UNIT, "cores": O.num_threads(), "kind": "port",
-                        "sample": "one full view of the workload (forward + backward), C++/OpenMP restatement in oracle/",
-                        "ms_per_view": round(sec * 1e3, 1)}
-    reference_cuda = reference_cuda_numbers(scene, view, v_images_host[0]) if world == 1 and not args.skip_reference_cuda else None
+    reference_cuda = reference_cuda_numbers(scene, view0, v_image0) if world == 1 and not args.skip_reference_cuda else None
 
     peak, peak_src = measured_peaks()
     if optimizer:
         optimizer["frac_of_hbm_peak"] = round(optimizer["achieved_GBps"] / peak, 4)
-    dom = "blend_backward"
-    dom_ms = stages_ms.get(dom)
-    roofline, roofline_fp32 = None, None
-    if dom_ms:
-        # algorithmic bytes of one backward-blend launch: 8 B pair + 48 B record gathered per list entry,
-        # 36 B of per-splat sums added per list entry, 20 B per pixel read (dL/dimage 12, final_T 4, final_idx 4),
-        # plus the 48 B/splat zero fill of the accumulator that the stage includes.
-        alg_bytes = K * (8 + 48 + 36) + 20 * H * W + 48 * scene.n
-        achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
-        # DRAM bytes of one blend_backward_kernel launch from the ncu capture summarised in
-        # profiles/blend_backward_c1.md (83,103,232 read + 4,211,712 written at config 1); it is dominated
-        # by the pair list and the gathered records, so other workloads scale it by their pair count.
-        traffic = int(87_314_944 * (K / 10_957_444))
-        roofline = {"kernel": dom, "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                    "frac": round(achieved / peak, 4), "traffic": traffic,
-                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on config 1, scaled by pairs",
-                    "peak_source": peak_src,
-                    "algorithmic_bytes": int(alg_bytes), "ms": dom_ms,
-                    "note": "this kernel is bound by FP32/SHFL issue, not HBM; see roofline_fp32"}
-        if pairs_bwd and clocks.get("sm_mhz"):
+    roofline, roofline_hbm, stage_achieved = None, None, None
+    if single:
+        # The dominant kernel, on the configuration's own camera, strict lists (the pairs it walks are the reference's).
+        sv = single["strict_lists"]
+        dom_ms, K = sv["stages_ms"].get("blend_backward"), sv["pairs"]
+        if dom_ms and pairs_bwd and clocks.get("sm_mhz"):
             flops = 74.0 * pairs_bwd
             fp32_peak = 148 * 128 * 2 * clocks["sm_mhz"] * 1e6 / 1e12
-            roofline_fp32 = {"kernel": dom, "achieved": round(flops / (dom_ms * 1e-3) / 1e12, 3), "peak": round(fp32_peak, 2),
-                             "unit": "TFLOP/s", "frac": round(flops / (dom_ms * 1e-3) / 1e12 / fp32_peak, 4),
-                             "pairs": int(pairs_bwd), "flop_per_pair": 74,
-                             "peak_source": "148 SMs x 128 FP32 lanes x 2 flop x median SM clock sampled during the run"}
+            # DRAM bytes of one blend_backward_kernel launch from the ncu capture summarised in
+            # profiles/blend_backward_c1.md (83,103,232 read + 4,211,712 written for 7,710,065 pairs); it is dominated by
+            # the first touch of the pair list and the gathered records, so it is scaled by the pairs of this launch.
+            traffic = int(87_314_944 * (K / 7_710_065))
+            roofline = {"kernel": "blend_backward_kernel", "bound": "fp32", "achieved": round(flops / (dom_ms * 1e-3) / 1e12, 3),
+                        "peak": round(fp32_peak, 2), "unit": "TFLOP/s", "frac": round(flops / (dom_ms * 1e-3) / 1e12 / fp32_peak, 4),
+                        "traffic": traffic, "ms": dom_ms, "pairs_visited": int(pairs_bwd), "flop_per_pair": 74,
+                        "peak_source": "148 SMs x 128 FP32 lanes x 2 flop x median SM clock sampled during the run (not in "
+                                       "MEASURED_PEAKS.json, which holds HBM and bf16 tensor peaks only)",
+                        "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on config 1, scaled by pairs",
+                        "note": "single-view call on the configuration's camera with the reference-identical pair list; the flop "
+                                "count is the reference algorithm's per visited (pixel, splat) pair, the kernel skips pixel blocks "
+                                "a splat cannot reach, so the fraction overstates pipe utilisation (see profiles/)"}
+            # 8 B pair + 48 B record gathered per list entry, 36 B of per-splat sums added per list entry, 20 B per pixel
+            # read (dL/dimage 12, final_T 4, final_idx 4), plus the 48 B/splat zero fill of the accumulator in the stage.
+            alg_bytes = K * (8 + 48 + 36) + 20 * H * W + 48 * scene.n
+            roofline_hbm = {"kernel": "blend_backward_kernel", "bound": "hbm", "achieved": round(alg_bytes / (dom_ms * 1e-3) / 1e9, 2),
+                            "peak": peak, "unit": "GB/s", "frac": round(alg_bytes / (dom_ms * 1e-3) / 1e9 / peak, 4),
+                            "algorithmic_bytes": int(alg_bytes), "peak_source": peak_src,
+                            "note": "secondary: the kernel is bound by FP32/SHFL issue, its working set is L2-resident"}
+        # K-sized stages on the pairs they actually move (strict: the reference's count; tight: the emitted subset)
+        stage_achieved = {}
+        for mode, sv_ in single.items():
+            k_, st = sv_["pairs"], sv_["stages_ms"]
+            rec = {}
+            if st.get("emit_pairs"):
+                rec["emit_pairs_GBps"] = round((8 * k_ + 36 * scene.n) / (st["emit_pairs"] * 1e-3) / 1e9, 1)
+            if st.get("tile_sort"):
+                rec["tile_sort_GBps"] = round(2 * 16 * k_ / (st["tile_sort"] * 1e-3) / 1e9, 1)
+            rec["frac_of_hbm_peak"] = {k2[:-5]: round(v / peak, 3) for k2, v in rec.items()}
+            stage_achieved[mode] = rec
 
     line = {"metric": METRIC, "value": round(views_per_s, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
-            "fwd_bwd_ms_per_view": round(ms_per_step / vpr, 4), "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
+            "fwd_bwd_ms_per_view": round(phases["render"] / vpr, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{scene.name}: {scene.n} splats SH-3, {W}x{H}, {vpr} view(s) per rank per step, fwd+bwd"
-                                   + (", gradient all-reduce of 59 floats/splat" if world > 1 else ""),
-                       "pairs_K": int(K), "pairs_emitted": int(K_emitted), "tiles": view.num_tiles, "view_streams": int(min(args.view_streams, vpr)), "l2": "inputs larger than L2 (236 MB of parameters + "
-                       "88 MB pair list per view; no explicit flush)", "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
-            "clocks": clocks, "gpu_launches": int(launches), "stages_ms": stages_ms, "roofline": roofline,
-            "roofline_fp32": roofline_fp32, "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda,
-            "optimizer": optimizer,
+            "config": {"workload": f"{scene.name}: {scene.n} splats SH-3, {W}x{H}, {vpr} distinct cameras per rank per step "
+                                   f"(camera 0 is the configuration's, the others turned +-5 degrees from it), fwd+bwd of each, "
+                                   + ("gradient reduce-scatter, Adam on 1/N of the parameters, parameter all-gather"
+                                      if world > 1 else "Adam step"),
+                       "pairs_reference_list_view0": K_ref, "pairs_emitted": pairs_emitted, "tiles": scene.views[0].num_tiles,
+                       "view_streams": int(min(args.view_streams, vpr)), "optimizer": "Adam, learning rate 0 (same reads and "
+                       "writes; the cloud stays the configuration's)", "reduce": args.reduce if world > 1 else "none",
+                       "nccl_registered_buffers": bool(nccl_registered),
+                       "l2": "inputs larger than L2 (236 MB of parameters + 62-88 MB pair list per view; no explicit flush)",
+                       "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
+            "clocks": clocks, "gpu_launches": int(launches), "step_breakdown_ms": phases,
+            "single_view_ms": single["tight_tiles"]["median_ms"] if single else None, "single_view": single,
+            "strict_lists": strict, "allreduce_form_ms_per_step": round(allreduce_form_ms, 4) if allreduce_form_ms else None,
+            "stages_ms": stages_ms, "stages_note": "per view, from a rerun of the same steps with the views on ONE stream",
+            "stage_achieved": stage_achieved, "roofline": roofline, "roofline_hbm": roofline_hbm,
+            "cpu_baseline": cpu_baseline, "e2e": e2e, "reference_cuda": reference_cuda, "optimizer": optimizer, "c3": c3,
             "pairs_evaluated": {"forward_per_pixel": pairs_fwd, "backward_per_pixel": pairs_bwd}}
     print(json.dumps(line), file=json_out, flush=True)
     if world > 1:

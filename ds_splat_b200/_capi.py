@@ -32,7 +32,8 @@ EXPORTS = (
     "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_adam_step",
     "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
-    "dsb_sort_pairs_static", "dsb_tile_marks_bytes",
+    "dsb_sort_pairs_static", "dsb_tile_marks_bytes", "dsb_forward", "dsb_take_device_status",
+    "dsb_debug_expire_scan_wait", "dsb_debug_expire_sort_wait", "dsb_debug_set_copy_wait_polls",
 )
 STATIC_SORT_MAX_ITEMS = 1 << 21
 
@@ -104,6 +105,12 @@ def lib():
             "dsb_image_loss_backward": [P, P, I32, I32, C.c_float, P, I64, P, P, P],
             "dsb_adam_step": [P, P, P, P, I64, C.c_double, C.c_double, C.c_double, C.c_double, I32, C.c_double, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
+            "dsb_forward": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, P, P, I64, P, I64] + [P] * 5
+                           + [C.POINTER(C.c_int64), C.POINTER(C.c_int32), P],
+            "dsb_take_device_status": [C.POINTER(C.c_int32), P],
+            "dsb_debug_expire_scan_wait": [CAM, I32, P, P, P, P, I64, C.c_uint32, P],
+            "dsb_debug_expire_sort_wait": [P, P, I64, I32, I32, P, I64, C.c_uint32, P],
+            "dsb_debug_set_copy_wait_polls": [C.c_uint32],
         }
         for name, argtypes in sig.items():
             fn = getattr(l, name)
@@ -116,6 +123,15 @@ def lib():
 def check(rc: int):
     if rc != 0:
         raise DsbError(rc, lib().dsb_last_error().decode(errors="replace"))
+
+
+def take_device_status() -> int:
+    """Synchronises the current stream and hands over the device's status word: raises ``DsbError`` when a bounded
+    wait inside a kernel expired since the last check (lists sorted since are not valid), returns a positive
+    DSB_STATUS_* note or 0 otherwise."""
+    status = C.c_int32(0)
+    check(lib().dsb_take_device_status(C.byref(status), stream_ptr()))
+    return int(status.value)
 
 
 def launch_count() -> int:
@@ -142,7 +158,17 @@ def ptr(t):
     return t.data_ptr()
 
 
-def stream_ptr():
+def stream_ptr(device=None):
+    """Handle of torch's current stream -- of ``device`` when given, which must then be the current device: the
+    library launches on the current device, so a stream of another one would take the kernels to the wrong GPU."""
+    if device is not None:
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError(f"the rasterizer runs on CUDA devices, not on {device}")
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        if index != torch.cuda.current_device():
+            raise RuntimeError(f"tensors live on cuda:{index} but the current device is cuda:{torch.cuda.current_device()}; "
+                               "wrap the call in torch.cuda.device(...)")
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -246,6 +272,7 @@ def sort_pairs(items, begin_bit, end_bit):
     in_alt = C.c_int32(0)
     check(lib().dsb_sort_pairs(ptr(items), ptr(alt), k, begin_bit, end_bit, ws.data_ptr(), ws_bytes, C.byref(in_alt),
                                stream_ptr()))
+    take_device_status()   # the sort never synchronises by itself; this wrapper does, and reports an expired wait
     return alt if in_alt.value else items
 
 
@@ -258,6 +285,7 @@ def sort_pairs_static(items, items_alt, begin_bit, end_bit):
     in_alt = C.c_int32(0)
     check(lib().dsb_sort_pairs_static(ptr(items), ptr(items_alt), items.shape[0], begin_bit, end_bit, C.byref(in_alt),
                                       stream_ptr()))
+    take_device_status()   # allocates nothing either: one 4-byte copy to the host and a stream synchronisation
     return items_alt if in_alt.value else items
 
 
@@ -270,6 +298,7 @@ def sort_by_keys(keys, values, begin_bit=0, end_bit=64):
     in_alt = C.c_int32(0)
     check(lib().dsb_sort_by_keys(ptr(keys), ptr(kalt), ptr(values), ptr(valt), k, begin_bit, end_bit, ws.data_ptr(),
                                  ws_bytes, C.byref(in_alt), stream_ptr()))
+    take_device_status()
     return (kalt, valt) if in_alt.value else (keys, values)
 
 

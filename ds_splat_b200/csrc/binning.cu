@@ -33,7 +33,8 @@ struct PlanTail {       // lives after the sort workspace
 __global__ void __launch_bounds__(kScanThreads)
 scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __restrict__ tiles, const int n,
                    const int drop_last, u32* __restrict__ offsets, u64* __restrict__ lookback, PlanTail* __restrict__ tail,
-                   const long long item_stride, const long long lookback_stride) {
+                   const long long item_stride, const long long lookback_stride, int* __restrict__ device_status,
+                   const u32 spin_limit) {
     __shared__ u32 s_wsum[32];
     // blockIdx.y: which view of the batch (each with its own keys, counts, offsets, look-back row and tail)
     depth_keys_sorted += blockIdx.y * item_stride; tiles += blockIdx.y * item_stride; offsets += blockIdx.y * item_stride;
@@ -97,8 +98,11 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
                 p -= take;
                 done = incl_in != 0;
                 if (!done && take < 32) {  // met a tile that has not published yet
-                    if (++polls > kSpinLimit) {
-                        if (lane == 0) atomicExch(&tail->status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                    if (++polls > spin_limit) {
+                        if (lane == 0) {
+                            atomicExch(&tail->status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                            atomicExch(device_status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                        }
                         break;
                     }
                     __nanosleep(40);
@@ -409,8 +413,12 @@ int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride
     }
     {
         StageScope scope(kStageScan, s);
+        int* device_status = nullptr;
+        const int rc = device_status_address(&device_status);
+        if (rc != DSB_OK) return rc;
         scan_counts_kernel<<<dim3((unsigned)scan_tiles, (unsigned)views), kScanThreads, 0, s>>>(
-            depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8);
+            depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8,
+            device_status, kSpinLimit);
         DSB_LAUNCH_CHECK();
     }
 
@@ -435,7 +443,14 @@ int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, i
     DSB_CUDA_CHECK(cudaMemcpyAsync(host_tail, tail, sizeof(HostTail) * views, cudaMemcpyDeviceToHost, s));
     DSB_CUDA_CHECK(cudaMemcpy2DAsync(sort_status, sizeof(int), base + sort_status_offset(), (size_t)sort_stride, sizeof(int),
                                      (size_t)views, cudaMemcpyDeviceToHost, s));
+    // ... and the device's status word, which also carries what the tile sorts of earlier renders recorded
+    int device_status = 0;
+    {
+        const int rc = begin_device_status_read(&device_status, s);
+        if (rc != DSB_OK) return rc;
+    }
     DSB_CUDA_CHECK(cudaStreamSynchronize(s));
+    const int earlier = finish_device_status_read(device_status, s);   // clears the word when it was set
     for (int v = 0; v < views; ++v) {
         if (host_tail[v].status != 0 || sort_status[v] != 0) {
             set_error("plan: a device-side wait expired (view %d: scan %d, sort %d)", v, host_tail[v].status, sort_status[v]);
@@ -443,6 +458,7 @@ int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, i
         }
         k_host[v] = (int64_t)host_tail[v].total;
     }
+    if (earlier != DSB_OK) return earlier;   // recorded by a kernel outside this plan (a render's tile sort)
     for (int v = 0; v < views; ++v) {
         if (host_tail[v].total >= (u64)DSB_MAX_PAIRS) {
             set_error("plan: %llu (tile, splat) pairs exceed the supported maximum of 2^30 - 1",
@@ -456,6 +472,39 @@ int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, i
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
     return launch_plan_views(cp, 1, n, n, tiles, depth_keys, depth_keys_alt, offsets, ws, ws_bytes, k_host, s);
+}
+
+// Test hook.  The scan of a single-view plan over at least two tiles in which the tile counter starts at 1: tile 0
+// is never processed and never publishes, so the warp that took tile 1 polls it `spin_limit` times, gives up,
+// records DSB_ERR_DEVICE_WAIT_EXPIRED in the plan's tail and in the device status word, and the kernel finishes.
+// `ws` is laid out as launch_plan lays it out, so read_plan_totals_views() on it afterwards reports the expiry the
+// way a real one would be reported.  depth_keys_sorted only has to hold splat ids below n in its low halves.
+int debug_expire_scan_wait(const CamParams& cp, int n, const int32_t* tiles, const u64* depth_keys_sorted, u32* offsets,
+                           void* ws, int64_t ws_bytes, u32 spin_limit, cudaStream_t s) {
+    DSB_REQUIRE(tiles && depth_keys_sorted && offsets && ws, "debug_expire_scan_wait: null pointer");
+    DSB_REQUIRE(n >= 2 * kScanTile, "debug_expire_scan_wait: needs at least two tiles of %d splats", kScanTile);
+    DSB_REQUIRE(spin_limit >= 1 && spin_limit <= 100000, "debug_expire_scan_wait: spin_limit must be in 1..100000");
+    const int64_t need = plan_workspace_bytes_views(n, 1);
+    if (ws_bytes < need) {
+        set_error("plan: workspace of %lld bytes is smaller than the %lld needed", (long long)ws_bytes, (long long)need);
+        return DSB_ERR_WORKSPACE_TOO_SMALL;
+    }
+    unsigned char* base = reinterpret_cast<unsigned char*>(ws);
+    const int64_t sort_bytes = sort_batch_stride_bytes(n);
+    const int64_t scan_tiles = ((int64_t)n + kScanTile - 1) / kScanTile;
+    u64* lookback = reinterpret_cast<u64*>(base + sort_bytes);
+    PlanTail* tail = reinterpret_cast<PlanTail*>(base + sort_bytes + plan_scan_row_bytes(n));
+    DSB_CUDA_CHECK(cudaMemsetAsync(ws, 0, (size_t)need, s));
+    static const u32 kOne = 1;
+    DSB_CUDA_CHECK(cudaMemcpyAsync(&tail->tile_counter, &kOne, sizeof(u32), cudaMemcpyHostToDevice, s));
+    int* device_status = nullptr;
+    const int rc = device_status_address(&device_status);
+    if (rc != DSB_OK) return rc;
+    scan_counts_kernel<<<dim3((unsigned)(scan_tiles - 1), 1), kScanThreads, 0, s>>>(
+        depth_keys_sorted, tiles, n, cp.drop_last, offsets, lookback, tail, 0, plan_scan_row_bytes(n) / 8, device_status,
+        spin_limit);
+    DSB_LAUNCH_CHECK();
+    return DSB_OK;
 }
 
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,

@@ -23,6 +23,50 @@ void set_error(const char* fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// ---- device status word ------------------------------------------------------------------------
+static __device__ int g_device_status;            // first DSB_ERR_* a kernel recorded since the host last took it
+constexpr int kMaxStatusDevices = 64;
+static int* g_device_status_address[kMaxStatusDevices] = {};
+static std::mutex g_device_status_mutex;
+static std::atomic<unsigned> g_copy_wait_polls{kCopyWaitPolls};
+
+int device_status_address(int** out) {
+    int dev = -1;
+    DSB_CUDA_CHECK(cudaGetDevice(&dev));
+    DSB_REQUIRE(dev >= 0 && dev < kMaxStatusDevices, "device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_device_status_mutex);
+    if (!g_device_status_address[dev]) {
+        // In host code the symbol's name is only a handle; the address a kernel can use differs per GPU.
+        void* p = nullptr;
+        DSB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_device_status));
+        DSB_REQUIRE(p != nullptr, "the device status word has no device address");
+        g_device_status_address[dev] = static_cast<int*>(p);
+    }
+    *out = g_device_status_address[dev];
+    return DSB_OK;
+}
+
+int begin_device_status_read(int* host, cudaStream_t s) {
+    int* word = nullptr;
+    const int rc = device_status_address(&word);
+    if (rc != DSB_OK) return rc;
+    DSB_CUDA_CHECK(cudaMemcpyAsync(host, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    return DSB_OK;
+}
+
+int finish_device_status_read(int value, cudaStream_t s) {
+    if (value >= 0) return DSB_OK;   // 0: nothing recorded; positive: a note about a slower path, results valid
+    int* word = nullptr;
+    const int rc = device_status_address(&word);
+    if (rc != DSB_OK) return rc;
+    DSB_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));   // taken: the next report starts from a clean word
+    set_error("a bounded device-side wait of an earlier call on this device expired (status %d): results of the calls "
+              "enqueued since the last status check are not valid", value);
+    return value == DSB_ERR_DEVICE_WAIT_EXPIRED ? DSB_ERR_DEVICE_WAIT_EXPIRED : DSB_ERR_CUDA;
+}
+
+u32 copy_wait_polls() { return g_copy_wait_polls.load(std::memory_order_relaxed); }
+
 // ---- stage timing ------------------------------------------------------------------------------
 struct EventPair { cudaEvent_t a, b; int stage; };
 static bool g_timing = false;
@@ -103,6 +147,41 @@ int dsb_stage_timing_enable(int32_t on) {
     return DSB_OK;
 }
 
+int dsb_take_device_status(int32_t* status_host, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    int value = 0;
+    int rc = begin_device_status_read(&value, s);
+    if (rc != DSB_OK) return rc;
+    DSB_CUDA_CHECK(cudaStreamSynchronize(s));
+    if (status_host) *status_host = value;
+    if (value > 0) {   // a note: hand it over once
+        int* word = nullptr;
+        rc = device_status_address(&word);
+        if (rc != DSB_OK) return rc;
+        DSB_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));
+    }
+    return finish_device_status_read(value, s);
+}
+
+int dsb_debug_set_copy_wait_polls(uint32_t polls) {
+    g_copy_wait_polls.store(polls ? polls : kCopyWaitPolls, std::memory_order_relaxed);
+    return DSB_OK;
+}
+
+int dsb_debug_expire_scan_wait(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched,
+                               const uint64_t* depth_keys_sorted, uint32_t* offsets, void* workspace,
+                               int64_t workspace_bytes, uint32_t spin_limit, void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    return debug_expire_scan_wait(cp, n, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets, workspace,
+                                  workspace_bytes, spin_limit, (cudaStream_t)stream);
+}
+
+int dsb_debug_expire_sort_wait(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit,
+                               void* workspace, int64_t workspace_bytes, uint32_t spin_limit, void* stream) {
+    return debug_expire_sort_wait(reinterpret_cast<u64*>(items), reinterpret_cast<u64*>(items_alt), k, begin_bit, end_bit,
+                                  workspace, workspace_bytes, spin_limit, (cudaStream_t)stream);
+}
+
 int32_t dsb_stage_count(void) { return kStageCount; }
 const char* dsb_stage_name(int32_t stage) { return (stage >= 0 && stage < kStageCount) ? kStageNames[stage] : ""; }
 
@@ -125,6 +204,7 @@ int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls)
 
 int64_t dsb_plan_workspace_bytes(int32_t n) { return plan_workspace_bytes(n < 0 ? 0 : n); }
 int64_t dsb_sort_workspace_bytes(int64_t k) { return sort_workspace_bytes(k < 0 ? 0 : k); }
+static int64_t sort_workspace_bytes_needed(int64_t k) { return k <= 1 ? 0 : sort_workspace_bytes(k); }
 int64_t dsb_tile_marks_bytes(int32_t image_height, int32_t image_width) {
     return (image_height > 0 && image_width > 0) ? tile_marks_bytes(image_height, image_width) : 0;
 }
@@ -304,6 +384,27 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
     StageScope scope(kStageBlendForward, s);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, depth,
                                 has_order ? tile_marks : nullptr, s);
+}
+
+int dsb_forward(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
+                const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
+                float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
+                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* plan_workspace,
+                int64_t plan_workspace_bytes, uint64_t* pairs, uint64_t* pairs_alt, int64_t pair_capacity,
+                void* sort_workspace, int64_t sort_workspace_bytes, int32_t* ranges, float* image, float* final_T,
+                int32_t* final_idx, float* depth, int64_t* k_host, int32_t* rendered_host, void* stream) {
+    DSB_REQUIRE(k_host && rendered_host, "forward: k_host or rendered_host is null");
+    *rendered_host = 0;
+    int rc = dsb_forward_plan(cam, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records, radii,
+                              tiles_touched, cov3d, depth_keys, depth_keys_alt, offsets, tile_marks, plan_workspace,
+                              plan_workspace_bytes, k_host, stream);
+    if (rc != DSB_OK) return rc;
+    const int64_t k = *k_host;
+    if (k > pair_capacity || sort_workspace_bytes < sort_workspace_bytes_needed(k)) return DSB_OK;   // caller grows and renders
+    rc = dsb_forward_render(cam, n, k, records, tiles_touched, depth_keys, offsets, pairs, pairs_alt, tile_marks, sort_workspace,
+                            sort_workspace_bytes, ranges, image, final_T, final_idx, depth, nullptr, stream);
+    if (rc == DSB_OK) *rendered_host = 1;
+    return rc;
 }
 
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales, const float* rotations,

@@ -90,9 +90,24 @@ __device__ __forceinline__ float mat_at(const float* m, int r, int c, int transp
 __device__ __forceinline__ u32 pack_rect(int lo, int hi) { return (u32)lo | ((u32)hi << 16); }
 
 // ---- bounded waits -----------------------------------------------------------------------------
-// Every spin in this library gives up after this many polls, records why in a status word and
-// returns, so a logic error can never hang the GPU.
+// Every spin in this library gives up after a fixed number of polls, records why in a status word and
+// returns, so a logic error can never hang the GPU.  The limit travels to the kernels as an argument
+// (kSpinLimit in normal use; the dsb_debug_* entry points pass a few hundred so that a test can watch a wait
+// run out in microseconds).
 constexpr u32 kSpinLimit = 1u << 22;
+constexpr u32 kCopyWaitPolls = 1u << 20;   // polls of an mbarrier that counts bulk copies in
+
+// One int per device that keeps the first DSB_ERR_* code any kernel of this library recorded since the host last
+// took it: kernels receive its address and atomicExch the code in when a bounded wait gives up.  It lives in
+// the library image (no allocation), its device address is looked up once per device with that device current.
+// Calls that synchronise anyway (the pair-count read-back of a plan) fetch it in the same synchronisation;
+// dsb_take_device_status() fetches it on demand.
+int device_status_address(int** out);
+// Copies the word to *host on stream s (no synchronisation); the caller synchronises, then calls
+// finish_device_status(value, s), which clears the word when it was set and returns the DSB_ code to report.
+int begin_device_status_read(int* host, cudaStream_t s);
+int finish_device_status_read(int value, cudaStream_t s);
+u32 copy_wait_polls();   // polls preprocess gives its bulk copies (kCopyWaitPolls unless a test lowered it)
 
 // ---- launchers (one per stage file) -----------------------------------------------------------------
 int launch_preprocess(const CamParams& cp, int n, const float* means, const float* shs, const float* colors_precomp,
@@ -140,6 +155,12 @@ int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride
 int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
+// Test hooks: one scan / one sort pass in which the first tile of the look-back chain is never processed, so the
+// second tile's bounded wait runs out after `spin_limit` polls (see dsb_debug_expire_*_wait in the header).
+int debug_expire_scan_wait(const CamParams& cp, int n, const int32_t* tiles, const u64* depth_keys_sorted, u32* offsets,
+                           void* ws, int64_t ws_bytes, u32 spin_limit, cudaStream_t s);
+int debug_expire_sort_wait(u64* items, u64* items_alt, int64_t k, int begin_bit, int end_bit, void* ws, int64_t ws_bytes,
+                           u32 spin_limit, cudaStream_t s);
 int launch_emit(const CamParams& cp, int n, int64_t k, const float* records, const int32_t* tiles,
                 const u64* depth_keys_sorted, const u32* offsets, u64* pairs, cudaStream_t s);
 // Grid of rectangle corner marks filled by the preprocess kernel; launch_tile_layout turns it into tile ranges

@@ -68,7 +68,7 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
                   const float* __restrict__ colors_precomp, const float* __restrict__ opac,
                   const float* __restrict__ scales, const float* __restrict__ rots,
                   const float* __restrict__ cov3d_precomp, float* __restrict__ cov3d, const int sh_vec4, const int use_bulk,
-                  const int marks_copy_ints) {
+                  const int marks_copy_ints, const u32 copy_polls, int* __restrict__ device_status) {
     extern __shared__ __align__(16) float4 dyn4[];
     __shared__ float s_cams[DSB_MAX_BATCH_VIEWS][32];   // per view: view rows 0..2 (12), projection (16), camera centre (3)
     __shared__ __align__(16) float s_means[kThreads * 3];
@@ -93,8 +93,11 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
     // Full blocks with 16-byte aligned inputs are staged by the bulk copy engine (TMA): every thread asks for
     // its own 192-byte SH row (into the padded row layout), one thread asks for the block's 3 KB of means
     // and of scales, and one mbarrier counts the bytes in.  No registers or load instructions are spent on
-    // the 54 KB a block brings in.  The wait is bounded; if it ever expires the ordinary loads below run.
-    bool staged = false;
+    // the 54 KB a block brings in.  The wait is bounded.  A block whose wait runs out goes `direct`: it never
+    // touches the buffers the copies may still be writing, reads its rows straight from global memory instead,
+    // leaves a note in the device status word, and before it exits waits once more (bounded again) so that it
+    // does not retire with copies of its own in flight.
+    bool staged = false, direct = false;
     if (use_bulk && cnt == kThreads) {
         if (tid == 0) mbar_init(&s_bar, 1);
         __syncthreads();
@@ -104,18 +107,19 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
             bulk_load(s_scales, scales + (size_t)base * 3, kThreads * 12u, &s_bar);
         }
         bulk_load(dyn4 + tid * kShRow4, shs + (size_t)i * 48, 192u, &s_bar);
-        bool ok = mbar_wait_bounded(&s_bar, 0);
-        if (!ok) ok = mbar_wait_bounded(&s_bar, 0);  // copies still in flight get a second, equally bounded chance
+        const bool ok = mbar_wait_bounded(&s_bar, 0, copy_polls);
         staged = __syncthreads_and(ok);
+        direct = !staged;
+        if (direct && tid == 0) atomicCAS(device_status, 0, DSB_STATUS_COPY_WAIT_FELL_BACK);   // never hides an error code
     }
-    if (!staged) {
+    if (!staged && !direct) {
         stage_floats(s_means, means + (size_t)base * 3, cnt * 3, tid);
         if (scales) stage_floats(s_scales, scales + (size_t)base * 3, cnt * 3, tid);
     }
 
     const int row_floats = 3 * cp.max_coeff;
     float* s_sh = reinterpret_cast<float*>(dyn4);
-    if (shs && !colors_precomp && !staged) {
+    if (shs && !colors_precomp && !staged && !direct) {
         if (sh_vec4) {  // 16 coefficients, 16-byte aligned rows: float4 in, padded float4 rows in shared memory
             const float4* g = reinterpret_cast<const float4*>(shs + (size_t)base * 48);
             const int total4 = cnt * 12;
@@ -142,7 +146,8 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
     float mx = 0.f, my = 0.f, mz = 0.f, opacity = 0.f;
     const bool live = tid < cnt;
     if (live) {
-        mx = s_means[3 * tid]; my = s_means[3 * tid + 1]; mz = s_means[3 * tid + 2];
+        const float* mrow = direct ? means + (size_t)i * 3 : s_means + 3 * tid;
+        mx = mrow[0]; my = mrow[1]; mz = mrow[2];
         opacity = opac[i];
         // 3-D covariance from scale and rotation (or taken as given).
         if (cov3d_precomp) {
@@ -153,8 +158,8 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
             float r = q.x, x = q.y, y = q.z, z = q.w;
             const float inv_norm = rsqrtf(r * r + x * x + y * y + z * z);
             r = r * inv_norm; x = x * inv_norm; y = y * inv_norm; z = z * inv_norm;
-            const float sx = s_scales[3 * tid] * cp.scale_modifier, sy = s_scales[3 * tid + 1] * cp.scale_modifier,
-                        sz = s_scales[3 * tid + 2] * cp.scale_modifier;
+            const float* srow = direct ? scales + (size_t)i * 3 : s_scales + 3 * tid;
+            const float sx = srow[0] * cp.scale_modifier, sy = srow[1] * cp.scale_modifier, sz = srow[2] * cp.scale_modifier;
             const float r00 = 1.0f - 2.0f * (y * y + z * z), r01 = 2.0f * (x * y - r * z), r02 = 2.0f * (x * z + r * y);
             const float r10 = 2.0f * (x * y + r * z), r11 = 1.0f - 2.0f * (x * x + z * z), r12 = 2.0f * (y * z - r * x);
             const float r20 = 2.0f * (x * z - r * y), r21 = 2.0f * (y * z + r * x), r22 = 1.0f - 2.0f * (x * x + y * y);
@@ -192,7 +197,8 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
                 dx = dx * inv_norm; dy = dy * inv_norm; dz = dz * inv_norm;
                 float f[48];
                 if (sh_vec4) {
-                    const float4* row = dyn4 + tid * kShRow4;
+                    // direct blocks (use_bulk implies 16-byte aligned rows) read the row where it lies
+                    const float4* row = direct ? reinterpret_cast<const float4*>(shs) + (size_t)i * 12 : dyn4 + tid * kShRow4;
     #pragma unroll
                     for (int j = 0; j < 12; ++j) {
                         const float4 v = row[j];
@@ -333,6 +339,14 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
         float* gcov = cov3d + (size_t)base * 6;
         for (int k = tid; k < cnt * 6; k += kThreads) gcov[k] = s_cov[k];
     }
+    if (direct) {   // block-uniform: the copies this block asked for must have landed before it retires
+        bool ok = false;
+        for (u32 poll = 0; poll < kCopyWaitPolls && !ok; ++poll) {
+            ok = mbar_try_wait(&s_bar, 0);
+            if (!ok) __nanosleep(64);
+        }
+        if (!ok && tid == 0) atomicExch(device_status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+    }
 }
 
 }  // namespace
@@ -377,8 +391,14 @@ int launch_preprocess_views(const CamParams* cps, int count, int n, const float*
     // the attribute belongs to the current device's context, so it is set at every launch rather than cached
     DSB_CUDA_CHECK(cudaFuncSetAttribute(preprocess_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
     const int blocks = (n + kThreads - 1) / kThreads;
+    int* device_status = nullptr;
+    {
+        const int rc = device_status_address(&device_status);
+        if (rc != DSB_OK) return rc;
+    }
     preprocess_kernel<<<blocks, kThreads, dyn, s>>>(pv, n, means, shs, colors_precomp, opac, scales, rots, cov3d_precomp, cov3d,
-                                                   sh_vec4, use_bulk, (int)tile_marks_copy_ints(cp.H, cp.W));
+                                                   sh_vec4, use_bulk, (int)tile_marks_copy_ints(cp.H, cp.W), copy_wait_polls(),
+                                                   device_status);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

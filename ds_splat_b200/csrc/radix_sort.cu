@@ -162,7 +162,8 @@ template <bool HAS_VALS, int NB, int ITEMS, bool FULL>
 __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin,
                                            u32* __restrict__ vout, const u32 n, const DigitSpec ds,
                                            const u32* __restrict__ hist, u32* __restrict__ lookback, int* __restrict__ status,
-                                           const u32 tile, const SweepShared sh) {
+                                           int* __restrict__ device_status, const u32 spin_limit, const u32 tile,
+                                           const SweepShared sh) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const u32 tile_base = tile * (u32)(kThreads * ITEMS);
     const u32 tile_n = FULL ? (u32)(kThreads * ITEMS) : n - tile_base;
@@ -252,7 +253,11 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
         while (p >= 0) {
             const u32 v = *(volatile const u32*)(lookback + (size_t)p * kRadix + tid);
             if ((v >> 30) == 0) {
-                if (++polls > kSpinLimit) { atomicExch(status, DSB_ERR_DEVICE_WAIT_EXPIRED); break; }
+                if (++polls > spin_limit) {
+                    atomicExch(status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                    atomicExch(device_status, DSB_ERR_DEVICE_WAIT_EXPIRED);
+                    break;
+                }
                 __nanosleep(40);
                 continue;
             }
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, DSB_SORT_MIN_BLOCKS)
 onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* __restrict__ vin, u32* __restrict__ vout,
                 const u32 n, const DigitSpec ds, const u32* __restrict__ hist, u32* __restrict__ tile_counter,
                 u32* __restrict__ lookback, int* __restrict__ status, const long long item_stride,
-                const long long ws_stride_u32) {
+                const long long ws_stride_u32, int* __restrict__ device_status, const u32 spin_limit) {
     extern __shared__ __align__(16) unsigned char dyn[];
     // blockIdx.y: which of the batch's independent lists (each with its own workspace slice)
     kin += blockIdx.y * item_stride; kout += blockIdx.y * item_stride;
@@ -317,21 +322,28 @@ onesweep_kernel(const u64* __restrict__ kin, u64* __restrict__ kout, const u32* 
     __syncthreads();
     const u32 tile = s_tile;
     if (n - tile * (u32)(kThreads * ITEMS) >= (u32)(kThreads * ITEMS))
-        sweep_tile<HAS_VALS, NB, ITEMS, true>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+        sweep_tile<HAS_VALS, NB, ITEMS, true>(kin, kout, vin, vout, n, ds, hist, lookback, status, device_status, spin_limit,
+                                              tile, sh);
     else
-        sweep_tile<HAS_VALS, NB, ITEMS, false>(kin, kout, vin, vout, n, ds, hist, lookback, status, tile, sh);
+        sweep_tile<HAS_VALS, NB, ITEMS, false>(kin, kout, vin, vout, n, ds, hist, lookback, status, device_status, spin_limit,
+                                               tile, sh);
 }
 
 template <bool HAS_VALS, int NB, int ITEMS>
 int launch_sweep(const u64* src, u64* dst, const u32* vsrc, u32* vdst, u32 n, const DigitSpec& ds, const u32* hist,
                  u32* tile_counter, u32* lookback, int* status, int64_t tiles, size_t dyn, int batch, long long item_stride,
-                 long long ws_stride_u32, cudaStream_t s) {
+                 long long ws_stride_u32, cudaStream_t s, u32 spin_limit = kSpinLimit) {
+    int* device_status = nullptr;
+    {
+        const int rc = device_status_address(&device_status);
+        if (rc != DSB_OK) return rc;
+    }
     // Keys alone fit the default 48 KB of shared memory per block; with values the block opts in to more.  The
     // attribute belongs to the current device's context, so it is set at every launch rather than cached.
     if (HAS_VALS || dyn + 10 * 1024 > 48 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(onesweep_kernel<HAS_VALS, NB, ITEMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     onesweep_kernel<HAS_VALS, NB, ITEMS><<<dim3((unsigned)tiles, (unsigned)batch), kThreads, dyn, s>>>(
-        src, dst, vsrc, vdst, n, ds, hist, tile_counter, lookback, status, item_stride, ws_stride_u32);
+        src, dst, vsrc, vdst, n, ds, hist, tile_counter, lookback, status, item_stride, ws_stride_u32, device_status, spin_limit);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
@@ -471,6 +483,38 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
         items, (u32)k, plan, hist, item_stride, batch > 1 ? sort_batch_stride_bytes(k) / 4 : 0);
     DSB_LAUNCH_CHECK();
     return sort_passes(items, items_alt, vals, vals_alt, k, plan, ws, in_alt, s, batch, item_stride);
+}
+
+// Test hook.  One histogram + ONE pass (so nothing ever reads the incomplete output) over a list of at least two
+// tiles in which the tile counter starts at 1: tile 0 is never processed, never publishes its counts, and the
+// block that took tile 1 polls tile 0's status words `spin_limit` times, gives up, records
+// DSB_ERR_DEVICE_WAIT_EXPIRED in the workspace status word and in the device status word, and finishes like every
+// other block.  All stores stay inside the buffers: a block's destination is the digit's global start plus the
+// counts of earlier tiles it did see plus its own rank, which never exceeds the digit's true range.
+int debug_expire_sort_wait(u64* items, u64* items_alt, int64_t k, int begin_bit, int end_bit, void* ws, int64_t ws_bytes,
+                           u32 spin_limit, cudaStream_t s) {
+    int rc = check_sort_args(items, items_alt, ws, k, begin_bit, end_bit);
+    if (rc != DSB_OK) return rc;
+    DSB_REQUIRE(end_bit - begin_bit <= 8, "debug_expire_sort_wait: one pass only (at most 8 bits)");
+    DSB_REQUIRE(k >= 2 * (int64_t)kTileItems, "debug_expire_sort_wait: needs at least two tiles of %d items", kTileItems);
+    DSB_REQUIRE(spin_limit >= 1 && spin_limit <= 100000, "debug_expire_sort_wait: spin_limit must be in 1..100000");
+    SortPlan plan = make_sort_plan(begin_bit, end_bit, false);
+    plan.tile_items = kTileItems;
+    u32* hist = nullptr;
+    rc = sort_begin(k, plan, ws, ws_bytes, &hist, s, 1);
+    if (rc != DSB_OK) return rc;
+    const int64_t chunks = (k + kThreads * 4 - 1) / (kThreads * 4);
+    radix_histogram_kernel<<<dim3((unsigned)(chunks < 1184 ? chunks : 1184), 1), kThreads, 0, s>>>(items, (u32)k, plan, hist, 0, 0);
+    DSB_LAUNCH_CHECK();
+    SortHeader* hdr = reinterpret_cast<SortHeader*>(ws);
+    static const u32 kOne = 1;
+    DSB_CUDA_CHECK(cudaMemcpyAsync(&hdr->tile_counter[0], &kOne, sizeof(u32), cudaMemcpyHostToDevice, s));
+    const int64_t tiles = tiles_of(k, plan);
+    DigitSpec ds;
+    ds.high = plan.shift[0] >= 32; ds.sh = plan.shift[0] & 31; ds.mask = plan.mask[0]; ds.flip = plan.flip[0];
+    return launch_sweep<false, 8, kItems>(items, items_alt, nullptr, nullptr, (u32)k, ds, hdr->hist[0], &hdr->tile_counter[0],
+                                          reinterpret_cast<u32*>(hdr + 1), &hdr->status, tiles - 1, (size_t)kTileItems * sizeof(u64),
+                                          1, 0, 0, s, spin_limit);
 }
 
 // ---- sort without any allocation ------------------------------------------------------------------

@@ -3,8 +3,9 @@
 // issuing block's own shared memory are used; nothing here multicasts.
 //
 // Rules the callers must keep: source and destination 16-byte aligned, size a multiple of 16 bytes.
-// Waiting is bounded: mbar_wait_bounded() gives up after a fixed number of polls and returns false, and
-// every caller then falls back to ordinary loads, so a kernel can never hang on a copy.
+// Waiting is bounded: mbar_wait_bounded() gives up after a fixed number of polls and returns false; the
+// caller then reads its data with ordinary loads into buffers the copies do not write, and waits again
+// (bounded) before its block exits, so a kernel can neither hang on a copy nor retire with one in flight.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>

@@ -32,6 +32,21 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+def _on_own_device(method):
+    """Runs a method with the object's device (``self.dev``) current: the library launches on the current device and
+    stream, so a renderer whose tensors live on another GPU than the current one must switch first."""
+    import functools
+
+    @functools.wraps(method)
+    def wrapped(self, *args, **kwargs):
+        dev = torch.device(self.dev)
+        if dev.type != "cuda":
+            raise RuntimeError(f"{type(self).__name__} launches CUDA kernels; its tensors are on {dev}")
+        with torch.cuda.device(dev):
+            return method(self, *args, **kwargs)
+    return wrapped
+
+
 SEGMENTS = (("means3d", 3), ("shs", 48), ("opacities", 1), ("scales", 3), ("rotations", 4))
 FLOATS_PER_SPLAT = sum(w for _, w in SEGMENTS)  # 59
 
@@ -44,19 +59,27 @@ def shard_views(num_views: int, rank: int, world_size: int) -> List[int]:
 
 
 class GradientBuffer:
-    """Flat fp32 gradient block with per-tensor views (see module docstring)."""
+    """Flat fp32 gradient block with per-tensor views (see module docstring).  ``shards`` > 1 pads the allocation to
+    ``shards`` equal slices of whole 16-byte lanes, the form reduce-scatter and all-gather take (``ShardedAdam``)."""
 
-    def __init__(self, n: int, device, sh_coeffs: int = 16):
+    def __init__(self, n: int, device, sh_coeffs: int = 16, shards: int = 1):
         self.n = n
+        self.sh_coeffs = sh_coeffs
         widths = dict(SEGMENTS)
         widths["shs"] = 3 * sh_coeffs
-        self.flat = torch.zeros(n * sum(widths.values()), dtype=torch.float32, device=device)
+        self.length = n * sum(widths.values())            # elements that carry gradients
+        quantum = 4 * max(1, int(shards))
+        padded = (self.length + quantum - 1) // quantum * quantum
+        self.storage = torch.zeros(padded, dtype=torch.float32, device=device)   # the padded allocation
+        self.flat = self.storage[:self.length]
         self.views: Dict[str, torch.Tensor] = {}
+        self.segments: Dict[str, tuple] = {}              # name -> (first element, one past the last) in the flat block
         off = 0
         for name, _ in SEGMENTS:
             w = widths[name]
             v = self.flat[off:off + n * w]
             self.views[name] = v.view(n, sh_coeffs, 3) if name == "shs" else v.view(n, w)
+            self.segments[name] = (off, off + n * w)
             off += n * w
 
     def zero_(self):
@@ -64,6 +87,20 @@ class GradientBuffer:
 
     def nbytes(self) -> int:
         return self.flat.numel() * 4
+
+
+class ParameterBuffer(GradientBuffer):
+    """The five parameter tensors of a splat cloud in ONE allocation laid out like the gradient block, so that a
+    rank's slice of the gradients lines up with the same slice of the parameters (``ShardedAdam``).  ``views`` are
+    what ``ViewRenderer`` takes as its tensors."""
+
+    @staticmethod
+    def from_tensors(params: Dict[str, torch.Tensor], shards: int = 1) -> "ParameterBuffer":
+        means = params["means3d"]
+        buf = ParameterBuffer(means.shape[0], means.device, sh_coeffs=params["shs"].shape[1], shards=shards)
+        for name, _ in SEGMENTS:
+            buf.views[name].copy_(params[name].reshape(buf.views[name].shape))
+        return buf
 
 
 def allreduce_gradients(buf: GradientBuffer, group=None) -> None:
@@ -195,6 +232,7 @@ class ViewRenderer:
         self.view_streams = max(1, int(view_streams))   # lanes render_views spreads a batch's views over
         self.lanes = [_Lane()]
         self.last_k = 0
+        self.last_ks = []
 
     # buffers of the view rendered last (kept as attributes for callers that inspect them)
     records = property(lambda self: self.cur.records)
@@ -271,20 +309,35 @@ class ViewRenderer:
         self._last_cam = cam
         return image
 
+    @_on_own_device
     def forward(self, cam: CameraTensors, slot: int = 0):
         """Returns the image tensor (owned by the renderer, overwritten by the next call of the same size)."""
         capi, lib, p = self._capi, self.lib, self.p
         sl = self._slot(slot)
         sl.cam = self._camera(cam)
-        k = C.c_int64(0)
-        capi.check(lib.dsb_forward_plan(
+        # plan and render in one library call when the pair buffers of the previous view are large enough (they are
+        # kept with 25% slack), so that no host work sits between the pair-count read-back and the render
+        ln = self.lanes[0]
+        cap = 0 if ln.pairs is None else ln.pairs.shape[1]
+        image, final_t, final_idx = self._image_buffers(cam.H, cam.W, 0)
+        ranges = self._ranges(sl, cam.H, cam.W)
+        k, rendered = C.c_int64(0), C.c_int32(0)
+        capi.check(lib.dsb_forward(
             C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
             p["scales"].data_ptr(), p["rotations"].data_ptr(), None, sl.records.data_ptr(), sl.radii.data_ptr(),
             sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_rows[1, slot].data_ptr(),
             sl.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
-            C.byref(k), capi.stream_ptr()))
-        return self._render(sl, cam, int(k.value))
+            ln.pairs[0].data_ptr() if cap else None, ln.pairs[1].data_ptr() if cap else None, cap,
+            ln.sort_ws.data_ptr() if cap else None, ln.sort_bytes if cap else 0, ranges.data_ptr(), image.data_ptr(),
+            final_t.data_ptr(), final_idx.data_ptr(), None, C.byref(k), C.byref(rendered), capi.stream_ptr()))
+        if not rendered.value:
+            return self._render(sl, cam, int(k.value))
+        self.last_k = int(k.value)
+        self.cur = sl
+        self._last_cam = cam
+        return image
 
+    @_on_own_device
     def backward(self, v_image: torch.Tensor, grads: GradientBuffer, accumulate: bool = True):
         """Backward of the view rendered by the last forward(); adds into (or overwrites) ``grads``."""
         capi, lib, p = self._capi, self.lib, self.p
@@ -300,6 +353,7 @@ class ViewRenderer:
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 
+    @_on_own_device
     def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False,
                      stats: Optional[DensifyStats] = None):
         """Forward + backward of ``cameras`` with the gradients of all of them summed into ``grads`` (added to its
@@ -313,6 +367,7 @@ class ViewRenderer:
         capi, lib, p = self._capi, self.lib, self.p
         g = grads.views
         b0, first = 0, True
+        self.last_ks = []          # pair count of every view of this call
         while b0 < len(cameras):
             size = (cameras[b0].H, cameras[b0].W)
             b1 = b0 + 1
@@ -341,6 +396,7 @@ class ViewRenderer:
             ks = (C.c_int64 * nv)()
             capi.check(lib.dsb_plan_totals_views(nv, self.n, self.plan_ws.data_ptr(), self.plan_bytes, ks,
                                                  capi.stream_ptr()))
+            self.last_ks.extend(int(k) for k in ks)
             # The K-sized stages of the views, dealt over the lanes: lane 0 is the caller's stream, the others wait for
             # the batch's plan, and the caller's stream waits for them before the per-splat backward.
             planned = torch.cuda.Event()
@@ -394,10 +450,16 @@ class ImageLoss:
         self.losses = []
 
     def gradient(self, image: torch.Tensor, target: torch.Tensor):
+        if not image.is_cuda or target.device != image.device:
+            raise RuntimeError(f"ImageLoss launches CUDA kernels: image is on {image.device}, target on {target.device}")
+        with torch.cuda.device(image.device):
+            return self._gradient(image, target)
+
+    def _gradient(self, image: torch.Tensor, target: torch.Tensor):
         h, w = image.shape[0], image.shape[1]
         # one set of buffers per stream: render_views calls this under the stream of the view's lane, and a buffer
         # shared by two lanes would be rewritten while the other lane's backward still reads it
-        stream = torch.cuda.current_stream(image.device).cuda_stream if image.is_cuda else 0
+        stream = self._capi.stream_ptr(image.device)
         key = (h, w, image.device, stream)
         if key not in self.buf:
             nbytes = int(self.lib.dsb_image_loss_workspace_bytes(h, w))
@@ -406,8 +468,7 @@ class ImageLoss:
         loss = torch.empty(1, dtype=torch.float32, device=image.device)
         image, target = image.contiguous(), target.contiguous()
         self._capi.check(self.lib.dsb_image_loss_backward(image.data_ptr(), target.data_ptr(), h, w, self.lam, ws.data_ptr(),
-                                                          ws.numel(), v_image.data_ptr(), loss.data_ptr(),
-                                                          self._capi.stream_ptr()))
+                                                          ws.numel(), v_image.data_ptr(), loss.data_ptr(), stream))
         return v_image, loss
 
     def __call__(self, index: int, image: torch.Tensor):
@@ -429,9 +490,11 @@ class FlatAdam:
         self.step_count = 0
         n = params["means3d"].shape[0]
         dev = params["means3d"].device
+        self.dev = dev
         self.m = GradientBuffer(n, dev, sh_coeffs=params["shs"].shape[1])
         self.v = GradientBuffer(n, dev, sh_coeffs=params["shs"].shape[1])
 
+    @_on_own_device
     def step(self, grads: GradientBuffer, grad_scale: float = 1.0):
         self.step_count += 1
         for name, _ in SEGMENTS:
@@ -444,6 +507,104 @@ class FlatAdam:
                 float(grad_scale), self._capi.stream_ptr()))
 
 
+def _group_info(group=None):
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+def _adam_kernel_update(capi):
+    lib = capi.lib()
+
+    def update(p, g, m, v, lr, beta1, beta2, eps, step, grad_scale):
+        with torch.cuda.device(p.device):
+            capi.check(lib.dsb_adam_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), float(lr),
+                                         float(beta1), float(beta2), float(eps), int(step), float(grad_scale),
+                                         capi.stream_ptr(p.device)))
+    return update
+
+
+class ShardedAdam:
+    """The optimizer step of a data-parallel training step with the gradient sum folded in:
+
+        reduce-scatter of the flat gradient block  ->  Adam on this rank's 1/G slice  ->  all-gather of the parameters
+
+    instead of all-reduce + Adam over everything on every rank.  The bytes that cross NVLink are those of the
+    all-reduce (a ring all-reduce is this reduce-scatter followed by this all-gather), the optimizer pass and its
+    moment buffers shrink to 1/G per rank, and the parameters every rank holds afterwards are identical to the
+    replicated form's up to the order in which the ranks' gradients are summed.  Both collectives run in place on
+    the two flat allocations (``GradientBuffer`` / ``ParameterBuffer`` built with ``shards=world_size``): the kernels'
+    output buffer is the communication buffer.  In a single process it degenerates to plain Adam over everything.
+
+    ``update`` is the per-slice Adam update, ``update(p, g, m, v, lr, beta1, beta2, eps, step, grad_scale)`` in place on
+    flat tensors; the default launches ``dsb_adam_step``.  (Tests on CPU ranks pass the checker's update.)"""
+
+    def __init__(self, params: ParameterBuffer, lrs: Dict[str, float], betas=(0.9, 0.999), eps: float = 1e-15, group=None,
+                 update=None):
+        self.params, self.lrs, self.betas, self.eps, self.group = params, dict(lrs), betas, float(eps), group
+        self.world, self.rank = _group_info(group)
+        total = params.storage.numel()
+        if total % (4 * self.world) != 0:
+            raise ValueError(f"the parameter block of {total} elements does not split into {self.world} slices of whole "
+                             f"16-byte lanes: build ParameterBuffer and GradientBuffer with shards={self.world}")
+        self.chunk = total // self.world
+        self.lo, self.hi = self.rank * self.chunk, (self.rank + 1) * self.chunk
+        dev = params.storage.device
+        self.m = torch.zeros(self.chunk, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.chunk, dtype=torch.float32, device=dev)
+        # the parts of this rank's slice that belong to each parameter tensor (each has its own learning rate)
+        self.pieces = []
+        for name, _ in SEGMENTS:
+            a, b = params.segments[name]
+            a, b = max(a, self.lo), min(b, self.hi)
+            if a < b:
+                self.pieces.append((name, a, b))
+        self.step_count = 0
+        if update is None:
+            from . import _capi
+            update = _adam_kernel_update(_capi)
+        self.update = update
+
+    def step(self, grads: GradientBuffer, grad_scale: float = 1.0):
+        import torch.distributed as dist
+        if grads.storage.numel() != self.params.storage.numel():
+            raise ValueError("gradient and parameter blocks are laid out differently")
+        self.step_count += 1
+        g_slice = grads.storage[self.lo:self.hi]
+        if self.world > 1:
+            dist.reduce_scatter_tensor(g_slice, grads.storage, op=dist.ReduceOp.SUM, group=self.group)
+        for name, a, b in self.pieces:
+            self.update(self.params.storage[a:b], grads.storage[a:b], self.m[a - self.lo:b - self.lo],
+                        self.v[a - self.lo:b - self.lo], self.lrs[name], self.betas[0], self.betas[1], self.eps,
+                        self.step_count, grad_scale)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.params.storage, self.params.storage[self.lo:self.hi], group=self.group)
+
+
+def register_with_nccl(make_buffers, group=None):
+    """Runs ``make_buffers()`` (a callable that allocates and returns the communication buffers) under a memory
+    pool of NCCL's own allocator and registers that pool with the process group, so that the collectives on those
+    buffers take NCCL's registered-buffer path (zero-copy, and in-switch reduction over NVSwitch where the
+    communicator has it).  Returns (buffers, pool or None): when the backend has no such allocator (gloo, an older
+    NCCL) or registration fails, the buffers come from torch's ordinary allocator and the second value is None --
+    the collectives still run, through NCCL's staging buffers.  Keep the pool alive as long as the buffers."""
+    import torch.distributed as dist
+    try:
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_backend(group) != "nccl":
+            return make_buffers(), None
+        backend = (group or dist.group.WORLD)._get_backend(torch.device("cuda"))
+        if not getattr(backend, "supports_mem_allocator", True):
+            return make_buffers(), None
+        pool = torch.cuda.MemPool(backend.mem_allocator)
+        with torch.cuda.use_mem_pool(pool):
+            buffers = make_buffers()
+        backend.register_mem_pool(pool)
+        return buffers, pool
+    except Exception:   # anything the running torch / NCCL pair does not offer: plain buffers
+        return make_buffers(), None
+
+
 def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads,
                        grads: GradientBuffer, group=None, stats: Optional[DensifyStats] = None) -> None:
     """One step of the multi-view batch on this rank: forward + backward of each local camera (gradients
@@ -454,3 +615,15 @@ def data_parallel_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors],
     else:
         renderer.render_views(cameras, image_grads, grads, accumulate=False, stats=stats)
     allreduce_gradients(grads, group)
+
+
+def training_step(renderer: ViewRenderer, cameras: Sequence[CameraTensors], image_grads, grads: GradientBuffer,
+                  optimizer: ShardedAdam, grad_scale: float = 1.0, stats: Optional[DensifyStats] = None) -> None:
+    """One whole training step on this rank: forward + backward of its cameras, then ``ShardedAdam.step`` (gradient
+    reduce-scatter, Adam on the rank's slice, parameter all-gather).  The renderer must have been built on the views
+    of the optimizer's ``ParameterBuffer`` so that the next step renders the updated cloud."""
+    if len(cameras) == 0:
+        grads.zero_()
+    else:
+        renderer.render_views(cameras, image_grads, grads, accumulate=False, stats=stats)
+    optimizer.step(grads, grad_scale=grad_scale)

@@ -74,6 +74,22 @@ class GaussianRasterizationSettings:
 
 
 def _camera_for(settings: GaussianRasterizationSettings, device):
+    """DsbCamera of the settings, rebuilt only when a field or a settings tensor changed since the last call (the
+    reference rebuilds its settings struct and transposes both matrices on every call, ds_splat/rasterizer.py:137-155)."""
+    tensors = (settings.viewmatrix, settings.projmatrix, settings.campos, settings.bg)
+    # The camera block only holds device POINTERS, so it stays valid while the settings tensors stay where they are
+    # (their contents may change in place).  Tensors that first have to be converted are not cached.
+    direct = all(t is None or (isinstance(t, torch.Tensor) and t.device == device and t.dtype == torch.float32
+                               and t.is_contiguous()) for t in tensors)
+    key = None
+    if direct:
+        key = (device, settings.image_height, settings.image_width, settings.tanfovx, settings.tanfovy,
+               settings.scale_modifier, settings.sh_degree, settings.max_sh_degree, settings.strict_reference,
+               settings.tight_tiles, tuple(0 if t is None else t.data_ptr() for t in tensors))
+        cached = getattr(settings, "_dsb_camera", None)
+        if cached is not None and cached[0] == key:
+            return cached[1], cached[2]
+
     def dev_f32(t, name, numel):
         if not isinstance(t, torch.Tensor):
             t = torch.as_tensor(t, dtype=torch.float32)
@@ -85,17 +101,70 @@ def _camera_for(settings: GaussianRasterizationSettings, device):
     proj = dev_f32(settings.projmatrix, "projmatrix", 16)
     campos = dev_f32(settings.campos, "campos", 3)
     bg = dev_f32(settings.bg, "bg", 3) if settings.bg is not None else None
-    if settings.max_sh_degree != 3 and settings.max_sh_degree not in (0, 1, 2):
+    if settings.max_sh_degree not in (0, 1, 2, 3):
         raise ValueError("max_sh_degree must be in 0..3")
-    return _capi.make_camera(settings.image_height, settings.image_width, settings.tanfovx, settings.tanfovy, view,
-                             proj, campos, bg, settings.sh_degree, settings.max_sh_degree, settings.scale_modifier,
-                             transposed=True, drop_last=settings.strict_reference, tight_tiles=settings.tight_tiles)
+    cam, keep = _capi.make_camera(settings.image_height, settings.image_width, settings.tanfovx, settings.tanfovy, view,
+                                  proj, campos, bg, settings.sh_degree, settings.max_sh_degree, settings.scale_modifier,
+                                  transposed=True, drop_last=settings.strict_reference, tight_tiles=settings.tight_tiles)
+    if key is not None:
+        settings._dsb_camera = (key, cam, keep)
+    return cam, keep
+
+
+def _up256(nbytes: int) -> int:
+    return (nbytes + 255) & ~255
+
+
+class _Layout:
+    """Byte offsets of the operator's internal buffers inside ONE allocation per call (the reference allocates
+    about twenty tensors per forward, cpp/rasterizer_torch.cu:139-157,52-53,90,106-107): everything whose size
+    follows from N and the image size.  Pure arithmetic, cached per (N, H, W)."""
+    _cache = {}
+
+    def __init__(self, n, h, w, lib):
+        off = 0
+
+        def take(nbytes):
+            nonlocal off
+            at = off
+            off += _up256(max(int(nbytes), 1))
+            return at
+
+        self.plan_bytes = int(lib.dsb_plan_workspace_bytes(n))
+        self.records = take(n * _capi.RECORD_FLOATS * 4)
+        self.tiles = take(n * 4)
+        self.cov3d = take(n * 24)
+        self.depth_keys = take(n * 8)
+        self.depth_keys_alt = take(n * 8)
+        self.offsets = take(n * 4)
+        self.tile_marks = take(int(lib.dsb_tile_marks_bytes(h, w)))
+        self.plan_ws = take(self.plan_bytes)
+        self.ranges = take((_capi.num_tiles(h, w) + 1) * 4)
+        self.final_t = take(h * w * 4)
+        self.final_idx = take(h * w * 4)
+        self.grad_acc = take(n * _capi.GRAD_FLOATS * 4)
+        self.total = off
+
+    @classmethod
+    def of(cls, n, h, w, lib):
+        key = (n, h, w)
+        got = cls._cache.get(key)
+        if got is None:
+            if len(cls._cache) > 64:
+                cls._cache.clear()
+            got = cls._cache[key] = cls(n, h, w, lib)
+        return got
+
+
+# pair count of the last forward per (device, N, H, W): the next call of that shape brings buffers for 25% more, so
+# that the render can follow the pair-count read-back inside one library call
+_pair_hint = {}
 
 
 class DsRasterizerFunction(torch.autograd.Function):
     """Counterpart of the reference's autograd Function (ds_splat/rasterizer.py:7-112): eight tensor inputs
     plus the settings; returns (image, radii) -- (image, radii, depth) with ``return_depth`` -- and backward returns
-    one gradient per tensor input."""
+    one gradient per tensor input, shaped like that input."""
 
     @staticmethod
     def forward(ctx, means_3d, means_2d, shs, colors_precomp, opacities, scales, rotations, cov_3d_precomp,
@@ -104,6 +173,8 @@ class DsRasterizerFunction(torch.autograd.Function):
         if not isinstance(means_3d, torch.Tensor) or not means_3d.is_cuda:
             raise RuntimeError("means_3d must be a CUDA tensor")
         dev = means_3d.device
+        shapes = tuple(t.shape if isinstance(t, torch.Tensor) else None
+                       for t in (means_3d, means_2d, shs, colors_precomp, opacities, scales, rotations, cov_3d_precomp))
         means_3d = _capi.as_f32(means_3d, dev, "means_3d")
         if means_3d is None:
             raise RuntimeError("means_3d is empty")
@@ -129,46 +200,48 @@ class DsRasterizerFunction(torch.autograd.Function):
         with torch.cuda.device(dev):
             cam, keep = _camera_for(raster_settings, dev)
             stream = _capi.stream_ptr()
-            f32 = dict(dtype=torch.float32, device=dev)
-            records = torch.empty((n, _capi.RECORD_FLOATS), **f32)
+            lay = _Layout.of(n, h, w, lib)
+            arena = torch.empty(lay.total, dtype=torch.uint8, device=dev)
+            a = arena.data_ptr()
             radii = torch.empty(n, dtype=torch.int32, device=dev)
-            tiles = torch.empty(n, dtype=torch.int32, device=dev)
-            cov3d = cov_3d_precomp if cov_3d_precomp is not None else torch.empty((n, 6), **f32)
-            depth_keys = torch.empty((2, n), dtype=torch.int64, device=dev)
-            offsets = torch.empty(n, dtype=torch.int32, device=dev)
-            tile_marks = torch.empty(int(lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device=dev)
-            plan_bytes = int(lib.dsb_plan_workspace_bytes(n))
-            plan_ws = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
-            k = C.c_int64(0)
-            _capi.check(lib.dsb_forward_plan(
-                C.byref(cam), n, _capi.ptr(means_3d), _capi.ptr(shs), _capi.ptr(colors_precomp), _capi.ptr(opacities),
-                _capi.ptr(scales), _capi.ptr(rotations), _capi.ptr(cov_3d_precomp), records.data_ptr(), radii.data_ptr(),
-                tiles.data_ptr(), cov3d.data_ptr(), depth_keys[0].data_ptr(), depth_keys[1].data_ptr(),
-                offsets.data_ptr(), tile_marks.data_ptr(), plan_ws.data_ptr(), plan_bytes, C.byref(k), stream))
-            k = int(k.value)
+            image = torch.empty((h, w, 3), dtype=torch.float32, device=dev)
+            depth = torch.empty((h, w), dtype=torch.float32, device=dev) if raster_settings.return_depth else None
+            cov3d_ptr = cov_3d_precomp.data_ptr() if cov_3d_precomp is not None else a + lay.cov3d
 
-            pairs = torch.empty((2, max(k, 1)), dtype=torch.int64, device=dev)
-            sort_bytes = int(lib.dsb_sort_workspace_bytes(k))
-            sort_ws = torch.empty(sort_bytes, dtype=torch.uint8, device=dev)
-            ranges = torch.empty(_capi.num_tiles(h, w) + 1, dtype=torch.int32, device=dev)
-            image = torch.empty((h, w, 3), **f32)
-            final_t = torch.empty((h, w), **f32)
-            final_idx = torch.empty((h, w), dtype=torch.int32, device=dev)
-            depth = torch.empty((h, w), **f32) if raster_settings.return_depth else None
-            _capi.check(lib.dsb_forward_render(
-                C.byref(cam), n, k, records.data_ptr(), tiles.data_ptr(), depth_keys[0].data_ptr(), offsets.data_ptr(),
-                pairs[0].data_ptr(), pairs[1].data_ptr(), tile_marks.data_ptr(), sort_ws.data_ptr(), sort_bytes,
-                ranges.data_ptr(),
-                image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), _capi.ptr(depth), None, stream))
-            sorted_pairs = pairs[0][:k]
+            hint_key = (dev, n, h, w, raster_settings.tight_tiles)
+            cap = max(int(_pair_hint.get(hint_key, 8 * n) * 1.25), 1024)
+            sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
+            pair_arena = torch.empty(2 * _up256(cap * 8) + sort_bytes, dtype=torch.uint8, device=dev)
+            b = pair_arena.data_ptr()
+            k, rendered = C.c_int64(0), C.c_int32(0)
+            _capi.check(lib.dsb_forward(
+                C.byref(cam), n, _capi.ptr(means_3d), _capi.ptr(shs), _capi.ptr(colors_precomp), _capi.ptr(opacities),
+                _capi.ptr(scales), _capi.ptr(rotations), _capi.ptr(cov_3d_precomp), a + lay.records, radii.data_ptr(),
+                a + lay.tiles, cov3d_ptr, a + lay.depth_keys, a + lay.depth_keys_alt, a + lay.offsets, a + lay.tile_marks,
+                a + lay.plan_ws, lay.plan_bytes, b, b + _up256(cap * 8), cap, b + 2 * _up256(cap * 8), sort_bytes,
+                a + lay.ranges, image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth),
+                C.byref(k), C.byref(rendered), stream))
+            k = int(k.value)
+            _pair_hint[hint_key] = k
+            if not rendered.value:   # more pairs than the buffers brought along hold: grow them and render
+                cap = max(k, 1)
+                sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
+                pair_arena = torch.empty(2 * _up256(cap * 8) + sort_bytes, dtype=torch.uint8, device=dev)
+                b = pair_arena.data_ptr()
+                _capi.check(lib.dsb_forward_render(
+                    C.byref(cam), n, k, a + lay.records, a + lay.tiles, a + lay.depth_keys, a + lay.offsets, b,
+                    b + _up256(cap * 8), a + lay.tile_marks, b + 2 * _up256(cap * 8), sort_bytes, a + lay.ranges,
+                    image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth), None, stream))
 
         ctx.raster_settings = raster_settings
         ctx.num_pairs = k
+        ctx.layout = lay
+        ctx.shapes = shapes
         ctx.had = (shs is not None, colors_precomp is not None, scales is not None, rotations is not None,
                    cov_3d_precomp is not None)
-        ctx.save_for_backward(means_3d, scales if scales is not None else means_3d.new_empty(0),
-                              rotations if rotations is not None else means_3d.new_empty(0), records, cov3d, radii,
-                              sorted_pairs, ranges, final_t, final_idx, tile_marks)
+        empty = means_3d.new_empty(0)
+        ctx.save_for_backward(means_3d, scales if scales is not None else empty, rotations if rotations is not None else empty,
+                              cov_3d_precomp if cov_3d_precomp is not None else empty, arena, pair_arena, radii)
         ctx.mark_non_differentiable(radii)
         if raster_settings.channels_first:
             image = image.permute(2, 0, 1)
@@ -179,25 +252,26 @@ class DsRasterizerFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, rendered_img_grad, _radii_grad, depth_grad=None):
         lib = _capi.lib()
-        (means_3d, scales, rotations, records, cov3d, radii, sorted_pairs, ranges, final_t, final_idx,
-         tile_order) = ctx.saved_tensors
-        settings = ctx.raster_settings
+        means_3d, scales, rotations, cov_3d_precomp, arena, pair_arena, radii = ctx.saved_tensors
+        settings, lay = ctx.raster_settings, ctx.layout
         had_shs, had_colors, had_scales, had_rots, had_cov = ctx.had
         dev = means_3d.device
         n = means_3d.shape[0]
+        h, w = settings.image_height, settings.image_width
         if rendered_img_grad is None:  # only the depth map took part in the loss
-            rendered_img_grad = final_t.new_zeros((settings.image_height, settings.image_width, 3))
+            rendered_img_grad = means_3d.new_zeros((h, w, 3))
         elif settings.channels_first:
             rendered_img_grad = rendered_img_grad.permute(1, 2, 0)
         v_image = rendered_img_grad.to(dtype=torch.float32).contiguous()
         v_depth = depth_grad.to(dtype=torch.float32).contiguous() if depth_grad is not None else None
         need = ctx.needs_input_grad
         coeffs = (settings.max_sh_degree + 1) ** 2
+        a = arena.data_ptr()
+        cov3d_ptr = cov_3d_precomp.data_ptr() if had_cov else a + lay.cov3d
 
         with torch.cuda.device(dev):
             cam, keep = _camera_for(settings, dev)
             f32 = dict(dtype=torch.float32, device=dev)
-            grad_acc = torch.empty((n, _capi.GRAD_FLOATS), **f32)
             v_means3d = torch.empty((n, 3), **f32) if need[0] else None
             v_means2d = torch.empty((n, 3), **f32) if need[1] else None
             v_shs = torch.empty((n, coeffs, 3), **f32) if (need[2] and had_shs) else None
@@ -207,14 +281,16 @@ class DsRasterizerFunction(torch.autograd.Function):
             v_rots = torch.empty((n, 4), **f32) if (need[6] and had_scales and had_rots) else None
             v_cov3d = torch.empty((n, 6), **f32) if (need[7] and had_cov) else None
             _capi.check(lib.dsb_backward(
-                C.byref(cam), n, means_3d.data_ptr(), _capi.ptr(scales), _capi.ptr(rotations), records.data_ptr(),
-                cov3d.data_ptr(), radii.data_ptr(), _capi.ptr(sorted_pairs), ranges.data_ptr(), final_t.data_ptr(),
-                final_idx.data_ptr(), v_image.data_ptr(), _capi.ptr(v_depth), tile_order.data_ptr(), grad_acc.data_ptr(),
-                _capi.ptr(v_means3d),
-                _capi.ptr(v_means2d),
-                _capi.ptr(v_shs), _capi.ptr(v_colors), _capi.ptr(v_opac), _capi.ptr(v_scales), _capi.ptr(v_rots),
-                _capi.ptr(v_cov3d), 0, _capi.stream_ptr()))
-        return v_means3d, v_means2d, v_shs, v_colors, v_opac, v_scales, v_rots, v_cov3d, None
+                C.byref(cam), n, means_3d.data_ptr(), _capi.ptr(scales), _capi.ptr(rotations), a + lay.records,
+                cov3d_ptr, radii.data_ptr(), pair_arena.data_ptr() if ctx.num_pairs else None, a + lay.ranges,
+                a + lay.final_t, a + lay.final_idx, v_image.data_ptr(), _capi.ptr(v_depth), a + lay.tile_marks,
+                a + lay.grad_acc, _capi.ptr(v_means3d), _capi.ptr(v_means2d), _capi.ptr(v_shs), _capi.ptr(v_colors),
+                _capi.ptr(v_opac), _capi.ptr(v_scales), _capi.ptr(v_rots), _capi.ptr(v_cov3d), 0, _capi.stream_ptr()))
+        grads = [v_means3d, v_means2d, v_shs, v_colors, v_opac, v_scales, v_rots, v_cov3d]
+        # gradients take the shape the caller's tensors had (opacities of shape [N], flattened shs, ...)
+        grads = [g.view(shape) if g is not None and shape is not None and tuple(g.shape) != tuple(shape) else g
+                 for g, shape in zip(grads, ctx.shapes)]
+        return (*grads, None)
 
 
 class GaussianRasterizer(torch.nn.Module):

@@ -133,6 +133,18 @@ def ring_views(count: int, radius: float, W: int, H: int, focal: float, seed: in
     return out
 
 
+def jittered_views(count: int, radius: float, W: int, H: int, focal: float, seed: int, degrees: float = 5.0) -> list:
+    """``count`` cameras at ``radius`` from the origin looking at it: the first is the canonical one on the -z axis,
+    the others are turned away from it by yaw and pitch angles drawn from U[-degrees, degrees] (seeded)."""
+    rng = np.random.default_rng(seed)
+    out = [make_view((0.0, 0.0, -radius), (0.0, 0.0, 0.0), W, H, focal)]
+    for _ in range(1, count):
+        yaw, pitch = (math.radians(float(a)) for a in rng.uniform(-degrees, degrees, size=2))
+        eye = (radius * math.sin(yaw) * math.cos(pitch), radius * math.sin(pitch), -radius * math.cos(yaw) * math.cos(pitch))
+        out.append(make_view(eye, (0.0, 0.0, 0.0), W, H, focal))
+    return out
+
+
 def tiny(n: int = 20_000, seed: int = 1000, W: int = 640, H: int = 480, focal: float = 600.0) -> Scene:
     """Config 0: uniform box [-2,2]^3, camera at z=-5 looking +z."""
     rng = np.random.default_rng(seed)
@@ -142,14 +154,17 @@ def tiny(n: int = 20_000, seed: int = 1000, W: int = 640, H: int = 480, focal: f
 
 
 def headline(n: int = 1_000_000, seed: int = 1001, W: int = 1920, H: int = 1080, focal: float = 1100.0,
-             views: int = 1) -> Scene:
-    """Config 1: 64 isotropic clusters (sigma 0.3) in [-4,4]^3, camera 6 units from the origin."""
+             views: int = 1, ring: bool = False) -> Scene:
+    """Config 1: 64 isotropic clusters (sigma 0.3) in [-4,4]^3, camera 6 units from the origin.  ``views`` > 1 adds
+    cameras around the first one (pose jittered by +-5 degrees; view 0 stays the configuration's own camera), or a
+    full ring of cameras with ``ring``."""
     rng = np.random.default_rng(seed)
     means = _cluster_means(rng, n)
     sc, q, op, sh = _appearance(rng, n, -3.5, 0.5, 0.0)
-    vs = [make_view((0, 0, -6.0), (0, 0, 0), W, H, focal)]
-    if views > 1:
+    if views > 1 and ring:
         vs = ring_views(views, 6.0, W, H, focal, seed + 17)
+    else:
+        vs = jittered_views(max(1, views), 6.0, W, H, focal, seed + 17)
     return Scene("c1_headline", means, sc, q, op, sh, vs)
 
 

@@ -4,7 +4,8 @@
  * Plain pointers and sizes only: every buffer is caller-owned DEVICE memory unless a parameter says
  * "host"; every call enqueues its work on `stream` (a cudaStream_t passed as void*) and returns an int
  * status (0 = ok, negative = error, text from dsb_last_error()).  The library keeps no state between
- * calls except the last error string and a launch counter.
+ * calls except the last error string, a launch counter and one status word per device (see
+ * dsb_take_device_status).
  *
  * Each entry point replaces one function of the reference's torch extension `ds_splat_cuda`
  * (bound in cpp/rasterizer_python.cpp:3-23); the comment above it cites that function.
@@ -26,6 +27,8 @@ extern "C" {
 #define DSB_ERR_TOO_MANY_PAIRS (-4)
 #define DSB_ERR_DEVICE_WAIT_EXPIRED (-5)
 #define DSB_ERR_UNSUPPORTED (-6)
+/* Positive values of the device status word are notes, not errors: results are valid. */
+#define DSB_STATUS_COPY_WAIT_FELL_BACK 1 /* a preprocess block gave up waiting for its bulk copies and read its rows with plain loads */
 
 /* The reference never emits (tile, splat) pairs for the splat with the highest index: it takes the
  * exclusive prefix of the last splat as the pair total (cpp/rasterizer_torch.cu:97-104).  With this
@@ -76,6 +79,44 @@ const char* dsb_last_error(void);
 int32_t dsb_version(void);
 /* Number of kernels this library has launched in this process (monotonic). */
 int64_t dsb_launch_count(void);
+
+/* ---- device status word (no reference counterpart: the reference checks no CUDA error after any launch and
+ * defines a CUDA_CALL macro it never uses, cpp/gsplat/config.h:6-17) ------------------------------------
+ * Every wait inside a kernel of this library (the look-back of the sorts and of the scan, the wait for bulk
+ * copies) is bounded: when it runs out the kernel records DSB_ERR_DEVICE_WAIT_EXPIRED in a per-device status
+ * word and finishes, so a logic error or a lost predecessor can never hang the GPU -- but the lists such a
+ * kernel wrote are incomplete and everything rendered from them since is invalid.  The word is sticky until the
+ * host takes it:
+ *   - dsb_plan_pairs / dsb_forward_plan / dsb_plan_pairs_views / dsb_plan_totals_views, which synchronise the
+ *     stream anyway to read the pair count, fetch it in the same synchronisation and return
+ *     DSB_ERR_DEVICE_WAIT_EXPIRED when an earlier call on the device (for instance the tile sort inside the
+ *     previous dsb_forward_render) recorded it;
+ *   - dsb_take_device_status() synchronises `stream`, writes the word to *status_host (HOST int, may be NULL),
+ *     clears it, and returns DSB_OK, or the error code the word held.  Callers of the sort entry points, which
+ *     never synchronise by themselves, call it after their own synchronisation point.
+ * Positive values (DSB_STATUS_*) are notes about a slower path taken with valid results; they are reported
+ * through *status_host only (the plan calls leave them in place). */
+int dsb_take_device_status(int32_t* status_host, void* stream);
+
+/* ---- test hooks for the bounded waits (no reference counterpart) ----------------------------------------
+ * Each runs ONE kernel of the normal path on well-formed input in a configuration where one wait can never be
+ * satisfied, with a poll limit of a few hundred, so that a test can check that the kernel returns, the status
+ * words are set and the host reports DSB_ERR_DEVICE_WAIT_EXPIRED.  Nothing faults or hangs: the starved block
+ * gives up after spin_limit polls (1..100000) and finishes like the others.
+ *   dsb_debug_expire_scan_wait: the offset scan of dsb_plan_pairs over n >= 2048 splats with the first tile of the
+ *       look-back chain left out; workspace as for dsb_plan_pairs (dsb_plan_workspace_bytes(n)), on which
+ *       dsb_plan_totals_views(1, n, ...) then reports the expiry.
+ *   dsb_debug_expire_sort_wait: one radix pass (end_bit - begin_bit <= 8) of dsb_sort_pairs over k >= 8192 items
+ *       with the first tile left out; items_alt receives an incomplete list.  dsb_take_device_status() reports it.
+ *   dsb_debug_set_copy_wait_polls: how often the preprocess kernel polls for its bulk copies before it falls back
+ *       to plain loads (0 restores the default); with 1 every block falls back, results must not change, and the
+ *       status word holds DSB_STATUS_COPY_WAIT_FELL_BACK afterwards. */
+int dsb_debug_expire_scan_wait(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched,
+                               const uint64_t* depth_keys_sorted, uint32_t* offsets, void* workspace,
+                               int64_t workspace_bytes, uint32_t spin_limit, void* stream);
+int dsb_debug_expire_sort_wait(uint64_t* items, uint64_t* items_alt, int64_t k, int32_t begin_bit, int32_t end_bit,
+                               void* workspace, int64_t workspace_bytes, uint32_t spin_limit, void* stream);
+int dsb_debug_set_copy_wait_polls(uint32_t polls);
 
 /* ---- per-stage device timing (no reference counterpart: the reference times with std::chrono in
  * its tests, tests/rasterizer_test.cpp:112-143) --------------------------------------------------
@@ -226,6 +267,22 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* 
                        float* depth /* may be NULL */,
                        const uint32_t* layout_hist /* NULL, or this view's layout_hist from dsb_preprocess_views */,
                        void* stream);
+/* dsb_forward = dsb_forward_plan, then -- without returning to the caller in between -- dsb_forward_render when the
+ * pair count fits the buffers the caller brought: pairs / pairs_alt hold pair_capacity words each and the sort
+ * workspace is at least dsb_sort_workspace_bytes(k).  *k_host receives the pair count either way; *rendered_host
+ * (HOST int) is 1 when the image was rendered and 0 when the buffers were too small, in which case the caller grows
+ * them and calls dsb_forward_render itself (everything the plan wrote stays valid).  A caller that sizes the buffers
+ * from the previous call's count with some slack pays the one host synchronisation of the forward (the pair-count
+ * read-back) without any of its own host work between the two halves.  Replaces rasterizer_forward_deepsense
+ * (cpp/rasterizer_torch.cu:170-208) as a whole. */
+int dsb_forward(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
+                const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
+                float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
+                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* plan_workspace,
+                int64_t plan_workspace_bytes, uint64_t* pairs, uint64_t* pairs_alt, int64_t pair_capacity,
+                void* sort_workspace, int64_t sort_workspace_bytes, int32_t* ranges, float* image, float* final_T,
+                int32_t* final_idx, float* depth /* may be NULL */, int64_t* k_host, int32_t* rendered_host,
+                void* stream);
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,

@@ -8,7 +8,7 @@
 // Parity status: the tile-range stage is pinned by the reference's two known-answer tests
 // (tests/rasterizer_test.cpp:66-110).  Every other stage has no golden vector in the reference
 // ("parity unpinned" by reference tests); those stages are pinned instead by running the reference's
-// own CUDA kernels (oracle/_ref, built by oracle/Makefile) on the GPU box against this file.
+// own CUDA kernels (oracle/_ref, built by oracle/Makefile) on a B200 against this file.
 //
 // Each function cites the reference file:line whose arithmetic it follows.  fp32 throughout, with
 // the reference's operation order; libm expf/sqrtf replace the GPU's approximate intrinsics, so
@@ -115,6 +115,26 @@ int orc_num_threads() {
     return omp_get_max_threads();
 #else
     return 1;
+#endif
+}
+
+// Number of hardware threads the host offers (what omp would use if nothing capped it).
+int orc_num_procs() {
+#ifdef _OPENMP
+    return omp_get_num_procs();
+#else
+    return 1;
+#endif
+}
+
+// Thread count of all following stages; n <= 0 means every hardware thread.  Launchers such as torchrun
+// export OMP_NUM_THREADS=1 to their workers, which would otherwise turn the timed CPU baseline into a
+// one-core run without saying so.
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    omp_set_num_threads(n > 0 ? n : omp_get_num_procs());
+#else
+    (void)n;
 #endif
 }
 

@@ -84,6 +84,18 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """Run every following stage on all hardware threads of the host, whatever OMP_NUM_THREADS says (launchers such
+    as torchrun export OMP_NUM_THREADS=1 to their workers); returns the thread count now in use."""
+    lib().orc_set_threads(C.c_int(0))
+    return num_threads()
+
+
+def set_threads(n: int) -> int:
+    lib().orc_set_threads(C.c_int(int(n)))
+    return num_threads()
+
+
 def _p(a, dtype=None):
     if a is None:
         return None

@@ -32,10 +32,22 @@ class _Args(C.Structure):
 STAGE_NAMES = ("preprocess", "keys", "sort", "ranges", "blend", "bwd_blend", "bwd_sh", "bwd_projection")
 
 
-def build(reference_root: str = "/root/reference") -> bool:
+def reference_root():
+    """Where the reference's sources lie: the directory DSB_REFERENCE_ROOT names, else a ``reference`` checkout beside
+    this repository; None when neither exists (a machine that only carries the prebuilt library)."""
+    candidates = [os.environ.get("DSB_REFERENCE_ROOT"),
+                  os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in candidates:
+        if c and os.path.isdir(os.path.join(c, "cpp")):
+            return c
+    return None
+
+
+def build(root=None) -> bool:
     """Run ``make ref`` when the reference checkout is present; returns availability."""
-    if os.path.isdir(reference_root):
-        subprocess.run(["make", "-C", _HERE, "ref", f"REF={reference_root}"], check=True)
+    root = root or reference_root()
+    if root and os.path.isdir(root):
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF={root}"], check=True)
     return available()
 
 

@@ -58,3 +58,27 @@ def unpack_records(records_np):
     return dict(xy=np.ascontiguousarray(r[:, 0:2]), conic=np.ascontiguousarray(np.stack([r[:, 2], r[:, 3], r[:, 4]], 1)),
                 opac=np.ascontiguousarray(r[:, 5]), rgb=np.ascontiguousarray(np.stack([r[:, 6], r[:, 7], r[:, 8]], 1)),
                 depth=np.ascontiguousarray(r[:, 9]), rect=rect)
+
+
+def gradient_gate(got, want, name, rel=1e-3, max_bad_fraction=1e-4):
+    """Per-element gradient comparison: an element fails when |got - want| > rel * |want| + rel * median|want| (the
+    median over the non-zero entries keeps entries far below the tensor's typical size from being judged on rounding
+    noise of the sums they came from; atomic accumulation order is not deterministic).  At most ``max_bad_fraction`` of
+    the elements may fail.  Prints the distribution of the per-element error so that a run's log shows how close the
+    gate was; returns the failing fraction."""
+    got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64).ravel()
+    assert got.shape == want.shape, f"{name}: shapes differ"
+    assert np.isfinite(got).all(), f"{name}: non-finite gradient"
+    nz = np.abs(want) > 0
+    typical = float(np.median(np.abs(want[nz]))) if nz.any() else 0.0
+    err = np.abs(got - want)
+    bound = rel * np.abs(want) + rel * typical
+    bad = err > bound
+    scaled = err / np.maximum(np.abs(want) + typical, 1e-300)
+    q = np.quantile(scaled, [0.5, 0.99, 0.9999, 1.0]) if scaled.size else np.zeros(4)
+    frac = float(bad.mean()) if bad.size else 0.0
+    print(f"[gradient gate] {name}: {bad.sum()} of {bad.size} elements outside {rel:g} relative (fraction {frac:.2e}); "
+          f"error / (|want| + median): median {q[0]:.2e}, p99 {q[1]:.2e}, p99.99 {q[2]:.2e}, max {q[3]:.2e}; "
+          f"typical |want| {typical:.3e}")
+    assert frac <= max_bad_fraction, f"{name}: {bad.sum()} of {bad.size} elements differ by more than {rel:g} relative"
+    return frac

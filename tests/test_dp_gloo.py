@@ -58,7 +58,7 @@ class OracleRenderer:
 
 
 def _scene():
-    return scenes.headline(n=1500, seed=9, W=96, H=64, focal=60.0, views=5)
+    return scenes.headline(n=1500, seed=9, W=96, H=64, focal=60.0, views=5, ring=True)
 
 
 def _worker(rank, world, port, out):
@@ -115,3 +115,74 @@ def test_two_rank_step_equals_serial_sum(tmp_path):
     assert got_stats[1].max() >= 2 and got_stats[2].max() > 0 and got_stats[0].max() > 0
     mean = serial_stats.mean_grad_norm().numpy()
     assert np.all(mean[got_stats[1] == 0] == 0) and np.isfinite(mean).all()
+
+
+# ---- sharded optimizer step: reduce-scatter -> Adam on 1/G -> all-gather ----------------------------------------
+
+def _checker_update(p, g, m, v, lr, beta1, beta2, eps, step, grad_scale):
+    """The per-slice Adam update on CPU tensors, through the checker's restatement (oracle.adam_step)."""
+    from oracle import oracle as O
+    pn, mn, vn = O.adam_step(p.numpy(), g.numpy(), m.numpy(), v.numpy(), lr=lr, beta1=beta1, beta2=beta2, eps=eps, step=step,
+                             grad_scale=grad_scale)
+    p.copy_(torch.from_numpy(pn)); m.copy_(torch.from_numpy(mn)); v.copy_(torch.from_numpy(vn))
+
+
+LRS = dict(means3d=1e-3, shs=2e-3, opacities=3e-3, scales=4e-3, rotations=5e-3)
+N_SHARDED = 37   # odd on purpose: 37 * 59 elements do not split into equal slices without padding
+
+
+def _rank_gradients(rank, step):
+    g = torch.Generator().manual_seed(100 * step + rank)
+    return torch.randn(N_SHARDED * 59, generator=g)
+
+
+def _initial_parameters():
+    g = torch.Generator().manual_seed(7)
+    return dict(means3d=torch.randn(N_SHARDED, 3, generator=g), shs=torch.randn(N_SHARDED, 16, 3, generator=g),
+                opacities=torch.rand(N_SHARDED, 1, generator=g), scales=torch.rand(N_SHARDED, 3, generator=g),
+                rotations=torch.randn(N_SHARDED, 4, generator=g))
+
+
+def _sharded_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    params = dp.ParameterBuffer.from_tensors(_initial_parameters(), shards=world)
+    grads = dp.GradientBuffer(N_SHARDED, "cpu", shards=world)
+    opt = dp.ShardedAdam(params, LRS, eps=1e-8, update=_checker_update)
+    assert opt.m.numel() * world == params.storage.numel()       # moments: 1/G per rank
+    for step in (1, 2, 3):
+        grads.flat.copy_(_rank_gradients(rank, step))
+        opt.step(grads, grad_scale=0.5)
+    np.save(f"{out}.{rank}.npy", params.flat.numpy())
+    dist.destroy_process_group()
+
+
+def test_sharded_adam_on_two_ranks_equals_allreduce_plus_full_adam(tmp_path):
+    out = str(tmp_path / "params")
+    world = 2
+    mp.spawn(_sharded_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    got = [np.load(f"{out}.{r}.npy") for r in range(world)]
+    np.testing.assert_array_equal(got[0], got[1])        # every rank ends with the same parameters
+    # replicated form in one process: sum of the ranks' gradients, Adam over everything
+    params = dp.ParameterBuffer.from_tensors(_initial_parameters())
+    m, v = torch.zeros(params.length), torch.zeros(params.length)
+    for step in (1, 2, 3):
+        total = sum(_rank_gradients(r, step) for r in range(world))
+        for name, _ in dp.SEGMENTS:
+            a, b = params.segments[name]
+            _checker_update(params.flat[a:b], total[a:b], m[a:b], v[a:b], LRS[name], 0.9, 0.999, 1e-8, step, 0.5)
+    np.testing.assert_allclose(got[0], params.flat.numpy(), rtol=1e-6, atol=1e-7)
+    assert np.abs(got[0] - dp.ParameterBuffer.from_tensors(_initial_parameters()).flat.numpy()).max() > 1e-3
+
+
+def test_sharded_adam_in_one_process_is_plain_adam():
+    params = dp.ParameterBuffer.from_tensors(_initial_parameters())
+    grads = dp.GradientBuffer(N_SHARDED, "cpu")
+    opt = dp.ShardedAdam(params, LRS, eps=1e-8, update=_checker_update)
+    assert opt.world == 1 and [p[0] for p in opt.pieces] == [n for n, _ in dp.SEGMENTS]
+    grads.flat.copy_(_rank_gradients(0, 1))
+    before = params.flat.clone()
+    opt.step(grads)
+    assert float((params.flat - before).abs().max()) > 0
+    with pytest.raises(ValueError, match="laid out differently"):
+        opt.step(dp.GradientBuffer(N_SHARDED + 1, "cpu"))

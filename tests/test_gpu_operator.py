@@ -147,7 +147,7 @@ def test_errors_are_python_exceptions():
 
 def test_view_renderer_accumulates_like_autograd():
     """The fused multi-view path (gradient accumulation into the flat buffer) equals summed autograd gradients."""
-    sc = scenes.headline(n=20_000, seed=91, W=320, H=192, focal=200.0, views=3)
+    sc = scenes.headline(n=20_000, seed=91, W=320, H=192, focal=200.0, views=3, ring=True)
     t = scene_tensors(sc)
     r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
     grads = GradientBuffer(sc.n, "cuda")
@@ -219,7 +219,7 @@ def test_return_depth_is_differentiable_and_leaves_the_image_alone():
 def test_batched_views_equal_one_view_at_a_time():
     """render_views sums the per-splat backward of up to eight views in one kernel; eleven views (two batches,
     the loss given as a callable) must give what eleven single-view backward calls with accumulation give."""
-    sc = scenes.headline(n=15_000, seed=92, W=256, H=160, focal=180.0, views=11)
+    sc = scenes.headline(n=15_000, seed=92, W=256, H=160, focal=180.0, views=11, ring=True)
     t = scene_tensors(sc)
     cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
     vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
@@ -250,7 +250,7 @@ def test_batched_views_equal_one_view_at_a_time():
 def test_densification_statistics_equal_what_a_loop_around_the_operator_collects(ndc_units):
     """The per-splat backward of a step keeps gradient-norm sums, visibility counts and largest radii; a training
     loop around the single-view operator builds the same numbers from v_means2d and radii of every view."""
-    sc = scenes.headline(n=12_000, seed=97, W=256, H=160, focal=180.0, views=10)
+    sc = scenes.headline(n=12_000, seed=97, W=256, H=160, focal=180.0, views=10, ring=True)
     t = scene_tensors(sc)
     cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
     vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
@@ -277,7 +277,7 @@ def test_densification_statistics_equal_what_a_loop_around_the_operator_collects
 
 def test_preprocess_of_several_views_is_bit_identical_to_one_at_a_time():
     from conftest import capi_camera
-    sc = scenes.headline(n=30_000, seed=94, W=400, H=240, focal=260.0, views=5)
+    sc = scenes.headline(n=30_000, seed=94, W=400, H=240, focal=260.0, views=5, ring=True)
     t = scene_tensors(sc)
     cams, keep = zip(*[capi_camera(v) for v in sc.views])
     outs, cov3d = _capi.preprocess_views(list(cams), t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
@@ -377,7 +377,7 @@ def test_plan_of_several_views_equals_one_at_a_time():
     view's sorted keys, offsets and pair count must equal those of dsb_plan_pairs on that view alone."""
     import ctypes as C
     from conftest import capi_camera
-    sc = scenes.headline(n=70_001, seed=98, W=640, H=400, focal=380.0, views=3)   # odd length: rows are not tile-aligned
+    sc = scenes.headline(n=70_001, seed=98, W=640, H=400, focal=380.0, views=3, ring=True)   # odd length: rows are not tile-aligned
     t = scene_tensors(sc)
     cams, keep = zip(*[capi_camera(v) for v in sc.views])
     n, nv, lib = sc.n, 3, _capi.lib()
@@ -461,7 +461,7 @@ def test_image_loss_gradient_matches_the_autograd_checker():
         scale = float(np.abs(grad_o).max())
         assert float(np.abs(v.cpu().numpy() - grad_o).max()) <= 2e-4 * scale, (h, w, lam)
     # as the loss of a multi-view step: the gradients equal those of a step fed with the checker's dL/dimage
-    sc = scenes.headline(n=10_000, seed=99, W=240, H=144, focal=170.0, views=3)
+    sc = scenes.headline(n=10_000, seed=99, W=240, H=144, focal=170.0, views=3, ring=True)
     t = scene_tensors(sc)
     cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
     targets = [torch.from_numpy(rng.uniform(0, 1, (144, 240, 3)).astype(np.float32)).cuda() for _ in cams]
@@ -485,3 +485,49 @@ def test_image_loss_gradient_matches_the_autograd_checker():
     assert v_main.data_ptr() != v_side.data_ptr() and torch.equal(v_main, v_side)
     assert _rel(g_fused.views["shs"].cpu().numpy(), g_check.views["shs"].cpu().numpy()) < 1e-3
     assert _rel(g_fused.views["means3d"].cpu().numpy(), g_check.views["means3d"].cpu().numpy()) < 1e-3
+
+
+def test_gradients_take_the_shape_of_non_canonical_inputs():
+    """opacities given as [N] and shs flattened to [N, 48] render like the canonical shapes, and autograd receives
+    gradients of exactly those shapes (the reference refuses such inputs with a TORCH_CHECK; here they are accepted)."""
+    sc = scenes.tiny(n=3000, seed=72, W=160, H=128, focal=140.0)
+    view = sc.views[0]
+    t = scene_tensors(sc)
+    rast = GaussianRasterizer(settings_for(view))
+    v = torch.from_numpy(sc.image_grad()).cuda()
+    canon = {k: x.clone().requires_grad_(True) for k, x in t.items()}
+    img, _ = rast(canon["means"], None, canon["shs"], None, canon["opacities"], canon["scales"], canon["rotations"], None)
+    img.backward(v)
+    flat = {k: x.clone() for k, x in t.items()}
+    flat["opacities"] = flat["opacities"].reshape(-1)
+    flat["shs"] = flat["shs"].reshape(sc.n, 48)
+    flat = {k: x.requires_grad_(True) for k, x in flat.items()}
+    img2, _ = rast(flat["means"], None, flat["shs"], None, flat["opacities"], flat["scales"], flat["rotations"], None)
+    assert torch.equal(img2, img)
+    img2.backward(v)
+    torch.cuda.synchronize()
+    assert flat["opacities"].grad.shape == (sc.n,) and flat["shs"].grad.shape == (sc.n, 48)
+    assert _rel(flat["opacities"].grad.cpu().numpy(), canon["opacities"].grad.reshape(-1).cpu().numpy()) < 1e-4
+    assert _rel(flat["shs"].grad.cpu().numpy(), canon["shs"].grad.reshape(sc.n, 48).cpu().numpy()) < 1e-4
+
+
+def test_operator_reuses_its_pair_buffers_from_the_previous_count():
+    """The second call of a shape brings pair buffers sized from the first call's count, so plan and render run inside
+    one library call; a view with many more pairs than the hint still renders correctly (buffers are grown)."""
+    sc = scenes.headline(n=30_000, seed=73, W=400, H=240, focal=260.0, views=3, ring=True)
+    t = scene_tensors(sc)
+    imgs = []
+    for rep in range(2):
+        for v in sc.views:
+            img, _ = GaussianRasterizer(settings_for(v))(t["means"], None, t["shs"], None, t["opacities"], t["scales"],
+                                                        t["rotations"], None)
+            imgs.append(img.clone())
+    torch.cuda.synchronize()
+    for a, b in zip(imgs[:3], imgs[3:]):
+        assert torch.equal(a, b)
+    # a much heavier view of the same shape (scales x4): the hint is too small, the operator grows the buffers
+    big = t["scales"] * 4.0
+    img_big, _ = GaussianRasterizer(settings_for(sc.views[0]))(t["means"], None, t["shs"], None, t["opacities"], big,
+                                                              t["rotations"], None)
+    r = ViewRenderer(t["means"], t["shs"], t["opacities"], big, t["rotations"], batch_views=1)
+    assert torch.equal(img_big, r.forward(CameraTensors.from_view(sc.views[0], "cuda")))

@@ -56,3 +56,36 @@ def test_graphdeco_keyword_names_are_accepted():
     with pytest.raises(RuntimeError, match="CUDA"):  # gets past argument mapping, stops at the device check
         r(means3D=torch.zeros(2, 3), means2D=torch.zeros(2, 3), shs=torch.zeros(2, 16, 3), opacities=torch.zeros(2, 1),
           scales=torch.ones(2, 3), rotations=torch.ones(2, 4), cov3D_precomp=None)
+
+
+def test_launching_classes_refuse_tensors_that_are_not_on_a_cuda_device():
+    """ImageLoss, FlatAdam and ViewRenderer launch kernels on the current device and stream; tensors that live
+    elsewhere must raise instead of reaching a launch with foreign pointers."""
+    import torch
+    from ds_splat_b200 import _capi, dp
+    with pytest.raises(RuntimeError, match="CUDA"):
+        _capi.stream_ptr(torch.device("cpu"))
+    img = torch.zeros(8, 8, 3)
+    loss = dp.ImageLoss.__new__(dp.ImageLoss)   # no library needed for the device check
+    with pytest.raises(RuntimeError, match="CUDA kernels"):
+        loss.gradient(img, img)
+    adam = dp.FlatAdam.__new__(dp.FlatAdam)
+    adam.dev = torch.device("cpu")
+    with pytest.raises(RuntimeError, match="launches CUDA kernels"):
+        adam.step(dp.GradientBuffer(4, "cpu"))
+
+
+def test_gradient_and_parameter_blocks_share_one_layout_and_pad_to_shards():
+    import torch
+    from ds_splat_b200 import dp
+    g = dp.GradientBuffer(5, "cpu", shards=4)
+    assert g.length == 5 * 59 and g.storage.numel() % 16 == 0 and g.storage.numel() - g.length < 16
+    assert g.flat.data_ptr() == g.storage.data_ptr() and g.flat.numel() == g.length
+    params = dict(means3d=torch.randn(5, 3), shs=torch.randn(5, 16, 3), opacities=torch.rand(5, 1), scales=torch.rand(5, 3),
+                  rotations=torch.randn(5, 4))
+    p = dp.ParameterBuffer.from_tensors(params, shards=4)
+    assert p.segments == g.segments
+    for name, tensor in params.items():
+        assert torch.equal(p.views[name], tensor)
+        a, b = p.segments[name]
+        assert torch.equal(p.storage[a:b], tensor.reshape(-1))

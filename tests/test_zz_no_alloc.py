@@ -3,7 +3,8 @@
 It exists for callers that cannot get device memory at the moment they need a sort -- a renderer living as a
 plug-in in another engine's frame loop that owns all GPU memory, or a loop where cudaMalloc's device-wide stall is
 not acceptable -- so its scratch is a fixed array inside the library.  The test checks that it produces exactly the
-list dsb_sort_pairs produces (integer work: bit-exact), on two calls in a row with different sizes and bit ranges,
+list dsb_sort_pairs produces and the list an independent stable sort (torch.sort) produces on the same bits (integer
+work: bit-exact), on two calls in a row with different sizes and bit ranges,
 so that leftovers of the first call in the shared array would show up in the second, and that lists beyond the
 built-in limit are refused with a clear error.  This file sorts last in collection order on purpose: with
 ``pytest -x`` every other test has already run when it starts.
@@ -37,9 +38,9 @@ def test_static_sort_matches_workspace_sort_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before  # nothing was taken from torch's allocator either
         assert torch.equal(got, want)
-        # stable: equal tile ids keep their input order
-        tile_sorted = got >> 32
-        assert bool((tile_sorted[1:] >= tile_sorted[:-1]).all())
+        # ... and the list an independent stable sort on the same bits produces (equal digits keep their input order)
+        digit = (pairs >> b0) & ((1 << (b1 - b0)) - 1)
+        assert torch.equal(got, pairs[torch.sort(digit, stable=True).indices])
 
 
 def test_static_sort_refuses_lists_beyond_its_limit():
