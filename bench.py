@@ -541,32 +541,39 @@ def main():
         pinned_view = torch.from_numpy(view.viewmatrix_t).pin_memory()
         pinned_proj = torch.from_numpy(view.projmatrix_t).pin_memory()
         pinned_pos = torch.from_numpy(np.ascontiguousarray(view.campos)).pin_memory()
-        out_image = torch.empty((H, W, 3), dtype=torch.float32).pin_memory()
-        out_radii = torch.empty(scene.n, dtype=torch.int32).pin_memory()
+        # two sets of host result buffers and of device-side gradient buffers: step i's result is read on the host while
+        # step i + 1 is already enqueued (a training loop logs the loss of the step before the one in flight)
+        out_image = [torch.empty((H, W, 3), dtype=torch.float32).pin_memory() for _ in range(2)]
+        out_radii = [torch.empty(scene.n, dtype=torch.int32).pin_memory() for _ in range(2)]
         leaves = {k: v.detach().clone().requires_grad_(True) for k, v in params.views.items()}
         means2d = torch.zeros_like(leaves["means3d"], requires_grad=True)
         bg = torch.zeros(3, device=dev)
         vm, pm, cp = (torch.empty_like(x, device=dev) for x in (pinned_view, pinned_proj, pinned_pos))
-        vg = torch.empty((H, W, 3), dtype=torch.float32, device=dev)
+        vg = [torch.empty((H, W, 3), dtype=torch.float32, device=dev) for _ in range(2)]
         settings = GaussianRasterizationSettings(H, W, view.tanfovx, view.tanfovy, bg, 1.0, vm, pm, scene.sh_degree, 3, cp,
                                                  False, False)
         rasterizer = GaussianRasterizer(settings)
         h2d = pinned_grad.numel() * 4 + (16 + 16 + 3) * 4
-        d2h = out_image.numel() * 4 + out_radii.numel() * 4
+        d2h = out_image[0].numel() * 4 + out_radii[0].numel() * 4
         copy_stream = torch.cuda.Stream(device=dev)
         main_stream = torch.cuda.current_stream()
-        grad_ready, rendered, copied = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        grad_ready, rendered = torch.cuda.Event(), torch.cuda.Event()
+        backward_done = [torch.cuda.Event(), torch.cuda.Event()]
+        result_on_host = [torch.cuda.Event(), torch.cuda.Event()]
+        checksum = [0.0]
 
-        def e2e_step():
+        def e2e_step(i):
             # A training loop's usual overlap: the image gradient travels to the device while the forward runs, the
-            # rendered image travels back while the backward runs (second stream, events).  The device-side
-            # destinations are the step's own buffers, reused from step to step as a loop's batch buffers are.
+            # rendered image travels back while the backward runs (second stream, events), and the host reads the
+            # result of step i - 1 after it has enqueued step i.  Every step's inputs come from pinned host memory and
+            # every step's result is read on the host inside the timed region.
+            s = i & 1
             vm.copy_(pinned_view, non_blocking=True)
             pm.copy_(pinned_proj, non_blocking=True)
             cp.copy_(pinned_pos, non_blocking=True)
-            copy_stream.wait_event(copied)   # the previous step's backward has read vg (event recorded after it)
             with torch.cuda.stream(copy_stream):
-                vg.copy_(pinned_grad, non_blocking=True)
+                copy_stream.wait_event(backward_done[s])   # the backward that last read vg[s] (two steps ago)
+                vg[s].copy_(pinned_grad, non_blocking=True)
                 grad_ready.record(copy_stream)
             for leaf in leaves.values():
                 leaf.grad = None
@@ -576,24 +583,35 @@ def main():
             rendered.record(main_stream)
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(rendered)
-                out_image.copy_(image.detach(), non_blocking=True)
-                out_radii.copy_(radii, non_blocking=True)
+                out_image[s].copy_(image.detach(), non_blocking=True)
+                out_radii[s].copy_(radii, non_blocking=True)
+                result_on_host[s].record(copy_stream)
             image.record_stream(copy_stream)
             radii.record_stream(copy_stream)
             main_stream.wait_event(grad_ready)
-            image.backward(vg)
-            copied.record(main_stream)
-            torch.cuda.synchronize()  # the caller reads the result on the host every step
+            image.backward(vg[s])
+            backward_done[s].record(main_stream)
+            if i > 0:   # the previous step's result, on the host
+                result_on_host[s ^ 1].synchronize()
+                checksum[0] += float(out_image[s ^ 1][0, 0, 0]) + int(out_radii[s ^ 1][0])
 
-        copied.record(main_stream)
-        for _ in range(warmup):
-            e2e_step()
+        def e2e_drain(i):   # the last step's result
+            result_on_host[(i - 1) & 1].synchronize()
+            checksum[0] += float(out_image[(i - 1) & 1][0, 0, 0])
+            torch.cuda.synchronize()
+
+        for ev in backward_done:
+            ev.record(main_stream)
+        for i in range(warmup):
+            e2e_step(i)
+        e2e_drain(warmup)
         timer.barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall0 = time.perf_counter()
         a.record()
-        for _ in range(args.steps):
-            e2e_step()
+        for i in range(args.steps):
+            e2e_step(i)
+        e2e_drain(args.steps)
         b.record()
         timer.barrier()
         wall = time.perf_counter() - wall0
@@ -602,7 +620,8 @@ def main():
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": round(e_ms / args.steps, 4),
                "note": "GaussianRasterizer + autograd, one view per step; per step H2D camera + dL/dimage from pinned memory, "
-                       "D2H image + radii; splat parameters are model state resident on the device"
+                       "D2H image + radii, read on the host one step behind the step being enqueued; splat parameters are "
+                       "model state resident on the device"
                        + ("; per-rank rendering with no collective in it (N independent render loops)" if world > 1 else "")}
         del leaves, means2d, rasterizer
 

@@ -196,7 +196,7 @@ struct LayoutViews {       // one block per view
 };
 __global__ void __launch_bounds__(kLayoutThreads)
 tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x, const int tiles_y, const SortPlan plan,
-                   const int use_smem) {
+                   const int use_smem, const int trailing_quirk) {
     extern __shared__ int s_grid[];
     int* __restrict__ marks = lv.marks[blockIdx.x];
     u32* __restrict__ hist = lv.hist[blockIdx.x];
@@ -204,8 +204,10 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     __shared__ u32 s_hist[4][256];
     __shared__ u32 s_wsum[32];
     __shared__ u32 s_carry;
+    __shared__ u64 s_last;   // (index of the last non-empty tile + 1) << 32 | start of its range; 0: no tile has pairs
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int stride = tiles_x + 1, rows = tiles_y + 1;
+    if (tid == 0) s_last = 0;
     for (int i = tid; i < 4 * 256; i += kLayoutThreads) (&s_hist[0][0])[i] = 0;
     // The grid is worked on in shared memory when it fits (up to about 4K images), else in place.
     int* diff = use_smem ? s_grid : marks;
@@ -282,12 +284,26 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     }
     __syncthreads();
     u32 running = s_wsum[warp] + incl - mine;
+    u64 my_last = 0;
     for (int t = t_begin; t < t_end; ++t) {
         const int ty = t / tiles_x, tx = t - ty * tiles_x;
         ranges[t] = (int32_t)running;
-        running += (u32)max(diff[ty * stride + tx], 0);
+        const u32 c = (u32)max(diff[ty * stride + tx], 0);
+        if (c) my_last = ((u64)(u32)(t + 1) << 32) | running;
+        running += c;
     }
     if (tid == 0) ranges[num_tiles] = (int32_t)s_carry;
+    if (trailing_quirk) {
+        // The reference never marks the end of the last non-empty tile (see tile_ranges_kernel): the empty tiles after
+        // it repeat its start, which hands its pairs to the final tile.  Reproduced when the lists are the reference's.
+        if (my_last) atomicMax(&s_last, my_last);
+        __syncthreads();
+        const u64 last = s_last;
+        if (last) {
+            const int last_tile = (int)(last >> 32) - 1;
+            for (int t = max(t_begin, last_tile + 1); t < t_end; ++t) ranges[t] = (int32_t)(u32)last;
+        }
+    }
     if (hist)
         for (int i = tid; i < plan.npass * 256 && i < 4 * 256; i += kLayoutThreads) hist[i] = (&s_hist[0][0])[i];
     if (!use_smem) return;  // the grid lives in `marks` itself: no room for the order, callers fall back to tile order
@@ -330,16 +346,26 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     }
 }
 
-// ranges[t] = number of sorted items whose tile id (high 32 bits, signed) is < t, t = 0..T.
+// ranges[t] = number of sorted items whose tile id (high 32 bits, signed) is < t, t = 0..T -- with one habit of the
+// reference kept on purpose: it marks a tile's END only where the NEXT item belongs to another tile
+// (cpp/rasterizer_kernels.cu:313-322) and fills unmarked entries with a running maximum
+// (cpp/rasterizer_torch.cu:37-39), so the end of the LAST non-empty tile is never marked; when empty tiles follow
+// it, their entries (and the end of that tile) repeat its START, and its items fall to the final tile, whose end
+// the host sets to K (:31-32).  trailing_quirk reproduces exactly that; without it the ranges are a clean partition.
 __global__ void tile_ranges_kernel(const u64* __restrict__ sorted, const u32 k, const int num_tiles,
-                                   int32_t* __restrict__ ranges) {
+                                   int32_t* __restrict__ ranges, const int trailing_quirk) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t > num_tiles) return;
+    int t_search = t;
+    if (trailing_quirk && k > 0) {
+        const int last_tile = (int32_t)(sorted[k - 1] >> 32);
+        if (t > last_tile && t < num_tiles) t_search = max(last_tile, 0);
+    }
     u32 lo = 0, hi = k;
     while (lo < hi) {
         const u32 mid = lo + ((hi - lo) >> 1);
         const int32_t tile = (int32_t)(sorted[mid] >> 32);
-        if (tile < t) lo = mid + 1; else hi = mid;
+        if (tile < t_search) lo = mid + 1; else hi = mid;
     }
     ranges[t] = (t == num_tiles) ? (int32_t)k : (int32_t)lo;
 }
@@ -550,8 +576,10 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
     if (has_order) *has_order = use_smem;
     if (use_smem && grid_bytes > 40 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
+    // lists identical to the reference's (its rectangles, its dropped last splat): keep its range habit too
+    const int trailing_quirk = cp.drop_last && !cp.tight_tiles;
     tile_layout_kernel<<<count, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(lv, (int)tile_marks_copy_ints(cp.H, cp.W),
-                                                                               cp.tiles_x, cp.tiles_y, plan, use_smem);
+                                                                               cp.tiles_x, cp.tiles_y, plan, use_smem, trailing_quirk);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
@@ -567,12 +595,12 @@ SortPlan tile_sort_plan(const CamParams& cp) {   // only the tile id is sorted: 
     return make_sort_plan(32, 32 + tile_bits, false);
 }
 
-int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s) {
+int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s, int trailing_quirk) {
     DSB_REQUIRE(H > 0 && W > 0 && ranges, "ranges: bad arguments");
     DSB_REQUIRE(k == 0 || sorted, "ranges: null list");
     DSB_REQUIRE(k < ((int64_t)1 << 31), "ranges: too many items");
     const int t = ((W + kTile - 1) / kTile) * ((H + kTile - 1) / kTile);
-    tile_ranges_kernel<<<(t + 1 + 255) / 256, 256, 0, s>>>(sorted, (u32)k, t, ranges);
+    tile_ranges_kernel<<<(t + 1 + 255) / 256, 256, 0, s>>>(sorted, (u32)k, t, ranges, trailing_quirk);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -179,7 +179,7 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
                              int32_t* const* ranges, int* has_order, cudaStream_t s);
 SortPlan tile_sort_plan(const CamParams& cp);
 bool tile_order_available(int H, int W);  // whether launch_tile_layout leaves the tile order for this image size
-int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s);
+int launch_ranges(const u64* sorted, int64_t k, int H, int W, int32_t* ranges, cudaStream_t s, int trailing_quirk = 1);
 int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* keys, int32_t* ids, cudaStream_t s);
 
 int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,

@@ -46,6 +46,14 @@ __device__ __forceinline__ float sh_channel(const float* f, int ch, int degree, 
     return fmaxf(res + 0.5f, 0.0f);
 }
 
+// a a' + b b' + c c' with the fusion into multiply-adds fixed (intrinsics with explicit rounding are never re-fused):
+__device__ __forceinline__ float dot3_first_plain(float a, float a2, float b, float b2, float c, float c2) {
+    return __fmaf_rn(c, c2, __fmaf_rn(b, b2, __fmul_rn(a, a2)));
+}
+__device__ __forceinline__ float dot3_second_plain(float a, float a2, float b, float b2, float c, float c2) {
+    return __fmaf_rn(c, c2, __fmaf_rn(a, a2, __fmul_rn(b, b2)));
+}
+
 // Cooperative copy of `count` floats from global to shared (coalesced 4-byte lanes).
 __device__ __forceinline__ void stage_floats(float* dst, const float* src, int count, int tid) {
     for (int k = tid; k < count; k += kThreads) dst[k] = src[k];
@@ -166,12 +174,16 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
             const float m00 = sx * r00, m01 = sy * r01, m02 = sz * r02;
             const float m10 = sx * r10, m11 = sy * r11, m12 = sz * r12;
             const float m20 = sx * r20, m21 = sy * r21, m22 = sz * r22;
-            S[0] = m00 * m00 + m01 * m01 + m02 * m02;
-            S[1] = m00 * m10 + m01 * m11 + m02 * m12;
-            S[2] = m00 * m20 + m01 * m21 + m02 * m22;
-            S[3] = m10 * m10 + m11 * m11 + m12 * m12;
-            S[4] = m10 * m20 + m11 * m21 + m12 * m22;
-            S[5] = m20 * m20 + m21 * m21 + m22 * m22;
+            // Sigma = M M^T.  Which two of the three products of a sum the compiler fuses into multiply-adds depends
+            // on the code around the expression, and the integer stages downstream (radius, tile rectangle) must
+            // agree bit for bit with the reference's build, so the fusion that build was measured to use is spelled
+            // out: entries xx and xz keep the FIRST product as the plain multiply, the other four the SECOND.
+            S[0] = dot3_first_plain(m00, m00, m01, m01, m02, m02);
+            S[1] = dot3_second_plain(m00, m10, m01, m11, m02, m12);
+            S[2] = dot3_first_plain(m00, m20, m01, m21, m02, m22);
+            S[3] = dot3_second_plain(m10, m10, m11, m11, m12, m12);
+            S[4] = dot3_second_plain(m10, m20, m11, m21, m12, m22);
+            S[5] = dot3_second_plain(m20, m20, m21, m21, m22, m22);
         }
 
     }
@@ -262,7 +274,8 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
             const float px = cv.fx * tx * z_inv + cv.cx, py = cv.fy * ty * z_inv + cv.cy;
 
             // Radius from the larger eigenvalue, 3 sigma, rounded up.
-            const float det = ca * cc - cb2 * cb2;
+// a c - b^2 as the reference's build fuses it (checked bit for bit on 6M splats); spelled out like Sigma above
+            const float det = __fmaf_rn(ca, cc, -__fmul_rn(cb2, cb2));
             const float mid = 0.5f * (ca + cc);
             const float diff = mid * mid - det;
             const float lambda1 = mid + sqrtf(max(0.1f, diff));

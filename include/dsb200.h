@@ -201,7 +201,12 @@ int dsb_sort_pairs_static(uint64_t* items, uint64_t* items_alt, int64_t k, int32
 /* ---- stage (d) ------------------------------------------------------------------------------
  * Replaces identify_tile_ranges (cpp/rasterizer_torch.cu:23-42, kernel cpp/rasterizer_kernels.cu:
  * 308-323).  `sorted` holds k 64-bit words whose high 32 bits are the tile id (the reference's keys
- * and this library's packed pairs both qualify).  ranges [tiles+1] int32: tile t owns [r[t], r[t+1]). */
+ * and this library's packed pairs both qualify).  ranges [tiles+1] int32: tile t owns [r[t], r[t+1]).
+ * One habit of the reference is kept because the result must be its array bit for bit: it marks the end of a tile
+ * only where the next item belongs to another tile and fills the gaps with a running maximum, so when EMPTY tiles
+ * follow the last non-empty tile, that tile's end is never marked -- its range comes out empty and its items belong
+ * to the final tile, whose end is K.  (The fused render does the same when its pair list is the reference's, i.e.
+ * with DSB_FLAG_DROP_LAST_SPLAT and without DSB_FLAG_TIGHT_TILES; otherwise its ranges are a clean partition.) */
 int dsb_identify_tile_ranges(const uint64_t* sorted, int64_t k, int32_t image_height, int32_t image_width,
                              int32_t* ranges, void* stream);
 

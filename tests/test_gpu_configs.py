@@ -45,7 +45,11 @@ def test_full_size_config_against_reference_cuda(name):
     # ---- lists: per-stage calls with the reference's own tile rectangles
     cam, keep = capi_camera(view)
     records, radii, tiles, cov3d, depth_keys = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
-    assert torch.equal(radii, up(ref["radii"])), "radii differ from the reference CUDA path"
+    bad = int((radii != up(ref["radii"])).sum())
+    assert bad == 0, f"{bad} radii differ from the reference CUDA path"
+    as_bits = lambda x: x.contiguous().view(torch.int32)
+    assert torch.equal(as_bits(records[:, 2:5]), as_bits(up(ref["conic"]))), "conic differs from the reference's bit pattern"
+    assert torch.equal(as_bits(cov3d), as_bits(up(ref["cov3d"]))), "3-D covariance differs from the reference's bit pattern"
     offsets, k = _capi.plan_pairs(cam, tiles, depth_keys)
     assert k == ref["K"] and k > 50_000_000
     pairs = _capi.emit_pairs(cam, k, records, tiles, depth_keys, offsets)

@@ -40,6 +40,14 @@ def test_against_reference_cuda(name):
     assert mism == 0, f"{mism} radii differ from the reference CUDA path"
     rec = records.cpu().numpy()
     np.testing.assert_array_equal(rec[:, 9].view(np.uint32), np.ascontiguousarray(ref["depth"]).view(np.uint32))
+    # everything a blend decision depends on is bit-identical too: pixel mean, conic, and the 3-D covariance behind them
+    # (the fusion of their sums into multiply-adds is spelled out in the preprocess kernel to match the reference's build)
+    bits = lambda a: np.ascontiguousarray(a, np.float32).view(np.uint32)
+    np.testing.assert_array_equal(bits(rec[:, 0:2]), bits(ref["xy"]))
+    np.testing.assert_array_equal(bits(rec[:, 2:5]), bits(ref["conic"]))
+    np.testing.assert_array_equal(bits(cov3d.cpu().numpy()), bits(ref["cov3d"]))
+    colour_off = (bits(rec[:, 6:9]) != bits(ref["rgb"])).any(axis=1).mean()
+    assert colour_off < 0.03 and np.abs(rec[:, 6:9] - ref["rgb"]).max() < 1e-6   # SH sums: last-bit differences only
     assert k == ref["K"]
     np.testing.assert_array_equal(keys_g.cpu().numpy(), ref["keys_sorted"])
     np.testing.assert_array_equal(ids_g.cpu().numpy(), ref["ids_sorted"])
