@@ -21,12 +21,14 @@ RECORD_FLOATS = 12
 GRAD_FLOATS = 12
 MAX_BATCH_VIEWS = 8
 MAX_PAIRS = 1 << 30
+LAYOUT_WORDS = 1024   # per-view layout block of the fused render
 
 EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
     "dsb_preprocess", "dsb_plan_pairs", "dsb_emit_pairs", "dsb_sort_pairs", "dsb_sort_by_keys",
     "dsb_identify_tile_ranges", "dsb_blend_forward", "dsb_blend_backward", "dsb_geometry_backward",
-    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_pairs_views", "dsb_plan_totals_views",
+    "dsb_forward_plan", "dsb_forward_render", "dsb_backward", "dsb_preprocess_views", "dsb_plan_workspace_bytes_views", "dsb_plan_views", "dsb_plan_totals_views",
+    "dsb_render_workspace_bytes", "dsb_row_binning_supported",
     "dsb_backward_blend",
     "dsb_geometry_backward_views", "dsb_geometry_backward_views_stats",
     "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_adam_step",
@@ -76,6 +78,10 @@ def lib():
         l.dsb_sort_workspace_bytes.argtypes = [C.c_int64]
         l.dsb_tile_marks_bytes.restype = C.c_int64
         l.dsb_tile_marks_bytes.argtypes = [C.c_int32, C.c_int32]
+        l.dsb_render_workspace_bytes.restype = C.c_int64
+        l.dsb_render_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_int64]
+        l.dsb_row_binning_supported.restype = C.c_int32
+        l.dsb_row_binning_supported.argtypes = [C.c_int32, C.c_int32]
         l.dsb_stage_name.restype = C.c_char_p
         l.dsb_stage_name.argtypes = [C.c_int32]
         l.dsb_stage_count.restype = C.c_int32
@@ -92,12 +98,12 @@ def lib():
             "dsb_blend_forward": [CAM, P, P, P, P, P, P, P, P],
             "dsb_blend_backward": [CAM, P, P, P, P, P, P, P, P, P],
             "dsb_geometry_backward": [CAM, I32] + [P] * 7 + [P] * 8 + [I32, P],
-            "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, C.POINTER(C.c_int64), P],
-            "dsb_forward_render": [CAM, I32, I64] + [P] * 8 + [I64] + [P] * 7,
+            "dsb_forward_plan": [CAM, I32] + [P] * 7 + [P] * 10 + [P, I64, C.POINTER(C.c_int64), C.POINTER(C.c_int64), P],
+            "dsb_forward_render": [CAM, I32, I64, I64] + [P] * 8 + [P, I64] + [P] * 4 + [P],
             "dsb_backward": [CAM, I32] + [P] * 14 + [P] * 8 + [I32, P],
             "dsb_preprocess_views": [P, I32, I32] + [P] * 16,
-            "dsb_plan_pairs_views": [CAM, I32, I32, I64, P, P, P, P, P, I64, P, P],
-            "dsb_plan_totals_views": [I32, I32, P, I64, P, P],
+            "dsb_plan_views": [CAM, I32, I32, I64, P, P, P, P, P, P, P, I64, P, P, P],
+            "dsb_plan_totals_views": [I32, I32, P, I64, P, P, P],
             "dsb_backward_blend": [CAM, I32] + [P] * 10,
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_geometry_backward_views_stats": [P, I32, I32] + [P] * 15 + [I32, C.c_float, C.c_float, P, P, P, P],
@@ -105,8 +111,8 @@ def lib():
             "dsb_image_loss_backward": [P, P, I32, I32, C.c_float, P, I64, P, P, P],
             "dsb_adam_step": [P, P, P, P, I64, C.c_double, C.c_double, C.c_double, C.c_double, I32, C.c_double, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
-            "dsb_forward": [CAM, I32] + [P] * 7 + [P] * 9 + [I64, P, P, I64, P, I64] + [P] * 5
-                           + [C.POINTER(C.c_int64), C.POINTER(C.c_int32), P],
+            "dsb_forward": [CAM, I32] + [P] * 7 + [P] * 10 + [P, I64] + [P, I64] + [P, I64] + [P] * 4
+                           + [C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32), P],
             "dsb_take_device_status": [C.POINTER(C.c_int32), P],
             "dsb_debug_expire_scan_wait": [CAM, I32, P, P, P, P, I64, C.c_uint32, P],
             "dsb_debug_expire_sort_wait": [P, P, I64, I32, I32, P, I64, C.c_uint32, P],
@@ -202,6 +208,11 @@ def make_camera(image_height, image_width, tanfovx, tanfovy, viewmatrix, projmat
     cam.viewmatrix, cam.projmatrix, cam.campos = viewmatrix.data_ptr(), projmatrix.data_ptr(), campos.data_ptr()
     cam.bg = bg.data_ptr() if bg is not None else None
     return cam, [viewmatrix, projmatrix, campos, bg]
+
+
+def dsb_row_binned(h, w) -> bool:
+    """Whether the fused render row-bins images of this size (at most 256 x 509 tiles) or sorts whole pair lists."""
+    return bool(lib().dsb_row_binning_supported(int(h), int(w)))
 
 
 def num_tiles(h, w):

@@ -24,17 +24,25 @@ constexpr u64 kScanInclusive = 1ull << 63;
 constexpr u64 kScanValue = (1ull << 62) - 1;
 
 struct PlanTail {       // lives after the sort workspace
-    u64 total;
+    u64 total;          // pairs of the view
+    u64 total_rows;     // row items of the view (row-binned plans; 0 otherwise)
     u32 tile_counter;
     int status;
+    u64 pad;
+};
+struct ScanViews {      // row-binned plans: every view's records (for the rectangles) and layout block (for K)
+    const float4* records[DSB_MAX_BATCH_VIEWS];
+    const u32* row_info[DSB_MAX_BATCH_VIEWS];
 };
 
-// Single-pass exclusive scan of tiles_touched taken in depth order.
+// Single-pass exclusive scan, in depth order, of the splats' tile counts (ROWS = false: offsets = first pair of every
+// splat) or of the heights of their tile rectangles (ROWS = true: offsets = first row item of every splat).
+template <bool ROWS>
 __global__ void __launch_bounds__(kScanThreads)
 scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __restrict__ tiles, const int n,
                    const int drop_last, u32* __restrict__ offsets, u64* __restrict__ lookback, PlanTail* __restrict__ tail,
                    const long long item_stride, const long long lookback_stride, int* __restrict__ device_status,
-                   const u32 spin_limit) {
+                   const u32 spin_limit, const ScanViews sv) {
     __shared__ u32 s_wsum[32];
     // blockIdx.y: which view of the batch (each with its own keys, counts, offsets, look-back row and tail)
     depth_keys_sorted += blockIdx.y * item_stride; tiles += blockIdx.y * item_stride; offsets += blockIdx.y * item_stride;
@@ -54,6 +62,10 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
     for (int q = 0; q < kScanItems; ++q) {
         c[q] = j0 + q < n ? (u32)tiles[id[q]] : 0u;
         if (drop_last && id[q] == (u32)(n - 1)) c[q] = 0;  // the reference never emits pairs for the last splat
+        if (ROWS && c[q]) {                                // height of the tile rectangle
+            const u32 ry = __float_as_uint(__ldg(sv.records[blockIdx.y] + (size_t)id[q] * 3 + 2).w);
+            c[q] = (ry >> 16) - (ry & 0xffffu);
+        }
         mine += c[q];
     }
     u32 incl = mine;
@@ -112,7 +124,15 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
         }
         if (lane == 0) {
             s_prefix = earlier;
-            if ((int)tile == (n + kScanTile - 1) / kScanTile - 1) tail->total = earlier + block_total;
+            if ((int)tile == (n + kScanTile - 1) / kScanTile - 1) {
+                if (ROWS) {
+                    tail->total_rows = earlier + block_total;
+                    const u32* info = sv.row_info[blockIdx.y];   // written by the tile layout, earlier on this stream
+                    tail->total = (u64)info[kRowInfoTotal] | ((u64)info[kRowInfoTotal + 1] << 32);
+                } else {
+                    tail->total = earlier + block_total;
+                }
+            }
         }
     }
     __syncthreads();
@@ -196,7 +216,7 @@ struct LayoutViews {       // one block per view
 };
 __global__ void __launch_bounds__(kLayoutThreads)
 tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x, const int tiles_y, const SortPlan plan,
-                   const int use_smem, const int trailing_quirk) {
+                   const int use_smem, const int trailing_quirk, const int row_binned) {
     extern __shared__ int s_grid[];
     int* __restrict__ marks = lv.marks[blockIdx.x];
     u32* __restrict__ hist = lv.hist[blockIdx.x];
@@ -205,9 +225,11 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     __shared__ u32 s_wsum[32];
     __shared__ u32 s_carry;
     __shared__ u64 s_last;   // (index of the last non-empty tile + 1) << 32 | start of its range; 0: no tile has pairs
+    __shared__ u32 s_row_start[kRowInfoStarts];   // first list position of every tile row (row-binned images)
+    __shared__ u64 s_total;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int stride = tiles_x + 1, rows = tiles_y + 1;
-    if (tid == 0) s_last = 0;
+    if (tid == 0) { s_last = 0; s_total = 0; }
     for (int i = tid; i < 4 * 256; i += kLayoutThreads) (&s_hist[0][0])[i] = 0;
     // The grid is worked on in shared memory when it fits (up to about 4K images), else in place.
     int* diff = use_smem ? s_grid : marks;
@@ -258,7 +280,7 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
         const int ty = t / tiles_x, tx = t - ty * tiles_x;
         const u32 c = (u32)max(diff[ty * stride + tx], 0);
         mine += c;
-        if (c && hist) {
+        if (c && hist && !row_binned) {
             const u64 key = (u64)(u32)t << 32;
             for (int q = 0; q < plan.npass && q < 4; ++q)
                 atomicAdd(&s_hist[q][sort_digit(key, plan.shift[q], plan.mask[q], plan.flip[q])], c);
@@ -285,9 +307,11 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     __syncthreads();
     u32 running = s_wsum[warp] + incl - mine;
     u64 my_last = 0;
+    if (mine) atomicAdd(&s_total, (u64)mine);   // the pair total in 64 bits (32-bit positions wrap beyond 2^32 pairs)
     for (int t = t_begin; t < t_end; ++t) {
         const int ty = t / tiles_x, tx = t - ty * tiles_x;
         ranges[t] = (int32_t)running;
+        if (row_binned && tx == 0) s_row_start[ty] = running;
         const u32 c = (u32)max(diff[ty * stride + tx], 0);
         if (c) my_last = ((u64)(u32)(t + 1) << 32) | running;
         running += c;
@@ -304,8 +328,24 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
             for (int t = max(t_begin, last_tile + 1); t < t_end; ++t) ranges[t] = (int32_t)(u32)last;
         }
     }
-    if (hist)
+    if (hist && !row_binned)
         for (int i = tid; i < plan.npass * 256 && i < 4 * 256; i += kLayoutThreads) hist[i] = (&s_hist[0][0])[i];
+    if (hist && row_binned) {   // what row_scatter_kernel and the plan's scan read (layout of the block: common.cuh)
+        __syncthreads();
+        if (tid == 0) {
+            s_row_start[tiles_y] = s_carry;
+            hist[kRowInfoTotal] = (u32)s_total;
+            hist[kRowInfoTotal + 1] = (u32)(s_total >> 32);
+            u32 blocks = 0;
+            for (int r = 0; r < tiles_y; ++r) {
+                hist[r] = blocks;
+                blocks += (s_row_start[r + 1] - s_row_start[r] + (u32)kRowTile - 1u) / (u32)kRowTile;
+            }
+            hist[tiles_y] = blocks;
+        }
+        __syncthreads();
+        for (int r = tid; r <= tiles_y; r += kLayoutThreads) hist[kRowInfoStarts + r] = s_row_start[r];
+    }
     if (!use_smem) return;  // the grid lives in `marks` itself: no room for the order, callers fall back to tile order
 
     // ---- tile order by falling count: counting sort over 256 classes (exponent and three mantissa bits)
@@ -397,10 +437,14 @@ int64_t plan_workspace_bytes(int n) { return plan_workspace_bytes_views(n, 1); }
 // offsets hold one row of `n` entries per view, `item_stride` entries apart; k_host receives one total per view.
 // k_host == nullptr: only the launches; read_plan_totals_views() fetches the totals later.
 int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
-                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
+                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s,
+                      const float* const* records, const u32* const* row_info, int64_t* k_rows_host) {
     DSB_REQUIRE(views >= 1 && views <= DSB_MAX_BATCH_VIEWS, "plan: between 1 and %d views per call", DSB_MAX_BATCH_VIEWS);
+    DSB_REQUIRE(!records == !row_info, "plan: records and layout blocks go together");
     if (k_host)
         for (int v = 0; v < views; ++v) k_host[v] = 0;
+    if (k_rows_host)
+        for (int v = 0; v < views; ++v) k_rows_host[v] = 0;
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(tiles && depth_keys && depth_keys_alt && offsets && ws, "plan: null pointer");
     DSB_REQUIRE(views == 1 || item_stride >= n, "plan: rows of the views overlap");
@@ -442,28 +486,43 @@ int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride
         int* device_status = nullptr;
         const int rc = device_status_address(&device_status);
         if (rc != DSB_OK) return rc;
-        scan_counts_kernel<<<dim3((unsigned)scan_tiles, (unsigned)views), kScanThreads, 0, s>>>(
-            depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8,
-            device_status, kSpinLimit);
+        ScanViews sv = {};
+        if (records) {
+            for (int v = 0; v < views; ++v) {
+                DSB_REQUIRE(records[v] && row_info[v], "plan: null records or layout block for view %d", v);
+                sv.records[v] = reinterpret_cast<const float4*>(records[v]);
+                sv.row_info[v] = row_info[v];
+            }
+            scan_counts_kernel<true><<<dim3((unsigned)scan_tiles, (unsigned)views), kScanThreads, 0, s>>>(
+                depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8,
+                device_status, kSpinLimit, sv);
+        } else {
+            scan_counts_kernel<false><<<dim3((unsigned)scan_tiles, (unsigned)views), kScanThreads, 0, s>>>(
+                depth_keys, tiles, n, cp.drop_last, offsets, lookback, tail, views > 1 ? item_stride : 0, scan_row / 8,
+                device_status, kSpinLimit, sv);
+        }
         DSB_LAUNCH_CHECK();
     }
 
     if (!k_host) return DSB_OK;
-    return read_plan_totals_views(views, n, ws, ws_bytes, k_host, s);
+    return read_plan_totals_views(views, n, ws, ws_bytes, k_host, s, k_rows_host);
 }
 
 // The pair totals of a plan launched before on stream s (one host synchronisation), and the status words of its
 // bounded waits.
-int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s) {
+int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s,
+                           int64_t* k_rows_host) {
     DSB_REQUIRE(k_host, "plan: k_host is null");
     DSB_REQUIRE(views >= 1 && views <= DSB_MAX_BATCH_VIEWS, "plan: between 1 and %d views per call", DSB_MAX_BATCH_VIEWS);
     for (int v = 0; v < views; ++v) k_host[v] = 0;
+    if (k_rows_host)
+        for (int v = 0; v < views; ++v) k_rows_host[v] = 0;
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(ws && ws_bytes >= plan_workspace_bytes_views(n, views), "plan: not the workspace the plan was launched with");
     const unsigned char* base = reinterpret_cast<const unsigned char*>(ws);
     const int64_t sort_stride = sort_batch_stride_bytes(n), sort_bytes = (int64_t)views * sort_stride;
     const PlanTail* tail = reinterpret_cast<const PlanTail*>(base + sort_bytes + (int64_t)views * plan_scan_row_bytes(n));
-    struct HostTail { u64 total; u32 counter; int status; } host_tail[DSB_MAX_BATCH_VIEWS];
+    struct HostTail { u64 total; u64 total_rows; u32 counter; int status; u64 pad; } host_tail[DSB_MAX_BATCH_VIEWS];
     int sort_status[DSB_MAX_BATCH_VIEWS] = {};
     static_assert(sizeof(HostTail) == sizeof(PlanTail), "host mirror of the plan tail");
     DSB_CUDA_CHECK(cudaMemcpyAsync(host_tail, tail, sizeof(HostTail) * views, cudaMemcpyDeviceToHost, s));
@@ -483,6 +542,7 @@ int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, i
             return DSB_ERR_DEVICE_WAIT_EXPIRED;
         }
         k_host[v] = (int64_t)host_tail[v].total;
+        if (k_rows_host) k_rows_host[v] = (int64_t)host_tail[v].total_rows;
     }
     if (earlier != DSB_OK) return earlier;   // recorded by a kernel outside this plan (a render's tile sort)
     for (int v = 0; v < views; ++v) {
@@ -526,9 +586,9 @@ int debug_expire_scan_wait(const CamParams& cp, int n, const int32_t* tiles, con
     int* device_status = nullptr;
     const int rc = device_status_address(&device_status);
     if (rc != DSB_OK) return rc;
-    scan_counts_kernel<<<dim3((unsigned)(scan_tiles - 1), 1), kScanThreads, 0, s>>>(
+    scan_counts_kernel<false><<<dim3((unsigned)(scan_tiles - 1), 1), kScanThreads, 0, s>>>(
         depth_keys_sorted, tiles, n, cp.drop_last, offsets, lookback, tail, 0, plan_scan_row_bytes(n) / 8, device_status,
-        spin_limit);
+        spin_limit, ScanViews{});
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }
@@ -564,6 +624,7 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
                              int32_t* const* ranges, int* has_order, cudaStream_t s) {
     DSB_REQUIRE(count >= 1 && count <= DSB_MAX_BATCH_VIEWS, "tile_layout: between 1 and %d views", DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(plan.npass <= 4, "tile_layout: at most 4 digit passes");
+    DSB_REQUIRE(!row_binning_supported(cp) || hist, "tile_layout: a row-binned image needs its layout block");
     LayoutViews lv;
     for (int v = 0; v < count; ++v) {
         DSB_REQUIRE(tile_marks[v] && ranges[v], "tile_layout: null pointer");
@@ -579,7 +640,8 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
     // lists identical to the reference's (its rectangles, its dropped last splat): keep its range habit too
     const int trailing_quirk = cp.drop_last && !cp.tight_tiles;
     tile_layout_kernel<<<count, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(lv, (int)tile_marks_copy_ints(cp.H, cp.W),
-                                                                               cp.tiles_x, cp.tiles_y, plan, use_smem, trailing_quirk);
+                                                                               cp.tiles_x, cp.tiles_y, plan, use_smem, trailing_quirk,
+                                                                               row_binning_supported(cp) ? 1 : 0);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -204,7 +204,6 @@ int dsb_stage_timing_read(int32_t stage_count, double* ms_total, int64_t* calls)
 
 int64_t dsb_plan_workspace_bytes(int32_t n) { return plan_workspace_bytes(n < 0 ? 0 : n); }
 int64_t dsb_sort_workspace_bytes(int64_t k) { return sort_workspace_bytes(k < 0 ? 0 : k); }
-static int64_t sort_workspace_bytes_needed(int64_t k) { return k <= 1 ? 0 : sort_workspace_bytes(k); }
 int64_t dsb_tile_marks_bytes(int32_t image_height, int32_t image_width) {
     return (image_height > 0 && image_width > 0) ? tile_marks_bytes(image_height, image_width) : 0;
 }
@@ -235,20 +234,38 @@ int64_t dsb_plan_workspace_bytes_views(int32_t n, int32_t num_views) {
     return (n >= 0 && num_views >= 1 && num_views <= DSB_MAX_BATCH_VIEWS) ? plan_workspace_bytes_views(n, num_views) : 0;
 }
 
-int dsb_plan_pairs_views(const DsbCamera* cam, int32_t num_views, int32_t n, int64_t row_stride,
-                         const int32_t* tiles_touched, uint64_t* depth_keys, uint64_t* depth_keys_alt, uint32_t* offsets,
-                         void* workspace, int64_t workspace_bytes, int64_t* k_host, void* stream) {
+int dsb_plan_views(const DsbCamera* cam, int32_t num_views, int32_t n, int64_t row_stride, const float* const* records,
+                   const int32_t* tiles_touched, uint64_t* depth_keys, uint64_t* depth_keys_alt, uint32_t* offsets,
+                   const uint32_t* const* layout, void* workspace, int64_t workspace_bytes, int64_t* k_host,
+                   int64_t* k_rows_host, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
+    const bool rows = row_binning_supported(cp);
+    DSB_REQUIRE(!rows || (records && layout), "plan_views: records and layout blocks are required for this image size");
     return launch_plan_views(cp, num_views, n, row_stride, tiles_touched, reinterpret_cast<u64*>(depth_keys),
                              reinterpret_cast<u64*>(depth_keys_alt), offsets, workspace, workspace_bytes, k_host,
-                             (cudaStream_t)stream);
+                             (cudaStream_t)stream, rows ? records : nullptr, rows ? layout : nullptr, k_rows_host);
 }
 
 int dsb_plan_totals_views(int32_t num_views, int32_t n, const void* workspace, int64_t workspace_bytes, int64_t* k_host,
-                          void* stream) {
+                          int64_t* k_rows_host, void* stream) {
     DSB_REQUIRE(n >= 0, "n must be non-negative");
-    return read_plan_totals_views(num_views, n, workspace, workspace_bytes, k_host, (cudaStream_t)stream);
+    return read_plan_totals_views(num_views, n, workspace, workspace_bytes, k_host, (cudaStream_t)stream, k_rows_host);
+}
+
+int32_t dsb_row_binning_supported(int32_t image_height, int32_t image_width) {
+    if (image_height <= 0 || image_width <= 0) return 0;
+    CamParams cp = {};
+    cp.H = image_height; cp.W = image_width;
+    cp.tiles_x = (cp.W + kTile - 1) / kTile; cp.tiles_y = (cp.H + kTile - 1) / kTile;
+    return row_binning_supported(cp) ? 1 : 0;
+}
+
+int64_t dsb_render_workspace_bytes(int32_t image_height, int32_t image_width, int64_t k, int64_t k_rows) {
+    if (k < 0) k = 0;
+    if (k_rows < 0) k_rows = 0;
+    if (dsb_row_binning_supported(image_height, image_width)) return row_workspace_bytes(k, k_rows);
+    return ((k * 8 + 255) / 256) * 256 + sort_workspace_bytes(k);   // alternate pair buffer + tile sort scratch
 }
 
 int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
@@ -318,12 +335,13 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
 int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
                      const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
                      float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
-                     uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* workspace,
-                     int64_t workspace_bytes, int64_t* k_host, void* stream) {
+                     uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, int32_t* ranges, uint32_t* layout,
+                     void* workspace, int64_t workspace_bytes, int64_t* k_host, int64_t* k_rows_host, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
-    DSB_REQUIRE(tile_marks, "forward_plan: tile_marks is null");
-    DSB_REQUIRE(k_host, "forward_plan: k_host is null");
+    DSB_REQUIRE(tile_marks && ranges && layout, "forward_plan: null tile_marks, ranges or layout");
+    DSB_REQUIRE(k_host && k_rows_host, "forward_plan: k_host or k_rows_host is null");
+    *k_host = 0; *k_rows_host = 0;
     cudaStream_t s = (cudaStream_t)stream;
     {
         StageScope scope(kStagePreprocess, s);
@@ -333,76 +351,90 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
                                          tile_marks, s);
         if (rc != DSB_OK) return rc;
     }
-    return launch_plan(cp, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
-                       offsets, workspace, workspace_bytes, k_host, s);
+    {   // tile ranges, tile order and the row-binning block (or the tile sort's digit counts) from the corner marks
+        StageScope scope(kStageRanges, s);
+        int has_order = 0;
+        const int rc = launch_tile_layout(cp, tile_marks, tile_sort_plan(cp), layout, ranges, &has_order, s);
+        if (rc != DSB_OK) return rc;
+    }
+    if (n == 0) return DSB_OK;
+    const bool rows = row_binning_supported(cp);
+    const float* rec = records;
+    const u32* info = layout;
+    return launch_plan_views(cp, 1, n, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
+                             offsets, workspace, workspace_bytes, k_host, s, rows ? &rec : nullptr, rows ? &info : nullptr,
+                             k_rows_host);
 }
 
-int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records, const int32_t* tiles_touched,
-                       const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs, uint64_t* pairs_alt,
-                       int32_t* tile_marks, void* workspace, int64_t workspace_bytes, int32_t* ranges, float* image,
-                       float* final_T, int32_t* final_idx, float* depth, const uint32_t* layout_hist, void* stream) {
+int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, int64_t k_rows, const float* records,
+                       const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets, uint64_t* pairs,
+                       const int32_t* tile_marks, const int32_t* ranges, const uint32_t* layout, void* workspace,
+                       int64_t workspace_bytes, float* image, float* final_T, int32_t* final_idx, float* depth, void* stream) {
     CAM_OR_RETURN(cam, cp);
     cudaStream_t s = (cudaStream_t)stream;
-    // Only the tile id needs sorting: ceil(log2(tiles)) live bits above bit 32.  The preprocess kernel marked
-    // every splat's tile rectangle in a small grid; one block turns that grid into the tile ranges and the sort's
-    // digit counts, so nothing reads the K pairs except the sort passes themselves.
-    DSB_REQUIRE(k < DSB_MAX_PAIRS, "too many pairs");
-    DSB_REQUIRE(tile_marks && ranges, "forward_render: null tile_marks or ranges");
-    DSB_REQUIRE(k <= 1 || (pairs && pairs_alt && workspace), "forward_render: null pair buffers or workspace");
-    const SortPlan plan = tile_sort_plan(cp);
-    int has_order = 0;
-    u32* hist = nullptr;
-    int rc;
-    {
-        StageScope scope(kStageEmit, s);
-        rc = sort_begin(k, plan, workspace, workspace_bytes, &hist, s);
+    DSB_REQUIRE(k >= 0 && k < DSB_MAX_PAIRS, "too many pairs");
+    DSB_REQUIRE(tile_marks && ranges && layout, "forward_render: null tile_marks, ranges or layout");
+    DSB_REQUIRE(k == 0 || (pairs && workspace), "forward_render: null pair buffer or workspace");
+    const int has_order = tile_order_available(cp.H, cp.W);
+    int rc = DSB_OK;
+    if (row_binning_supported(cp)) {
+        // depth-ordered splats -> row items -> ONE pass over the pairs (row_binning.cu)
+        rc = launch_row_binning(cp, n, k, k_rows, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
+                                ranges, layout, reinterpret_cast<u64*>(pairs), workspace, workspace_bytes, s);
         if (rc != DSB_OK) return rc;
-        rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
-                         reinterpret_cast<u64*>(pairs), s);
-    }
-    if (rc != DSB_OK) return rc;
-    if (layout_hist) {   // the layout of this view was made by dsb_preprocess_views: ranges and tile order are in place
-        has_order = tile_order_available(cp.H, cp.W);
+    } else if (k > 0) {
+        // Images wider than 256 tiles or taller than 509: pairs written in depth order, then a stable sort on their
+        // tile bits with the digit counts the layout left; the workspace holds the alternate buffer and the scratch.
+        const int64_t alt_bytes = ((k * 8 + 255) / 256) * 256;
+        DSB_REQUIRE(workspace_bytes >= alt_bytes + sort_workspace_bytes(k), "forward_render: workspace too small");
+        u64* pairs_alt = reinterpret_cast<u64*>(workspace);
+        void* sort_ws = reinterpret_cast<unsigned char*>(workspace) + alt_bytes;
+        const SortPlan plan = tile_sort_plan(cp);
+        u32* hist = nullptr;
+        {
+            StageScope scope(kStageEmit, s);
+            rc = sort_begin(k, plan, sort_ws, workspace_bytes - alt_bytes, &hist, s);
+            if (rc != DSB_OK) return rc;
+            rc = launch_emit(cp, n, k, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
+                             reinterpret_cast<u64*>(pairs), s);
+            if (rc != DSB_OK) return rc;
+        }
         if (hist)
-            DSB_CUDA_CHECK(cudaMemcpyAsync(hist, layout_hist, (size_t)plan.npass * 256 * sizeof(u32), cudaMemcpyDeviceToDevice, s));
-    } else {
-        StageScope scope(kStageRanges, s);
-        rc = launch_tile_layout(cp, tile_marks, plan, hist, ranges, &has_order, s);
-    }
-#ifdef DSB_NO_TILE_ORDER
-    has_order = 0;
-#endif
-    if (rc != DSB_OK) return rc;
-    int in_alt = 0;
-    {
+            DSB_CUDA_CHECK(cudaMemcpyAsync(hist, layout, (size_t)plan.npass * 256 * sizeof(u32), cudaMemcpyDeviceToDevice, s));
+        int in_alt = 0;
         StageScope scope(kStageTileSort, s);
-        rc = sort_passes(reinterpret_cast<u64*>(pairs), reinterpret_cast<u64*>(pairs_alt), nullptr, nullptr, k, plan,
-                         workspace, &in_alt, s);
+        rc = sort_passes(reinterpret_cast<u64*>(pairs), pairs_alt, nullptr, nullptr, k, plan, sort_ws, &in_alt, s);
         if (rc != DSB_OK) return rc;
         if (in_alt) DSB_CUDA_CHECK(cudaMemcpyAsync(pairs, pairs_alt, (size_t)k * 8, cudaMemcpyDeviceToDevice, s));
     }
     StageScope scope(kStageBlendForward, s);
     return launch_blend_forward(cp, records, reinterpret_cast<const u64*>(pairs), ranges, image, final_T, final_idx, depth,
+#ifdef DSB_NO_TILE_ORDER
+                                nullptr, s);
+#else
                                 has_order ? tile_marks : nullptr, s);
+#endif
 }
 
 int dsb_forward(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
                 const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
                 float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
-                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* plan_workspace,
-                int64_t plan_workspace_bytes, uint64_t* pairs, uint64_t* pairs_alt, int64_t pair_capacity,
-                void* sort_workspace, int64_t sort_workspace_bytes, int32_t* ranges, float* image, float* final_T,
-                int32_t* final_idx, float* depth, int64_t* k_host, int32_t* rendered_host, void* stream) {
-    DSB_REQUIRE(k_host && rendered_host, "forward: k_host or rendered_host is null");
+                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, int32_t* ranges, uint32_t* layout,
+                void* plan_workspace, int64_t plan_workspace_bytes, uint64_t* pairs, int64_t pair_capacity,
+                void* render_workspace, int64_t render_workspace_bytes, float* image, float* final_T, int32_t* final_idx,
+                float* depth, int64_t* k_host, int64_t* k_rows_host, int32_t* rendered_host, void* stream) {
+    DSB_REQUIRE(k_host && k_rows_host && rendered_host, "forward: k_host, k_rows_host or rendered_host is null");
     *rendered_host = 0;
     int rc = dsb_forward_plan(cam, n, means3d, shs, colors_precomp, opacities, scales, rotations, cov3d_precomp, records, radii,
-                              tiles_touched, cov3d, depth_keys, depth_keys_alt, offsets, tile_marks, plan_workspace,
-                              plan_workspace_bytes, k_host, stream);
+                              tiles_touched, cov3d, depth_keys, depth_keys_alt, offsets, tile_marks, ranges, layout,
+                              plan_workspace, plan_workspace_bytes, k_host, k_rows_host, stream);
     if (rc != DSB_OK) return rc;
     const int64_t k = *k_host;
-    if (k > pair_capacity || sort_workspace_bytes < sort_workspace_bytes_needed(k)) return DSB_OK;   // caller grows and renders
-    rc = dsb_forward_render(cam, n, k, records, tiles_touched, depth_keys, offsets, pairs, pairs_alt, tile_marks, sort_workspace,
-                            sort_workspace_bytes, ranges, image, final_T, final_idx, depth, nullptr, stream);
+    if (k > pair_capacity ||
+        (k > 0 && render_workspace_bytes < dsb_render_workspace_bytes(cam->image_height, cam->image_width, k, *k_rows_host)))
+        return DSB_OK;   // the caller grows its buffers and renders
+    rc = dsb_forward_render(cam, n, k, *k_rows_host, records, tiles_touched, depth_keys, offsets, pairs, tile_marks, ranges,
+                            layout, render_workspace, render_workspace_bytes, image, final_T, final_idx, depth, stream);
     if (rc == DSB_OK) *rendered_host = 1;
     return rc;
 }
@@ -563,9 +595,9 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
     const size_t nn = (size_t)n;
     const size_t b_records = up(nn * 48), b_i32 = up(nn * 4), b_cov = up(nn * 24), b_keys = up(nn * 8);
     const size_t b_marks = up((size_t)tile_marks_bytes(cp.H, cp.W)), b_plan = up((size_t)plan_workspace_bytes(n));
-    const size_t b_ranges = up(((size_t)cp.tiles_x * cp.tiles_y + 1) * 4), b_pix = up(pixels * 4);
+    const size_t b_ranges = up(((size_t)cp.tiles_x * cp.tiles_y + 1) * 4), b_pix = up(pixels * 4), b_layout = up(kLayoutWords * 4);
     unsigned char* a = nullptr;   // arena 1: everything whose size is known before the pair count
-    const size_t bytes1 = b_records + 3 * b_i32 + b_cov + 2 * b_keys + b_marks + b_plan + b_ranges + 2 * b_pix;
+    const size_t bytes1 = b_records + 3 * b_i32 + b_cov + 2 * b_keys + b_marks + b_plan + b_ranges + b_layout + 2 * b_pix;
     DSB_CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&a), bytes1, s));
     unsigned char* p = a;
     auto take = [&p](size_t b) { unsigned char* r = p; p += b; return r; };
@@ -579,22 +611,23 @@ int dsb_forward_core(const float* means3d, const float* shs, const float* opacit
     int32_t* marks = reinterpret_cast<int32_t*>(take(b_marks));
     void* plan_ws = take(b_plan);
     int32_t* ranges = reinterpret_cast<int32_t*>(take(b_ranges));
+    uint32_t* layout = reinterpret_cast<uint32_t*>(take(b_layout));
     float* final_T = reinterpret_cast<float*>(take(b_pix));
     int32_t* final_idx = reinterpret_cast<int32_t*>(take(b_pix));
-    int64_t k = 0;
+    int64_t k = 0, k_rows = 0;
     int rc = dsb_forward_plan(&cam, n, means3d, shs, nullptr, opacities, scales, rotations, nullptr, records, radii, tiles, cov3d,
-                              keys, keys_alt, offsets, marks, plan_ws, (int64_t)b_plan, &k, stream);
-    unsigned char* b = nullptr;   // arena 2: pair list and sort workspace
+                              keys, keys_alt, offsets, marks, ranges, layout, plan_ws, (int64_t)b_plan, &k, &k_rows, stream);
+    unsigned char* b = nullptr;   // arena 2: pair list and render workspace
     if (rc == DSB_OK) {
-        const size_t b_pairs = up((size_t)(k > 0 ? k : 1) * 8), b_sort = up((size_t)sort_workspace_bytes(k));
-        const cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&b), 2 * b_pairs + b_sort, s);
+        const size_t b_pairs = up((size_t)(k > 0 ? k : 1) * 8);
+        const size_t b_render = up((size_t)dsb_render_workspace_bytes(image_height, image_width, k, k_rows));
+        const cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&b), b_pairs + b_render, s);
         if (e != cudaSuccess) {
             set_error("forward_core: cudaMallocAsync of the pair list failed: %s", cudaGetErrorString(e));
             rc = DSB_ERR_CUDA;
         } else {
-            rc = dsb_forward_render(&cam, n, k, records, tiles, keys, offsets, reinterpret_cast<uint64_t*>(b),
-                                    reinterpret_cast<uint64_t*>(b + b_pairs), marks, b + 2 * b_pairs, (int64_t)b_sort, ranges,
-                                    output_image, final_T, final_idx, nullptr, nullptr, stream);
+            rc = dsb_forward_render(&cam, n, k, k_rows, records, tiles, keys, offsets, reinterpret_cast<uint64_t*>(b), marks, ranges,
+                                    layout, b + b_pairs, (int64_t)b_render, output_image, final_T, final_idx, nullptr, stream);
         }
     }
     if (b) cudaFreeAsync(b, s);

@@ -148,11 +148,33 @@ int sort_begin(int64_t k, const SortPlan& plan, void* ws, int64_t ws_bytes, u32*
 int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k, const SortPlan& plan, void* ws,
                 int* in_alt, cudaStream_t s, int batch = 1, int64_t item_stride = 0);
 
+// ---- row binning (row_binning.cu): the fused render's way from depth-ordered splats to the sorted pair list ----
+// Row item: one (splat, tile row) of a splat's tile rectangle, 64 bits: row | first column | width | splat id.
+constexpr int kRowItemRowShift = 52, kRowItemX0Shift = 42, kRowItemWShift = 32;
+constexpr u32 kRowItemFieldMask = 1023u;
+constexpr int kRowScatterItems = 8;                 // pairs per thread of the scatter pass
+constexpr int kRowTile = 256 * kRowScatterItems;    // pairs per block of the scatter pass
+// What tile_layout_kernel leaves in a view's 1024-word layout block when the view is row-binned:
+//   [0 .. tiles_y]                      blocks of the scatter pass before each tile row (and their total)
+//   [kRowInfoStarts .. + tiles_y]       first final-list position of each tile row (and K)
+//   [kRowInfoTotal, kRowInfoTotal + 1]  K as 64 bits (exact even where 32-bit positions would wrap)
+constexpr int kRowInfoStarts = 512, kRowInfoTotal = 1022;
+constexpr int kLayoutWords = 1024;
+bool row_binning_supported(const CamParams& cp);
+int64_t row_workspace_bytes(int64_t k, int64_t k_rows);
+int launch_row_binning(const CamParams& cp, int n, int64_t k, int64_t k_rows, const float* records, const int32_t* tiles,
+                       const u64* depth_keys_sorted, const u32* row_offsets, const int32_t* ranges, const u32* row_info,
+                       u64* pairs, void* ws, int64_t ws_bytes, cudaStream_t s);
+
 int64_t plan_workspace_bytes(int n);
 int64_t plan_workspace_bytes_views(int n, int views);
+// records / row_info: null for the per-stage plan (offsets = first PAIR of every depth-ordered splat), else one
+// pointer per view (offsets = first ROW ITEM of every depth-ordered splat; the pair total comes from row_info).
 int launch_plan_views(const CamParams& cp, int views, int n, int64_t item_stride, const int32_t* tiles, u64* depth_keys,
-                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
-int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
+                      u64* depth_keys_alt, u32* offsets, void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s,
+                      const float* const* records = nullptr, const u32* const* row_info = nullptr, int64_t* k_rows_host = nullptr);
+int read_plan_totals_views(int views, int n, const void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s,
+                           int64_t* k_rows_host = nullptr);
 int launch_plan(const CamParams& cp, int n, const int32_t* tiles, u64* depth_keys, u64* depth_keys_alt, u32* offsets,
                 void* ws, int64_t ws_bytes, int64_t* k_host, cudaStream_t s);
 // Test hooks: one scan / one sort pass in which the first tile of the look-back chain is never processed, so the
@@ -175,6 +197,8 @@ int64_t tile_marks_bytes(int H, int W);
 int64_t tile_marks_copy_ints(int H, int W);   // distance between two copies, in ints
 int launch_tile_layout(const CamParams& cp, int* tile_marks, const SortPlan& plan, u32* hist, int32_t* ranges,
                        int* has_order, cudaStream_t s);
+// hist: per view kLayoutWords words that receive the tile sort's digit counts, or the row-binning block (see above)
+// when the image is row-binned.
 int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_marks, const SortPlan& plan, u32* const* hist,
                              int32_t* const* ranges, int* has_order, cudaStream_t s);
 SortPlan tile_sort_plan(const CamParams& cp);

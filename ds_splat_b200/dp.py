@@ -142,7 +142,7 @@ class _Slot:
         self.grad_acc = torch.empty((n, capi.GRAD_FLOATS), **f32)
         self.marks = {}     # (H, W) -> tile-mark grid, later the tile order
         self.ranges = {}    # (H, W) -> tile ranges of the view
-        self.layout_hist = torch.empty(1024, dtype=torch.int32, device=dev)   # the tile sort's digit counts
+        self.layout = torch.empty(capi.LAYOUT_WORDS, dtype=torch.int32, device=dev)   # layout block of the fused render
         self.cam = None     # (DsbCamera, keep-alive) of the view the slot holds
 
 
@@ -193,9 +193,11 @@ class _Lane:
 
     def __init__(self, stream=None):
         self.stream = stream    # None: whatever stream is current
-        self.pairs = None
-        self.sort_ws = None
-        self.sort_bytes = 0
+        self.pairs = None       # sorted (tile, splat) pairs of the lane's view
+        self.cap = 0            # pairs the list holds
+        self.render_ws = None   # row items, their sort and scan, the scatter's look-back words
+        self.render_bytes = 0
+        self.cap_rows = 0       # row items the workspace was sized for
         self.img = {}
 
 
@@ -232,6 +234,7 @@ class ViewRenderer:
         self.view_streams = max(1, int(view_streams))   # lanes render_views spreads a batch's views over
         self.lanes = [_Lane()]
         self.last_k = 0
+        self.last_k_rows = 0
         self.last_ks = []
 
     # buffers of the view rendered last (kept as attributes for callers that inspect them)
@@ -279,32 +282,34 @@ class ViewRenderer:
                                     self.offset_rows[i]))
         return self.slots[j]
 
-    def _pair_buffers(self, k: int, lane: int = 0) -> _Lane:
+    def _pair_buffers(self, k: int, k_rows: int, h: int, w: int, lane: int = 0) -> _Lane:
+        """Pair list and render workspace of a lane, grown (with 25% slack) when a view needs more than they hold."""
         ln = self.lanes[lane]
-        if ln.pairs is None or ln.pairs.shape[1] < k:
-            cap = max(int(k * 1.25), 1024)
+        need = int(self.lib.dsb_render_workspace_bytes(h, w, k, k_rows))
+        if ln.pairs is None or ln.cap < k or ln.render_bytes < need:
             if ln.pairs is not None and ln.stream is not None:
                 ln.stream.synchronize()   # the old buffers go back to the allocator of another stream
-            ln.pairs = torch.empty((2, cap), dtype=torch.int64, device=self.dev)
-            ln.sort_bytes = int(self.lib.dsb_sort_workspace_bytes(cap))
-            ln.sort_ws = torch.empty(ln.sort_bytes, dtype=torch.uint8, device=self.dev)
+            ln.cap = max(int(k * 1.25), 1024, ln.cap)
+            ln.cap_rows = max(int(k_rows * 1.25), 1024, ln.cap_rows)
+            ln.pairs = torch.empty(ln.cap, dtype=torch.int64, device=self.dev)
+            ln.render_bytes = int(self.lib.dsb_render_workspace_bytes(h, w, ln.cap, ln.cap_rows))
+            ln.render_ws = torch.empty(ln.render_bytes, dtype=torch.uint8, device=self.dev)
         return ln
 
-    def _render(self, slot: _Slot, cam: CameraTensors, k: int, layout_done: bool = False, lane: int = 0):
-        """Second half of a forward: pairs, tile layout (unless the batch made it already), tile sort, blend, on
-        the current stream with the buffers of ``lane``.  Returns the image buffer."""
+    def _render(self, slot: _Slot, cam: CameraTensors, k: int, k_rows: int, lane: int = 0):
+        """Second half of a forward: from the depth-ordered splats to the sorted pair list and the blended image, on the
+        current stream with the buffers of ``lane``.  Returns the image buffer."""
         capi, lib = self._capi, self.lib
         c, _keep = slot.cam
         image, final_t, final_idx = self._image_buffers(cam.H, cam.W, lane)
         ranges = self._ranges(slot, cam.H, cam.W)
-        ln = self._pair_buffers(k, lane)
+        ln = self._pair_buffers(k, k_rows, cam.H, cam.W, lane)
         capi.check(lib.dsb_forward_render(
-            C.byref(c), self.n, k, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
-            slot.offsets.data_ptr(), ln.pairs[0].data_ptr(), ln.pairs[1].data_ptr(),
-            self._marks(slot, cam.H, cam.W).data_ptr(), ln.sort_ws.data_ptr(), ln.sort_bytes, ranges.data_ptr(),
-            image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None,
-            slot.layout_hist.data_ptr() if layout_done else None, capi.stream_ptr()))
-        self.last_k = k
+            C.byref(c), self.n, k, k_rows, slot.records.data_ptr(), slot.tiles.data_ptr(), slot.depth_keys.data_ptr(),
+            slot.offsets.data_ptr(), ln.pairs.data_ptr(), self._marks(slot, cam.H, cam.W).data_ptr(), ranges.data_ptr(),
+            slot.layout.data_ptr(), ln.render_ws.data_ptr(), ln.render_bytes, image.data_ptr(), final_t.data_ptr(),
+            final_idx.data_ptr(), None, capi.stream_ptr()))
+        self.last_k, self.last_k_rows = k, k_rows
         self.cur = slot
         self._last_cam = cam
         return image
@@ -318,21 +323,20 @@ class ViewRenderer:
         # plan and render in one library call when the pair buffers of the previous view are large enough (they are
         # kept with 25% slack), so that no host work sits between the pair-count read-back and the render
         ln = self.lanes[0]
-        cap = 0 if ln.pairs is None else ln.pairs.shape[1]
         image, final_t, final_idx = self._image_buffers(cam.H, cam.W, 0)
         ranges = self._ranges(sl, cam.H, cam.W)
-        k, rendered = C.c_int64(0), C.c_int32(0)
+        k, k_rows, rendered = C.c_int64(0), C.c_int64(0), C.c_int32(0)
         capi.check(lib.dsb_forward(
             C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
             p["scales"].data_ptr(), p["rotations"].data_ptr(), None, sl.records.data_ptr(), sl.radii.data_ptr(),
             sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_rows[1, slot].data_ptr(),
-            sl.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
-            ln.pairs[0].data_ptr() if cap else None, ln.pairs[1].data_ptr() if cap else None, cap,
-            ln.sort_ws.data_ptr() if cap else None, ln.sort_bytes if cap else 0, ranges.data_ptr(), image.data_ptr(),
-            final_t.data_ptr(), final_idx.data_ptr(), None, C.byref(k), C.byref(rendered), capi.stream_ptr()))
+            sl.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), ranges.data_ptr(), sl.layout.data_ptr(),
+            self.plan_ws.data_ptr(), self.plan_bytes, ln.pairs.data_ptr() if ln.cap else None, ln.cap,
+            ln.render_ws.data_ptr() if ln.cap else None, ln.render_bytes, image.data_ptr(), final_t.data_ptr(),
+            final_idx.data_ptr(), None, C.byref(k), C.byref(k_rows), C.byref(rendered), capi.stream_ptr()))
         if not rendered.value:
-            return self._render(sl, cam, int(k.value))
-        self.last_k = int(k.value)
+            return self._render(sl, cam, int(k.value), int(k_rows.value))
+        self.last_k, self.last_k_rows = int(k.value), int(k_rows.value)
         self.cur = sl
         self._last_cam = cam
         return image
@@ -347,7 +351,7 @@ class ViewRenderer:
         g = grads.views
         capi.check(lib.dsb_backward(
             C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(),
-            sl.records.data_ptr(), self.cov3d.data_ptr(), sl.radii.data_ptr(), self.pairs[0].data_ptr(),
+            sl.records.data_ptr(), self.cov3d.data_ptr(), sl.radii.data_ptr(), self.pairs.data_ptr(),
             ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
             self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(),
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
@@ -387,14 +391,14 @@ class ViewRenderer:
                 p["scales"].data_ptr(), p["rotations"].data_ptr(), None, ptrs([sl.records for sl in slots]),
                 ptrs([sl.radii for sl in slots]), ptrs([sl.tiles for sl in slots]), self.cov3d.data_ptr(),
                 ptrs([sl.depth_keys for sl in slots]), ptrs([self._marks(sl, *size) for sl in slots]),
-                ptrs([self._ranges(sl, *size) for sl in slots]), ptrs([sl.layout_hist for sl in slots]), capi.stream_ptr()))
-            # depth order and pair offsets of all views: launched without a host wait, then ONE read-back of the totals
-            capi.check(lib.dsb_plan_pairs_views(
-                C.byref(slots[0].cam[0]), nv, self.n, self.n, self.tiles_rows.data_ptr(), self.depth_rows[0].data_ptr(),
-                self.depth_rows[1].data_ptr(), self.offset_rows.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes,
-                None, capi.stream_ptr()))
-            ks = (C.c_int64 * nv)()
-            capi.check(lib.dsb_plan_totals_views(nv, self.n, self.plan_ws.data_ptr(), self.plan_bytes, ks,
+                ptrs([self._ranges(sl, *size) for sl in slots]), ptrs([sl.layout for sl in slots]), capi.stream_ptr()))
+            # depth order and row-item offsets of all views: launched without a host wait, then ONE read-back of the totals
+            capi.check(lib.dsb_plan_views(
+                C.byref(slots[0].cam[0]), nv, self.n, self.n, ptrs([sl.records for sl in slots]), self.tiles_rows.data_ptr(),
+                self.depth_rows[0].data_ptr(), self.depth_rows[1].data_ptr(), self.offset_rows.data_ptr(),
+                ptrs([sl.layout for sl in slots]), self.plan_ws.data_ptr(), self.plan_bytes, None, None, capi.stream_ptr()))
+            ks, krs = (C.c_int64 * nv)(), (C.c_int64 * nv)()
+            capi.check(lib.dsb_plan_totals_views(nv, self.n, self.plan_ws.data_ptr(), self.plan_bytes, ks, krs,
                                                  capi.stream_ptr()))
             self.last_ks.extend(int(k) for k in ks)
             # The K-sized stages of the views, dealt over the lanes: lane 0 is the caller's stream, the others wait for
@@ -406,12 +410,12 @@ class ViewRenderer:
             for j, sl in enumerate(slots):
                 cam, li = cameras[b0 + j], j % nl
                 with torch.cuda.stream(lanes[li].stream if li else main):
-                    image = self._render(sl, cam, int(ks[j]), layout_done=True, lane=li)
+                    image = self._render(sl, cam, int(ks[j]), int(krs[j]), lane=li)
                     v_image = image_grads(b0 + j, image) if callable(image_grads) else image_grads[b0 + j]
                     _img, final_t, final_idx = self._image_buffers(cam.H, cam.W, li)
                     ranges = self._ranges(sl, cam.H, cam.W)
                     capi.check(lib.dsb_backward_blend(
-                        C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), lanes[li].pairs[0].data_ptr(),
+                        C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), lanes[li].pairs.data_ptr(),
                         ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
                         self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
             for ln in lanes[1:]:

@@ -140,6 +140,7 @@ class _Layout:
         self.tile_marks = take(int(lib.dsb_tile_marks_bytes(h, w)))
         self.plan_ws = take(self.plan_bytes)
         self.ranges = take((_capi.num_tiles(h, w) + 1) * 4)
+        self.layout = take(_capi.LAYOUT_WORDS * 4)
         self.final_t = take(h * w * 4)
         self.final_idx = take(h * w * 4)
         self.grad_acc = take(n * _capi.GRAD_FLOATS * 4)
@@ -208,30 +209,33 @@ class DsRasterizerFunction(torch.autograd.Function):
             depth = torch.empty((h, w), dtype=torch.float32, device=dev) if raster_settings.return_depth else None
             cov3d_ptr = cov_3d_precomp.data_ptr() if cov_3d_precomp is not None else a + lay.cov3d
 
+            # Pair list and render workspace are sized from the counts of the previous call of this shape, with 25%
+            # slack, so that plan and render run inside one library call; a view that needs more gets more.
             hint_key = (dev, n, h, w, raster_settings.tight_tiles)
-            cap = max(int(_pair_hint.get(hint_key, 8 * n) * 1.25), 1024)
-            sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
-            pair_arena = torch.empty(2 * _up256(cap * 8) + sort_bytes, dtype=torch.uint8, device=dev)
+            hint_k, hint_rows = _pair_hint.get(hint_key, (8 * n, 3 * n))
+            cap, cap_rows = max(int(hint_k * 1.25), 1024), max(int(hint_rows * 1.25), 1024)
+            ws_bytes = int(lib.dsb_render_workspace_bytes(h, w, cap, cap_rows))
+            pair_arena = torch.empty(_up256(cap * 8) + ws_bytes, dtype=torch.uint8, device=dev)
             b = pair_arena.data_ptr()
-            k, rendered = C.c_int64(0), C.c_int32(0)
+            k, k_rows, rendered = C.c_int64(0), C.c_int64(0), C.c_int32(0)
             _capi.check(lib.dsb_forward(
                 C.byref(cam), n, _capi.ptr(means_3d), _capi.ptr(shs), _capi.ptr(colors_precomp), _capi.ptr(opacities),
                 _capi.ptr(scales), _capi.ptr(rotations), _capi.ptr(cov_3d_precomp), a + lay.records, radii.data_ptr(),
                 a + lay.tiles, cov3d_ptr, a + lay.depth_keys, a + lay.depth_keys_alt, a + lay.offsets, a + lay.tile_marks,
-                a + lay.plan_ws, lay.plan_bytes, b, b + _up256(cap * 8), cap, b + 2 * _up256(cap * 8), sort_bytes,
-                a + lay.ranges, image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth),
-                C.byref(k), C.byref(rendered), stream))
-            k = int(k.value)
-            _pair_hint[hint_key] = k
-            if not rendered.value:   # more pairs than the buffers brought along hold: grow them and render
+                a + lay.ranges, a + lay.layout, a + lay.plan_ws, lay.plan_bytes, b, cap, b + _up256(cap * 8), ws_bytes,
+                image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth),
+                C.byref(k), C.byref(k_rows), C.byref(rendered), stream))
+            k, k_rows = int(k.value), int(k_rows.value)
+            _pair_hint[hint_key] = (k, k_rows)
+            if not rendered.value:   # more pairs or row items than the buffers brought along hold: grow them and render
                 cap = max(k, 1)
-                sort_bytes = int(lib.dsb_sort_workspace_bytes(cap))
-                pair_arena = torch.empty(2 * _up256(cap * 8) + sort_bytes, dtype=torch.uint8, device=dev)
+                ws_bytes = int(lib.dsb_render_workspace_bytes(h, w, k, k_rows))
+                pair_arena = torch.empty(_up256(cap * 8) + ws_bytes, dtype=torch.uint8, device=dev)
                 b = pair_arena.data_ptr()
                 _capi.check(lib.dsb_forward_render(
-                    C.byref(cam), n, k, a + lay.records, a + lay.tiles, a + lay.depth_keys, a + lay.offsets, b,
-                    b + _up256(cap * 8), a + lay.tile_marks, b + 2 * _up256(cap * 8), sort_bytes, a + lay.ranges,
-                    image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth), None, stream))
+                    C.byref(cam), n, k, k_rows, a + lay.records, a + lay.tiles, a + lay.depth_keys, a + lay.offsets, b,
+                    a + lay.tile_marks, a + lay.ranges, a + lay.layout, b + _up256(cap * 8), ws_bytes,
+                    image.data_ptr(), a + lay.final_t, a + lay.final_idx, _capi.ptr(depth), stream))
 
         ctx.raster_settings = raster_settings
         ctx.num_pairs = k

@@ -246,48 +246,54 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
                           float* v_rotations, float* v_cov3d, int32_t accumulate, void* stream);
 
 /* ---- fused calls the Python operator uses ----------------------------------------------------
- * dsb_forward_plan   = dsb_preprocess + dsb_plan_pairs            (first half of
- *                      rasterizer_forward_deepsense, cpp/rasterizer_torch.cu:170-196)
- * dsb_forward_render = dsb_emit_pairs + dsb_sort_pairs + dsb_identify_tile_ranges + dsb_blend_forward
- *                      (second half, :196-207); sorted pairs end in `pairs` (copied back if needed).
- *                      Same results as the four calls, but the tile ranges and the sort's digit counts come
- *                      from tile_marks -- a small grid in which dsb_forward_plan's preprocess kernel marked the
- *                      corners of every splat's tile rectangle and whose 2-D prefix sum is the number of pairs
- *                      per tile -- instead of passes over the pairs.  tile_marks (dsb_tile_marks_bytes) is
- *                      written by dsb_forward_plan and consumed by dsb_forward_render, which leaves in it the
- *                      tile order (tile ids by falling pair count) that dsb_backward accepts as tile_order;
- *                      workspace: dsb_sort_workspace_bytes(k)
+ * dsb_forward_plan   = the first half of rasterizer_forward_deepsense (cpp/rasterizer_torch.cu:170-196): preprocess,
+ *                      then -- from a small grid in which the preprocess kernel marked the corners of every splat's
+ *                      tile rectangle, and whose 2-D prefix sum is the number of pairs per tile -- the tile ranges
+ *                      (`ranges`, [tiles+1]), the tile order (left in tile_marks: tile ids by falling pair count, which
+ *                      the blend kernels and dsb_backward accept as tile_order) and a 1024-word `layout` block for the
+ *                      render; then the depth order of the splats and a scan over it.  One host synchronisation
+ *                      reads back *k_host (pairs) and *k_rows_host (row items, see below).
+ *                      tile_marks: dsb_tile_marks_bytes(H, W); workspace: dsb_plan_workspace_bytes(n).
+ * dsb_forward_render = the second half (:196-207): from the depth-ordered splats to the sorted pair list in `pairs`
+ *                      (k words) and the blended image.  Images of at most 256 x 509 tiles (4096 x 8144 pixels) are
+ *                      "row-binned": every (splat, tile row) of a splat's rectangle becomes one 8-byte row item,
+ *                      the k_rows row items are sorted by row (one radix pass), a scan of their widths gives each
+ *                      its first position in the list, and ONE pass over the k pairs expands them, ranks them by tile
+ *                      column and writes each pair to its final place -- instead of writing k pairs and moving them
+ *                      through two radix passes.  `offsets` is then the first ROW ITEM of every depth-ordered splat.
+ *                      Larger images write the pairs in depth order and sort them on their tile bits as the
+ *                      per-stage calls do (`offsets` = first pair of every splat, k_rows = 0).  The list is the same
+ *                      either way: the one the reference's sort produces.
+ *                      workspace: dsb_render_workspace_bytes(H, W, k, k_rows), 256-byte aligned.
+ * dsb_forward        = dsb_forward_plan, then -- without returning to the caller in between -- dsb_forward_render
+ *                      when the counts fit the buffers the caller brought (pairs holds pair_capacity words, the render
+ *                      workspace is large enough).  *rendered_host (HOST int) tells which: 0 means the caller grows
+ *                      its buffers and calls dsb_forward_render itself (everything the plan wrote stays valid).  A
+ *                      caller that sizes the buffers from the previous call's counts with some slack pays the one
+ *                      host synchronisation of a forward without any host work of its own between the two halves.
  * dsb_backward       = dsb_blend_backward + dsb_geometry_backward (rasterizer_backward_deepsense,
  *                      cpp/rasterizer_torch.cu:263-316); grad_acc is zeroed inside. */
+int64_t dsb_render_workspace_bytes(int32_t image_height, int32_t image_width, int64_t k, int64_t k_rows);
+int32_t dsb_row_binning_supported(int32_t image_height, int32_t image_width);
 int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs,
                      const float* colors_precomp, const float* opacities, const float* scales,
                      const float* rotations, const float* cov3d_precomp, float* records, int32_t* radii,
                      int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys, uint64_t* depth_keys_alt,
-                     uint32_t* offsets, int32_t* tile_marks, void* workspace, int64_t workspace_bytes,
-                     int64_t* k_host, void* stream);
-int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, const float* records,
+                     uint32_t* offsets, int32_t* tile_marks, int32_t* ranges, uint32_t* layout /* [1024] */,
+                     void* workspace, int64_t workspace_bytes, int64_t* k_host, int64_t* k_rows_host, void* stream);
+int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, int64_t k_rows, const float* records,
                        const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
-                       uint64_t* pairs, uint64_t* pairs_alt, int32_t* tile_marks, void* workspace,
-                       int64_t workspace_bytes, int32_t* ranges, float* image, float* final_T, int32_t* final_idx,
-                       float* depth /* may be NULL */,
-                       const uint32_t* layout_hist /* NULL, or this view's layout_hist from dsb_preprocess_views */,
-                       void* stream);
-/* dsb_forward = dsb_forward_plan, then -- without returning to the caller in between -- dsb_forward_render when the
- * pair count fits the buffers the caller brought: pairs / pairs_alt hold pair_capacity words each and the sort
- * workspace is at least dsb_sort_workspace_bytes(k).  *k_host receives the pair count either way; *rendered_host
- * (HOST int) is 1 when the image was rendered and 0 when the buffers were too small, in which case the caller grows
- * them and calls dsb_forward_render itself (everything the plan wrote stays valid).  A caller that sizes the buffers
- * from the previous call's count with some slack pays the one host synchronisation of the forward (the pair-count
- * read-back) without any of its own host work between the two halves.  Replaces rasterizer_forward_deepsense
- * (cpp/rasterizer_torch.cu:170-208) as a whole. */
+                       uint64_t* pairs, const int32_t* tile_marks, const int32_t* ranges, const uint32_t* layout,
+                       void* workspace, int64_t workspace_bytes, float* image, float* final_T, int32_t* final_idx,
+                       float* depth /* may be NULL */, void* stream);
 int dsb_forward(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs, const float* colors_precomp,
                 const float* opacities, const float* scales, const float* rotations, const float* cov3d_precomp,
                 float* records, int32_t* radii, int32_t* tiles_touched, float* cov3d, uint64_t* depth_keys,
-                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, void* plan_workspace,
-                int64_t plan_workspace_bytes, uint64_t* pairs, uint64_t* pairs_alt, int64_t pair_capacity,
-                void* sort_workspace, int64_t sort_workspace_bytes, int32_t* ranges, float* image, float* final_T,
-                int32_t* final_idx, float* depth /* may be NULL */, int64_t* k_host, int32_t* rendered_host,
-                void* stream);
+                uint64_t* depth_keys_alt, uint32_t* offsets, int32_t* tile_marks, int32_t* ranges, uint32_t* layout,
+                void* plan_workspace, int64_t plan_workspace_bytes, uint64_t* pairs, int64_t pair_capacity,
+                void* render_workspace, int64_t render_workspace_bytes, float* image, float* final_T,
+                int32_t* final_idx, float* depth /* may be NULL */, int64_t* k_host, int64_t* k_rows_host,
+                int32_t* rendered_host, void* stream);
 int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const float* scales,
                  const float* rotations, const float* records, const float* cov3d, const int32_t* radii,
                  const uint64_t* sorted_pairs, const int32_t* ranges, const float* final_T,
@@ -304,15 +310,16 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
  *   per step:   dsb_preprocess_views          (= the preprocess half of dsb_forward_plan for up to
  *                                              DSB_MAX_BATCH_VIEWS cameras: the splat parameters are read once,
  *                                              the 3-D covariance computed once; clears and fills each
- *                                              view's tile_marks; when ranges and layout_hist (1024
+ *                                              view's tile_marks; when ranges and layout (1024
  *                                              uint32 per view) are given it also makes every view's tile
- *                                              layout, and dsb_forward_render is then told so by passing
- *                                              the view's layout_hist)
- *               dsb_plan_pairs_views          (= dsb_plan_pairs for all those views in the same launches and
- *                                              with ONE host synchronisation: tiles_touched, depth_keys,
- *                                              depth_keys_alt and offsets hold one row of n entries per
- *                                              view, row_stride entries apart; k_host receives num_views
- *                                              totals; workspace: dsb_plan_workspace_bytes_views)
+ *                                              layout, as dsb_forward_plan does for one view)
+ *               dsb_plan_views                (= the plan half of dsb_forward_plan for all those views in the same
+ *                                              launches and with ONE host synchronisation: tiles_touched,
+ *                                              depth_keys, depth_keys_alt and offsets hold one row of n entries
+ *                                              per view, row_stride entries apart; records and layout are the
+ *                                              views' record buffers and layout blocks; k_host and k_rows_host
+ *                                              receive num_views totals each; workspace:
+ *                                              dsb_plan_workspace_bytes_views)
  *   per view:   dsb_forward_render, then
  *               dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
  *   per step:   dsb_geometry_backward_views   over up to DSB_MAX_BATCH_VIEWS views at a time
@@ -328,19 +335,19 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
                          const float* scales, const float* rotations, const float* cov3d_precomp,
                          float* const* records, int32_t* const* radii, int32_t* const* tiles_touched,
                          float* cov3d, uint64_t* const* depth_keys, int32_t* const* tile_marks,
-                         int32_t* const* ranges /* may be NULL */, uint32_t* const* layout_hist /* may be NULL */,
+                         int32_t* const* ranges /* may be NULL */, uint32_t* const* layout /* 1024 words per view; may be NULL */,
                          void* stream);
 int64_t dsb_plan_workspace_bytes_views(int32_t n, int32_t num_views);
-int dsb_plan_pairs_views(const DsbCamera* cam /* any of the views: only its flags are used */, int32_t num_views,
-                         int32_t n, int64_t row_stride, const int32_t* tiles_touched, uint64_t* depth_keys,
-                         uint64_t* depth_keys_alt, uint32_t* offsets, void* workspace, int64_t workspace_bytes,
-                         int64_t* k_host, void* stream);
-/* dsb_plan_pairs_views with k_host == NULL only launches (no host synchronisation); dsb_plan_totals_views then
- * fetches the totals of that plan from the same workspace on the same stream (one synchronisation of that stream) and
- * reports an expired device-side wait.  Lets a caller queue other work, or a second batch on another stream, between
- * the two. */
+int dsb_plan_views(const DsbCamera* cam /* any of the views: its flags and image size are used */, int32_t num_views,
+                   int32_t n, int64_t row_stride, const float* const* records, const int32_t* tiles_touched,
+                   uint64_t* depth_keys, uint64_t* depth_keys_alt, uint32_t* offsets, const uint32_t* const* layout,
+                   void* workspace, int64_t workspace_bytes, int64_t* k_host, int64_t* k_rows_host, void* stream);
+/* dsb_plan_views with k_host == NULL only launches (no host synchronisation); dsb_plan_totals_views then fetches the
+ * totals of that plan from the same workspace on the same stream (one synchronisation of that stream) and reports an
+ * expired device-side wait.  Lets a caller queue other work, or a second batch on another stream, between the two.
+ * k_rows_host may be NULL. */
 int dsb_plan_totals_views(int32_t num_views, int32_t n, const void* workspace, int64_t workspace_bytes,
-                          int64_t* k_host, void* stream);
+                          int64_t* k_host, int64_t* k_rows_host, void* stream);
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
                        const float* v_image, const float* v_depth /* may be NULL */,

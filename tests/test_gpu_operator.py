@@ -173,7 +173,7 @@ def test_fused_render_matches_stage_calls():
     r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], tight_tiles=False)
     image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
     k = r.last_k
-    fused_pairs = r.pairs[0][:k].clone()
+    fused_pairs = r.pairs[:k].clone()
     fused_ranges = r._ranges(r.cur, view.H, view.W)
     from conftest import capi_camera
     cam, keep = capi_camera(view)
@@ -351,7 +351,7 @@ def test_large_tile_grid_takes_the_global_memory_layout_path():
     r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], tight_tiles=False)
     image = r.forward(CameraTensors.from_view(view, "cuda")).clone()
     k = r.last_k
-    fused_pairs = r.pairs[0][:k].clone()
+    fused_pairs = r.pairs[:k].clone()
     fused_ranges = r._ranges(r.cur, view.H, view.W).clone()
     g = GradientBuffer(sc.n, "cuda")
     r.backward(torch.from_numpy(sc.image_grad()).cuda(), g, accumulate=False)   # backward without a tile order
@@ -373,39 +373,72 @@ def test_large_tile_grid_takes_the_global_memory_layout_path():
 
 
 def test_plan_of_several_views_equals_one_at_a_time():
-    """dsb_plan_pairs_views sorts the depth keys and scans the pair offsets of a batch in the same launches; every
-    view's sorted keys, offsets and pair count must equal those of dsb_plan_pairs on that view alone."""
+    """dsb_plan_views sorts the depth keys and scans the row-item offsets of a batch in the same launches; every view's
+    sorted keys, offsets and totals must equal those of the same call on that view alone, and what plain tensor
+    operations give: keys in ascending order, offsets = running sum of the rectangle heights in that order (the last
+    splat skipped, as the reference skips it), pairs = sum of the tile counts."""
     import ctypes as C
     from conftest import capi_camera
     sc = scenes.headline(n=70_001, seed=98, W=640, H=400, focal=380.0, views=3, ring=True)   # odd length: rows are not tile-aligned
     t = scene_tensors(sc)
     cams, keep = zip(*[capi_camera(v) for v in sc.views])
     n, nv, lib = sc.n, 3, _capi.lib()
-    tiles = torch.empty((nv, n), dtype=torch.int32, device="cuda")
+    h, w = sc.views[0].H, sc.views[0].W
+    i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device="cuda")
+    records = [torch.empty((n, _capi.RECORD_FLOATS), dtype=torch.float32, device="cuda") for _ in range(nv)]
+    radii, tiles, offsets = [i32(n) for _ in range(nv)], i32(nv, n), i32(nv, n)
     keys = torch.empty((2, nv, n), dtype=torch.int64, device="cuda")
-    offsets = torch.empty((nv, n), dtype=torch.int32, device="cuda")
-    singles = []
-    for v, cam in enumerate(cams):
-        _, _, tl, _, dk = _capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"])
-        tiles[v].copy_(tl); keys[0, v].copy_(dk)
-        off, k = _capi.plan_pairs(cam, tl, dk)
-        singles.append((dk, off, k))
+    marks = [torch.empty(int(lib.dsb_tile_marks_bytes(h, w)), dtype=torch.uint8, device="cuda") for _ in range(nv)]
+    ranges = [i32(_capi.num_tiles(h, w) + 1) for _ in range(nv)]
+    layout = [i32(_capi.LAYOUT_WORDS) for _ in range(nv)]
+    cov3d = torch.empty((n, 6), dtype=torch.float32, device="cuda")
+    ptrs = lambda ts: (C.c_void_p * len(ts))(*[x.data_ptr() for x in ts])
+    _capi.check(lib.dsb_preprocess_views((_capi.DsbCamera * nv)(*cams), nv, n, t["means"].data_ptr(), t["shs"].data_ptr(), None,
+                                         t["opacities"].data_ptr(), t["scales"].data_ptr(), t["rotations"].data_ptr(), None,
+                                         ptrs(records), ptrs(radii), ptrs([tiles[v] for v in range(nv)]), cov3d.data_ptr(),
+                                         ptrs([keys[0, v] for v in range(nv)]), ptrs(marks), ptrs(ranges), ptrs(layout),
+                                         _capi.stream_ptr()))
+    unsorted = keys[0].clone()
     ws_bytes = int(lib.dsb_plan_workspace_bytes_views(n, nv))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
-    ks = (C.c_int64 * nv)()
-    _capi.check(lib.dsb_plan_pairs_views(C.byref(cams[0]), nv, n, n, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
-                                         offsets.data_ptr(), ws.data_ptr(), ws_bytes, ks, _capi.stream_ptr()))
+    ks, krs = (C.c_int64 * nv)(), (C.c_int64 * nv)()
+    _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, ptrs(records), tiles.data_ptr(), keys[0].data_ptr(),
+                                   keys[1].data_ptr(), offsets.data_ptr(), ptrs(layout), ws.data_ptr(), ws_bytes, ks, krs,
+                                   _capi.stream_ptr()))
     torch.cuda.synchronize()
-    for v, (dk, off, k) in enumerate(singles):
-        assert int(ks[v]) == k
-        assert torch.equal(keys[0, v], dk) and torch.equal(offsets[v], off)
+    assert _capi.dsb_row_binned(h, w)
+    for v in range(nv):
+        want_keys = torch.sort(unsorted[v]).values           # (depth bits, id): all distinct, depths positive
+        assert torch.equal(keys[0, v], want_keys)
+        ids = (want_keys & 0xFFFFFFFF)
+        ry = records[v][:, 11].contiguous().view(torch.int32).to(torch.int64)
+        height = torch.where(tiles[v].to(torch.int64) > 0, (ry >> 16) - (ry & 0xFFFF), torch.zeros_like(ry))
+        count = tiles[v].to(torch.int64).clone()
+        height[n - 1] = 0; count[n - 1] = 0                  # capi_camera() keeps the reference's dropped last splat
+        in_order = height[ids]
+        want_off = torch.cumsum(in_order, 0) - in_order
+        assert torch.equal(offsets[v].to(torch.int64), want_off)
+        assert int(krs[v]) == int(height.sum()) and int(ks[v]) == int(count.sum())
+        assert int(ranges[v][-1]) == int(ks[v])
+        # the same view alone
+        k1, kr1 = (C.c_int64 * 1)(), (C.c_int64 * 1)()
+        key1 = torch.stack([unsorted[v], torch.empty_like(unsorted[v])])
+        off1 = i32(n)
+        _capi.check(lib.dsb_plan_views(C.byref(cams[v]), 1, n, n, ptrs([records[v]]), tiles[v].data_ptr(), key1[0].data_ptr(),
+                                       key1[1].data_ptr(), off1.data_ptr(), ptrs([layout[v]]), ws.data_ptr(), ws_bytes, k1, kr1,
+                                       _capi.stream_ptr()))
+        assert int(k1[0]) == int(ks[v]) and int(kr1[0]) == int(krs[v])
+        assert torch.equal(key1[0], keys[0, v]) and torch.equal(off1, offsets[v])
     # argument checks of the multi-view calls
     with pytest.raises(_capi.DsbError):
-        _capi.check(lib.dsb_plan_pairs_views(C.byref(cams[0]), 9, n, n, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
-                                             offsets.data_ptr(), ws.data_ptr(), ws_bytes, ks, _capi.stream_ptr()))
+        _capi.check(lib.dsb_plan_views(C.byref(cams[0]), 9, n, n, ptrs(records), tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
+                                       offsets.data_ptr(), ptrs(layout), ws.data_ptr(), ws_bytes, ks, krs, _capi.stream_ptr()))
     with pytest.raises(_capi.DsbError):
-        _capi.check(lib.dsb_plan_pairs_views(C.byref(cams[0]), nv, n, n, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
-                                             offsets.data_ptr(), ws.data_ptr(), 1024, ks, _capi.stream_ptr()))
+        _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, ptrs(records), tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
+                                       offsets.data_ptr(), ptrs(layout), ws.data_ptr(), 1024, ks, krs, _capi.stream_ptr()))
+    with pytest.raises(_capi.DsbError):
+        _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, None, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
+                                       offsets.data_ptr(), None, ws.data_ptr(), ws_bytes, ks, krs, _capi.stream_ptr()))
 
 
 def test_adam_step_matches_the_checker_and_a_training_step_lowers_the_loss():

@@ -40,7 +40,7 @@ def test_scan_wait_runs_out_and_the_plan_read_back_reports_it():
     _capi.check(lib.dsb_debug_expire_scan_wait(C.byref(cam), n, tiles.data_ptr(), depth_keys.data_ptr(), offsets.data_ptr(),
                                                ws.data_ptr(), ws_bytes, 200, _capi.stream_ptr()))
     k = (C.c_int64 * 1)()
-    rc = lib.dsb_plan_totals_views(1, n, ws.data_ptr(), ws_bytes, k, _capi.stream_ptr())
+    rc = lib.dsb_plan_totals_views(1, n, ws.data_ptr(), ws_bytes, k, None, _capi.stream_ptr())
     assert rc == WAIT_EXPIRED
     assert "wait expired" in lib.dsb_last_error().decode()
     # the read-back took the device's status word with it: the next check is clean, and a real plan works
