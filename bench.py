@@ -338,10 +338,11 @@ def timed_allreduce_form(timer, renderer, cams, v_images, grads, params, args, w
     return ms
 
 
-def single_view_timing(renderer_cls, params_views, scene, cam, v_image, grads, tight_tiles, iters, warmup, capi):
+def single_view_timing(renderer_cls, params_views, scene, cam, v_image, grads, tight_tiles, iters, warmup, capi, row_binning=False):
     """Median device time of ONE forward+backward through the fused single-view calls, and the stage times of it."""
     import torch
-    r = renderer_cls(**params_views, sh_degree=scene.sh_degree, batch_views=1, tight_tiles=tight_tiles, view_streams=1)
+    r = renderer_cls(**params_views, sh_degree=scene.sh_degree, batch_views=1, tight_tiles=tight_tiles, view_streams=1,
+                     row_binning=row_binning)
     for _ in range(warmup):
         r.forward(cam)
         r.backward(v_image, grads, accumulate=False)
@@ -356,7 +357,7 @@ def single_view_timing(renderer_cls, params_views, scene, cam, v_image, grads, t
         evs.append((a, b))
     torch.cuda.synchronize()
     times = sorted(a.elapsed_time(b) for a, b in evs)
-    k = r.last_k
+    k, r_rows = r.last_k, r.last_k_rows
     capi.stage_timing(True)
     for _ in range(min(iters, 20)):
         r.forward(cam)
@@ -367,7 +368,7 @@ def single_view_timing(renderer_cls, params_views, scene, cam, v_image, grads, t
     stages = {name: round(ms / calls, 5) for name, (ms, calls) in raw.items() if calls}
     del r
     return {"median_ms": round(statistics.median(times), 4), "min_ms": round(times[0], 4), "iters": iters,
-            "pairs": int(k), "stages_ms": stages}
+            "pairs": int(k), "row_items": int(r_rows), "stages_ms": stages}
 
 
 def run_flythrough(args):
@@ -511,7 +512,11 @@ def main():
         v0 = t(scene.image_grad(0, seed=7))
         iters = max(20, min(args.steps, 100))
         single = {"tight_tiles": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, True, iters, 5, _capi),
-                  "strict_lists": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, False, iters, 5, _capi)}
+                  "strict_lists": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, False, iters, 5, _capi),
+                  # the other way to the same list (DSB_FLAG_ROW_BINNING), for the record: emit_pairs = row items,
+                  # tile_sort = their sort, the width scan and the one pass over the pairs
+                  "strict_lists_row_binning": single_view_timing(ViewRenderer, params.views, scene, cam0, v0, grads, False,
+                                                                 iters, 5, _capi, row_binning=True)}
         del cam0, v0
     timer.barrier()
 
@@ -700,6 +705,8 @@ def main():
         # K-sized stages on the pairs they actually move (strict: the reference's count; tight: the emitted subset)
         stage_achieved = {}
         for mode, sv_ in single.items():
+            if sv_["row_items"]:
+                continue   # row-binned: its stages move row items, not pairs
             k_, st = sv_["pairs"], sv_["stages_ms"]
             rec = {}
             if st.get("emit_pairs"):

@@ -17,6 +17,7 @@ LIB_PATH = os.environ.get("DSB200_LIBRARY") or os.path.join(_HERE, "libdsb200.so
 
 DSB_FLAG_DROP_LAST_SPLAT = 1
 DSB_FLAG_TIGHT_TILES = 2
+DSB_FLAG_ROW_BINNING = 4
 RECORD_FLOATS = 12
 GRAD_FLOATS = 12
 MAX_BATCH_VIEWS = 8
@@ -197,21 +198,22 @@ def as_f32(t, device, name):
 
 
 def make_camera(image_height, image_width, tanfovx, tanfovy, viewmatrix, projmatrix, campos, bg=None, sh_degree=3,
-                max_sh_degree=3, scale_modifier=1.0, transposed=True, drop_last=True, tight_tiles=False):
+                max_sh_degree=3, scale_modifier=1.0, transposed=True, drop_last=True, tight_tiles=False, row_binning=False):
     """Build a DsbCamera; returns (struct, keepalive list)."""
     cam = DsbCamera()
     cam.image_height, cam.image_width = int(image_height), int(image_width)
     cam.tanfovx, cam.tanfovy, cam.scale_modifier = float(tanfovx), float(tanfovy), float(scale_modifier)
     cam.sh_degree, cam.max_sh_degree = int(sh_degree), int(max_sh_degree)
     cam.matrices_transposed = 1 if transposed else 0
-    cam.flags = (DSB_FLAG_DROP_LAST_SPLAT if drop_last else 0) | (DSB_FLAG_TIGHT_TILES if tight_tiles else 0)
+    cam.flags = ((DSB_FLAG_DROP_LAST_SPLAT if drop_last else 0) | (DSB_FLAG_TIGHT_TILES if tight_tiles else 0)
+                 | (DSB_FLAG_ROW_BINNING if row_binning else 0))
     cam.viewmatrix, cam.projmatrix, cam.campos = viewmatrix.data_ptr(), projmatrix.data_ptr(), campos.data_ptr()
     cam.bg = bg.data_ptr() if bg is not None else None
     return cam, [viewmatrix, projmatrix, campos, bg]
 
 
 def dsb_row_binned(h, w) -> bool:
-    """Whether the fused render row-bins images of this size (at most 256 x 509 tiles) or sorts whole pair lists."""
+    """Whether an image of this size is within the limits of row binning (at most 256 x 509 tiles)."""
     return bool(lib().dsb_row_binning_supported(int(h), int(w)))
 
 

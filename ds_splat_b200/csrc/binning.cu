@@ -17,7 +17,7 @@ namespace dsb {
 namespace {
 
 constexpr int kScanThreads = 256;
-constexpr int kScanItems = 4;                      // consecutive items per thread: four gathers in flight
+constexpr int kScanItems = 8;                      // consecutive items per thread: eight gathers in flight
 constexpr int kScanTile = kScanThreads * kScanItems;
 constexpr u64 kScanAggregate = 1ull << 62;
 constexpr u64 kScanInclusive = 1ull << 63;
@@ -307,7 +307,12 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
     __syncthreads();
     u32 running = s_wsum[warp] + incl - mine;
     u64 my_last = 0;
-    if (mine) atomicAdd(&s_total, (u64)mine);   // the pair total in 64 bits (32-bit positions wrap beyond 2^32 pairs)
+    {   // the pair total in 64 bits (32-bit positions wrap beyond 2^32 pairs): warp sums, then one atomic per warp
+        u64 wsum = mine;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+        if (lane == 0 && wsum) atomicAdd(&s_total, wsum);
+    }
     for (int t = t_begin; t < t_end; ++t) {
         const int ty = t / tiles_x, tx = t - ty * tiles_x;
         ranges[t] = (int32_t)running;
@@ -336,12 +341,29 @@ tile_layout_kernel(const LayoutViews lv, const int copy_ints, const int tiles_x,
             s_row_start[tiles_y] = s_carry;
             hist[kRowInfoTotal] = (u32)s_total;
             hist[kRowInfoTotal + 1] = (u32)(s_total >> 32);
-            u32 blocks = 0;
-            for (int r = 0; r < tiles_y; ++r) {
-                hist[r] = blocks;
-                blocks += (s_row_start[r + 1] - s_row_start[r] + (u32)kRowTile - 1u) / (u32)kRowTile;
+        }
+        __syncthreads();
+        if (warp == 0) {   // blocks of the scatter pass before each row: lane l takes rows 16 l .. 16 l + 15
+            u32 b[16], sum = 0;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                const int r = lane * 16 + q;
+                b[q] = r < tiles_y ? (s_row_start[r + 1] - s_row_start[r] + (u32)kRowTile - 1u) / (u32)kRowTile : 0u;
+                sum += b[q];
             }
-            hist[tiles_y] = blocks;
+            u32 inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const u32 u = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += u;
+            }
+            u32 run = inc - sum;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                const int r = lane * 16 + q;
+                if (r <= tiles_y) hist[r] = run;
+                run += b[q];
+            }
         }
         __syncthreads();
         for (int r = tid; r <= tiles_y; r += kLayoutThreads) hist[kRowInfoStarts + r] = s_row_start[r];
@@ -624,7 +646,7 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
                              int32_t* const* ranges, int* has_order, cudaStream_t s) {
     DSB_REQUIRE(count >= 1 && count <= DSB_MAX_BATCH_VIEWS, "tile_layout: between 1 and %d views", DSB_MAX_BATCH_VIEWS);
     DSB_REQUIRE(plan.npass <= 4, "tile_layout: at most 4 digit passes");
-    DSB_REQUIRE(!row_binning_supported(cp) || hist, "tile_layout: a row-binned image needs its layout block");
+    DSB_REQUIRE(!row_binned(cp) || hist, "tile_layout: a row-binned image needs its layout block");
     LayoutViews lv;
     for (int v = 0; v < count; ++v) {
         DSB_REQUIRE(tile_marks[v] && ranges[v], "tile_layout: null pointer");
@@ -641,7 +663,7 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
     const int trailing_quirk = cp.drop_last && !cp.tight_tiles;
     tile_layout_kernel<<<count, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(lv, (int)tile_marks_copy_ints(cp.H, cp.W),
                                                                                cp.tiles_x, cp.tiles_y, plan, use_smem, trailing_quirk,
-                                                                               row_binning_supported(cp) ? 1 : 0);
+                                                                               row_binned(cp) ? 1 : 0);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

@@ -118,6 +118,7 @@ int make_cam_params(const DsbCamera* cam, CamParams* out) {
     p.transposed = cam->matrices_transposed != 0;
     p.drop_last = (cam->flags & DSB_FLAG_DROP_LAST_SPLAT) != 0;
     p.tight_tiles = (cam->flags & DSB_FLAG_TIGHT_TILES) != 0;
+    p.row_binning = (cam->flags & DSB_FLAG_ROW_BINNING) != 0;
     *out = p;
     return DSB_OK;
 }
@@ -240,8 +241,8 @@ int dsb_plan_views(const DsbCamera* cam, int32_t num_views, int32_t n, int64_t r
                    int64_t* k_rows_host, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
-    const bool rows = row_binning_supported(cp);
-    DSB_REQUIRE(!rows || (records && layout), "plan_views: records and layout blocks are required for this image size");
+    const bool rows = row_binned(cp);
+    DSB_REQUIRE(!rows || (records && layout), "plan_views: row binning needs the views' records and layout blocks");
     return launch_plan_views(cp, num_views, n, row_stride, tiles_touched, reinterpret_cast<u64*>(depth_keys),
                              reinterpret_cast<u64*>(depth_keys_alt), offsets, workspace, workspace_bytes, k_host,
                              (cudaStream_t)stream, rows ? records : nullptr, rows ? layout : nullptr, k_rows_host);
@@ -264,7 +265,8 @@ int32_t dsb_row_binning_supported(int32_t image_height, int32_t image_width) {
 int64_t dsb_render_workspace_bytes(int32_t image_height, int32_t image_width, int64_t k, int64_t k_rows) {
     if (k < 0) k = 0;
     if (k_rows < 0) k_rows = 0;
-    if (dsb_row_binning_supported(image_height, image_width)) return row_workspace_bytes(k, k_rows);
+    // k_rows > 0: the plan row-binned the view
+    if (k_rows > 0 && dsb_row_binning_supported(image_height, image_width)) return row_workspace_bytes(k, k_rows);
     return ((k * 8 + 255) / 256) * 256 + sort_workspace_bytes(k);   // alternate pair buffer + tile sort scratch
 }
 
@@ -358,7 +360,7 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
         if (rc != DSB_OK) return rc;
     }
     if (n == 0) return DSB_OK;
-    const bool rows = row_binning_supported(cp);
+    const bool rows = row_binned(cp);
     const float* rec = records;
     const u32* info = layout;
     return launch_plan_views(cp, 1, n, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
@@ -377,14 +379,14 @@ int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, int64_t k_row
     DSB_REQUIRE(k == 0 || (pairs && workspace), "forward_render: null pair buffer or workspace");
     const int has_order = tile_order_available(cp.H, cp.W);
     int rc = DSB_OK;
-    if (row_binning_supported(cp)) {
+    if (row_binned(cp)) {
         // depth-ordered splats -> row items -> ONE pass over the pairs (row_binning.cu)
         rc = launch_row_binning(cp, n, k, k_rows, records, tiles_touched, reinterpret_cast<const u64*>(depth_keys_sorted), offsets,
                                 ranges, layout, reinterpret_cast<u64*>(pairs), workspace, workspace_bytes, s);
         if (rc != DSB_OK) return rc;
     } else if (k > 0) {
-        // Images wider than 256 tiles or taller than 509: pairs written in depth order, then a stable sort on their
-        // tile bits with the digit counts the layout left; the workspace holds the alternate buffer and the scratch.
+        // Pairs written in depth order, then a stable sort on their tile bits with the digit counts the layout left;
+        // the workspace holds the alternate buffer and the sort's scratch.
         const int64_t alt_bytes = ((k * 8 + 255) / 256) * 256;
         DSB_REQUIRE(workspace_bytes >= alt_bytes + sort_workspace_bytes(k), "forward_render: workspace too small");
         u64* pairs_alt = reinterpret_cast<u64*>(workspace);

@@ -75,6 +75,7 @@ struct CamParams {
     int transposed;              // matrices still in the caller's transposed layout
     int drop_last;
     int tight_tiles;             // tile rectangles shrunk to where the splat can contribute
+    int row_binning;             // the fused render builds its pair list by row binning (row_binning.cu)
 };
 
 int make_cam_params(const DsbCamera* cam, CamParams* out);
@@ -152,7 +153,7 @@ int sort_passes(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
 // Row item: one (splat, tile row) of a splat's tile rectangle, 64 bits: row | first column | width | splat id.
 constexpr int kRowItemRowShift = 52, kRowItemX0Shift = 42, kRowItemWShift = 32;
 constexpr u32 kRowItemFieldMask = 1023u;
-constexpr int kRowScatterItems = 8;                 // pairs per thread of the scatter pass
+constexpr int kRowScatterItems = 16;                // pairs per thread of the scatter pass
 constexpr int kRowTile = 256 * kRowScatterItems;    // pairs per block of the scatter pass
 // What tile_layout_kernel leaves in a view's 1024-word layout block when the view is row-binned:
 //   [0 .. tiles_y]                      blocks of the scatter pass before each tile row (and their total)
@@ -160,7 +161,8 @@ constexpr int kRowTile = 256 * kRowScatterItems;    // pairs per block of the sc
 //   [kRowInfoTotal, kRowInfoTotal + 1]  K as 64 bits (exact even where 32-bit positions would wrap)
 constexpr int kRowInfoStarts = 512, kRowInfoTotal = 1022;
 constexpr int kLayoutWords = 1024;
-bool row_binning_supported(const CamParams& cp);
+bool row_binning_supported(const CamParams& cp);   // image size within the limits
+bool row_binned(const CamParams& cp);                // asked for and within the limits
 int64_t row_workspace_bytes(int64_t k, int64_t k_rows);
 int launch_row_binning(const CamParams& cp, int n, int64_t k, int64_t k_rows, const float* records, const int32_t* tiles,
                        const u64* depth_keys_sorted, const u32* row_offsets, const int32_t* ranges, const u32* row_info,

@@ -208,7 +208,7 @@ class ViewRenderer:
     docstring) and is what ``data_parallel_step`` uses."""
 
     def __init__(self, means3d, shs, opacities, scales, rotations, sh_degree: int = 3, strict_reference: bool = True,
-                 batch_views: int = 8, tight_tiles: bool = True, view_streams: int = 2):
+                 batch_views: int = 8, tight_tiles: bool = True, view_streams: int = 2, row_binning: bool = False):
         from . import _capi
         self._capi = _capi
         self.lib = _capi.lib()
@@ -220,6 +220,9 @@ class ViewRenderer:
         self.coeffs = shs.shape[1]
         self.strict = strict_reference
         self.tight_tiles = tight_tiles   # pairs only for tiles a splat can contribute to: same results, shorter lists
+        # row binning (DSB_FLAG_ROW_BINNING): one pass over the pairs instead of writing them and sorting them in two;
+        # the same list, faster when splats are wide (many tiles per tile row), slower on the benchmark clouds
+        self.row_binning = row_binning
         n, dev = self.n, self.dev
         self.batch_views = max(1, min(int(batch_views), _capi.MAX_BATCH_VIEWS))
         bv = self.batch_views
@@ -273,7 +276,7 @@ class ViewRenderer:
         max_deg = {1: 0, 4: 1, 9: 2, 16: 3}[self.coeffs]
         return self._capi.make_camera(cam.H, cam.W, cam.tanfovx, cam.tanfovy, cam.viewmatrix, cam.projmatrix, cam.campos,
                                       cam.bg, self.sh_degree, max_deg, 1.0, transposed=True, drop_last=self.strict,
-                                      tight_tiles=self.tight_tiles)
+                                      tight_tiles=self.tight_tiles, row_binning=self.row_binning)
 
     def _slot(self, j: int) -> _Slot:
         while len(self.slots) <= j:
@@ -290,7 +293,7 @@ class ViewRenderer:
             if ln.pairs is not None and ln.stream is not None:
                 ln.stream.synchronize()   # the old buffers go back to the allocator of another stream
             ln.cap = max(int(k * 1.25), 1024, ln.cap)
-            ln.cap_rows = max(int(k_rows * 1.25), 1024, ln.cap_rows)
+            ln.cap_rows = max(int(k_rows * 1.25), ln.cap_rows) if k_rows else ln.cap_rows   # only row-binned views have any
             ln.pairs = torch.empty(ln.cap, dtype=torch.int64, device=self.dev)
             ln.render_bytes = int(self.lib.dsb_render_workspace_bytes(h, w, ln.cap, ln.cap_rows))
             ln.render_ws = torch.empty(ln.render_bytes, dtype=torch.uint8, device=self.dev)

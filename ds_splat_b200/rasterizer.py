@@ -212,8 +212,8 @@ class DsRasterizerFunction(torch.autograd.Function):
             # Pair list and render workspace are sized from the counts of the previous call of this shape, with 25%
             # slack, so that plan and render run inside one library call; a view that needs more gets more.
             hint_key = (dev, n, h, w, raster_settings.tight_tiles)
-            hint_k, hint_rows = _pair_hint.get(hint_key, (8 * n, 3 * n))
-            cap, cap_rows = max(int(hint_k * 1.25), 1024), max(int(hint_rows * 1.25), 1024)
+            hint_k, hint_rows = _pair_hint.get(hint_key, (8 * n, 0))
+            cap, cap_rows = max(int(hint_k * 1.25), 1024), int(hint_rows * 1.25)   # row items only when views are row-binned
             ws_bytes = int(lib.dsb_render_workspace_bytes(h, w, cap, cap_rows))
             pair_arena = torch.empty(_up256(cap * 8) + ws_bytes, dtype=torch.uint8, device=dev)
             b = pair_arena.data_ptr()

@@ -43,6 +43,15 @@ extern "C" {
  * ranges are exactly the reference's. */
 #define DSB_FLAG_TIGHT_TILES 2
 
+/* How the fused render (dsb_forward_plan / dsb_forward_render / dsb_plan_views) gets from depth-ordered splats to the
+ * sorted pair list.  Off: it writes the k pairs in depth order and sorts them on their tile bits (two radix passes at
+ * 1080p and 4K).  On, for images of at most 256 x 509 tiles: "row binning" -- one 8-byte item per (splat, tile row),
+ * sorted by row, then ONE pass over the k pairs that expands, ranks and places them.  Same list either way.  Measured
+ * on B200: row binning is the faster of the two when splats are wide (row items under about an eighth of the pairs,
+ * as in the high-overlap stress configuration) and the slower one on the 1M and 6M clouds, whose splats are about 3.5
+ * tiles wide; hence off by default.  Every view of one call, and the plan and render calls of one view, must agree. */
+#define DSB_FLAG_ROW_BINNING 4
+
 #define DSB_RECORD_FLOATS 12  /* packed per-splat record: 3 x float4, see DsbCamera notes below   */
 #define DSB_MAX_BATCH_VIEWS 8 /* views one dsb_geometry_backward_views call takes                  */
 #define DSB_GRAD_FLOATS 12    /* per-splat accumulator row written by dsb_blend_backward          */
@@ -255,15 +264,15 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
  *                      reads back *k_host (pairs) and *k_rows_host (row items, see below).
  *                      tile_marks: dsb_tile_marks_bytes(H, W); workspace: dsb_plan_workspace_bytes(n).
  * dsb_forward_render = the second half (:196-207): from the depth-ordered splats to the sorted pair list in `pairs`
- *                      (k words) and the blended image.  Images of at most 256 x 509 tiles (4096 x 8144 pixels) are
- *                      "row-binned": every (splat, tile row) of a splat's rectangle becomes one 8-byte row item,
- *                      the k_rows row items are sorted by row (one radix pass), a scan of their widths gives each
- *                      its first position in the list, and ONE pass over the k pairs expands them, ranks them by tile
- *                      column and writes each pair to its final place -- instead of writing k pairs and moving them
- *                      through two radix passes.  `offsets` is then the first ROW ITEM of every depth-ordered splat.
- *                      Larger images write the pairs in depth order and sort them on their tile bits as the
- *                      per-stage calls do (`offsets` = first pair of every splat, k_rows = 0).  The list is the same
- *                      either way: the one the reference's sort produces.
+ *                      (k words) and the blended image.  By default the pairs are written in depth order and sorted
+ *                      on their tile bits as the per-stage calls do (`offsets` = first pair of every depth-ordered
+ *                      splat, k_rows = 0).  With DSB_FLAG_ROW_BINNING, images of at most 256 x 509 tiles (4096 x
+ *                      8144 pixels) are "row-binned": every (splat, tile row) of a splat's rectangle becomes one
+ *                      8-byte row item, the k_rows row items are sorted by row (one radix pass), a scan of their
+ *                      widths gives each its first position in the list, and ONE pass over the k pairs expands them,
+ *                      ranks them by tile column and writes each pair to its final place.  `offsets` is then the
+ *                      first ROW ITEM of every depth-ordered splat.  The list is the same either way: the one the
+ *                      reference's sort produces.
  *                      workspace: dsb_render_workspace_bytes(H, W, k, k_rows), 256-byte aligned.
  * dsb_forward        = dsb_forward_plan, then -- without returning to the caller in between -- dsb_forward_render
  *                      when the counts fit the buffers the caller brought (pairs holds pair_capacity words, the render
@@ -274,7 +283,7 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
  * dsb_backward       = dsb_blend_backward + dsb_geometry_backward (rasterizer_backward_deepsense,
  *                      cpp/rasterizer_torch.cu:263-316); grad_acc is zeroed inside. */
 int64_t dsb_render_workspace_bytes(int32_t image_height, int32_t image_width, int64_t k, int64_t k_rows);
-int32_t dsb_row_binning_supported(int32_t image_height, int32_t image_width);
+int32_t dsb_row_binning_supported(int32_t image_height, int32_t image_width);   /* image size within the limits of DSB_FLAG_ROW_BINNING */
 int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, const float* shs,
                      const float* colors_precomp, const float* opacities, const float* scales,
                      const float* rotations, const float* cov3d_precomp, float* records, int32_t* radii,

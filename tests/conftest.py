@@ -27,7 +27,8 @@ def scene_tensors(scene, device="cuda"):
                 rotations=t(scene.rotations))
 
 
-def capi_camera(view, device="cuda", sh_degree=3, max_sh_degree=3, transposed=True, drop_last=True, bg=(0.0, 0.0, 0.0)):
+def capi_camera(view, device="cuda", sh_degree=3, max_sh_degree=3, transposed=True, drop_last=True, bg=(0.0, 0.0, 0.0),
+                row_binning=False):
     """DsbCamera for a scenes.View; returns (cam, keepalive)."""
     import torch
     from ds_splat_b200 import _capi
@@ -36,7 +37,7 @@ def capi_camera(view, device="cuda", sh_degree=3, max_sh_degree=3, transposed=Tr
     cp = torch.from_numpy(np.ascontiguousarray(view.campos)).to(device)
     bgt = torch.tensor(bg, dtype=torch.float32, device=device)
     return _capi.make_camera(view.H, view.W, view.tanfovx, view.tanfovy, vm, pm, cp, bgt, sh_degree, max_sh_degree, 1.0,
-                             transposed=transposed, drop_last=drop_last)
+                             transposed=transposed, drop_last=drop_last, row_binning=row_binning)
 
 
 def settings_for(view, device="cuda", sh_degree=3, **kw):

@@ -62,20 +62,26 @@ def test_full_size_config_against_reference_cuda(name):
     assert torch.equal(ids_g, up(ref["ids_sorted"])), "sorted id list differs"
     assert torch.equal(keys_g, up(ref["keys_sorted"])), "sorted key list differs"
     del keys_g, ids_g, sorted_pairs, records, depth_keys, offsets, tiles, cov3d
-    for key in ("keys_sorted", "ids_sorted"):
-        ref.pop(key)
+    ref_ids = ref.pop("ids_sorted")
+    ref.pop("keys_sorted")
     gc.collect()
     torch.cuda.empty_cache()
 
     # ---- image, radii, gradients through the fused calls, both pair-list forms
     want_image = up(ref["image"])
-    for tight in (False, True):
-        r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], batch_views=1, tight_tiles=tight)
+    for tight, rows in ((False, False), (True, False), (False, True)):   # rows: the row-binned way to the same pair list
+        r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], batch_views=1, tight_tiles=tight,
+                         row_binning=rows)
         image = r.forward(CameraTensors.from_view(view, dev))
         err = float((image - want_image).abs().max())
         assert err <= 1e-5, f"tight_tiles={tight}: image differs by {err}"
         assert torch.equal(r.radii, up(ref["radii"]))
         assert (r.last_k == ref["K"]) if not tight else (r.last_k < ref["K"])
+        assert (r.last_k_rows > 0) == rows
+        if not tight:
+            assert torch.equal(r._ranges(r.cur, view.H, view.W), up(ref["tile_indices"]))
+            if rows:   # the list itself, against the reference's sorted ids
+                assert torch.equal((r.pairs[:r.last_k] & 0xFFFFFFFF).to(torch.int32), up(ref_ids))
         g = GradientBuffer(sc.n, dev)
         r.backward(up(v_image), g, accumulate=False)
         torch.cuda.synchronize()
@@ -84,6 +90,6 @@ def test_full_size_config_against_reference_cuda(name):
                       v_scale=g.views["scales"], v_rot=g.views["rotations"])
         for gname, got in pairs_.items():
             want = ref[gname]
-            gradient_gate(got.cpu().numpy().reshape(want.shape), want, f"{name}/tight={tight}/{gname}")
+            gradient_gate(got.cpu().numpy().reshape(want.shape), want, f"{name}/tight={tight}/rows={rows}/{gname}")
         del r, g, image
         torch.cuda.empty_cache()

@@ -372,16 +372,18 @@ def test_large_tile_grid_takes_the_global_memory_layout_path():
     assert _rel(g.views["means3d"].cpu().numpy(), out["v_means3d"].cpu().numpy()) < 1e-4
 
 
-def test_plan_of_several_views_equals_one_at_a_time():
-    """dsb_plan_views sorts the depth keys and scans the row-item offsets of a batch in the same launches; every view's
-    sorted keys, offsets and totals must equal those of the same call on that view alone, and what plain tensor
-    operations give: keys in ascending order, offsets = running sum of the rectangle heights in that order (the last
-    splat skipped, as the reference skips it), pairs = sum of the tile counts."""
+@pytest.mark.parametrize("rows", [False, True])
+def test_plan_of_several_views_equals_one_at_a_time(rows):
+    """dsb_plan_views sorts the depth keys and scans the offsets of a batch in the same launches; every view's sorted
+    keys, offsets and totals must equal those of the same call on that view alone, and what plain tensor operations
+    give: keys in ascending order, offsets = running sum, in that order, of the tile counts (or, with row binning, of
+    the rectangle heights: the first row item of every splat) with the last splat skipped as the reference skips it,
+    pairs = sum of the tile counts."""
     import ctypes as C
     from conftest import capi_camera
     sc = scenes.headline(n=70_001, seed=98, W=640, H=400, focal=380.0, views=3, ring=True)   # odd length: rows are not tile-aligned
     t = scene_tensors(sc)
-    cams, keep = zip(*[capi_camera(v) for v in sc.views])
+    cams, keep = zip(*[capi_camera(v, row_binning=rows) for v in sc.views])
     n, nv, lib = sc.n, 3, _capi.lib()
     h, w = sc.views[0].H, sc.views[0].W
     i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device="cuda")
@@ -415,10 +417,10 @@ def test_plan_of_several_views_equals_one_at_a_time():
         height = torch.where(tiles[v].to(torch.int64) > 0, (ry >> 16) - (ry & 0xFFFF), torch.zeros_like(ry))
         count = tiles[v].to(torch.int64).clone()
         height[n - 1] = 0; count[n - 1] = 0                  # capi_camera() keeps the reference's dropped last splat
-        in_order = height[ids]
+        in_order = (height if rows else count)[ids]
         want_off = torch.cumsum(in_order, 0) - in_order
         assert torch.equal(offsets[v].to(torch.int64), want_off)
-        assert int(krs[v]) == int(height.sum()) and int(ks[v]) == int(count.sum())
+        assert int(krs[v]) == (int(height.sum()) if rows else 0) and int(ks[v]) == int(count.sum())
         assert int(ranges[v][-1]) == int(ks[v])
         # the same view alone
         k1, kr1 = (C.c_int64 * 1)(), (C.c_int64 * 1)()
@@ -436,9 +438,10 @@ def test_plan_of_several_views_equals_one_at_a_time():
     with pytest.raises(_capi.DsbError):
         _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, ptrs(records), tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
                                        offsets.data_ptr(), ptrs(layout), ws.data_ptr(), 1024, ks, krs, _capi.stream_ptr()))
-    with pytest.raises(_capi.DsbError):
-        _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, None, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
-                                       offsets.data_ptr(), None, ws.data_ptr(), ws_bytes, ks, krs, _capi.stream_ptr()))
+    if rows:   # row binning needs the records (for the rectangle heights) and the layout blocks (for the pair totals)
+        with pytest.raises(_capi.DsbError):
+            _capi.check(lib.dsb_plan_views(C.byref(cams[0]), nv, n, n, None, tiles.data_ptr(), keys[0].data_ptr(), keys[1].data_ptr(),
+                                           offsets.data_ptr(), None, ws.data_ptr(), ws_bytes, ks, krs, _capi.stream_ptr()))
 
 
 def test_adam_step_matches_the_checker_and_a_training_step_lowers_the_loss():
@@ -564,3 +567,30 @@ def test_operator_reuses_its_pair_buffers_from_the_previous_count():
                                                               t["rotations"], None)
     r = ViewRenderer(t["means"], t["shs"], t["opacities"], big, t["rotations"], batch_views=1)
     assert torch.equal(img_big, r.forward(CameraTensors.from_view(sc.views[0], "cuda")))
+
+
+@pytest.mark.parametrize("tight", [False, True])
+def test_row_binning_builds_the_same_list_ranges_image_and_gradients(tight):
+    """DSB_FLAG_ROW_BINNING changes how the fused render gets from depth-ordered splats to the sorted pair list (row
+    items + one pass over the pairs instead of writing the pairs and sorting them); list, ranges, image and gradients
+    must not change.  Ragged image size, a multi-view step, and a scene whose last tiles are empty."""
+    sc = scenes.headline(n=60_000, seed=74, W=500, H=297, focal=300.0, views=3, ring=True)
+    t = scene_tensors(sc)
+    cams = [CameraTensors.from_view(v, "cuda") for v in sc.views]
+    vimgs = [torch.from_numpy(sc.image_grad(i)).cuda() for i in range(len(sc.views))]
+    out = {}
+    for rows in (False, True):
+        r = ViewRenderer(t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"], tight_tiles=tight, row_binning=rows)
+        image = r.forward(cams[0]).clone()
+        k = r.last_k
+        assert (r.last_k_rows > 0) == rows
+        single = (image, r.pairs[:k].clone(), r._ranges(r.cur, sc.views[0].H, sc.views[0].W).clone(), k)
+        g = GradientBuffer(sc.n, "cuda")
+        r.render_views(cams, vimgs, g)
+        torch.cuda.synchronize()
+        assert _capi.take_device_status() == 0
+        out[rows] = single + (g.flat.clone(), list(r.last_ks))
+    a, b = out[False], out[True]
+    assert a[3] == b[3] and a[3] > 0 and a[5] == b[5]
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
+    assert _rel(b[4].cpu().numpy(), a[4].cpu().numpy()) < 1e-4
