@@ -37,6 +37,7 @@ EXPORTS = (
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
     "dsb_sort_pairs_static", "dsb_tile_marks_bytes", "dsb_forward", "dsb_take_device_status",
     "dsb_debug_expire_scan_wait", "dsb_debug_expire_sort_wait", "dsb_debug_set_copy_wait_polls",
+    "dsb_debug_blend_forward_variant",
 )
 STATIC_SORT_MAX_ITEMS = 1 << 21
 
@@ -118,6 +119,7 @@ def lib():
             "dsb_debug_expire_scan_wait": [CAM, I32, P, P, P, P, I64, C.c_uint32, P],
             "dsb_debug_expire_sort_wait": [P, P, I64, I32, I32, P, I64, C.c_uint32, P],
             "dsb_debug_set_copy_wait_polls": [C.c_uint32],
+            "dsb_debug_blend_forward_variant": [CAM, I32, I32, I64, P, P, P, P, P, P, P, P, I64, P],
         }
         for name, argtypes in sig.items():
             fn = getattr(l, name)

@@ -66,6 +66,35 @@ __device__ __forceinline__ bool splat_reaches_rect(const float gx, const float g
     return !(fminf(q1, q2) > thr);
 }
 
+// The same test with the two per-splat constants handed in: thr = ln(255 opacity) + margin and nbc = -b / c.
+template <int BX, int BY>
+__device__ __forceinline__ bool splat_reaches_rect_pre(const float gx, const float gy, const float a, const float b,
+                                                       const float c, const float thr, const float nbc, const float x0,
+                                                       const float y0) {
+    if (!(a > 0.f && c > 0.f && a * c > b * b) || !(thr == thr)) return true;
+    const float dxl = x0 + 0.5f - gx, dxh = dxl + (float)(BX - 1);
+    const float dyl = y0 + 0.5f - gy, dyh = dyl + (float)(BY - 1);
+    const float ex = fminf(fmaxf(0.f, dxl), dxh);
+    const float ey = fminf(fmaxf(0.f, dyl), dyh);
+    const bool in_x = ex == 0.f, in_y = ey == 0.f;
+    if (in_x && in_y) return !(0.f > thr);
+    float q1 = 3.0e38f, q2 = 3.0e38f;
+    if (!in_x) {
+        const float dy = fminf(fmaxf(nbc * ex, dyl), dyh);
+        q1 = 0.5f * (a * ex * ex + c * dy * dy) + b * ex * dy;
+    }
+    if (!in_y) {
+        const float dx = fminf(fmaxf(-b / a * ey, dxl), dxh);
+        q2 = 0.5f * (a * dx * dx + c * ey * ey) + b * dx * ey;
+    }
+    return !(fminf(q1, q2) > thr);
+}
+__device__ __forceinline__ bool splat_reaches_block_pre(const float gx, const float gy, const float a, const float b,
+                                                        const float c, const float thr, const float nbc, const float x0,
+                                                        const float y0) {
+    return splat_reaches_rect_pre<kWarpPixelsX, kWarpPixelsY>(gx, gy, a, b, c, thr, nbc, x0, y0);
+}
+
 // The 8x4 block of warp_pixels().
 __device__ __forceinline__ bool splat_reaches_block(const float gx, const float gy, const float a, const float b,
                                                     const float c, const float thr, const float x0, const float y0) {

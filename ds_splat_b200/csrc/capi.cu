@@ -314,6 +314,15 @@ int dsb_blend_forward(const DsbCamera* cam, const float* records, const uint64_t
                                 final_idx, depth, nullptr, (cudaStream_t)stream);
 }
 
+int dsb_debug_blend_forward_variant(const DsbCamera* cam, int32_t variant, int32_t n, int64_t k, const float* records,
+                                    const uint64_t* sorted_pairs, const int32_t* ranges, float* image, float* final_T,
+                                    int32_t* final_idx, const int32_t* tile_order, void* scratch, int64_t scratch_bytes,
+                                    void* stream) {
+    CAM_OR_RETURN(cam, cp);
+    return launch_blend_forward_variant(cp, variant, n, k, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, image,
+                                        final_T, final_idx, tile_order, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
 int dsb_blend_backward(const DsbCamera* cam, const float* records, const uint64_t* sorted_pairs, const int32_t* ranges,
                        const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
                        float* grad_acc, void* stream) {

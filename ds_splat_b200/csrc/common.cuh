@@ -211,6 +211,9 @@ int launch_export(const u64* sorted, int64_t k, const float* records, int64_t* k
 int launch_blend_forward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
                          float* image, float* final_T, int32_t* final_idx, float* depth, const int32_t* tile_order,
                          cudaStream_t s);
+int launch_blend_forward_variant(const CamParams& cp, int variant, int n, int64_t k, const float* records, const u64* sorted,
+                                 const int32_t* ranges, float* image, float* final_T, int32_t* final_idx,
+                                 const int32_t* tile_order, void* scratch, int64_t scratch_bytes, cudaStream_t s);
 int launch_blend_backward(const CamParams& cp, const float* records, const u64* sorted, const int32_t* ranges,
                           const float* final_T, const int32_t* final_idx, const float* v_image, const float* v_depth,
                           float* grad_acc, const int32_t* tile_order, cudaStream_t s);

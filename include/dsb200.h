@@ -127,6 +127,22 @@ int dsb_debug_expire_sort_wait(uint64_t* items, uint64_t* items_alt, int64_t k, 
                                void* workspace, int64_t workspace_bytes, uint32_t spin_limit, void* stream);
 int dsb_debug_set_copy_wait_polls(uint32_t polls);
 
+/* ---- measurement hook: the forward blend with another way of fetching the records (no reference counterpart) -----
+ * dsb_blend_forward's kernel fetches a chunk of 32 list entries with three 16-byte loads per lane (variant 0).  The
+ * alternatives that were weighed against it stay callable so that the comparison can be repeated and so that a test
+ * can check that all of them render the same image bit for bit:
+ *   1  every lane asks the bulk copy engine (cp.async.bulk, global -> shared, this GPU's memory only, no multicast)
+ *      for its 48-byte record, all of a chunk's copies completing on the warp's mbarrier (bounded wait);
+ *   2  a gather pass first writes the records in list order into `scratch` (k x 48 bytes); a chunk is then ONE
+ *      contiguous bulk copy of up to 1536 bytes;
+ *   3  variant 0 with the cull's per-splat constants (ln(255 opacity) + margin, -b/c) read from a copy of the records
+ *      in `scratch` (n x 48 bytes) instead of being recomputed by every warp that meets the splat.
+ * tile_order may be NULL. */
+int dsb_debug_blend_forward_variant(const DsbCamera* cam, int32_t variant, int32_t n, int64_t k, const float* records,
+                                    const uint64_t* sorted_pairs, const int32_t* ranges, float* image, float* final_T,
+                                    int32_t* final_idx, const int32_t* tile_order, void* scratch, int64_t scratch_bytes,
+                                    void* stream);
+
 /* ---- per-stage device timing (no reference counterpart: the reference times with std::chrono in
  * its tests, tests/rasterizer_test.cpp:112-143) --------------------------------------------------
  * While enabled, every stage inside the calls below is bracketed by a cudaEvent pair on the caller's

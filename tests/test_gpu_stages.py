@@ -229,3 +229,28 @@ def test_depth_map_and_its_gradient_match_oracle(run):
                                      run["radii"].cpu().numpy(), np.ascontiguousarray(a[:, 0:2]), v_conic_g,
                                      np.ascontiguousarray(a[:, 9]))
     gradient_gate(out["v_means3d"].cpu().numpy(), vm, "vm")
+
+
+def test_every_way_of_fetching_records_renders_the_same_image(run):
+    """The forward blend's product path (three 16-byte loads per lane) against the alternatives that were measured
+    against it -- a 48-byte bulk copy per lane, one contiguous bulk copy per chunk from a packed list-ordered stream,
+    cull constants read from the record: image, transmittance and last contributor bit for bit."""
+    import ctypes as C
+    lib = _capi.lib()
+    cam, view = run["cam"], run["view"]
+    n, k = run["sc"].n, run["k"]
+    scratch = torch.empty(max(k, n) * 48 + 256, dtype=torch.uint8, device="cuda")
+    for variant in (0, 1, 2, 3):
+        image = torch.full((view.H, view.W, 3), -1.0, dtype=torch.float32, device="cuda")
+        final_t = torch.full((view.H, view.W), -1.0, dtype=torch.float32, device="cuda")
+        final_idx = torch.full((view.H, view.W), -1, dtype=torch.int32, device="cuda")
+        _capi.check(lib.dsb_debug_blend_forward_variant(
+            C.byref(cam), variant, n, k, run["records"].data_ptr(), run["sorted_pairs"].data_ptr(), run["ranges"].data_ptr(),
+            image.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), None, scratch.data_ptr(), scratch.numel(),
+            _capi.stream_ptr()))
+        assert _capi.take_device_status() == 0
+        assert torch.equal(image, run["image"]), f"variant {variant}: image differs"
+        assert torch.equal(final_t, run["final_t"]) and torch.equal(final_idx, run["final_idx"]), f"variant {variant}"
+    assert lib.dsb_debug_blend_forward_variant(C.byref(cam), 7, n, k, run["records"].data_ptr(), run["sorted_pairs"].data_ptr(),
+                                               run["ranges"].data_ptr(), image.data_ptr(), final_t.data_ptr(),
+                                               final_idx.data_ptr(), None, None, 0, None) == -1
