@@ -23,6 +23,7 @@ GRAD_FLOATS = 12
 MAX_BATCH_VIEWS = 8
 MAX_PAIRS = 1 << 30
 LAYOUT_WORDS = 1024   # per-view layout block of the fused render
+DSB_ERR_TOO_MANY_PAIRS = -4
 
 EXPORTS = (
     "dsb_last_error", "dsb_version", "dsb_launch_count", "dsb_plan_workspace_bytes", "dsb_sort_workspace_bytes",
@@ -45,7 +46,7 @@ STATIC_SORT_MAX_ITEMS = 1 << 21
 class DsbCamera(C.Structure):
     _fields_ = [("image_height", C.c_int32), ("image_width", C.c_int32), ("tanfovx", C.c_float), ("tanfovy", C.c_float),
                 ("scale_modifier", C.c_float), ("sh_degree", C.c_int32), ("max_sh_degree", C.c_int32),
-                ("matrices_transposed", C.c_int32), ("flags", C.c_int32), ("reserved", C.c_int32),
+                ("matrices_transposed", C.c_int32), ("flags", C.c_int32), ("tile_row_band", C.c_int32),
                 ("viewmatrix", C.c_void_p), ("projmatrix", C.c_void_p), ("campos", C.c_void_p), ("bg", C.c_void_p)]
 
 
@@ -106,7 +107,7 @@ def lib():
             "dsb_preprocess_views": [P, I32, I32] + [P] * 16,
             "dsb_plan_views": [CAM, I32, I32, I64, P, P, P, P, P, P, P, I64, P, P, P],
             "dsb_plan_totals_views": [I32, I32, P, I64, P, P, P],
-            "dsb_backward_blend": [CAM, I32] + [P] * 10,
+            "dsb_backward_blend": [CAM, I32] + [P] * 9 + [I32, P],
             "dsb_geometry_backward_views": [P, I32, I32] + [P] * 15 + [I32, P],
             "dsb_geometry_backward_views_stats": [P, I32, I32] + [P] * 15 + [I32, C.c_float, C.c_float, P, P, P, P],
             "dsb_forward_core": [P, P, P, P, P, I32, P, P, P, I32, I32, C.c_float, C.c_float, C.c_float, I32, I32, P, P],

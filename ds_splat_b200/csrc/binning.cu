@@ -660,7 +660,7 @@ int launch_tile_layout_views(const CamParams& cp, int count, int* const* tile_ma
     if (use_smem && grid_bytes > 40 * 1024)
         DSB_CUDA_CHECK(cudaFuncSetAttribute(tile_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grid_bytes));
     // lists identical to the reference's (its rectangles, its dropped last splat): keep its range habit too
-    const int trailing_quirk = cp.drop_last && !cp.tight_tiles;
+    const int trailing_quirk = cp.drop_last && !cp.tight_tiles && cp.band_y0 == 0 && cp.band_y1 == cp.tiles_y;
     tile_layout_kernel<<<count, kLayoutThreads, use_smem ? grid_bytes : 0, s>>>(lv, (int)tile_marks_copy_ints(cp.H, cp.W),
                                                                                cp.tiles_x, cp.tiles_y, plan, use_smem, trailing_quirk,
                                                                                row_binned(cp) ? 1 : 0);

@@ -78,7 +78,7 @@ blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_
                      const float4* __restrict__ records, const u64* __restrict__ sorted,
                      const int32_t* __restrict__ ranges, float* __restrict__ image, float* __restrict__ final_T,
                      int32_t* __restrict__ final_idx, float* __restrict__ depth, const int32_t* __restrict__ tile_order,
-                     int* __restrict__ device_status) {
+                     int* __restrict__ device_status, const int band_tile0, const int band_tile1) {
     constexpr bool kBulk = VARIANT == 1 || VARIANT == 2;
     __shared__ float4 s_q0[kBulk ? 1 : kWarps][32];  // x, y, conic a, conic b
     __shared__ float4 s_q1[kBulk ? 1 : kWarps][32];  // conic c, opacity, r, g
@@ -93,6 +93,7 @@ blend_forward_kernel(const int W, const int H, const int tiles_x, const int num_
     if (slot >= num_tiles) return;               // whole warps only; no block-wide barrier below
     const int tile = tile_order ? tile_order[slot] : slot;   // longest lists first when the order is known
     if ((unsigned)tile >= (unsigned)num_tiles) return;       // a caller's stale order must not index outside the ranges
+    if (tile < band_tile0 || tile >= band_tile1) return;     // a view rendered in bands: the other bands' pixels are not touched
     const WarpPixels wp = warp_pixels(tile % tiles_x, tile / tiles_x, wb % kWarpsPerTile, lane);
     const int x = wp.x, y = wp.y;
     const bool inside = x < W && y < H;
@@ -229,7 +230,8 @@ int launch_variant(const CamParams& cp, const float4* records, const u64* sorted
     const int rc = device_status_address(&device_status);
     if (rc != DSB_OK) return rc;
     blend_forward_kernel<DEPTH, VARIANT><<<grid, kThreads, 0, s>>>(cp.W, cp.H, cp.tiles_x, num_tiles, records, sorted, ranges, image,
-                                                                 final_T, final_idx, depth, tile_order, device_status);
+                                                                 final_T, final_idx, depth, tile_order, device_status,
+                                                                 cp.band_y0 * cp.tiles_x, cp.band_y1 * cp.tiles_x);
     DSB_LAUNCH_CHECK();
     return DSB_OK;
 }

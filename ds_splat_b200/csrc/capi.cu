@@ -119,6 +119,12 @@ int make_cam_params(const DsbCamera* cam, CamParams* out) {
     p.drop_last = (cam->flags & DSB_FLAG_DROP_LAST_SPLAT) != 0;
     p.tight_tiles = (cam->flags & DSB_FLAG_TIGHT_TILES) != 0;
     p.row_binning = (cam->flags & DSB_FLAG_ROW_BINNING) != 0;
+    p.band_y0 = 0; p.band_y1 = p.tiles_y;
+    if (cam->tile_row_band != 0) {
+        const int lo = cam->tile_row_band & 0xffff, hi = (int)(((uint32_t)cam->tile_row_band) >> 16);
+        DSB_REQUIRE(lo < hi && hi <= p.tiles_y, "tile_row_band [%d, %d) is not a band of the image's %d tile rows", lo, hi, p.tiles_y);
+        p.band_y0 = lo; p.band_y1 = hi;
+    }
     *out = p;
     return DSB_OK;
 }
@@ -513,14 +519,14 @@ int dsb_preprocess_views(const DsbCamera* cams, int32_t num_views, int32_t n, co
 
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx, const float* v_image,
-                       const float* v_depth, const int32_t* tile_order, float* grad_acc, void* stream) {
+                       const float* v_depth, const int32_t* tile_order, float* grad_acc, int32_t keep_grad_acc, void* stream) {
     CAM_OR_RETURN(cam, cp);
     DSB_REQUIRE(n >= 0, "n must be non-negative");
     if (n == 0) return DSB_OK;
     DSB_REQUIRE(grad_acc, "backward_blend: grad_acc is null");
     cudaStream_t s = (cudaStream_t)stream;
     StageScope scope(kStageBlendBackward, s);
-    DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
+    if (!keep_grad_acc) DSB_CUDA_CHECK(cudaMemsetAsync(grad_acc, 0, (size_t)n * DSB_GRAD_FLOATS * sizeof(float), s));
     return launch_blend_backward(cp, records, reinterpret_cast<const u64*>(sorted_pairs), ranges, final_T, final_idx,
                                  v_image, v_depth, grad_acc,
 #ifdef DSB_NO_TILE_ORDER

@@ -76,6 +76,7 @@ struct CamParams {
     int drop_last;
     int tight_tiles;             // tile rectangles shrunk to where the splat can contribute
     int row_binning;             // the fused render builds its pair list by row binning (row_binning.cu)
+    int band_y0, band_y1;        // tile rows [band_y0, band_y1) that get pairs and pixels (the whole image: 0, tiles_y)
 };
 
 int make_cam_params(const DsbCamera* cam, CamParams* out);

@@ -311,6 +311,8 @@ preprocess_kernel(const PreViews pv, const int n, const float* __restrict__ mean
             // A centre behind the camera can pass the frustum test (w < 0 flips both signs).  The reference
             // still reports its radius but, because the negative depth bits spill over the tile id of its
             // keys, never draws it; here it simply gets no pairs.
+            // a view rendered in bands of tile rows: only the band's part of the rectangle gets pairs
+            y0 = min(max(y0, cv.band_y0), cv.band_y1); y1 = max(min(y1, cv.band_y1), y0);
             count = (x1 - x0) * (y1 - y0) * (radius > 0 && tz > 0.f);
             // Corner marks of the tile rectangle (+1, -1, -1, +1) in a (tiles_y + 1) x (tiles_x + 1) grid: its 2-D
             // prefix sum is the number of (tile, splat) pairs per tile, from which tile ranges and the tile sort's

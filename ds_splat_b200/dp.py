@@ -360,6 +360,86 @@ class ViewRenderer:
             g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None, g["opacities"].data_ptr(), g["scales"].data_ptr(),
             g["rotations"].data_ptr(), None, 1 if accumulate else 0, capi.stream_ptr()))
 
+    # ---- views with more pairs than one list may hold: rendered in bands of tile rows --------------------------------
+    def _plan_band(self, sl: _Slot, cam: CameraTensors, band):
+        """Preprocess + plan of one band of tile rows (None: the whole image).  Returns (pairs, row items, status):
+        the exact pair count also when it is beyond what one list may hold (status DSB_ERR_TOO_MANY_PAIRS)."""
+        capi, lib, p = self._capi, self.lib, self.p
+        sl.cam = self._camera(cam)
+        sl.cam[0].tile_row_band = 0 if band is None else (band[0] | (band[1] << 16))
+        k, k_rows = C.c_int64(0), C.c_int64(0)
+        rc = lib.dsb_forward_plan(
+            C.byref(sl.cam[0]), self.n, p["means3d"].data_ptr(), p["shs"].data_ptr(), None, p["opacities"].data_ptr(),
+            p["scales"].data_ptr(), p["rotations"].data_ptr(), None, sl.records.data_ptr(), sl.radii.data_ptr(),
+            sl.tiles.data_ptr(), self.cov3d.data_ptr(), sl.depth_keys.data_ptr(), self.depth_rows[1, 0].data_ptr(),
+            sl.offsets.data_ptr(), self._marks(sl, cam.H, cam.W).data_ptr(), self._ranges(sl, cam.H, cam.W).data_ptr(),
+            sl.layout.data_ptr(), self.plan_ws.data_ptr(), self.plan_bytes, C.byref(k), C.byref(k_rows), capi.stream_ptr())
+        if rc not in (0, capi.DSB_ERR_TOO_MANY_PAIRS):
+            capi.check(rc)
+        return int(k.value), int(k_rows.value), rc
+
+    @_on_own_device
+    def forward_banded(self, cam: CameraTensors, max_pairs: Optional[int] = None):
+        """Forward of a view whose pair list may exceed what one list holds (DSB_MAX_PAIRS - 1; ``max_pairs`` lowers the
+        limit, which is how the tests exercise this path at small sizes): the image is rendered in bands of tile rows,
+        each with its own plan, pair list and ranges, all writing into the same image.  The bands are found by halving:
+        a band whose exact pair count is over the limit is split in two.  Returns the image; ``backward_banded`` follows.
+        The image is bit for bit the unbanded one; ``self.bands`` lists (first row, one past the last, pairs)."""
+        capi = self._capi
+        limit = min(int(max_pairs), capi.MAX_PAIRS - 1) if max_pairs else capi.MAX_PAIRS - 1
+        tiles_y = (cam.H + 15) // 16
+        sl = self._slot(0)
+        image, final_t, final_idx = self._image_buffers(cam.H, cam.W, 0)
+        todo, done = [(0, tiles_y)], []
+        while todo:
+            y0, y1 = todo.pop(0)
+            whole = (y0, y1) == (0, tiles_y)
+            k, k_rows, rc = self._plan_band(sl, cam, None if whole else (y0, y1))
+            if k > limit or rc != 0:
+                if y1 - y0 == 1:
+                    raise capi.DsbError(capi.DSB_ERR_TOO_MANY_PAIRS, f"tile row {y0} alone holds {k} pairs, more than one list may hold")
+                mid = (y0 + y1) // 2
+                todo[:0] = [(y0, mid), (mid, y1)]
+                continue
+            # this band fits: render it into the shared image with buffers of its own, kept for the backward
+            band = _Lane()
+            band.img = self.lanes[0].img      # every band writes into the one image
+            self.lanes.append(band)
+            try:
+                self._render(sl, cam, k, k_rows, lane=len(self.lanes) - 1)
+            finally:
+                self.lanes.pop()
+            done.append(dict(rows=(y0, y1), k=k, pairs=band.pairs, cam=sl.cam, ranges=self._ranges(sl, cam.H, cam.W).clone(),
+                             order=self._marks(sl, cam.H, cam.W).clone()))
+            band.render_ws = None   # only the list survives
+        self._banded = (cam, done)
+        self.bands = [(b["rows"][0], b["rows"][1], b["k"]) for b in done]
+        self.cur, self._last_cam = sl, cam
+        return image
+
+    @_on_own_device
+    def backward_banded(self, v_image: torch.Tensor, grads: GradientBuffer, accumulate: bool = True):
+        """Backward of the view ``forward_banded`` rendered: every band's backward blend adds into the one accumulator
+        (the records differ between bands only in their tile rectangles, which the backward does not read), then the
+        per-splat backward runs once."""
+        capi, lib, p = self._capi, self.lib, self.p
+        cam, bands = self._banded
+        sl = self.cur
+        _image, final_t, final_idx = self._image_buffers(cam.H, cam.W, 0)
+        for i, b in enumerate(bands):
+            capi.check(lib.dsb_backward_blend(
+                C.byref(b["cam"][0]), self.n, sl.records.data_ptr(), b["pairs"].data_ptr(), b["ranges"].data_ptr(),
+                final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None, b["order"].data_ptr(),
+                sl.grad_acc.data_ptr(), 1 if i else 0, capi.stream_ptr()))
+        g = grads.views
+        cams = (capi.DsbCamera * 1)(bands[0]["cam"][0])
+        ptrs = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+        capi.check(lib.dsb_geometry_backward_views(
+            cams, 1, self.n, p["means3d"].data_ptr(), p["scales"].data_ptr(), p["rotations"].data_ptr(), self.cov3d.data_ptr(),
+            ptrs([sl.records]), ptrs([sl.radii]), ptrs([sl.grad_acc]), g["means3d"].data_ptr(), None, g["shs"].data_ptr(), None,
+            g["opacities"].data_ptr(), g["scales"].data_ptr(), g["rotations"].data_ptr(), None, 1 if accumulate else 0,
+            capi.stream_ptr()))
+
     @_on_own_device
     def render_views(self, cameras, image_grads, grads: GradientBuffer, accumulate: bool = False,
                      stats: Optional[DensifyStats] = None):
@@ -420,7 +500,7 @@ class ViewRenderer:
                     capi.check(lib.dsb_backward_blend(
                         C.byref(sl.cam[0]), self.n, sl.records.data_ptr(), lanes[li].pairs.data_ptr(),
                         ranges.data_ptr(), final_t.data_ptr(), final_idx.data_ptr(), v_image.data_ptr(), None,
-                        self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), capi.stream_ptr()))
+                        self._marks(sl, cam.H, cam.W).data_ptr(), sl.grad_acc.data_ptr(), 0, capi.stream_ptr()))
             for ln in lanes[1:]:
                 done = torch.cuda.Event()
                 done.record(ln.stream)

@@ -52,6 +52,13 @@ extern "C" {
  * tiles wide; hence off by default.  Every view of one call, and the plan and render calls of one view, must agree. */
 #define DSB_FLAG_ROW_BINNING 4
 
+/* Bands.  One view may hold at most DSB_MAX_PAIRS - 1 pairs (positions in the list are 32-bit, as in the reference,
+ * whose own 32-bit pair count wraps at 2^31, cpp/rasterizer_torch.cu:101-107).  A view with more is rendered in BANDS of
+ * tile rows: with tile_row_band set, the preprocess clips every splat's tile rectangle to the band, so plan, pair list
+ * and ranges cover only the band's pairs, the forward blend writes only the band's pixels, and the backward blend only
+ * adds the band's contributions to grad_acc (dsb_backward_blend with keep_grad_acc).  The bands of a view tile the image,
+ * share image, final_T, final_idx and grad_acc, and each keeps its own pair list and ranges until the backward.
+ * Rendering in bands changes nothing in the image; gradients agree up to the order of the atomic sums. */
 #define DSB_RECORD_FLOATS 12  /* packed per-splat record: 3 x float4, see DsbCamera notes below   */
 #define DSB_MAX_BATCH_VIEWS 8 /* views one dsb_geometry_backward_views call takes                  */
 #define DSB_GRAD_FLOATS 12    /* per-splat accumulator row written by dsb_blend_backward          */
@@ -77,7 +84,8 @@ typedef struct DsbCamera {
     int32_t max_sh_degree;        /* degree the shs tensor is laid out for: (max+1)^2 rows of 3   */
     int32_t matrices_transposed;
     int32_t flags;                /* DSB_FLAG_*                                                   */
-    int32_t reserved;
+    int32_t tile_row_band;        /* 0: the whole image; else (first tile row) | (one past the last) << 16: only this band of
+                                     tile rows gets pairs and pixels, see "bands" below                                */
     const float* viewmatrix;      /* device, 16 floats */
     const float* projmatrix;      /* device, 16 floats */
     const float* campos;          /* device, 3 floats  */
@@ -346,7 +354,8 @@ int dsb_backward(const DsbCamera* cam, int32_t n, const float* means3d, const fl
  *                                              receive num_views totals each; workspace:
  *                                              dsb_plan_workspace_bytes_views)
  *   per view:   dsb_forward_render, then
- *               dsb_backward_blend            (= first half of dsb_backward: zero grad_acc, backward blend)
+ *               dsb_backward_blend            (= first half of dsb_backward: zero grad_acc unless told to keep it,
+ *                                              backward blend)
  *   per step:   dsb_geometry_backward_views   over up to DSB_MAX_BATCH_VIEWS views at a time
  * records, radii, tiles_touched, depth_keys, tile_marks and grad_acc are HOST arrays of num_views device pointers (one buffer per view, all of the
  * layouts dsb_preprocess / dsb_blend_backward use); cams is a host array of num_views cameras that must
@@ -376,7 +385,9 @@ int dsb_plan_totals_views(int32_t num_views, int32_t n, const void* workspace, i
 int dsb_backward_blend(const DsbCamera* cam, int32_t n, const float* records, const uint64_t* sorted_pairs,
                        const int32_t* ranges, const float* final_T, const int32_t* final_idx,
                        const float* v_image, const float* v_depth /* may be NULL */,
-                       const int32_t* tile_order /* may be NULL */, float* grad_acc, void* stream);
+                       const int32_t* tile_order /* may be NULL */, float* grad_acc,
+                       int32_t keep_grad_acc /* 0: grad_acc is zeroed first; else added to (further bands of a view) */,
+                       void* stream);
 int dsb_geometry_backward_views(const DsbCamera* cams, int32_t num_views, int32_t n, const float* means3d,
                                 const float* scales, const float* rotations, const float* cov3d,
                                 const float* const* records, const int32_t* const* radii,
