@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument("--reduce", default="sharded", choices=["sharded", "allreduce"],
                     help="sharded: reduce-scatter + Adam on 1/N + all-gather; allreduce: all-reduce + Adam over everything")
     ap.add_argument("--no-nccl-registration", action="store_true")
+    ap.add_argument("--row-binning", action="store_true",
+                    help="build the pair lists by row binning (DSB_FLAG_ROW_BINNING) instead of writing and sorting the pairs")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-reference-cuda", action="store_true")
@@ -268,7 +270,8 @@ def build_training(scene, cams, v_images, dev, args, world, tight_tiles=True):
         (params, grads), pool = make(), None
     for name, arr in host.items():
         params.views[name].copy_(t(arr).reshape(params.views[name].shape))
-    renderer = ViewRenderer(**params.views, sh_degree=scene.sh_degree, view_streams=args.view_streams, tight_tiles=tight_tiles)
+    renderer = ViewRenderer(**params.views, sh_degree=scene.sh_degree, view_streams=args.view_streams, tight_tiles=tight_tiles,
+                            row_binning=args.row_binning)
     # Learning rate zero: the kernel reads and writes exactly what it does in training (parameters, gradients, both
     # moments), but the cloud stays the configuration's cloud over hundreds of timed steps.  (Adam's normalised
     # update would otherwise move every scale by lr per step whatever the gradient, and 300 steps destroy the scene.)
@@ -560,7 +563,8 @@ def main():
         rasterizer = GaussianRasterizer(settings)
         h2d = pinned_grad.numel() * 4 + (16 + 16 + 3) * 4
         d2h = out_image[0].numel() * 4 + out_radii[0].numel() * 4
-        copy_stream = torch.cuda.Stream(device=dev)
+        copy_stream = torch.cuda.Stream(device=dev)      # results to the host
+        upload_stream = torch.cuda.Stream(device=dev)    # inputs to the device (its own stream: the two directions do not queue)
         main_stream = torch.cuda.current_stream()
         grad_ready, rendered = torch.cuda.Event(), torch.cuda.Event()
         backward_done = [torch.cuda.Event(), torch.cuda.Event()]
@@ -576,10 +580,10 @@ def main():
             vm.copy_(pinned_view, non_blocking=True)
             pm.copy_(pinned_proj, non_blocking=True)
             cp.copy_(pinned_pos, non_blocking=True)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(backward_done[s])   # the backward that last read vg[s] (two steps ago)
+            with torch.cuda.stream(upload_stream):
+                upload_stream.wait_event(backward_done[s])   # the backward that last read vg[s] (two steps ago)
                 vg[s].copy_(pinned_grad, non_blocking=True)
-                grad_ready.record(copy_stream)
+                grad_ready.record(upload_stream)
             for leaf in leaves.values():
                 leaf.grad = None
             means2d.grad = None
@@ -725,7 +729,7 @@ def main():
                                    + ("gradient reduce-scatter, Adam on 1/N of the parameters, parameter all-gather"
                                       if world > 1 else "Adam step"),
                        "pairs_reference_list_view0": K_ref, "pairs_emitted": pairs_emitted, "tiles": scene.views[0].num_tiles,
-                       "view_streams": int(min(args.view_streams, vpr)), "optimizer": "Adam, learning rate 0 (same reads and "
+                       "view_streams": int(min(args.view_streams, vpr)), "row_binning": bool(args.row_binning), "optimizer": "Adam, learning rate 0 (same reads and "
                        "writes; the cloud stays the configuration's)", "reduce": args.reduce if world > 1 else "none",
                        "nccl_registered_buffers": bool(nccl_registered),
                        "l2": "inputs larger than L2 (236 MB of parameters + 62-88 MB pair list per view; no explicit flush)",
