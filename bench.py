@@ -214,6 +214,39 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+_AFFINITY_AT_START = None
+
+
+def bind_to_gpu_numa_node(dev_index: int):
+    """Best effort: keeps this process (and so the pinned host buffers it allocates afterwards, which are placed on
+    the allocating thread's node) on the host cores of the NUMA node the GPU hangs off.  Reads sysfs only; returns
+    what it did for the bench line."""
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(dev_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"node": None, "bound": False, "why": "the GPU reports no NUMA node"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        global _AFFINITY_AT_START
+        allowed = os.sched_getaffinity(0)
+        _AFFINITY_AT_START = set(allowed)
+        local = sorted(cpus & allowed)
+        if not local:
+            return {"node": node, "bound": False, "why": "none of the node's cores is in this process's affinity set"}
+        if len(local) < len(allowed):
+            os.sched_setaffinity(0, local)
+        return {"node": node, "bound": True, "cores": len(local)}
+    except Exception as e:   # no sysfs entry, no permission: run unbound
+        return {"node": None, "bound": False, "why": type(e).__name__}
+
+
 class Timed:
     """CUDA-event timing of a callable on the current stream: barrier + synchronize on both sides, max over ranks."""
 
@@ -433,6 +466,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the rasterizer has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = bind_to_gpu_numa_node(local_rank)   # before the first pinned allocation
     json_out = sys.stdout
     if world > 1:
         # Libraries below write to file descriptor 1 (NCCL prints its version there): keep a private copy of it
@@ -660,6 +694,8 @@ def main():
     cpu_baseline, pairs_bwd, pairs_fwd, K_ref = None, None, None, None
     if rank == 0 and not args.skip_cpu_baseline:
         from oracle import oracle as O
+        if _AFFINITY_AT_START:   # the CPU baseline gets every core the process started with, not only the GPU's node
+            os.sched_setaffinity(0, _AFFINITY_AT_START)
         cores = O.use_all_host_threads()   # torchrun exports OMP_NUM_THREADS=1 to its workers
         sec, fwd_o, bwd_o = oracle_one_view(scene, view0, v_image0)
         pairs_fwd, pairs_bwd, K_ref = fwd_o["pairs_fwd"], bwd_o["pairs_bwd"], fwd_o["K"]
@@ -731,7 +767,7 @@ def main():
                        "pairs_reference_list_view0": K_ref, "pairs_emitted": pairs_emitted, "tiles": scene.views[0].num_tiles,
                        "view_streams": int(min(args.view_streams, vpr)), "row_binning": bool(args.row_binning), "optimizer": "Adam, learning rate 0 (same reads and "
                        "writes; the cloud stays the configuration's)", "reduce": args.reduce if world > 1 else "none",
-                       "nccl_registered_buffers": bool(nccl_registered),
+                       "nccl_registered_buffers": bool(nccl_registered), "host_numa": numa,
                        "l2": "inputs larger than L2 (236 MB of parameters + 62-88 MB pair list per view; no explicit flush)",
                        "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
             "clocks": clocks, "gpu_launches": int(launches), "step_breakdown_ms": phases,

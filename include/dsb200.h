@@ -104,7 +104,7 @@ int64_t dsb_launch_count(void);
  * word and finishes, so a logic error or a lost predecessor can never hang the GPU -- but the lists such a
  * kernel wrote are incomplete and everything rendered from them since is invalid.  The word is sticky until the
  * host takes it:
- *   - dsb_plan_pairs / dsb_forward_plan / dsb_plan_pairs_views / dsb_plan_totals_views, which synchronise the
+ *   - dsb_plan_pairs / dsb_forward_plan / dsb_plan_views / dsb_plan_totals_views, which synchronise the
  *     stream anyway to read the pair count, fetch it in the same synchronisation and return
  *     DSB_ERR_DEVICE_WAIT_EXPIRED when an earlier call on the device (for instance the tile sort inside the
  *     previous dsb_forward_render) recorded it;
