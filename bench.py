@@ -729,12 +729,18 @@ def main():
             roofline = {"kernel": "blend_backward_kernel", "bound": "fp32", "achieved": round(flops / (dom_ms * 1e-3) / 1e12, 3),
                         "peak": round(fp32_peak, 2), "unit": "TFLOP/s", "frac": round(flops / (dom_ms * 1e-3) / 1e12 / fp32_peak, 4),
                         "traffic": traffic, "ms": dom_ms, "pairs_visited": int(pairs_bwd), "flop_per_pair": 74,
+                        # what the kernel itself executes per visited pair after its regrouping (one running dot product
+                        # per pixel instead of three colour buffers, moments instead of per-pixel gradients): 37 flop of
+                        # blending arithmetic + 14 adds of the warp reduction shared by a lane's four pixels
+                        "executed": {"flop_per_pair": 40.5, "achieved": round(40.5 * pairs_bwd / (dom_ms * 1e-3) / 1e12, 3),
+                                     "frac": round(40.5 * pairs_bwd / (dom_ms * 1e-3) / 1e12 / fp32_peak, 4)},
                         "peak_source": "148 SMs x 128 FP32 lanes x 2 flop x median SM clock sampled during the run (not in "
                                        "MEASURED_PEAKS.json, which holds HBM and bf16 tensor peaks only)",
                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on config 1, scaled by pairs",
-                        "note": "single-view call on the configuration's camera with the reference-identical pair list; the flop "
-                                "count is the reference algorithm's per visited (pixel, splat) pair, the kernel skips pixel blocks "
-                                "a splat cannot reach, so the fraction overstates pipe utilisation (see profiles/)"}
+                        "note": "single-view call on the configuration's camera with the reference-identical pair list; 'achieved' "
+                                "counts the reference algorithm's 74 flop per visited (pixel, splat) pair as written in its "
+                                "kernel; this kernel reaches the same sums with fewer operations, so 'executed' is the figure "
+                                "that describes the FP32 pipes (issue-slot and pipe counters in profiles/)"}
             # 8 B pair + 48 B record gathered per list entry, 36 B of per-splat sums added per list entry, 20 B per pixel
             # read (dL/dimage 12, final_T 4, final_idx 4), plus the 48 B/splat zero fill of the accumulator in the stage.
             alg_bytes = K * (8 + 48 + 36) + 20 * H * W + 48 * scene.n

@@ -144,28 +144,36 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
     }
 }
 
-// One warp per 32 depth-ordered splats: their pair ranges are consecutive, so the warp walks the
-// concatenated range 32 positions at a time; each lane finds the owning splat by a 5-step search over
-// the lanes' running counts and writes one packed pair.  All stores are consecutive 8-byte lanes.
+// One warp per 32 depth-ordered splats: their pair ranges are consecutive, so the warp walks the concatenated
+// range 32 positions at a time and every lane writes one packed pair; all stores are consecutive 8-byte lanes.
+// The splats that have pairs are first packed into the warp's low lanes (through shared memory).  In each round
+// the packed splats whose range starts inside the round's 32 positions set the bit of that position; one
+// warp-wide OR gives the round's start mask, and the owner of position q is the number of starts at or before q
+// (a population count) plus the starts of earlier rounds -- no search.  The position inside the owner's rectangle
+// is split into row and column with a float reciprocal and one correction step (integer division for rectangles
+// of more than 2^22 tiles).
 __global__ void __launch_bounds__(256)
 emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_last, const float4* __restrict__ records,
                   const int32_t* __restrict__ tiles, const u64* __restrict__ depth_keys_sorted,
                   const u32* __restrict__ offsets, u64* __restrict__ pairs) {
-    const int lane = threadIdx.x & 31;
+    __shared__ u32 s_id[8][32], s_xy[8][32], s_w[8][32], s_excl[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;  // position in depth order; warps are aligned to 32
-    u32 id = 0, c = 0, off = 0;
-    int x0 = 0, y0 = 0, w = 1;
+    // A splat's pair count is the distance to the next splat's offset (the scan already left out the dropped last
+    // splat), read along the depth order: no gather of the per-splat counts.
+    u32 id = 0, c = 0, xy = 0, w = 1;
+    const u32 off = j < n ? offsets[j] : k;
+    u32 next = __shfl_down_sync(0xffffffffu, off, 1);
+    if (lane == 31) next = j + 1 < n ? offsets[j + 1] : k;
     if (j < n) {
         id = (u32)depth_keys_sorted[j];
-        c = (u32)tiles[id];
-        if (drop_last && id == (u32)(n - 1)) c = 0;
-        off = offsets[j];
+        c = next > off ? next - off : 0u;   // offsets never decrease; a caller's wrong k must not turn into a huge count
         if (c) {
             const float4 q2 = __ldg(records + (size_t)id * 3 + 2);
             const u32 rx = __float_as_uint(q2.z), ry = __float_as_uint(q2.w);
-            x0 = (int)(rx & 0xffffu);
-            w = (int)(rx >> 16) - x0;
-            y0 = (int)(ry & 0xffffu);
+            const u32 x0 = rx & 0xffffu;
+            w = (rx >> 16) - x0;
+            xy = x0 | (ry << 16);   // first column | first row << 16
         }
     }
     u32 incl = c;
@@ -174,28 +182,44 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
         const u32 t = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += t;
     }
-    const u32 excl = incl - c;
     const u32 total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total == 0) return;
     const u32 warp_base = __shfl_sync(0xffffffffu, off, 0);
+    const u32 have = __ballot_sync(0xffffffffu, c != 0);
+    const int packed = __popc(have);
+    if (c) {
+        const int slot = __popc(have & ((1u << lane) - 1u));
+        s_id[warp][slot] = id; s_xy[warp][slot] = xy; s_w[warp][slot] = w; s_excl[warp][slot] = incl - c;
+    }
+    __syncwarp();
+    const bool mine = lane < packed;
+    const u32 cid = mine ? s_id[warp][lane] : 0u, cxy = mine ? s_xy[warp][lane] : 0u, cw = mine ? s_w[warp][lane] : 1u;
+    const u32 cexcl = mine ? s_excl[warp][lane] : 0xffffffffu;
+    const u32 le_mask = 0xffffffffu >> (31 - lane);   // positions of the round at or before this lane's
+    u32 started = 0;                                  // packed splats whose range starts before the round
     for (u32 base = 0; base < total; base += 32) {
+        const u32 rel = cexcl - base;
+        const u32 starts = __reduce_or_sync(0xffffffffu, (mine && rel < 32u) ? (1u << rel) : 0u);
+        const int owner = (int)started + __popc(starts & le_mask) - 1;   // >= 0: position 0 of the first round is a start
+        started += (u32)__popc(starts);
+        const u32 o_excl = __shfl_sync(0xffffffffu, cexcl, owner);
+        const u32 o_id = __shfl_sync(0xffffffffu, cid, owner);
+        const u32 o_xy = __shfl_sync(0xffffffffu, cxy, owner);
+        const u32 o_w = __shfl_sync(0xffffffffu, cw, owner);
         const u32 p = base + lane;
-        // owner = number of lanes whose inclusive count is <= p
-        int owner = 0;
-#pragma unroll
-        for (int step = 16; step >= 1; step >>= 1) {
-            const u32 t = __shfl_sync(0xffffffffu, incl, owner + step - 1);
-            if (t <= p) owner += step;
-        }
-        owner = min(owner, 31);
-        const u32 o_excl = __shfl_sync(0xffffffffu, excl, owner);
-        const u32 o_id = __shfl_sync(0xffffffffu, id, owner);
-        const int o_x0 = __shfl_sync(0xffffffffu, x0, owner);
-        const int o_y0 = __shfl_sync(0xffffffffu, y0, owner);
-        const int o_w = __shfl_sync(0xffffffffu, w, owner);
         if (p < total) {
             const u32 r = p - o_excl;
-            const u32 ry = r / (u32)o_w;
-            const u32 tile = (u32)(o_y0 + (int)ry) * (u32)tiles_x + (u32)o_x0 + (r - ry * (u32)o_w);
+            int ry, rx;
+            if (r < (1u << 22)) {   // quotient off by at most one before the correction: exact
+                ry = (int)(((float)r + 0.5f) * __frcp_rn((float)o_w));
+                rx = (int)r - ry * (int)o_w;
+                if (rx < 0) { --ry; rx += (int)o_w; }
+                else if (rx >= (int)o_w) { ++ry; rx -= (int)o_w; }
+            } else {                // a rectangle of more than four million tiles
+                ry = (int)(r / o_w);
+                rx = (int)(r - (u32)ry * o_w);
+            }
+            const u32 tile = ((o_xy >> 16) + (u32)ry) * (u32)tiles_x + (o_xy & 0xffffu) + (u32)rx;
             const u32 dst = warp_base + p;
             if (dst < k) pairs[dst] = ((u64)tile << 32) | o_id;
         }

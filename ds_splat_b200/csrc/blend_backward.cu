@@ -109,7 +109,7 @@ static_assert(kBlockH <= kTile && kTile % kBlockH == 0, "a warp's pixel block mu
 #define DSB_BWD_THREADS 64
 #endif
 #ifndef DSB_BWD_MIN_BLOCKS
-#define DSB_BWD_MIN_BLOCKS 12  // 80 registers; without the bound the compiler takes 91 and two fewer blocks fit
+#define DSB_BWD_MIN_BLOCKS 14  // 72 registers, nothing spilled; measured 12 / 14 / 16 blocks: 0.434 / 0.418 / 0.436 ms (16 spills)
 #endif
 constexpr int kThreads = DSB_BWD_THREADS, kWarps = kThreads / 32;
 
