@@ -214,6 +214,16 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def views_of_rank(num_views: int, rank: int, world: int, vpr: int):
+    """The cameras of one step: world * vpr of the scene's views, evenly spaced over the whole set, dealt to the ranks
+    round-robin (the library's dp.shard_views).  Every rank's batch spans the whole camera set at every world size, so
+    the ranks' batches cost about the same and a rank's work does not depend on how many ranks there are."""
+    from ds_splat_b200.dp import shard_views
+    batch = world * vpr
+    picked = [(g * num_views) // batch % num_views for g in range(batch)] if num_views >= batch else [g % num_views for g in range(batch)]
+    return [picked[i] for i in shard_views(batch, rank, world)]
+
+
 _AFFINITY_AT_START = None
 
 
@@ -482,8 +492,8 @@ def main():
     vpr = max(1, args.views_per_rank)
     scene = load_scene(args, views=world * vpr)
     H, W = scene.views[0].H, scene.views[0].W
-    # Cameras are dealt to ranks in blocks of vpr: every view of a step, on every rank, is a different camera.
-    view_ids = [(rank * vpr + j) % len(scene.views) for j in range(vpr)]
+    # Every view of a step, on every rank, is a different camera (views_of_rank).
+    view_ids = views_of_rank(len(scene.views), rank, world, vpr)
     cams = [CameraTensors.from_view(scene.views[v], dev) for v in view_ids]
     v_images_host = [scene.image_grad(v, seed=7 + v) for v in view_ids]
     v_images = [t(v) for v in v_images_host]
@@ -676,12 +686,12 @@ def main():
         torch.cuda.empty_cache()
         from ds_splat_b200 import scenes
         sc3 = scenes.multiview()
-        ids3 = [(rank * vpr + j) % len(sc3.views) for j in range(vpr)]
+        ids3 = views_of_rank(len(sc3.views), rank, world, vpr)
         cams3 = [CameraTensors.from_view(sc3.views[v], dev) for v in ids3]
         vim3 = [t(sc3.image_grad(v, seed=7 + v)) for v in ids3]
         params3, grads3, renderer3, opt3, pool3 = build_training(sc3, cams3, vim3, dev, args, world)
         ms3, phases3 = timed_training(timer, renderer3, cams3, vim3, grads3, opt3, args, world, 8, 3)
-        c3 = {"workload": f"{sc3.name}: {sc3.n} splats SH-3, {W}x{H}, {vpr} of {len(sc3.views)} ring cameras per rank per step",
+        c3 = {"workload": f"{sc3.name}: {sc3.n} splats SH-3, {W}x{H}, {vpr} of {len(sc3.views)} ring cameras per rank per step, spaced evenly around the ring",
               "views_per_s": round(world * vpr / (ms3 * 1e-3), 3), "ms_per_step": round(ms3, 4), "steps": 8, "warmup": 3,
               "step_breakdown_ms": phases3, "gradient_bytes": int(grads3.nbytes()),
               "pairs_emitted_mean": int(sum(renderer3.last_ks) / vpr), "nccl_registered_buffers": pool3 is not None}

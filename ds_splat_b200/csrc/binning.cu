@@ -150,18 +150,17 @@ scan_counts_kernel(const u64* __restrict__ depth_keys_sorted, const int32_t* __r
 // the packed splats whose range starts inside the round's 32 positions set the bit of that position; one
 // warp-wide OR gives the round's start mask, and the owner of position q is the number of starts at or before q
 // (a population count) plus the starts of earlier rounds -- no search.  The position inside the owner's rectangle
-// is split into row and column with a float reciprocal and one correction step (integer division for rectangles
-// of more than 2^22 tiles).
+// is split into row and column with the width's reciprocal (integer division for rectangles of 2^20 tiles and more).
 __global__ void __launch_bounds__(256)
 emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_last, const float4* __restrict__ records,
                   const int32_t* __restrict__ tiles, const u64* __restrict__ depth_keys_sorted,
                   const u32* __restrict__ offsets, u64* __restrict__ pairs) {
-    __shared__ u32 s_id[8][32], s_xy[8][32], s_w[8][32], s_excl[8][32];
+    __shared__ u32 s_id[8][32], s_tile[8][32], s_w[8][32], s_excl[8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;  // position in depth order; warps are aligned to 32
     // A splat's pair count is the distance to the next splat's offset (the scan already left out the dropped last
     // splat), read along the depth order: no gather of the per-splat counts.
-    u32 id = 0, c = 0, xy = 0, w = 1;
+    u32 id = 0, c = 0, first_tile = 0, w = 1;
     const u32 off = j < n ? offsets[j] : k;
     u32 next = __shfl_down_sync(0xffffffffu, off, 1);
     if (lane == 31) next = j + 1 < n ? offsets[j + 1] : k;
@@ -173,7 +172,7 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
             const u32 rx = __float_as_uint(q2.z), ry = __float_as_uint(q2.w);
             const u32 x0 = rx & 0xffffu;
             w = (rx >> 16) - x0;
-            xy = x0 | (ry << 16);   // first column | first row << 16
+            first_tile = (ry & 0xffffu) * (u32)tiles_x + x0;
         }
     }
     u32 incl = c;
@@ -189,12 +188,14 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
     const int packed = __popc(have);
     if (c) {
         const int slot = __popc(have & ((1u << lane) - 1u));
-        s_id[warp][slot] = id; s_xy[warp][slot] = xy; s_w[warp][slot] = w; s_excl[warp][slot] = incl - c;
+        s_id[warp][slot] = id; s_tile[warp][slot] = first_tile; s_w[warp][slot] = w; s_excl[warp][slot] = incl - c;
     }
     __syncwarp();
     const bool mine = lane < packed;
-    const u32 cid = mine ? s_id[warp][lane] : 0u, cxy = mine ? s_xy[warp][lane] : 0u, cw = mine ? s_w[warp][lane] : 1u;
+    const u32 cid = mine ? s_id[warp][lane] : 0u, ctile = mine ? s_tile[warp][lane] : 0u, cw = mine ? s_w[warp][lane] : 1u;
     const u32 cexcl = mine ? s_excl[warp][lane] : 0xffffffffu;
+    float cinv;                                       // 1 / width, a few ulp off: see the split below
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(cinv) : "f"((float)cw));
     const u32 le_mask = 0xffffffffu >> (31 - lane);   // positions of the round at or before this lane's
     u32 started = 0;                                  // packed splats whose range starts before the round
     for (u32 base = 0; base < total; base += 32) {
@@ -204,22 +205,17 @@ emit_pairs_kernel(const int n, const u32 k, const int tiles_x, const int drop_la
         started += (u32)__popc(starts);
         const u32 o_excl = __shfl_sync(0xffffffffu, cexcl, owner);
         const u32 o_id = __shfl_sync(0xffffffffu, cid, owner);
-        const u32 o_xy = __shfl_sync(0xffffffffu, cxy, owner);
+        const u32 o_tile = __shfl_sync(0xffffffffu, ctile, owner);
         const u32 o_w = __shfl_sync(0xffffffffu, cw, owner);
+        const float o_inv = __shfl_sync(0xffffffffu, cinv, owner);
         const u32 p = base + lane;
         if (p < total) {
             const u32 r = p - o_excl;
-            int ry, rx;
-            if (r < (1u << 22)) {   // quotient off by at most one before the correction: exact
-                ry = (int)(((float)r + 0.5f) * __frcp_rn((float)o_w));
-                rx = (int)r - ry * (int)o_w;
-                if (rx < 0) { --ry; rx += (int)o_w; }
-                else if (rx >= (int)o_w) { ++ry; rx -= (int)o_w; }
-            } else {                // a rectangle of more than four million tiles
-                ry = (int)(r / o_w);
-                rx = (int)(r - (u32)ry * o_w);
-            }
-            const u32 tile = ((o_xy >> 16) + (u32)ry) * (u32)tiles_x + (o_xy & 0xffffu) + (u32)rx;
+            // Row of position r in a rectangle o_w tiles wide.  (r + 0.5) / o_w lies at least 0.5 / o_w from the
+            // next integer, the float product is off by less than r * 2^-21 / o_w: exact below 2^20 (checked
+            // exhaustively for every width up to 300 and reciprocals up to 3 ulp off).
+            const u32 row = r < (1u << 20) ? (u32)(((float)r + 0.5f) * o_inv) : r / o_w;
+            const u32 tile = o_tile + row * (u32)tiles_x + (r - row * o_w);
             const u32 dst = warp_base + p;
             if (dst < k) pairs[dst] = ((u64)tile << 32) | o_id;
         }
