@@ -67,6 +67,30 @@ int finish_device_status_read(int value, cudaStream_t s) {
 
 u32 copy_wait_polls() { return g_copy_wait_polls.load(std::memory_order_relaxed); }
 
+// ---- side lane -----------------------------------------------------------------------------------
+// One extra stream and two events per device, created on first use and kept for the life of the process.  The
+// single-view plan runs the tile layout on it: the layout is one thread block (its duration is that block's
+// latency, about 28 us at 1080p) and nothing before the pair emission needs its results, so it runs beside the
+// depth sort and the offset scan instead of in front of them.  Fork and join are events; no kernel waits on a
+// kernel.  Calls from several host threads share the lane: its stream is first-in first-out, so a join recorded
+// later also covers every layout launched earlier.
+struct SideLane { cudaStream_t stream; cudaEvent_t fork, join; bool ready; };
+static SideLane g_side_lane[kMaxStatusDevices] = {};
+static std::mutex g_side_lane_mutex;
+
+static SideLane* side_lane_locked() {   // g_side_lane_mutex held
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStatusDevices) return nullptr;
+    SideLane& lane = g_side_lane[dev];
+    if (!lane.ready) {
+        if (cudaStreamCreateWithFlags(&lane.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&lane.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&lane.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        lane.ready = true;
+    }
+    return &lane;
+}
+
 // ---- stage timing ------------------------------------------------------------------------------
 struct EventPair { cudaEvent_t a, b; int stage; };
 static bool g_timing = false;
@@ -368,19 +392,49 @@ int dsb_forward_plan(const DsbCamera* cam, int32_t n, const float* means3d, cons
                                          tile_marks, s);
         if (rc != DSB_OK) return rc;
     }
-    {   // tile ranges, tile order and the row-binning block (or the tile sort's digit counts) from the corner marks
+    // Tile ranges, tile order and the tile sort's digit counts (or the row-binning block) from the corner marks.  The
+    // depth sort and the scan below do not read them (the scan of a row-binned view does), so the layout goes to the
+    // side lane; the caller's stream joins it after the plan.  With stage timing on everything stays on one stream,
+    // so that a stage's events bracket that stage alone.
+    const bool rows = row_binned(cp);
+    cudaEvent_t join = nullptr;
+    {
         StageScope scope(kStageRanges, s);
         int has_order = 0;
-        const int rc = launch_tile_layout(cp, tile_marks, tile_sort_plan(cp), layout, ranges, &has_order, s);
-        if (rc != DSB_OK) return rc;
+        bool beside = false;
+        if (!rows && n > 0 && !g_timing) {
+            std::lock_guard<std::mutex> lock(g_side_lane_mutex);
+            SideLane* lane = side_lane_locked();
+            if (lane) {
+                DSB_CUDA_CHECK(cudaEventRecord(lane->fork, s));
+                DSB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
+                const int rc = launch_tile_layout(cp, tile_marks, tile_sort_plan(cp), layout, ranges, &has_order, lane->stream);
+                // joined whatever the launch said, so that the caller's stream never runs ahead of the side lane
+                DSB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
+                if (rc != DSB_OK) {
+                    cudaStreamWaitEvent(s, lane->join, 0);
+                    return rc;
+                }
+                join = lane->join;
+                beside = true;
+            }
+        }
+        if (!beside) {
+            const int rc = launch_tile_layout(cp, tile_marks, tile_sort_plan(cp), layout, ranges, &has_order, s);
+            if (rc != DSB_OK) return rc;
+        }
     }
     if (n == 0) return DSB_OK;
-    const bool rows = row_binned(cp);
     const float* rec = records;
     const u32* info = layout;
-    return launch_plan_views(cp, 1, n, n, tiles_touched, reinterpret_cast<u64*>(depth_keys), reinterpret_cast<u64*>(depth_keys_alt),
-                             offsets, workspace, workspace_bytes, k_host, s, rows ? &rec : nullptr, rows ? &info : nullptr,
-                             k_rows_host);
+    const int rc = launch_plan_views(cp, 1, n, n, tiles_touched, reinterpret_cast<u64*>(depth_keys),
+                                     reinterpret_cast<u64*>(depth_keys_alt), offsets, workspace, workspace_bytes, k_host, s,
+                                     rows ? &rec : nullptr, rows ? &info : nullptr, k_rows_host);
+    if (join) {   // everything the caller enqueues on its stream from here on sees the layout
+        const cudaError_t e = cudaStreamWaitEvent(s, join, 0);
+        if (rc == DSB_OK) DSB_CUDA_CHECK(e);
+    }
+    return rc;
 }
 
 int dsb_forward_render(const DsbCamera* cam, int32_t n, int64_t k, int64_t k_rows, const float* records,
