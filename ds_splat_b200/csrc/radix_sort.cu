@@ -247,8 +247,8 @@ __device__ __forceinline__ void sweep_tile(const u64* __restrict__ kin, u64* __r
     // Decoupled look-back over earlier tiles for this digit.  Measured alternatives, all slower: requesting the
     // status words of several predecessors at once (the extra registers spill); several threads per digit reading
     // as many predecessors per step; the whole block fetching the sixteen nearest rows per round with asynchronous
-    // copies into the key staging area (12% slower: a block's wait is covered by the other resident blocks, the
-    // extra barriers are not).
+    // copies into the key staging area (12% slower on lists of several waves of blocks, 25% slower on one-wave
+    // lists: a block's wait is covered by the other resident blocks, the extra barriers and re-fetched rows are not).
     u32 earlier = 0;
     if (tile > 0 && owner) {
         int p = (int)tile - 1;
