@@ -733,9 +733,9 @@ def main():
             flops = 74.0 * pairs_bwd
             fp32_peak = 148 * 128 * 2 * clocks["sm_mhz"] * 1e6 / 1e12
             # DRAM bytes of one blend_backward_kernel launch from the ncu capture summarised in
-            # profiles/blend_backward_c1.md (83,103,232 read + 4,211,712 written for 7,710,065 pairs); it is dominated by
+            # profiles/blend_backward_c1.md (83,856,640 read + 3,512,064 written for 7,710,065 pairs); it is dominated by
             # the first touch of the pair list and the gathered records, so it is scaled by the pairs of this launch.
-            traffic = int(87_314_944 * (K / 7_710_065))
+            traffic = int(87_368_704 * (K / 7_710_065))
             roofline = {"kernel": "blend_backward_kernel", "bound": "fp32", "achieved": round(flops / (dom_ms * 1e-3) / 1e12, 3),
                         "peak": round(fp32_peak, 2), "unit": "TFLOP/s", "frac": round(flops / (dom_ms * 1e-3) / 1e12 / fp32_peak, 4),
                         "traffic": traffic, "ms": dom_ms, "pairs_visited": int(pairs_bwd), "flop_per_pair": 74,
