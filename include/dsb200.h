@@ -287,6 +287,11 @@ int dsb_geometry_backward(const DsbCamera* cam, int32_t n, const float* means3d,
  *                      render; then the depth order of the splats and a scan over it.  One host synchronisation
  *                      reads back *k_host (pairs) and *k_rows_host (row items, see below).
  *                      tile_marks: dsb_tile_marks_bytes(H, W); workspace: dsb_plan_workspace_bytes(n).
+ *                      The layout step is one thread block and nothing before the pair emission reads what it
+ *                      writes, so it runs beside the depth sort and the scan on a stream of the library's own (one
+ *                      per device, created on first use; fork and join are events, and `stream` has joined it when
+ *                      the call returns: whatever the caller enqueues on `stream` afterwards sees ranges, tile order
+ *                      and layout).  Row-binned views and calls made while stage timing is on stay on `stream`.
  * dsb_forward_render = the second half (:196-207): from the depth-ordered splats to the sorted pair list in `pairs`
  *                      (k words) and the blended image.  By default the pairs are written in depth order and sorted
  *                      on their tile bits as the per-stage calls do (`offsets` = first pair of every depth-ordered

@@ -254,3 +254,34 @@ def test_every_way_of_fetching_records_renders_the_same_image(run):
     assert lib.dsb_debug_blend_forward_variant(C.byref(cam), 7, n, k, run["records"].data_ptr(), run["sorted_pairs"].data_ptr(),
                                                run["ranges"].data_ptr(), image.data_ptr(), final_t.data_ptr(),
                                                final_idx.data_ptr(), None, None, 0, None) == -1
+
+
+def test_emit_walks_rectangles_of_more_than_a_million_tiles():
+    """The emit kernel splits a list position into row and column of its splat's rectangle with the width's reciprocal
+    below 2^20 tiles and with an integer division from there on.  One splat that covers every tile of a 16400 x 16400
+    image (1025 x 1025 = 1,050,625 tiles) crosses that border: its pairs must be the tile ids in row-major order.
+    Stage calls only: no image of that size is rendered."""
+    W = H = 16400
+    view = scenes.make_view((0.0, 0.0, -1.0), (0.0, 0.0, 0.0), W, H, focal=8200.0)
+    assert view.num_tiles == 1025 * 1025
+    dev = "cuda"
+    means = torch.tensor([[0.0, 0.0, 0.0], [0.3, 0.2, 0.5], [0.0, 0.0, 0.0]], device=dev)      # the last one is dropped
+    scales = torch.tensor([[1.0, 1.0, 1.0], [0.001, 0.001, 0.001], [1.0, 1.0, 1.0]], device=dev)
+    rots = torch.tensor([[1.0, 0.0, 0.0, 0.0]] * 3, device=dev)
+    opac = torch.tensor([[0.9], [0.9], [0.9]], device=dev)
+    shs = torch.zeros((3, 16, 3), device=dev)
+    cam, keep = capi_camera(view)
+    records, radii, tiles, cov3d, dk = _capi.preprocess(cam, means, shs, opac, scales, rots)
+    assert int(tiles[0]) == view.num_tiles and 0 < int(tiles[1]) < 64
+    offsets, k = _capi.plan_pairs(cam, tiles, dk)
+    assert k == view.num_tiles + int(tiles[1])
+    pairs = _capi.emit_pairs(cam, k, records, tiles, dk, offsets)
+    torch.cuda.synchronize()
+    big = pairs[(pairs & 0xffffffff) == 0]
+    assert big.shape[0] == view.num_tiles
+    assert torch.equal(big >> 32, torch.arange(view.num_tiles, device=dev, dtype=torch.int64))
+    small = pairs[(pairs & 0xffffffff) == 1] >> 32
+    rec = unpack_records(records.cpu().numpy())
+    x0, x1, y0, y1 = (int(v) for v in rec["rect"][1])
+    want = [y * 1025 + x for y in range(y0, y1) for x in range(x0, x1)]
+    assert small.cpu().tolist() == want
