@@ -19,9 +19,9 @@ Rank 0 prints ONE JSON line.
                    reference's; the default pairs a splat only with tiles it can contribute to, a subset with
                    identical image, radii and gradients);
   strict_lists     the multi-view step again with the reference-identical lists;
-  e2e              one view per step through the public Python operator (GaussianRasterizer + autograd) with the
-                   step's inputs (camera, upstream image gradient) copied from pinned host memory and the
-                   rendered image + radii copied back inside the timed region;
+  e2e              one training iteration per step through the public Python operator (GaussianRasterizer +
+                   autograd): camera and 8-bit target image copied from pinned host memory, torch L1 loss, backward,
+                   and the loss value read on the host, all inside the timed region;
   roofline         the dominant kernel (backward blend) on the configuration's own camera against the FP32 pipe
                    (148 SMs x 128 lanes x 2 flop x sampled SM clock), timed live with the cudaEvent pairs the
                    library records around each stage; ``roofline_hbm`` is the same launch against the measured
@@ -588,69 +588,62 @@ def main():
     # ---- end to end through the public operator, host buffers -----------------------------------------
     e2e = None
     if not args.skip_e2e:
+        # One training iteration the way a user of the operator writes it: the camera and the step's target image (8-bit
+        # RGB, the form datasets hold) come from pinned host memory, the loss is torch's L1 on the rendered image,
+        # autograd drives the operator's backward, and the loss value is read on the host.
         view = scene.views[view_ids[0]]
-        pinned_grad = torch.from_numpy(v_images_host[0]).pin_memory()
+        rng = np.random.default_rng(11)
+        pinned_target = torch.from_numpy(rng.integers(0, 256, size=(H, W, 3), dtype=np.uint8)).pin_memory()
         pinned_view = torch.from_numpy(view.viewmatrix_t).pin_memory()
         pinned_proj = torch.from_numpy(view.projmatrix_t).pin_memory()
         pinned_pos = torch.from_numpy(np.ascontiguousarray(view.campos)).pin_memory()
-        # two sets of host result buffers and of device-side gradient buffers: step i's result is read on the host while
-        # step i + 1 is already enqueued (a training loop logs the loss of the step before the one in flight)
-        out_image = [torch.empty((H, W, 3), dtype=torch.float32).pin_memory() for _ in range(2)]
-        out_radii = [torch.empty(scene.n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        # two sets of buffers: step i's loss is read on the host while step i + 1 is already enqueued (a training loop
+        # logs the loss of the step before the one in flight)
+        loss_host = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        target_dev = [torch.empty((H, W, 3), dtype=torch.uint8, device=dev) for _ in range(2)]
         leaves = {k: v.detach().clone().requires_grad_(True) for k, v in params.views.items()}
         means2d = torch.zeros_like(leaves["means3d"], requires_grad=True)
         bg = torch.zeros(3, device=dev)
         vm, pm, cp = (torch.empty_like(x, device=dev) for x in (pinned_view, pinned_proj, pinned_pos))
-        vg = [torch.empty((H, W, 3), dtype=torch.float32, device=dev) for _ in range(2)]
         settings = GaussianRasterizationSettings(H, W, view.tanfovx, view.tanfovy, bg, 1.0, vm, pm, scene.sh_degree, 3, cp,
                                                  False, False)
         rasterizer = GaussianRasterizer(settings)
-        h2d = pinned_grad.numel() * 4 + (16 + 16 + 3) * 4
-        d2h = out_image[0].numel() * 4 + out_radii[0].numel() * 4
-        copy_stream = torch.cuda.Stream(device=dev)      # results to the host
-        upload_stream = torch.cuda.Stream(device=dev)    # inputs to the device (its own stream: the two directions do not queue)
+        h2d = pinned_target.numel() + (16 + 16 + 3) * 4
+        d2h = 4
+        upload_stream = torch.cuda.Stream(device=dev)    # the target image travels while the forward runs
         main_stream = torch.cuda.current_stream()
-        grad_ready, rendered = torch.cuda.Event(), torch.cuda.Event()
+        target_ready = torch.cuda.Event()
         backward_done = [torch.cuda.Event(), torch.cuda.Event()]
         result_on_host = [torch.cuda.Event(), torch.cuda.Event()]
         checksum = [0.0]
 
         def e2e_step(i):
-            # A training loop's usual overlap: the image gradient travels to the device while the forward runs, the
-            # rendered image travels back while the backward runs (second stream, events), and the host reads the
-            # result of step i - 1 after it has enqueued step i.  Every step's inputs come from pinned host memory and
-            # every step's result is read on the host inside the timed region.
             s = i & 1
             vm.copy_(pinned_view, non_blocking=True)
             pm.copy_(pinned_proj, non_blocking=True)
             cp.copy_(pinned_pos, non_blocking=True)
             with torch.cuda.stream(upload_stream):
-                upload_stream.wait_event(backward_done[s])   # the backward that last read vg[s] (two steps ago)
-                vg[s].copy_(pinned_grad, non_blocking=True)
-                grad_ready.record(upload_stream)
+                upload_stream.wait_event(backward_done[s])   # the loss that last read target_dev[s] (two steps ago)
+                target_dev[s].copy_(pinned_target, non_blocking=True)
+                target_ready.record(upload_stream)
             for leaf in leaves.values():
                 leaf.grad = None
             means2d.grad = None
             image, radii = rasterizer(leaves["means3d"], means2d, leaves["shs"], None, leaves["opacities"],
                                       leaves["scales"], leaves["rotations"], None)
-            rendered.record(main_stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(rendered)
-                out_image[s].copy_(image.detach(), non_blocking=True)
-                out_radii[s].copy_(radii, non_blocking=True)
-                result_on_host[s].record(copy_stream)
-            image.record_stream(copy_stream)
-            radii.record_stream(copy_stream)
-            main_stream.wait_event(grad_ready)
-            image.backward(vg[s])
+            main_stream.wait_event(target_ready)
+            loss = torch.nn.functional.l1_loss(image, target_dev[s] / 255.0)
+            loss.backward()
             backward_done[s].record(main_stream)
-            if i > 0:   # the previous step's result, on the host
+            loss_host[s].copy_(loss.detach(), non_blocking=True)
+            result_on_host[s].record(main_stream)
+            if i > 0:   # the previous step's loss, on the host
                 result_on_host[s ^ 1].synchronize()
-                checksum[0] += float(out_image[s ^ 1][0, 0, 0]) + int(out_radii[s ^ 1][0])
+                checksum[0] += float(loss_host[s ^ 1])
 
-        def e2e_drain(i):   # the last step's result
+        def e2e_drain(i):   # the last step's loss
             result_on_host[(i - 1) & 1].synchronize()
-            checksum[0] += float(out_image[(i - 1) & 1][0, 0, 0])
+            checksum[0] += float(loss_host[(i - 1) & 1])
             torch.cuda.synchronize()
 
         for ev in backward_done:
@@ -672,10 +665,11 @@ def main():
         e2e = {"value": round(world * args.steps / (e_ms * 1e-3), 3), "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": round(e_ms / args.steps, 4),
-               "note": "GaussianRasterizer + autograd, one view per step; per step H2D camera + dL/dimage from pinned memory, "
-                       "D2H image + radii, read on the host one step behind the step being enqueued; splat parameters are "
-                       "model state resident on the device"
-                       + ("; per-rank rendering with no collective in it (N independent render loops)" if world > 1 else "")}
+               "note": "one training iteration per step through GaussianRasterizer + autograd: camera and the 8-bit target "
+                       "image from pinned host memory (second stream), torch L1 loss on the rendered image, backward, the loss "
+                       "value read on the host one step behind the step being enqueued; splat parameters are model state "
+                       "resident on the device"
+                       + ("; per-rank iterations with no collective in them (N independent loops)" if world > 1 else "")}
         del leaves, means2d, rasterizer
 
     nccl_registered = pool is not None

@@ -398,7 +398,10 @@ int launch_preprocess_views(const CamParams* cps, int count, int n, const float*
     }
     const int sh_vec4 = shs && cp.max_coeff == 16 && ((uintptr_t)shs & 15) == 0;
     // bulk-copy staging needs every streamed input 16-byte aligned and the default input form
-    const int use_bulk = sh_vec4 && !colors_precomp && !cov3d_precomp && scales && ((uintptr_t)means & 15) == 0 &&
+#ifndef DSB_PRE_BULK
+#define DSB_PRE_BULK 1   // 0: stage with ordinary 16-byte loads (kept for measurements)
+#endif
+    const int use_bulk = DSB_PRE_BULK && sh_vec4 && !colors_precomp && !cov3d_precomp && scales && ((uintptr_t)means & 15) == 0 &&
                          ((uintptr_t)scales & 15) == 0;
     // dynamic shared memory: the padded SH rows
     const size_t dyn = sh_vec4 ? (size_t)kThreads * kShRow4 * 16 : (size_t)kThreads * ((3 * cp.max_coeff) | 1) * 4;
