@@ -77,6 +77,9 @@ def parse_args():
     ap.add_argument("--skip-optimizer", action="store_true", help="skip the separate Adam / image-loss kernel timings")
     ap.add_argument("--skip-c3", action="store_true")
     ap.add_argument("--skip-strict", action="store_true")
+    ap.add_argument("--optimizer-chunks", type=int, default=1,
+                    help="N > 1: cut the gradient/parameter blocks into this many chunks and pipeline reduce-scatter, Adam and "
+                         "all-gather over two communicators (1: one reduce-scatter, one update, one all-gather)")
     ap.add_argument("--frames", type=int, default=120, help="frames of the fly-through workload")
     return ap.parse_args()
 
@@ -225,6 +228,7 @@ def views_of_rank(num_views: int, rank: int, world: int, vpr: int):
 
 
 _AFFINITY_AT_START = None
+GATHER_GROUP = [None]   # second communicator over all ranks, made once in main() when the optimizer step is pipelined
 
 
 def bind_to_gpu_numa_node(dev_index: int):
@@ -255,6 +259,47 @@ def bind_to_gpu_numa_node(dev_index: int):
         return {"node": node, "bound": True, "cores": len(local)}
     except Exception as e:   # no sysfs entry, no permission: run unbound
         return {"node": None, "bound": False, "why": type(e).__name__}
+
+
+def check_sharded_optimizer(dev, world, rank, chunks, gather_group):
+    """N > 1, a few milliseconds: the forms of the optimizer step must agree on the device they will be timed on.  A small
+    cloud, learning rates that move every parameter, three steps with gradients that differ per rank and step; compared
+    are (a) all-reduce + Adam over everything, (b) ShardedAdam in one piece, (c) ShardedAdam in `chunks` pipelined chunks
+    over the second communicator.  Returns the largest absolute parameter difference of (b) and of (c) against (a)."""
+    import torch
+    from ds_splat_b200.dp import FlatAdam, GradientBuffer, ParameterBuffer, ShardedAdam, allreduce_gradients
+    n = 4099
+    lrs = {"means3d": 1e-3, "shs": 2e-3, "opacities": 5e-2, "scales": 5e-3, "rotations": 1e-3}
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    init = torch.randn(n * 59, generator=gen)
+
+    def fresh(shards):
+        p, g = ParameterBuffer(n, dev, shards=shards), GradientBuffer(n, dev, shards=shards)
+        p.flat.copy_(init.to(dev)[:p.flat.numel()])
+        return p, g
+
+    def gradients(step):
+        gg = torch.Generator(device="cpu").manual_seed(1000 * step + rank)
+        return torch.randn(n * 59, generator=gg).to(dev)
+
+    forms = {}
+    pa, ga = fresh(1)
+    oa = FlatAdam(pa.views, lrs, eps=1e-8)
+    pb, gb = fresh(world)
+    ob = ShardedAdam(pb, lrs, eps=1e-8)
+    pc, gc = fresh(world * chunks)
+    oc = ShardedAdam(pc, lrs, eps=1e-8, chunks=chunks, gather_group=gather_group)
+    for step in range(1, 4):
+        g = gradients(step)
+        ga.flat.copy_(g[:ga.flat.numel()]); gb.flat.copy_(g[:gb.flat.numel()]); gc.flat.copy_(g[:gc.flat.numel()])
+        allreduce_gradients(ga)
+        oa.step(ga, grad_scale=1.0 / world)
+        ob.step(gb, grad_scale=1.0 / world)
+        oc.step(gc, grad_scale=1.0 / world)
+    torch.cuda.synchronize()
+    forms["sharded"] = float((pb.flat - pa.flat).abs().max())
+    forms["sharded_pipelined" if oc.pipelined() else "sharded_chunked"] = float((pc.flat - pa.flat).abs().max())
+    return forms
 
 
 class Timed:
@@ -304,11 +349,14 @@ def build_training(scene, cams, v_images, dev, args, world, tight_tiles=True):
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     host = dict(means3d=scene.means, shs=scene.shs, opacities=scene.opacities, scales=scene.scales, rotations=scene.rotations)
 
+    chunks = max(1, args.optimizer_chunks) if world > 1 else 1
+    gather_group = GATHER_GROUP[0] if (world > 1 and chunks > 1) else None
+
     def make():
-        return (ParameterBuffer(scene.n, dev, shards=world), GradientBuffer(scene.n, dev, shards=world))
+        return (ParameterBuffer(scene.n, dev, shards=world * chunks), GradientBuffer(scene.n, dev, shards=world * chunks))
 
     if world > 1 and not args.no_nccl_registration:
-        (params, grads), pool = register_with_nccl(make)
+        (params, grads), pool = register_with_nccl(make, more_groups=[gather_group] if gather_group is not None else ())
     else:
         (params, grads), pool = make(), None
     for name, arr in host.items():
@@ -318,7 +366,7 @@ def build_training(scene, cams, v_images, dev, args, world, tight_tiles=True):
     # Learning rate zero: the kernel reads and writes exactly what it does in training (parameters, gradients, both
     # moments), but the cloud stays the configuration's cloud over hundreds of timed steps.  (Adam's normalised
     # update would otherwise move every scale by lr per step whatever the gradient, and 300 steps destroy the scene.)
-    opt = ShardedAdam(params, {k: 0.0 for k in LRS})
+    opt = ShardedAdam(params, {k: 0.0 for k in LRS}, chunks=chunks, gather_group=gather_group)
     return params, grads, renderer, opt, pool
 
 
@@ -329,28 +377,25 @@ def timed_training(timer, renderer, cams, v_images, grads, opt, args, world, ste
     vpr = len(cams)
     marks = []
 
+    pipelined = opt.pipelined()
+
     def step(record=False):
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
+        # the library's own training step: render the rank's cameras, then ShardedAdam.step
+        ev = []
+        mark = None
         if record:
-            ev[0].record()
+            def mark():
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                ev.append(e)
+            mark()
         renderer.render_views(cams, v_images, grads, accumulate=False)
         if record:
-            ev[1].record()
-        g_slice = grads.storage[opt.lo:opt.hi]
-        opt.step_count += 1
-        if world > 1:
-            dist.reduce_scatter_tensor(g_slice, grads.storage, op=dist.ReduceOp.SUM)
+            mark()
+        opt.step(grads, grad_scale=1.0 / (vpr * world), marks=None if pipelined else mark)
         if record:
-            ev[2].record()
-        for name, a, b in opt.pieces:
-            opt.update(opt.params.storage[a:b], grads.storage[a:b], opt.m[a - opt.lo:b - opt.lo], opt.v[a - opt.lo:b - opt.lo],
-                       opt.lrs[name], opt.betas[0], opt.betas[1], opt.eps, opt.step_count, 1.0 / (vpr * world))
-        if record:
-            ev[3].record()
-        if world > 1:
-            dist.all_gather_into_tensor(opt.params.storage, opt.params.storage[opt.lo:opt.hi])
-        if record:
-            ev[4].record()
+            if pipelined:
+                mark()
             marks.append(ev)
 
     ms = timer.run(step, steps, warmup) / steps
@@ -359,9 +404,17 @@ def timed_training(timer, renderer, cams, v_images, grads, opt, args, world, ste
     for _ in range(min(steps, 10)):
         step(record=True)
     torch.cuda.synchronize()
-    names = ("render", "reduce_scatter", "adam", "all_gather")
-    phases = {n: round(timer.max_over_ranks(sum(e[i].elapsed_time(e[i + 1]) for e in marks) / len(marks)), 4)
-              for i, n in enumerate(names)}
+
+    def mean_ms(pairs):   # pairs of event indices whose intervals are added up
+        return round(timer.max_over_ranks(sum(sum(e[i].elapsed_time(e[j]) for i, j in pairs) for e in marks) / len(marks)), 4)
+    if pipelined:   # reduce-scatter, update and all-gather of the chunks overlap: one figure
+        phases = {"render": mean_ms([(0, 1)]), "sharded_step_pipelined": mean_ms([(1, 2)])}
+    else:           # per chunk: reduce-scatter, update, all-gather
+        c = opt.chunks
+        phases = {"render": mean_ms([(0, 1)]),
+                  "reduce_scatter": mean_ms([(1 + 3 * k, 2 + 3 * k) for k in range(c)]),
+                  "adam": mean_ms([(2 + 3 * k, 3 + 3 * k) for k in range(c)]),
+                  "all_gather": mean_ms([(3 + 3 * k, 4 + 3 * k) for k in range(c)])}
     timer.launches = launches
     return ms, phases
 
@@ -485,9 +538,21 @@ def main():
         json_out = os.fdopen(os.dup(1), "w")
         os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
+        if args.optimizer_chunks > 1:
+            try:
+                GATHER_GROUP[0] = dist.new_group(backend="nccl", device_id=dev)
+            except TypeError:   # a torch whose new_group takes no device
+                GATHER_GROUP[0] = dist.new_group(backend="nccl")
     _capi.lib()  # fail loudly if the library is missing
     timer = Timed(world, dev)
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    optimizer_check = None
+    if world > 1:
+        optimizer_check = check_sharded_optimizer(dev, world, rank, max(2, args.optimizer_chunks), GATHER_GROUP[0])
+        optimizer_check = {k: timer.max_over_ranks(v) for k, v in optimizer_check.items()}
+        bad = {k: v for k, v in optimizer_check.items() if not v < 1e-5}
+        if bad:
+            raise SystemExit(f"the forms of the optimizer step disagree on this machine: {bad}")
 
     vpr = max(1, args.views_per_rank)
     scene = load_scene(args, views=world * vpr)
@@ -498,6 +563,7 @@ def main():
     v_images_host = [scene.image_grad(v, seed=7 + v) for v in view_ids]
     v_images = [t(v) for v in v_images_host]
     params, grads, renderer, opt, pool = build_training(scene, cams, v_images, dev, args, world)
+    opt_chunks, opt_pipelined = int(opt.chunks), bool(opt.pipelined())
     warmup = max(args.warmup, 3)
 
     # ---- device-timed training steps ------------------------------------------------------------------
@@ -778,6 +844,8 @@ def main():
                        "view_streams": int(min(args.view_streams, vpr)), "row_binning": bool(args.row_binning), "optimizer": "Adam, learning rate 0 (same reads and "
                        "writes; the cloud stays the configuration's)", "reduce": args.reduce if world > 1 else "none",
                        "nccl_registered_buffers": bool(nccl_registered), "host_numa": numa,
+                       "optimizer_chunks": opt_chunks, "optimizer_pipelined": opt_pipelined,
+                       "optimizer_forms_max_abs_difference": optimizer_check,
                        "l2": "inputs larger than L2 (236 MB of parameters + 62-88 MB pair list per view; no explicit flush)",
                        "parallelism": f"dp{world} (cameras sharded, splats replicated)"},
             "clocks": clocks, "gpu_launches": int(launches), "step_breakdown_ms": phases,

@@ -621,61 +621,123 @@ class ShardedAdam:
     all-reduce (a ring all-reduce is this reduce-scatter followed by this all-gather), the optimizer pass and its
     moment buffers shrink to 1/G per rank, and the parameters every rank holds afterwards are identical to the
     replicated form's up to the order in which the ranks' gradients are summed.  Both collectives run in place on
-    the two flat allocations (``GradientBuffer`` / ``ParameterBuffer`` built with ``shards=world_size``): the kernels'
-    output buffer is the communication buffer.  In a single process it degenerates to plain Adam over everything.
+    the two flat allocations (``GradientBuffer`` / ``ParameterBuffer`` built with ``shards=world_size * chunks``): the
+    kernels' output buffer is the communication buffer.  In a single process it degenerates to plain Adam over
+    everything.
+
+    ``chunks`` > 1 cuts the block into that many contiguous chunks, each reduce-scattered, updated and all-gathered on
+    its own; a rank then owns slice ``rank`` of every chunk.  With ``gather_group`` (a second process group over the
+    same ranks, i.e. a second communicator) on CUDA devices the chunks are pipelined: the update and the all-gather of
+    chunk c run on a second stream beside the reduce-scatter of chunk c + 1.  A reduce-scatter mostly sends and an
+    all-gather mostly receives when the switch reduces and multicasts (NVLS), so the two directions of the links work
+    at the same time; over rings or a single peer link the pipeline costs nothing and gains little.  Results do not
+    depend on ``chunks`` beyond the order of the sums.
 
     ``update`` is the per-slice Adam update, ``update(p, g, m, v, lr, beta1, beta2, eps, step, grad_scale)`` in place on
     flat tensors; the default launches ``dsb_adam_step``.  (Tests on CPU ranks pass the checker's update.)"""
 
     def __init__(self, params: ParameterBuffer, lrs: Dict[str, float], betas=(0.9, 0.999), eps: float = 1e-15, group=None,
-                 update=None):
+                 update=None, chunks: int = 1, gather_group=None):
         self.params, self.lrs, self.betas, self.eps, self.group = params, dict(lrs), betas, float(eps), group
         self.world, self.rank = _group_info(group)
+        self.chunks = max(1, int(chunks))
+        self.gather_group = gather_group
         total = params.storage.numel()
-        if total % (4 * self.world) != 0:
-            raise ValueError(f"the parameter block of {total} elements does not split into {self.world} slices of whole "
-                             f"16-byte lanes: build ParameterBuffer and GradientBuffer with shards={self.world}")
-        self.chunk = total // self.world
-        self.lo, self.hi = self.rank * self.chunk, (self.rank + 1) * self.chunk
+        if total % (4 * self.world * self.chunks) != 0:
+            raise ValueError(f"the parameter block of {total} elements does not split into {self.world * self.chunks} "
+                             f"slices of whole 16-byte lanes: build ParameterBuffer and GradientBuffer with "
+                             f"shards={self.world * self.chunks}")
+        self.span = total // self.chunks          # elements of one chunk
+        self.piece = self.span // self.world      # this rank's slice of a chunk
+        self.chunk = total // self.world          # elements this rank owns in all
         dev = params.storage.device
         self.m = torch.zeros(self.chunk, dtype=torch.float32, device=dev)
         self.v = torch.zeros(self.chunk, dtype=torch.float32, device=dev)
-        # the parts of this rank's slice that belong to each parameter tensor (each has its own learning rate)
-        self.pieces = []
-        for name, _ in SEGMENTS:
-            a, b = params.segments[name]
-            a, b = max(a, self.lo), min(b, self.hi)
-            if a < b:
-                self.pieces.append((name, a, b))
+        # per chunk: this rank's slice [lo, hi) of the flat block and the parts of it that belong to each parameter
+        # tensor (each has its own learning rate) with their place in the moment buffers
+        self.slices = []
+        for c in range(self.chunks):
+            lo = c * self.span + self.rank * self.piece
+            hi = lo + self.piece
+            parts = []
+            for name, _ in SEGMENTS:
+                a, b = params.segments[name]
+                a, b = max(a, lo), min(b, hi)
+                if a < b:
+                    parts.append((name, a, b, c * self.piece + (a - lo)))
+            self.slices.append((lo, hi, parts))
+        self.lo, self.hi = self.slices[0][0], self.slices[0][1]           # the one slice when chunks == 1
+        self.pieces = [(name, a, b) for _, _, parts in self.slices for name, a, b, _ in parts]
         self.step_count = 0
         if update is None:
             from . import _capi
             update = _adam_kernel_update(_capi)
         self.update = update
+        self._streams = None
 
-    def step(self, grads: GradientBuffer, grad_scale: float = 1.0):
+    def _update_slice(self, grads: GradientBuffer, c: int, grad_scale: float):
+        for name, a, b, mo in self.slices[c][2]:
+            self.update(self.params.storage[a:b], grads.storage[a:b], self.m[mo:mo + (b - a)], self.v[mo:mo + (b - a)],
+                        self.lrs[name], self.betas[0], self.betas[1], self.eps, self.step_count, grad_scale)
+
+    def pipelined(self) -> bool:
+        return (self.world > 1 and self.chunks > 1 and self.gather_group is not None
+                and self.params.storage.device.type == "cuda")
+
+    def step(self, grads: GradientBuffer, grad_scale: float = 1.0, marks=None):
+        """``marks``: an optional callable invoked after each phase of an unpipelined step (reduce-scatter, update,
+        all-gather, in that order, once per chunk), for callers that record events between the phases."""
         import torch.distributed as dist
         if grads.storage.numel() != self.params.storage.numel():
             raise ValueError("gradient and parameter blocks are laid out differently")
         self.step_count += 1
-        g_slice = grads.storage[self.lo:self.hi]
-        if self.world > 1:
-            dist.reduce_scatter_tensor(g_slice, grads.storage, op=dist.ReduceOp.SUM, group=self.group)
-        for name, a, b in self.pieces:
-            self.update(self.params.storage[a:b], grads.storage[a:b], self.m[a - self.lo:b - self.lo],
-                        self.v[a - self.lo:b - self.lo], self.lrs[name], self.betas[0], self.betas[1], self.eps,
-                        self.step_count, grad_scale)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.params.storage, self.params.storage[self.lo:self.hi], group=self.group)
+        P, G = self.params.storage, grads.storage
+        if not self.pipelined():
+            for c, (lo, hi, _) in enumerate(self.slices):
+                first, last = c * self.span, (c + 1) * self.span
+                if self.world > 1:
+                    dist.reduce_scatter_tensor(G[lo:hi], G[first:last], op=dist.ReduceOp.SUM, group=self.group)
+                if marks:
+                    marks()
+                self._update_slice(grads, c, grad_scale)
+                if marks:
+                    marks()
+                if self.world > 1:
+                    dist.all_gather_into_tensor(P[first:last], P[lo:hi], group=self.gather_group or self.group)
+                if marks:
+                    marks()
+            return
+        # Pipelined: reduce-scatters in order on one stream (first communicator), update + all-gather of every chunk on a
+        # second stream (second communicator) as soon as that chunk's reduce-scatter is done.
+        if self._streams is None:
+            dev = P.device
+            self._streams = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev),
+                             [torch.cuda.Event() for _ in range(self.chunks)])
+        reduce_stream, gather_stream, reduced = self._streams
+        caller = torch.cuda.current_stream(P.device)
+        reduce_stream.wait_stream(caller)
+        gather_stream.wait_stream(caller)
+        for c, (lo, hi, _) in enumerate(self.slices):
+            first, last = c * self.span, (c + 1) * self.span
+            with torch.cuda.stream(reduce_stream):
+                dist.reduce_scatter_tensor(G[lo:hi], G[first:last], op=dist.ReduceOp.SUM, group=self.group)
+                reduced[c].record(reduce_stream)
+            with torch.cuda.stream(gather_stream):
+                gather_stream.wait_event(reduced[c])
+                self._update_slice(grads, c, grad_scale)
+                dist.all_gather_into_tensor(P[first:last], P[lo:hi], group=self.gather_group)
+        caller.wait_stream(reduce_stream)
+        caller.wait_stream(gather_stream)
 
 
-def register_with_nccl(make_buffers, group=None):
+def register_with_nccl(make_buffers, group=None, more_groups=()):
     """Runs ``make_buffers()`` (a callable that allocates and returns the communication buffers) under a memory
     pool of NCCL's own allocator and registers that pool with the process group, so that the collectives on those
     buffers take NCCL's registered-buffer path (zero-copy, and in-switch reduction over NVSwitch where the
     communicator has it).  Returns (buffers, pool or None): when the backend has no such allocator (gloo, an older
     NCCL) or registration fails, the buffers come from torch's ordinary allocator and the second value is None --
-    the collectives still run, through NCCL's staging buffers.  Keep the pool alive as long as the buffers."""
+    the collectives still run, through NCCL's staging buffers.  Keep the pool alive as long as the buffers.
+    ``more_groups``: further process groups whose communicators should know the pool as well."""
     import torch.distributed as dist
     try:
         if not (dist.is_available() and dist.is_initialized()) or dist.get_backend(group) != "nccl":
@@ -687,6 +749,11 @@ def register_with_nccl(make_buffers, group=None):
         with torch.cuda.use_mem_pool(pool):
             buffers = make_buffers()
         backend.register_mem_pool(pool)
+        for g in more_groups:   # further communicators over the same ranks that will use the buffers (ShardedAdam's gather_group)
+            try:
+                g._get_backend(torch.device("cuda")).register_mem_pool(pool)
+            except Exception:
+                pass            # that communicator stages through its own buffers
         return buffers, pool
     except Exception:   # anything the running torch / NCCL pair does not offer: plain buffers
         return make_buffers(), None

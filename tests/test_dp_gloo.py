@@ -143,13 +143,16 @@ def _initial_parameters():
                 rotations=torch.randn(N_SHARDED, 4, generator=g))
 
 
-def _sharded_worker(rank, world, port, out):
+def _sharded_worker(rank, world, port, out, chunks=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    params = dp.ParameterBuffer.from_tensors(_initial_parameters(), shards=world)
-    grads = dp.GradientBuffer(N_SHARDED, "cpu", shards=world)
-    opt = dp.ShardedAdam(params, LRS, eps=1e-8, update=_checker_update)
+    params = dp.ParameterBuffer.from_tensors(_initial_parameters(), shards=world * chunks)
+    grads = dp.GradientBuffer(N_SHARDED, "cpu", shards=world * chunks)
+    # a second group as the pipelined form takes it; on CPU ranks the chunks simply run one after the other
+    second = dist.new_group(backend="gloo") if chunks > 1 else None
+    opt = dp.ShardedAdam(params, LRS, eps=1e-8, update=_checker_update, chunks=chunks, gather_group=second)
     assert opt.m.numel() * world == params.storage.numel()       # moments: 1/G per rank
+    assert len(opt.slices) == chunks and not opt.pipelined()
     for step in (1, 2, 3):
         grads.flat.copy_(_rank_gradients(rank, step))
         opt.step(grads, grad_scale=0.5)
@@ -157,10 +160,11 @@ def _sharded_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_sharded_adam_on_two_ranks_equals_allreduce_plus_full_adam(tmp_path):
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_sharded_adam_on_two_ranks_equals_allreduce_plus_full_adam(tmp_path, chunks):
     out = str(tmp_path / "params")
     world = 2
-    mp.spawn(_sharded_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    mp.spawn(_sharded_worker, args=(world, _free_port(), out, chunks), nprocs=world, join=True)
     got = [np.load(f"{out}.{r}.npy") for r in range(world)]
     np.testing.assert_array_equal(got[0], got[1])        # every rank ends with the same parameters
     # replicated form in one process: sum of the ranks' gradients, Adam over everything
