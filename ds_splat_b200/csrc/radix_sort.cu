@@ -472,6 +472,9 @@ int launch_sort(u64* items, u64* items_alt, u32* vals, u32* vals_alt, int64_t k,
     DSB_REQUIRE(!vals == !vals_alt, "sort: values and alternate values must both be given or both be null");
     SortPlan plan = make_sort_plan(begin_bit, end_bit, end_bit == 64 && vals != nullptr);  // signed keys in the pair interface
     if (large_tiles_only) plan.tile_items = kTileItems;
+    // Half-size tiles pay only while the whole launch is one wave of blocks; a batch of lists fills the GPU several
+    // times over even when each list alone would not.
+    if ((int64_t)batch * k > kSmallListLimit) plan.tile_items = kTileItems;
     u32* hist = nullptr;
     DSB_REQUIRE(batch >= 1 && (batch == 1 || item_stride >= k), "sort: bad batch layout");
     rc = sort_begin(k, plan, ws, ws_bytes, &hist, s, batch);
