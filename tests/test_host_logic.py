@@ -89,3 +89,29 @@ def test_gradient_and_parameter_blocks_share_one_layout_and_pad_to_shards():
         assert torch.equal(p.views[name], tensor)
         a, b = p.segments[name]
         assert torch.equal(p.storage[a:b], tensor.reshape(-1))
+
+
+def test_sharded_adam_slices_cover_every_chunk_once():
+    """One process, three chunks: the rank's slices are the chunks themselves, every element belongs to exactly one
+    part, the parts' places in the moment buffers do not overlap, and a block that does not split is refused."""
+    import torch
+    from ds_splat_b200 import dp
+    params = dict(means3d=torch.randn(7, 3), shs=torch.randn(7, 16, 3), opacities=torch.rand(7, 1), scales=torch.rand(7, 3),
+                  rotations=torch.randn(7, 4))
+    lrs = {name: 1e-3 for name, _ in dp.SEGMENTS}
+    p = dp.ParameterBuffer.from_tensors(params, shards=3)
+    calls = []
+    opt = dp.ShardedAdam(p, lrs, chunks=3, update=lambda *a: calls.append((a[0].data_ptr(), a[0].numel(), a[2].data_ptr())))
+    assert len(opt.slices) == 3 and not opt.pipelined()
+    covered = torch.zeros(p.storage.numel(), dtype=torch.int32)
+    moments = torch.zeros(opt.m.numel(), dtype=torch.int32)
+    for lo, hi, parts in opt.slices:
+        for name, a, b, mo in parts:
+            assert lo <= a < b <= hi and p.segments[name][0] <= a and b <= p.segments[name][1]
+            covered[a:b] += 1
+            moments[mo:mo + (b - a)] += 1
+    assert int(covered[:p.length].min()) == 1 and int(covered.max()) == 1 and int(moments.max()) == 1
+    opt.step(dp.GradientBuffer(7, "cpu", shards=3))
+    assert sum(n for _, n, _ in calls) == p.length
+    with pytest.raises(ValueError):
+        dp.ShardedAdam(dp.ParameterBuffer.from_tensors(params, shards=1), lrs, chunks=7)
