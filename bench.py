@@ -81,6 +81,7 @@ def parse_args():
                     help="N > 1: cut the gradient/parameter blocks into this many chunks and pipeline reduce-scatter, Adam and "
                          "all-gather over two communicators (1: one reduce-scatter, one update, one all-gather)")
     ap.add_argument("--frames", type=int, default=120, help="frames of the fly-through workload")
+    ap.add_argument("--image", default="", help="fly-through only: WIDTHxHEIGHT instead of 1920x1080 (same field of view)")
     return ap.parse_args()
 
 
@@ -141,6 +142,9 @@ def load_scene(args, views: int = 1):
     if args.splats:
         kw["n"] = args.splats
     name = "c1" if args.workload == "flythrough" else args.workload
+    if args.workload == "flythrough" and args.image:
+        w, h = (int(x) for x in args.image.lower().split("x"))
+        kw.update(W=w, H=h, focal=1100.0 * w / 1920.0)
     if name == "c1":
         kw["views"] = views   # view 0 is the configuration's camera, the others are turned +-5 degrees away from it
     return scenes.CONFIGS[name](**kw)
