@@ -194,7 +194,9 @@ int dsb_plan_pairs(const DsbCamera* cam, int32_t n, const int32_t* tiles_touched
 
 /* ---- stage (b), second half -----------------------------------------------------------------
  * Replaces calculate_keys_and_indices_kernel (cpp/rasterizer_kernels.cu:252-306).  Writes k packed
- * pairs (tile id << 32 | splat id), splats in (depth, id) order, each rectangle row-major. */
+ * pairs (tile id << 32 | splat id), splats in (depth, id) order, each rectangle row-major.  k must be the
+ * total dsb_plan_pairs returned for these offsets: a splat's pair count is taken as the distance to the next
+ * splat's offset, the last one's as k minus its offset (tiles_touched is not read). */
 int dsb_emit_pairs(const DsbCamera* cam, int32_t n, int64_t k, const float* records,
                    const int32_t* tiles_touched, const uint64_t* depth_keys_sorted, const uint32_t* offsets,
                    uint64_t* pairs, void* stream);
