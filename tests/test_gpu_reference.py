@@ -68,6 +68,40 @@ def test_against_reference_cuda(name):
         gradient_gate(g.cpu().numpy(), ref[name_], f"{name}/{name_}")
 
 
+def test_background_term_of_the_backward_against_reference_cuda():
+    """The reference composites no background in the forward image but keeps the background term in the backward
+    (cpp/gsplat/backward.cu:161-164): -T_final (bg . v_out) / (1 - alpha) in v_alpha.  The backward blend here folds that
+    term into the start value of its per-pixel running sum, so it gets a test of its own with a background that is
+    not black: same image as without, gradients those of the reference CUDA path, and noticeably different from the
+    black-background ones."""
+    sc = scenes.tiny()
+    view = sc.views[0]
+    v_image = sc.image_grad()
+    bg = (0.3, 0.6, 0.1)
+    ref = ref_cuda.run(view, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image=v_image, bg=bg)
+    black = ref_cuda.run(view, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image=v_image)
+    t = scene_tensors(sc)
+
+    def operator_gradients(background):
+        rast = GaussianRasterizer(settings_for(view, bg=background))
+        p = {k_: v.clone().requires_grad_(True) for k_, v in t.items()}
+        means2d = torch.zeros_like(p["means"], requires_grad=True)
+        image, _ = rast(p["means"], means2d, p["shs"], None, p["opacities"], p["scales"], p["rotations"], None)
+        image.backward(torch.from_numpy(v_image).cuda())
+        torch.cuda.synchronize()
+        return image.detach().cpu().numpy(), dict(v_mean=p["means"].grad, v_sh=p["shs"].grad,
+                                                  v_opacity=p["opacities"].grad.reshape(-1), v_scale=p["scales"].grad,
+                                                  v_rot=p["rotations"].grad, v_xy=means2d.grad[:, :2])
+
+    image, grads = operator_gradients(bg)
+    assert np.abs(image - ref["image"]).max() <= 1e-5
+    np.testing.assert_array_equal(ref["image"], black["image"])        # the forward ignores the background
+    for name_, g in grads.items():
+        gradient_gate(g.cpu().numpy(), ref[name_], f"background/{name_}")
+    moved = np.abs(ref["v_opacity"] - black["v_opacity"]).max() / np.abs(black["v_opacity"]).max()
+    assert moved > 1e-2, "the background must change the opacity gradients for this test to mean anything"
+
+
 import json  # noqa: E402
 import os  # noqa: E402
 
