@@ -65,7 +65,7 @@ def lib():
 
 
 def run(view, means, shs, opacities, scales, rots, v_image=None, sh_degree=3, k_capacity=None, iters=1, warmup=0,
-        outputs=True, bg=(0.0, 0.0, 0.0)):
+        outputs=True, bg=(0.0, 0.0, 0.0), scale_modifier=1.0):
     """Run the reference's forward (and backward when ``v_image`` is given) on the current CUDA device.
 
     ``view`` is any object with H, W, tanfovx, tanfovy, view, proj, campos (row-major matrices).
@@ -76,7 +76,7 @@ def run(view, means, shs, opacities, scales, rots, v_image=None, sh_degree=3, k_
     t = ((W + 15) // 16) * ((H + 15) // 16)
     a = _Args()
     a.N, a.H, a.W, a.sh_degree, a.max_sh_degree = n, H, W, sh_degree, 3
-    a.tanfovx, a.tanfovy, a.scale_modifier = view.tanfovx, view.tanfovy, 1.0
+    a.tanfovx, a.tanfovy, a.scale_modifier = view.tanfovx, view.tanfovy, float(scale_modifier)
     vm, pm, cp, bgc = f32(view.view).reshape(16), f32(view.proj).reshape(16), f32(view.campos), f32(bg)
     keep = [means, shs, opacities, scales, rots, vm, pm, cp, bgc]
     for name, arr in zip(("means", "shs", "opac", "scales", "rots", "view", "proj", "campos", "bg"), keep):

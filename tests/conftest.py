@@ -40,12 +40,12 @@ def capi_camera(view, device="cuda", sh_degree=3, max_sh_degree=3, transposed=Tr
                              transposed=transposed, drop_last=drop_last, row_binning=row_binning)
 
 
-def settings_for(view, device="cuda", sh_degree=3, bg=(0.0, 0.0, 0.0), **kw):
+def settings_for(view, device="cuda", sh_degree=3, bg=(0.0, 0.0, 0.0), scale_modifier=1.0, **kw):
     import torch
     from ds_splat_b200 import GaussianRasterizationSettings
     return GaussianRasterizationSettings(
         image_height=view.H, image_width=view.W, tanfovx=view.tanfovx, tanfovy=view.tanfovy,
-        bg=torch.tensor(bg, dtype=torch.float32, device=device), scale_modifier=1.0,
+        bg=torch.tensor(bg, dtype=torch.float32, device=device), scale_modifier=scale_modifier,
         viewmatrix=torch.from_numpy(view.viewmatrix_t).to(device), projmatrix=torch.from_numpy(view.projmatrix_t).to(device),
         sh_degree=sh_degree, max_sh_degree=3, campos=torch.from_numpy(np.ascontiguousarray(view.campos)).to(device),
         prefiltered=False, debug=False, **kw)

@@ -102,6 +102,31 @@ def test_background_term_of_the_backward_against_reference_cuda():
     assert moved > 1e-2, "the background must change the opacity gradients for this test to mean anything"
 
 
+def test_scale_modifier_against_reference_cuda():
+    """settings.scale_modifier multiplies every splat's scale before the covariance is formed
+    (cpp/rasterizer_kernels.cu:615-659) and its derivative multiplies the scale gradient
+    (cpp/gsplat/backward.cu:387-389).  With 0.7: radii bit-exact, image and gradients as the reference CUDA path."""
+    sc = scenes.tiny()
+    view = sc.views[0]
+    v_image = sc.image_grad()
+    ref = ref_cuda.run(view, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image=v_image, scale_modifier=0.7)
+    plain = ref_cuda.run(view, sc.means, sc.shs, sc.opacities, sc.scales, sc.rotations, v_image=v_image)
+    assert (ref["radii"] != plain["radii"]).mean() > 0.2          # the modifier does change the splats
+    t = scene_tensors(sc)
+    rast = GaussianRasterizer(settings_for(view, scale_modifier=0.7))
+    p = {k_: v.clone().requires_grad_(True) for k_, v in t.items()}
+    means2d = torch.zeros_like(p["means"], requires_grad=True)
+    image, radii = rast(p["means"], means2d, p["shs"], None, p["opacities"], p["scales"], p["rotations"], None)
+    image.backward(torch.from_numpy(v_image).cuda())
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(radii.cpu().numpy(), ref["radii"])
+    assert np.abs(image.detach().cpu().numpy() - ref["image"]).max() <= 1e-5
+    grads = dict(v_mean=p["means"].grad, v_sh=p["shs"].grad, v_opacity=p["opacities"].grad.reshape(-1),
+                 v_scale=p["scales"].grad, v_rot=p["rotations"].grad, v_xy=means2d.grad[:, :2])
+    for name_, g in grads.items():
+        gradient_gate(g.cpu().numpy(), ref[name_], f"scale_modifier/{name_}")
+
+
 import json  # noqa: E402
 import os  # noqa: E402
 
