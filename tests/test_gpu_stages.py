@@ -285,3 +285,19 @@ def test_emit_walks_rectangles_of_more_than_a_million_tiles():
     x0, x1, y0, y1 = (int(v) for v in rec["rect"][1])
     want = [y * 1025 + x for y in range(y0, y1) for x in range(x0, x1)]
     assert small.cpu().tolist() == want
+
+
+def test_row_major_and_transposed_camera_matrices_give_the_same_preprocess():
+    """DsbCamera takes the view and projection matrices either as the reference's Python layer holds them (transposed,
+    field matrices_transposed) or row-major as its C++ entry point does; records, radii, counts and depth keys must be
+    bit-identical."""
+    sc = scenes.tiny(n=3001, seed=21)
+    t = scene_tensors(sc)
+    outs = []
+    for transposed in (True, False):
+        cam, keep = capi_camera(sc.views[0], transposed=transposed)
+        outs.append(_capi.preprocess(cam, t["means"], t["shs"], t["opacities"], t["scales"], t["rotations"]))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a, b.view(torch.int32) if b.dtype == torch.float32 else b)
+    assert int(outs[0][2].sum()) > 0
