@@ -20,7 +20,7 @@ Rank 0 prints ONE JSON line.
                    identical image, radii and gradients);
   strict_lists     the multi-view step again with the reference-identical lists;
   e2e              one training iteration per step through the public Python operator (GaussianRasterizer +
-                   autograd): camera and 8-bit target image copied from pinned host memory, torch L1 loss, backward,
+                   autograd): camera and 8-bit target image copied from pinned host memory, L1 loss (dp.ImageLoss), backward,
                    and the loss value read on the host, all inside the timed region;
   roofline         the dominant kernel (backward blend) on the configuration's own camera against the FP32 pipe
                    (148 SMs x 128 lanes x 2 flop x sampled SM clock), timed live with the cudaEvent pairs the
@@ -657,8 +657,9 @@ def main():
     e2e = None
     if not args.skip_e2e:
         # One training iteration the way a user of the operator writes it: the camera and the step's target image (8-bit
-        # RGB, the form datasets hold) come from pinned host memory, the loss is torch's L1 on the rendered image,
-        # autograd drives the operator's backward, and the loss value is read on the host.
+        # RGB, the form datasets hold) come from pinned host memory, the loss is L1 on the rendered image (dp.ImageLoss
+        # with lambda_dssim = 0: one kernel for the loss value and dL/dimage), autograd drives the operator's backward, and
+        # the loss value is read on the host.
         view = scene.views[view_ids[0]]
         rng = np.random.default_rng(11)
         pinned_target = torch.from_numpy(rng.integers(0, 256, size=(H, W, 3), dtype=np.uint8)).pin_memory()
@@ -676,6 +677,8 @@ def main():
         settings = GaussianRasterizationSettings(H, W, view.tanfovx, view.tanfovy, bg, 1.0, vm, pm, scene.sh_degree, 3, cp,
                                                  False, False)
         rasterizer = GaussianRasterizer(settings)
+        from ds_splat_b200.dp import ImageLoss
+        loss_fn = ImageLoss(lambda_dssim=0.0)
         h2d = pinned_target.numel() + (16 + 16 + 3) * 4
         d2h = 4
         upload_stream = torch.cuda.Stream(device=dev)    # the target image travels while the forward runs
@@ -700,10 +703,10 @@ def main():
             image, radii = rasterizer(leaves["means3d"], means2d, leaves["shs"], None, leaves["opacities"],
                                       leaves["scales"], leaves["rotations"], None)
             main_stream.wait_event(target_ready)
-            loss = torch.nn.functional.l1_loss(image, target_dev[s] / 255.0)
-            loss.backward()
+            v_image, loss = loss_fn.gradient(image.detach(), target_dev[s])   # the library's one-pass L1 loss, 8-bit target
+            image.backward(v_image)
             backward_done[s].record(main_stream)
-            loss_host[s].copy_(loss.detach(), non_blocking=True)
+            loss_host[s].copy_(loss[0], non_blocking=True)
             result_on_host[s].record(main_stream)
             if i > 0:   # the previous step's loss, on the host
                 result_on_host[s ^ 1].synchronize()
@@ -734,11 +737,11 @@ def main():
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": round(e_ms / args.steps, 4),
                "note": "one training iteration per step through GaussianRasterizer + autograd: camera and the 8-bit target "
-                       "image from pinned host memory (second stream), torch L1 loss on the rendered image, backward, the loss "
+                       "image from pinned host memory (second stream), L1 loss on the rendered image (dp.ImageLoss), backward, the loss "
                        "value read on the host one step behind the step being enqueued; splat parameters are model state "
                        "resident on the device"
                        + ("; per-rank iterations with no collective in them (N independent loops)" if world > 1 else "")}
-        del leaves, means2d, rasterizer
+        del leaves, means2d, rasterizer, loss_fn
 
     nccl_registered = pool is not None
     # ---- config 3 beside it: 6M splats, 8 of the 64 ring cameras per rank and step, 1.416 GB of gradients ----------

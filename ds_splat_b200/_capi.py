@@ -33,7 +33,7 @@ EXPORTS = (
     "dsb_render_workspace_bytes", "dsb_row_binning_supported",
     "dsb_backward_blend",
     "dsb_geometry_backward_views", "dsb_geometry_backward_views_stats",
-    "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_adam_step",
+    "dsb_forward_core", "dsb_image_loss_workspace_bytes", "dsb_image_loss_backward", "dsb_l1_loss_backward_u8", "dsb_adam_step",
     "dsb_export_reference_lists",
     "dsb_stage_timing_enable", "dsb_stage_count", "dsb_stage_name", "dsb_stage_timing_read",
     "dsb_sort_pairs_static", "dsb_tile_marks_bytes", "dsb_forward", "dsb_take_device_status",
@@ -112,6 +112,7 @@ def lib():
             "dsb_geometry_backward_views_stats": [P, I32, I32] + [P] * 15 + [I32, C.c_float, C.c_float, P, P, P, P],
             "dsb_forward_core": [P, P, P, P, P, I32, P, P, P, I32, I32, C.c_float, C.c_float, C.c_float, I32, I32, P, P],
             "dsb_image_loss_backward": [P, P, I32, I32, C.c_float, P, I64, P, P, P],
+            "dsb_l1_loss_backward_u8": [P, P, I32, I32, P, P, P],
             "dsb_adam_step": [P, P, P, P, I64, C.c_double, C.c_double, C.c_double, C.c_double, I32, C.c_double, P],
             "dsb_export_reference_lists": [P, I64, P, P, P, P],
             "dsb_forward": [CAM, I32] + [P] * 7 + [P] * 10 + [P, I64] + [P, I64] + [P, I64] + [P] * 4

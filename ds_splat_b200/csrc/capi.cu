@@ -717,6 +717,11 @@ int dsb_image_loss_backward(const float* image, const float* target, int32_t ima
                              (cudaStream_t)stream);
 }
 
+int dsb_l1_loss_backward_u8(const float* image, const uint8_t* target, int32_t image_height, int32_t image_width,
+                            float* v_image, float* loss, void* stream) {
+    return launch_l1_loss_u8(image, target, image_height, image_width, v_image, loss, (cudaStream_t)stream);
+}
+
 int dsb_adam_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr,
                   double beta1, double beta2, double eps, int32_t step, double grad_scale, void* stream) {
     return launch_adam(params, grads, exp_avg, exp_avg_sq, count, lr, beta1, beta2, eps, step, grad_scale, (cudaStream_t)stream);

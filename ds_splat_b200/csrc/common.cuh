@@ -242,6 +242,7 @@ int launch_geometry_backward_views(const CamParams* cps, int count, int n, const
                                    const DensifyStats* stats = nullptr);
 
 int64_t image_loss_workspace_bytes(int H, int W);
+int launch_l1_loss_u8(const float* image, const unsigned char* target, int H, int W, float* v_image, float* loss, cudaStream_t s);
 int launch_image_loss(const float* image, const float* target, int H, int W, float lambda_dssim, void* workspace,
                       int64_t workspace_bytes, float* v_image, float* loss, cudaStream_t s);
 int launch_adam(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t count, double lr, double beta1,

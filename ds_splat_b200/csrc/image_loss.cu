@@ -189,6 +189,66 @@ ssim_gradient_kernel(const float* __restrict__ x, const float* __restrict__ y, c
     }
 }
 
+// lambda = 0: the loss is the plain L1 term and needs none of the windowed sums.  One pass: dL/dx = sign(x - y) / count,
+// the block's share of mean|x - y| added to the loss.  VEC: all arrays aligned for 4-element accesses.  U8: the
+// target is 8-bit (the form datasets hold images in) and stands for value / 255.
+template <bool VEC, bool U8>
+__global__ void __launch_bounds__(kLossThreads)
+l1_gradient_kernel(const float* __restrict__ x, const void* __restrict__ target, const long long count, const float inv_count,
+                   float* __restrict__ v_image, float* __restrict__ loss) {
+    const float* yf = static_cast<const float*>(target);
+    const unsigned char* yb = static_cast<const unsigned char*>(target);
+    const long long stride = (long long)gridDim.x * kLossThreads;
+    const long long first = (long long)blockIdx.x * kLossThreads + threadIdx.x;
+    float acc = 0.f;
+    auto one = [&](const float a, const float b) {
+        const float d = a - b;
+        acc += fabsf(d);
+        return d > 0.f ? inv_count : (d < 0.f ? -inv_count : 0.f);
+    };
+    auto target_at = [&](const long long i) { return U8 ? (float)yb[i] * (1.0f / 255.0f) : yf[i]; };
+    if (VEC) {
+        const long long quads = count / 4;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        float4* v4 = reinterpret_cast<float4*>(v_image);
+        for (long long i = first; i < quads; i += stride) {
+            const float4 a = __ldg(x4 + i);
+            float4 b;
+            if (U8) {
+                const uchar4 q = __ldg(reinterpret_cast<const uchar4*>(yb) + i);
+                b = make_float4(q.x * (1.0f / 255.0f), q.y * (1.0f / 255.0f), q.z * (1.0f / 255.0f), q.w * (1.0f / 255.0f));
+            } else {
+                b = __ldg(reinterpret_cast<const float4*>(yf) + i);
+            }
+            v4[i] = make_float4(one(a.x, b.x), one(a.y, b.y), one(a.z, b.z), one(a.w, b.w));
+        }
+        for (long long i = quads * 4 + first; i < count; i += stride) v_image[i] = one(x[i], target_at(i));   // at most three
+    } else {
+        for (long long i = first; i < count; i += stride) v_image[i] = one(x[i], target_at(i));
+    }
+    __shared__ float s_red[kLossThreads / 32];
+    const float total = block_sum(acc, s_red);
+    if (threadIdx.x == 0 && loss) atomicAdd(loss, total * inv_count);
+}
+
+static int launch_l1(const float* image, const void* target, bool u8, int H, int W, float* v_image, float* loss, cudaStream_t s) {
+    const long long elements = (long long)H * W * 3;
+    const float inv_count = 1.f / (float)((double)H * W * 3);
+    if (loss) DSB_CUDA_CHECK(cudaMemsetAsync(loss, 0, sizeof(float), s));
+    const long long want = (elements / 4 + kLossThreads - 1) / kLossThreads;
+    const int blocks = (int)(want < 148 * 8 ? (want > 0 ? want : 1) : 148 * 8);
+    const bool vec = (((uintptr_t)image | (uintptr_t)v_image) & 15) == 0 && ((uintptr_t)target & (u8 ? 3 : 15)) == 0;
+    if (u8) {
+        if (vec) l1_gradient_kernel<true, true><<<blocks, kLossThreads, 0, s>>>(image, target, elements, inv_count, v_image, loss);
+        else l1_gradient_kernel<false, true><<<blocks, kLossThreads, 0, s>>>(image, target, elements, inv_count, v_image, loss);
+    } else {
+        if (vec) l1_gradient_kernel<true, false><<<blocks, kLossThreads, 0, s>>>(image, target, elements, inv_count, v_image, loss);
+        else l1_gradient_kernel<false, false><<<blocks, kLossThreads, 0, s>>>(image, target, elements, inv_count, v_image, loss);
+    }
+    DSB_LAUNCH_CHECK();
+    return DSB_OK;
+}
+
 __global__ void finish_loss_kernel(const float* __restrict__ sums, const float inv_count, const float lambda, float* __restrict__ loss) {
     loss[0] = (1.f - lambda) * sums[0] * inv_count + lambda * (1.f - sums[1] * inv_count);
 }
@@ -208,6 +268,8 @@ int launch_image_loss(const float* image, const float* target, int H, int W, flo
         set_error("image_loss: workspace of %lld bytes is smaller than the %lld needed", (long long)workspace_bytes, (long long)need);
         return DSB_ERR_WORKSPACE_TOO_SMALL;
     }
+    const float count = (float)((double)H * W * 3);
+    if (lambda_dssim == 0.f) return launch_l1(image, target, false, H, W, v_image, loss, s);   // plain L1: one pass
     Window win;
     double sum = 0.0, raw[kWin];
     for (int t = 0; t < kWin; ++t) { raw[t] = std::exp(-(double)((t - kHalf) * (t - kHalf)) / (2.0 * 1.5 * 1.5)); sum += raw[t]; }
@@ -215,7 +277,6 @@ int launch_image_loss(const float* image, const float* target, int H, int W, flo
     float* maps = reinterpret_cast<float*>(workspace);
     float* sums = maps + (size_t)H * W * 3 * 3;
     DSB_CUDA_CHECK(cudaMemsetAsync(sums, 0, 2 * sizeof(float), s));
-    const float count = (float)((double)H * W * 3);
     const dim3 grid((W + kPatch - 1) / kPatch, (H + kPatch - 1) / kPatch), block(kLossThreads);
     ssim_moments_kernel<<<grid, block, 0, s>>>(image, target, H, W, win, -lambda_dssim / count, maps, sums);
     DSB_LAUNCH_CHECK();
@@ -226,6 +287,13 @@ int launch_image_loss(const float* image, const float* target, int H, int W, flo
         DSB_LAUNCH_CHECK();
     }
     return DSB_OK;
+}
+
+// L1 loss against an 8-bit target (value / 255): loss = mean|image - target|, v_image = dL/dimage.
+int launch_l1_loss_u8(const float* image, const unsigned char* target, int H, int W, float* v_image, float* loss, cudaStream_t s) {
+    DSB_REQUIRE(H > 0 && W > 0, "l1_loss: bad image size");
+    DSB_REQUIRE(image && target && v_image, "l1_loss: null pointer");
+    return launch_l1(image, target, true, H, W, v_image, loss, s);
 }
 
 }  // namespace dsb

@@ -524,7 +524,8 @@ class ViewRenderer:
 
 class ImageLoss:
     """L = (1 - lambda) * mean|image - target| + lambda * (1 - mean SSIM(image, target)) and dL/dimage in two kernel
-    launches (``dsb_image_loss_backward``), with buffers that are reused from call to call.  ``__call__`` returns
+    launches (``dsb_image_loss_backward``; one launch when lambda is 0), with buffers that are reused from call to call.
+    Targets are float images or 8-bit ones (value / 255).  ``__call__`` returns
     (dL/dimage [H, W, 3], loss as a one-element device tensor -- reading it is the caller's synchronisation);
     it has the ``(index, image)`` form ``ViewRenderer.render_views`` expects of its ``image_grads`` argument when
     built with a list of target images."""
@@ -554,6 +555,12 @@ class ImageLoss:
         ws, v_image = self.buf[key]
         loss = torch.empty(1, dtype=torch.float32, device=image.device)
         image, target = image.contiguous(), target.contiguous()
+        if target.dtype == torch.uint8:   # 8-bit targets stand for value / 255
+            if self.lam == 0.0:
+                self._capi.check(self.lib.dsb_l1_loss_backward_u8(image.data_ptr(), target.data_ptr(), h, w, v_image.data_ptr(),
+                                                                  loss.data_ptr(), stream))
+                return v_image, loss
+            target = target.to(torch.float32).mul_(1.0 / 255.0)
         self._capi.check(self.lib.dsb_image_loss_backward(image.data_ptr(), target.data_ptr(), h, w, self.lam, ws.data_ptr(),
                                                           ws.numel(), v_image.data_ptr(), loss.data_ptr(), stream))
         return v_image, loss

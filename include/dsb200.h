@@ -446,6 +446,10 @@ int64_t dsb_image_loss_workspace_bytes(int32_t image_height, int32_t image_width
 int dsb_image_loss_backward(const float* image, const float* target, int32_t image_height, int32_t image_width,
                             float lambda_dssim, void* workspace, int64_t workspace_bytes, float* v_image, float* loss,
                             void* stream);
+/* The same with lambda_dssim = 0 (plain L1, which dsb_image_loss_backward computes in one pass without touching its
+ * workspace) against an 8-bit target as datasets hold images: target [H][W][3] bytes standing for value / 255. */
+int dsb_l1_loss_backward_u8(const float* image, const uint8_t* target, int32_t image_height, int32_t image_width,
+                            float* v_image, float* loss, void* stream);
 
 /* ---- the step after the operator -------------------------------------------------------------------
  * Adam on one parameter tensor (no reference counterpart: users of the reference call torch.optim.Adam;

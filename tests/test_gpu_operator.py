@@ -487,7 +487,7 @@ def test_image_loss_gradient_matches_the_autograd_checker():
     from ds_splat_b200.dp import ImageLoss
     from oracle import loss_oracle as L
     rng = np.random.default_rng(8)
-    for (h, w), lam in (((37, 53), 0.2), ((64, 48), 1.0), ((19, 16), 0.0), ((130, 97), 0.2)):
+    for (h, w), lam in (((37, 53), 0.2), ((64, 48), 1.0), ((19, 16), 0.0), ((130, 97), 0.2), ((131, 97), 0.0), ((256, 512), 0.0)):
         img = rng.uniform(0, 1, (h, w, 3)).astype(np.float32)
         tgt = np.clip(img + rng.normal(0, 0.1, img.shape), 0, 1).astype(np.float32)
         loss_o, grad_o = L.image_loss_and_grad(img, tgt, lam)
@@ -496,6 +496,16 @@ def test_image_loss_gradient_matches_the_autograd_checker():
         assert abs(float(loss) - loss_o) <= 1e-5 * max(abs(loss_o), 1e-3)
         scale = float(np.abs(grad_o).max())
         assert float(np.abs(v.cpu().numpy() - grad_o).max()) <= 2e-4 * scale, (h, w, lam)
+    # 8-bit targets (value / 255): the one-pass L1 entry point, and the conversion in front of the D-SSIM form
+    for (h, w), lam in (((131, 97), 0.0), ((64, 64), 0.0), ((37, 53), 0.2)):
+        img = rng.uniform(0, 1, (h, w, 3)).astype(np.float32)
+        tgt8 = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        loss_o, grad_o = L.image_loss_and_grad(img, tgt8.astype(np.float32) / np.float32(255.0), lam)
+        v, loss = ImageLoss(lambda_dssim=lam).gradient(torch.from_numpy(img).cuda(), torch.from_numpy(tgt8).cuda())
+        torch.cuda.synchronize()
+        assert abs(float(loss) - loss_o) <= 1e-5 * max(abs(loss_o), 1e-3)
+        scale = float(np.abs(grad_o).max())
+        assert float(np.abs(v.cpu().numpy() - grad_o).max()) <= 2e-4 * scale, (h, w, lam, "u8")
     # as the loss of a multi-view step: the gradients equal those of a step fed with the checker's dL/dimage
     sc = scenes.headline(n=10_000, seed=99, W=240, H=144, focal=170.0, views=3, ring=True)
     t = scene_tensors(sc)
